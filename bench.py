@@ -1,0 +1,331 @@
+"""Benchmark of the state-tree decode hot path on B200: the fused decode + GEMV / GEMM sweep over Qwen3-8B-shaped
+linears (q/o 4096x4096, k/v 1024x4096, gate/up 12288x4096, down 4096x12288; 36 layers), synthetic seeded weights
+N(0, 0.02) with 1% of the columns scaled x8.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--impl reference]
+
+One step = every linear of all 36 layers once at batch M (default 1), captured in one CUDA graph.  All 36 layers own
+distinct record buffers (10.5 GB in total, far beyond the 126 MB L2), so every step streams the records from HBM.
+value    = algorithmic bytes (records + activations in + out) / device time, inputs resident in HBM
+e2e      = the same through the module API with pinned host activations copied in and results copied out every step
+roofline = the GEMV (or GEMM) kernel's achieved algorithmic GB/s against the measured HBM copy bandwidth
+cpu_baseline / --impl reference = the reference's CPU path (decode + BF16 matmul) restated in C, on the host cores,
+on a bounded sample (the linears of one layer).
+With N > 1 ranks (torchrun) the linears are tensor-parallel: q/k/v/gate/up split by rows, o/down split by columns
+and followed by an NCCL all-reduce of their [M, 4096] outputs; total work is fixed (strong scaling).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "statetree-representation_b200"), os.path.join(ROOT, "tests", "golden")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+LAYERS = 36
+HIDDEN, INTER, KVDIM = 4096, 12288, 1024
+# name, out rows, in cols, parallel kind ("col": rows split over ranks, "row": columns split + all-reduce)
+SHAPES = [("q", HIDDEN, HIDDEN, "col"), ("k", KVDIM, HIDDEN, "col"), ("v", KVDIM, HIDDEN, "col"),
+          ("o", HIDDEN, HIDDEN, "row"), ("gate", INTER, HIDDEN, "col"), ("up", INTER, HIDDEN, "col"),
+          ("down", HIDDEN, INTER, "row")]
+METRIC = "compressed GEMV/GEMM effective GB/s (Qwen3-8B linears, 36 layers)"
+
+
+def algorithmic_bytes(M, N, B):
+    """records + activations read + outputs written (the per-unit figure the roofline is computed from)"""
+    return (M // 16) * (N // 64) * 1552 + 2 * B * N + 2 * B * M
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """samples nvidia-smi clocks and throttle reasons during the timed region"""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference(steps, warmup, batch):
+    """the reference's CPU path (decode + BF16 matmul, restated in oracle/statetree_oracle.c) on the host cores;
+    one step = the seven linears of ONE layer (1/36 of the GPU step)"""
+    import numpy as np
+
+    import gen_inputs as G
+    import oracle
+    oracle.build()
+    encs, xs = [], {}
+    rs = np.random.RandomState(0)
+    for name, M, N, _ in SHAPES:
+        encs.append((name, M, N, oracle.encode(G.weights(M, N, len(encs), "llm"))))
+        if N not in xs:
+            xs[N] = G.to_bf16_bits(rs.standard_normal((batch, N)))
+    scratch = np.empty(INTER * HIDDEN, dtype=np.uint16)
+    nbytes = sum(algorithmic_bytes(M, N, batch) for _, M, N, _ in SHAPES)
+
+    def step():
+        for _, M, N, enc in encs:
+            oracle.linear_cpu(enc, xs[N], scratch[:M * N].reshape(M, N))
+
+    for _ in range(max(1, min(warmup, 1))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return nbytes / dt / 1e9, dt, oracle.threads()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1, help="activation rows M (1, 8, 32, 64, 256)")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": f"Qwen3-8B-shaped linears (q/o 4096x4096, k/v 1024x4096, gate/up 12288x4096, down 4096x12288)"
+                          f" x {args.layers} layers, batch M={args.batch}, seeds per shape, N(0,0.02) + 1% columns x8",
+              "batch": args.batch, "layers": args.layers,
+              "l2": "inputs larger than L2: 10.5 GB of distinct record buffers per step",
+              "parallelism": "single GPU" if world == 1 else f"tp{world} (col/row parallel + NCCL all-reduce)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = max(1, min(args.steps, 5))
+        val, dt, cores = cpu_reference(steps, args.warmup, args.batch)
+        sample = "the seven linears of one layer per step (1/36 of the GPU step's work)"
+        print(json.dumps({"metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+                          "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "impl": "reference", "config": config,
+                          "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+                          "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import statetree_b200 as S
+    from statetree_b200 import ops
+    from statetree_b200.linear import _state
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    E = ops.ext()
+    B = args.batch
+    assert 1 <= B <= 4096
+
+    # ---- weights: one encoded set per shape (this rank's shard), cloned into `layers` distinct buffers
+    gen = torch.Generator(device=dev)
+    layers = []
+    shard = []
+    for i, (name, M, N, kind) in enumerate(SHAPES):
+        gen.manual_seed(i)
+        W = torch.randn(M, N, device=dev, generator=gen) * 0.02
+        cols = torch.randperm(N, device=dev, generator=gen)[:N // 100]
+        W[:, cols] *= 8.0
+        W = W.to(torch.bfloat16)
+        if world > 1:                                  # each rank encodes its own shard, on 16-row / 64-col boundaries
+            if kind == "col":
+                W = W[rank * (M // world):(rank + 1) * (M // world)].contiguous()
+            else:
+                W = W[:, rank * (N // world):(rank + 1) * (N // world)].contiguous()
+        shard.append(S.TreeLinear.from_weight(W, verify=(i == 0)))
+        del W
+    for _ in range(args.layers):
+        row = []
+        for tl in shard:
+            c = S.TreeLinear(tl.in_features, tl.out_features, device="meta", n_esc=tl.esc_rows.numel())
+            c._buffers["tree"] = tl.tree.clone()
+            for k in ("esc_rows", "esc_cols", "esc_bits"):
+                c._buffers[k] = tl._buffers[k]
+            c._tables = tl.tables()
+            row.append(c)
+        layers.append(row)
+    del shard
+    torch.cuda.synchronize()
+
+    # ---- static buffers
+    Hs = HIDDEN // world if world > 1 else HIDDEN          # o's input columns on this rank
+    Is = INTER // world if world > 1 else INTER
+    x_h = torch.randn(B, HIDDEN, generator=torch.Generator().manual_seed(100)).to(torch.bfloat16).pin_memory()
+    x2_h = torch.randn(B, INTER, generator=torch.Generator().manual_seed(101)).to(torch.bfloat16).pin_memory()
+    x = x_h.to(dev)
+    x_o = x_h[:, rank * Hs:(rank + 1) * Hs].contiguous().to(dev)
+    x_d = x2_h[:, rank * Is:(rank + 1) * Is].contiguous().to(dev)
+    outs = [torch.empty(B, tl.out_features, dtype=torch.bfloat16, device=dev) for tl in layers[0]]
+    outs_h = [torch.empty(o.shape, dtype=torch.bfloat16).pin_memory() for o in outs]
+    ins = [x, x, x, x_o, x, x, x_d]
+    launches = 0
+    use_gemv = B <= 32
+    st = _state(dev)
+    ws_need = max((E.gemv_workspace_bytes if use_gemv else E.gemm_workspace_bytes)(tl.out_features, tl.in_features, B)
+                  for tl in layers[0])
+    ws = st.get_ws(ws_need)
+    cnt = st.get_cnt(4096)
+
+    def run_layers():
+        n = 0
+        for row in layers:
+            for tl, xin, y, (_, _, _, kind) in zip(row, ins, outs, SHAPES):
+                eo, el, eb = tl._tables
+                if use_gemv:
+                    E.gemv(tl.tree, eo, eb, el, xin, y, ws, cnt)
+                else:
+                    E.gemm(tl.tree, eo, el, xin, y, ws, cnt)
+                n += 1
+                if world > 1 and kind == "row":
+                    dist.all_reduce(y)
+        return n
+
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        launches = run_layers()                             # warm: function attributes, NCCL channels
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        run_layers()
+    torch.cuda.synchronize()
+    step_bytes = sum(algorithmic_bytes(M, N, B) for _, M, N, _ in SHAPES) * args.layers   # whole job, all ranks
+    step_flops = sum(2 * B * M * N for _, M, N, _ in SHAPES) * args.layers
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def dev_step():
+        graph.replay()
+
+    def e2e_step():
+        x.copy_(x_h, non_blocking=True)
+        x_o.copy_(x_h[:, rank * Hs:(rank + 1) * Hs], non_blocking=True)
+        x_d.copy_(x2_h[:, rank * Is:(rank + 1) * Is], non_blocking=True)
+        graph.replay()
+        for o, oh in zip(outs, outs_h):
+            oh.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()            # the caller reads the result every step
+
+    for _ in range(max(3, args.warmup)):
+        dev_step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(dev_step, args.steps)
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    status = ops.device_status()
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm, tf, which = peaks()
+    value = step_bytes / (ms * 1e-3) / 1e9
+    per_gpu = value / world
+    roof = {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s", "frac": per_gpu / hbm,
+            "traffic": None, "peak_source": f"of {which}", "frac_of_nominal_8TBs": per_gpu / 8000.0,
+            "kernel": "gemv_kernel" if use_gemv else "gemm_kernel",
+            "bytes_per_launch": step_bytes / world / launches, "us_per_launch": ms * 1e3 / launches}
+    if not use_gemv:
+        roof["tensor_tflops"] = step_flops / world / (ms * 1e-3) / 1e12
+        roof["tensor_frac"] = roof["tensor_tflops"] / tf
+    line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
+            "e2e": {"value": step_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": 2 * B * (HIDDEN + Hs + Is),
+                    "d2h_bytes_per_step": sum(o.numel() * 2 for o in outs)},
+            "gpu_launches": launches * args.steps, "roofline": roof, "device_status": status,
+            "bf16_equivalent_gbs": value * 16.0 / 12.125}
+    if not args.no_cpu and world == 1:
+        val, dt, cores = cpu_reference(2, 1, B)
+        line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                                "sample": "the seven linears of one layer, 2 timed passes (1/36 of a GPU step each)"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

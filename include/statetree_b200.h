@@ -1,0 +1,115 @@
+/* statetree_b200: C ABI of the sm_100a (B200) kernels for the state-tree decode hot path.
+ *
+ * This library takes the place of the reference project's two pybind extension modules, `statetree._C`
+ * (statetree/csrc/bindings.cpp:47-76) and `statetree._kv` (statetree/csrc/kvcache.cu:588-599).  Every entry point
+ * takes plain device pointers, sizes and a CUDA stream handle (a `cudaStream_t` passed as `void*`; NULL = the legacy
+ * default stream), launches on that stream without synchronising, allocates nothing per call and returns 0 on
+ * success.  A non-zero return means the arguments were rejected before any launch (or the launch itself failed);
+ * st_last_error() then holds the message, as the reference raised a RuntimeError from TORCH_CHECK.  The caller owns
+ * every buffer (outputs, fp32 workspaces, semaphores, KV pool), as in the reference.  Semaphore arrays must be zero
+ * on entry and are left zero by the kernels, so CUDA-graph replays need no memset.  The current CUDA device must be
+ * the one that owns the pointers.
+ *
+ * Data formats (frozen by the reference):
+ *   tree      uint8 [M/16, N/64, 1552]      weight records (statetree/format.py:9-12)
+ *   eo, el    escape side table: eo int32 [M/16 * N/64 + 1] offsets per record into el; el uint32 entries
+ *             bits << 16 | (record % 8) << 10 | row << 6 | col   (row, col inside the 16 x 64 record)
+ *   eb        uint32 [U, 16] per unit of up to 8 consecutive records of one 16-row tile (U = M/16 * ceil(N/512)):
+ *             word 0 = escapes in the unit, word 1 = offset of the unit's first entry in el, words 2..15 = the first
+ *             14 entries inline (the rest are read from el)
+ *   kv        uint8 [blocks, H, 2, 2, 1600] KV pages; pool uint32 [P, 16]; pool_cnt int32 [2]
+ *             (statetree/csrc/kvcache.cu:1-14)
+ *   X, Y      BF16 row-major, 16-byte aligned; Y[B, M] = X[B, N] * W[M, N]^T
+ */
+#ifndef STATETREE_B200_H
+#define STATETREE_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ST_ABI_VERSION 1
+
+/* replaces the `ABI` attribute check of statetree/ops.py:12 */
+int st_abi_version(void);
+/* message of the last failed call on this thread */
+const char* st_last_error(void);
+/* Reads (and clears) the device-side status word of the current device: 0 = no kernel gave up on a bounded wait.
+ * Synchronises the device.  No counterpart in the reference (its device-side waits are unbounded). */
+int st_device_status(void);
+
+/* ---- weights ---------------------------------------------------------------------------------------------------- */
+/* tree -> dense BF16 W [M, N].  Replaces `_C.dec(T, EO, EL, W)` (statetree/csrc/kernels.cu:1540-1582). */
+int st_dec(const void* tree, const int32_t* eo, const uint32_t* el, int64_t M, int64_t N, void* W, void* stream);
+/* out[i, :] = W[ids[i], :] (embedding lookup); ids int64.  Replaces `_C.rows` (statetree/csrc/kernels.cu:1587-1630). */
+int st_rows(const void* tree, const int32_t* eo, const uint32_t* el, int64_t M, int64_t N, const int64_t* ids,
+            int64_t n, void* out, void* stream);
+
+/* Small-batch fused decode + GEMV, 1 <= B <= 32.  Replaces the reference's mv / mvs / mvh / mvc / mvt entry points
+ * (statetree/csrc/kernels.cu:243-254, 370-400, 548-599, 771-808; statetree/csrc/hop.cu:993-1019).
+ * ws: fp32 workspace of st_gemv_workspace_bytes() bytes; cnt: int32 [M/16] semaphores, zero on entry and on exit
+ * (MoE: cnt int32 [problems * M/16], problems = S slots or nblk blocks).
+ * Yf32 (optional, may be NULL): the fp32 accumulators [B, M] before BF16 rounding, for verification. */
+int64_t st_gemv_workspace_bytes(int64_t M, int64_t N, int64_t B);
+int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X, void* Y,
+            float* Yf32, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);
+
+/* Large-batch fused decode + tcgen05 GEMM, B >= 1 (meant for B > 32), M % 128 == 0.  Replaces `_C.tm`, `_C.th`,
+ * `_C.tt` (statetree/csrc/kernels.cu:1892-1924, statetree/csrc/hop.cu:864-925, statetree/csrc/tt.cu:508-556).
+ * ws / cnt as for st_gemv (cnt: int32 [M/128 * ceil(B/256)]). */
+int64_t st_gemm_workspace_bytes(int64_t M, int64_t N, int64_t B);
+int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, const void* X, void* Y, float* Yf32, int64_t B,
+            int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);
+
+/* ---- mixture of experts ----------------------------------------------------------------------------------------- */
+/* y[s] = W[ids[s]] x[s / xdiv] for S (token, expert) slots; tp / eop / ebp / elp: int64 [E] device addresses of each
+ * expert's tree, eo, eb and el tables (all experts M x N); ids int32 (ids64 = 0) or int64 (ids64 = 1), clamped to [0, E).
+ * Replaces `_C.mvx` / `_C.mvwx` (statetree/csrc/kernels.cu:883-926, 1218-1246). */
+int64_t st_moe_gemv_workspace_bytes(int64_t S, int64_t M, int64_t N);
+int st_moe_gemv(const int64_t* tp, const int64_t* eop, const int64_t* ebp, const int64_t* elp, int64_t E, const void* X,
+                const void* ids, int ids64, void* Y, int64_t S, int64_t M, int64_t N, int64_t xdiv, void* ws,
+                int64_t ws_bytes, int32_t* cnt, void* stream);
+/* The same product for slots grouped by expert in the moe_align_block_size layout with block size 8: sorted int32
+ * [nblk * 8] slot ids padded with values >= S, bexp int32 [nblk] expert of each block (negative: skipped, another
+ * rank's expert), npost int32 [1] number of used entries of sorted.  Rows of skipped blocks are not written.
+ * Replaces `_C.mvg` / `_C.mvwg` / `_C.gtt` (statetree/csrc/kernels.cu:1043-1086, 1249-1279; statetree/csrc/gtt.cu:322-368). */
+int64_t st_moe_group_workspace_bytes(int64_t nblk, int64_t M, int64_t N);
+int st_moe_group_gemv(const int64_t* tp, const int64_t* eop, const int64_t* ebp, const int64_t* elp, int64_t E,
+                      const void* X, const int32_t* sorted, const int32_t* bexp, const int32_t* npost, int64_t nblk,
+                      void* Y, int64_t S, int64_t M, int64_t N, int64_t xdiv, void* ws, int64_t ws_bytes, int32_t* cnt,
+                      void* stream);
+/* out[t] = sum_j w[t, j] * Y[t * K + j] in fp32, expert order, BF16 out; w float32 (w_bf16 = 0) or BF16 (1).
+ * Replaces `_C.wsum` (statetree/csrc/kernels.cu:1489-1535). */
+int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H, void* stream);
+/* act[s, i] = silu(gu[s, i]) * gu[s, I + i]: silu in fp32, rounded to BF16, then multiplied (the rounding points of
+ * statetree/csrc/kernels.cu:1327-1333). */
+int st_silu_mul(const void* gu, void* act, int64_t S, int64_t I, void* stream);
+
+/* ---- KV pages --------------------------------------------------------------------------------------------------- */
+/* 6400 * H.  Replaces `_kv.page_bytes` (statetree/csrc/kvcache.cu:295). */
+int64_t st_kv_page_bytes(int64_t H);
+/* Append N tokens: K, V BF16 [N, H, 128] with token strides ks / vs (elements, heads contiguous); slot int64 [N]
+ * (block * 16 + row, negative = skipped).  Replaces `_kv.append` (statetree/csrc/kvcache.cu:297-324). */
+int st_kv_append(const void* K, const void* V, int64_t ks, int64_t vs, const int64_t* slot, int64_t N, int64_t H,
+                 void* kv, int64_t nblocks, uint32_t* pool, int64_t P, int32_t* pool_cnt, int reuse, void* stream);
+/* All pages -> dense BF16 Kd, Vd [nblocks, 16, H, 128].  Replaces `_kv.dequant` (statetree/csrc/kvcache.cu:326-336). */
+int st_kv_dequant(const void* kv, int64_t nblocks, int64_t H, const uint32_t* pool, int64_t P, void* Kd, void* Vd,
+                  void* stream);
+/* Listed pages -> dense BF16 [n, 16, H, 128]; ids outside [0, nblocks) give zeros.  Replaces `_kv.dequant_blocks`
+ * (statetree/csrc/kvcache.cu:338-354). */
+int st_kv_dequant_blocks(const void* kv, int64_t nblocks, int64_t H, const uint32_t* pool, int64_t P,
+                         const int32_t* blocks, int64_t n, void* Kd, void* Vd, void* stream);
+/* Decode attention, one query token per sequence: q, out BF16 [B, Hq, 128] with token strides qs / os; bt int32
+ * [B, bts] block table; lens int32 [B]; starts int32 [B] or NULL; S splits with >= minpps pages each; wo float
+ * [B, Hq, S, 128] and wml float [B, Hq, S, 2] hold the split partials (unnormalised O; max and sum in the exp2
+ * domain) when S > 1.  Replaces `_kv.attn` (statetree/csrc/kvcache.cu:536-585). */
+int st_kv_attn(const void* q, int64_t qs, int64_t B, int64_t Hq, const void* kv, int64_t nblocks, int64_t Hkv,
+               const uint32_t* pool, int64_t P, const int32_t* bt, int64_t bts, const int32_t* lens,
+               const int32_t* starts, void* out, int64_t os, float* wo, float* wml, double scale, int64_t S,
+               int64_t minpps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

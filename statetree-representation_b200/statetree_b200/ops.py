@@ -1,0 +1,259 @@
+"""Loads the C-ABI kernel library (libstatetree_b200.so) and exposes it as two objects with the call shapes of the
+reference's extension modules: ext() stands where `statetree._C` stood and kv_ext() where `statetree._kv` stood
+(reference: statetree/ops.py:7-27, 85-103).  Tensors are passed as device pointers plus sizes; the launch goes to
+torch's current stream of the tensors' device.  There is no fallback: a missing library or a non-CUDA tensor raises.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libstatetree_b200.so")
+ABI = 1
+_LIB = None
+
+_i64, _int, _vp, _dbl = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_double
+
+_SIGNATURES = {
+    "st_abi_version": (_int, []),
+    "st_last_error": (ctypes.c_char_p, []),
+    "st_device_status": (_int, []),
+    "st_dec": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "st_rows": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "st_gemv_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "st_gemv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "st_gemm_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "st_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "st_moe_gemv_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "st_moe_gemv": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "st_moe_group_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "st_moe_group_gemv": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp,
+                                 _i64, _vp, _vp]),
+    "st_wsum": (_int, [_vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
+    "st_silu_mul": (_int, [_vp, _vp, _i64, _i64, _vp]),
+    "st_kv_page_bytes": (_i64, [_i64]),
+    "st_kv_append": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _int, _vp]),
+    "st_kv_dequant": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
+    "st_kv_dequant_blocks": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
+    "st_kv_attn": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp,
+                          _dbl, _i64, _i64, _vp]),
+}
+
+
+def exported_symbols():
+    """names the header include/statetree_b200.h declares (used by the load test)"""
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    """the ctypes handle; raises when the library has not been built (python statetree-representation_b200/build.py)"""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"statetree_b200: {LIB_PATH} is missing; build it with "
+                               "`python statetree-representation_b200/build.py` (there is no fallback path)")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(L, name)                       # AttributeError if the library does not export it
+            fn.restype, fn.argtypes = res, args
+        if L.st_abi_version() != ABI:
+            raise RuntimeError(f"statetree_b200: library ABI {L.st_abi_version()} != {ABI}; rebuild it")
+        _LIB = L
+    return _LIB
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("statetree_b200: the kernels take CUDA tensors only (no CPU path)")
+    return t.data_ptr()
+
+
+def _ctx(t):
+    if not t.is_cuda:
+        raise RuntimeError("statetree_b200: the kernels take CUDA tensors only (no CPU path)")
+    return torch.cuda.device(t.device)
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check(rc):
+    if rc != 0:
+        raise RuntimeError(lib().st_last_error().decode())
+
+
+def device_status():
+    """0 unless a kernel gave up on one of its bounded waits since the last call (synchronises)"""
+    return int(lib().st_device_status())
+
+
+class _Weights:
+    """call shapes of the reference's `statetree._C` entry points that this library keeps"""
+    ABI = ABI
+
+    @staticmethod
+    def dec(T, EO, EL, W):
+        M, N = W.shape
+        with _ctx(T):
+            _check(lib().st_dec(_ptr(T), _ptr(EO), _ptr(EL), M, N, _ptr(W), _stream(T)))
+
+    @staticmethod
+    def rows(T, EO, EL, ids, out):
+        M, N = T.shape[0] * 16, T.shape[1] * 64
+        with _ctx(T):
+            _check(lib().st_rows(_ptr(T), _ptr(EO), _ptr(EL), M, N, _ptr(ids), ids.numel(), _ptr(out), _stream(T)))
+
+    @staticmethod
+    def gemv_workspace_bytes(M, N, B):
+        return int(lib().st_gemv_workspace_bytes(M, N, B))
+
+    @staticmethod
+    def gemv(T, EO, EB, EL, X, Y, WS, CNT, Yf32=None):
+        B, N = X.shape
+        M = Y.shape[1]
+        with _ctx(T):
+            _check(lib().st_gemv(_ptr(T), _ptr(EO), _ptr(EB), _ptr(EL), _ptr(X), _ptr(Y), _ptr(Yf32), B, M, N, _ptr(WS),
+                                 WS.numel() * WS.element_size(), _ptr(CNT), _stream(T)))
+
+    @staticmethod
+    def gemm_workspace_bytes(M, N, B):
+        return int(lib().st_gemm_workspace_bytes(M, N, B))
+
+    @staticmethod
+    def gemm(T, EO, EL, X, Y, WS, CNT, Yf32=None):
+        B, N = X.shape
+        M = Y.shape[1]
+        with _ctx(T):
+            _check(lib().st_gemm(_ptr(T), _ptr(EO), _ptr(EL), _ptr(X), _ptr(Y), _ptr(Yf32), B, M, N, _ptr(WS),
+                                 WS.numel() * WS.element_size(), _ptr(CNT), _stream(T)))
+
+    @staticmethod
+    def moe_gemv_workspace_bytes(S, M, N):
+        return int(lib().st_moe_gemv_workspace_bytes(S, M, N))
+
+    @staticmethod
+    def mvx(TP, EOP, EBP, ELP, X, ids, Y, WS, CNT, xdiv):
+        S, M = Y.shape
+        N = X.shape[1]
+        with _ctx(X):
+            _check(lib().st_moe_gemv(_ptr(TP), _ptr(EOP), _ptr(EBP), _ptr(ELP), TP.numel(), _ptr(X), _ptr(ids),
+                                     1 if ids.dtype == torch.int64 else 0, _ptr(Y), S, M, N, xdiv, _ptr(WS),
+                                     WS.numel() * WS.element_size(), _ptr(CNT), _stream(X)))
+
+    @staticmethod
+    def moe_group_workspace_bytes(nblk, M, N):
+        return int(lib().st_moe_group_workspace_bytes(nblk, M, N))
+
+    @staticmethod
+    def mvg(TP, EOP, EBP, ELP, X, sorted_ids, bexp, npost, Y, WS, CNT, xdiv):
+        S, M = Y.shape
+        N = X.shape[1]
+        with _ctx(X):
+            _check(lib().st_moe_group_gemv(_ptr(TP), _ptr(EOP), _ptr(EBP), _ptr(ELP), TP.numel(), _ptr(X),
+                                           _ptr(sorted_ids), _ptr(bexp), _ptr(npost), bexp.numel(), _ptr(Y), S, M, N,
+                                           xdiv, _ptr(WS), WS.numel() * WS.element_size(), _ptr(CNT), _stream(X)))
+
+    @staticmethod
+    def wsum(Y, W, out):
+        T, K = W.shape
+        with _ctx(Y):
+            _check(lib().st_wsum(_ptr(Y), _ptr(W), 1 if W.dtype == torch.bfloat16 else 0, _ptr(out), T, K, Y.shape[1],
+                                 _stream(Y)))
+
+    @staticmethod
+    def silu_mul(gu, act):
+        S, I2 = gu.shape
+        with _ctx(gu):
+            _check(lib().st_silu_mul(_ptr(gu), _ptr(act), S, I2 // 2, _stream(gu)))
+
+
+class _KV:
+    """call shapes of the reference's `statetree._kv` module (statetree/csrc/kvcache.cu:588-599)"""
+
+    @staticmethod
+    def version():
+        return 2
+
+    @staticmethod
+    def page_bytes(H):
+        return int(lib().st_kv_page_bytes(H))
+
+    @staticmethod
+    def append(K, V, slot, kv, pool, pool_cnt, reuse=False):
+        if not (K.dtype == V.dtype == torch.bfloat16 and K.dim() == 3 and V.dim() == 3):
+            raise RuntimeError("kv_append: K/V")
+        if not (K.size(2) == 128 and V.size(2) == 128 and K.stride(2) == 1 and V.stride(2) == 1 and
+                K.stride(1) == 128 and V.stride(1) == 128):
+            raise RuntimeError("kv_append: [N, H, 128] with heads contiguous")
+        if not (slot.dtype == torch.int64 and slot.is_contiguous() and slot.numel() == K.size(0)):
+            raise RuntimeError("kv_append: slots")
+        if not (kv.dtype == torch.uint8 and kv.is_contiguous() and kv.dim() == 5 and kv.size(1) == K.size(1) and
+                kv.size(4) == 1600):
+            raise RuntimeError("kv_append: cache [blocks, H, 2, 2, 1600]")
+        if not (pool.dtype == torch.int32 and pool.dim() == 2 and pool.size(1) == 16):
+            raise RuntimeError("kv_append: pool [P, 16]")
+        with _ctx(K):
+            _check(lib().st_kv_append(_ptr(K), _ptr(V), K.stride(0), V.stride(0), _ptr(slot), K.size(0), K.size(1),
+                                      _ptr(kv), kv.size(0), _ptr(pool), pool.size(0), _ptr(pool_cnt),
+                                      1 if reuse else 0, _stream(K)))
+
+    @staticmethod
+    def dequant(kv, pool, Kd, Vd):
+        nb, H = kv.size(0), kv.size(1)
+        if not (Kd.is_contiguous() and Vd.is_contiguous() and Kd.numel() == nb * 16 * H * 128 and
+                Vd.numel() == Kd.numel()):
+            raise RuntimeError("kv_dequant: outputs")
+        with _ctx(kv):
+            _check(lib().st_kv_dequant(_ptr(kv), nb, H, _ptr(pool), pool.size(0), _ptr(Kd), _ptr(Vd), _stream(kv)))
+
+    @staticmethod
+    def dequant_blocks(kv, pool, blocks, Kd, Vd):
+        if not (kv.dtype == torch.uint8 and kv.is_contiguous() and kv.dim() == 5 and kv.size(4) == 1600):
+            raise RuntimeError("kv_dequant_blocks: cache [blocks, H, 2, 2, 1600]")
+        if not (blocks.dtype == torch.int32 and blocks.is_contiguous() and blocks.dim() == 1):
+            raise RuntimeError("kv_dequant_blocks: blocks int32 [n]")
+        n, H = blocks.numel(), kv.size(1)
+        if not (Kd.dtype == Vd.dtype == torch.bfloat16 and Kd.is_contiguous() and Vd.is_contiguous() and
+                Kd.numel() >= n * 16 * H * 128 and Vd.numel() >= n * 16 * H * 128):
+            raise RuntimeError("kv_dequant_blocks: outputs [n, 16, H, 128]")
+        with _ctx(kv):
+            _check(lib().st_kv_dequant_blocks(_ptr(kv), kv.size(0), H, _ptr(pool), pool.size(0), _ptr(blocks), n,
+                                              _ptr(Kd), _ptr(Vd), _stream(kv)))
+
+    @staticmethod
+    def attn(q, kv, pool, bt, lens, out, wo, wml, scale, S, starts=None, minpps=1):
+        if not (q.dtype == torch.bfloat16 and q.dim() == 3 and q.size(2) == 128 and q.stride(2) == 1 and
+                q.stride(1) == 128):
+            raise RuntimeError("kv_attn: q [B, Hq, 128]")
+        if not (out.dtype == torch.bfloat16 and out.dim() == 3 and out.size(1) == q.size(1) and out.stride(2) == 1 and
+                out.stride(1) == 128):
+            raise RuntimeError("kv_attn: out [B, Hq, 128]")
+        if not (kv.dtype == torch.uint8 and kv.dim() == 5 and kv.size(4) == 1600):
+            raise RuntimeError("kv_attn: cache")
+        if not (bt.dtype == torch.int32 and bt.dim() == 2 and bt.stride(1) == 1 and lens.dtype == torch.int32):
+            raise RuntimeError("kv_attn: block table / lens int32")
+        B, Hq, Hkv = q.size(0), q.size(1), kv.size(1)
+        if Hq % Hkv or S < 1:
+            raise RuntimeError("kv_attn: heads / splits")
+        if S > 1 and not (wo.numel() >= B * Hq * S * 128 and wml.numel() >= B * Hq * S * 2):
+            raise RuntimeError("kv_attn: workspace")
+        if starts is not None and not (starts.dtype == torch.int32 and starts.numel() >= B):
+            raise RuntimeError("kv_attn: starts int32 [B]")
+        with _ctx(q):
+            _check(lib().st_kv_attn(_ptr(q), q.stride(0), B, Hq, _ptr(kv), kv.size(0), Hkv, _ptr(pool), pool.size(0),
+                                    _ptr(bt), bt.stride(0), _ptr(lens), _ptr(starts), _ptr(out), out.stride(0),
+                                    _ptr(wo), _ptr(wml), float(scale), int(S), int(minpps), _stream(q)))
+
+
+def ext():
+    lib()
+    return _Weights
+
+
+def kv_ext():
+    lib()
+    return _KV

@@ -1,0 +1,49 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol the header declares."""
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _built():
+    from statetree_b200 import ops
+    if not os.path.exists(ops.LIB_PATH):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("st_build", os.path.join(ROOT, "statetree-representation_b200",
+                                                                               "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build_library()
+    return ops
+
+
+def test_library_exports_header_symbols():
+    ops = _built()
+    with open(os.path.join(ROOT, "include", "statetree_b200.h")) as f:
+        text = f.read()
+    declared = set(re.findall(r"\b(st_[a-z0-9_]+)\s*\(", text))
+    assert declared == set(ops.exported_symbols()), declared ^ set(ops.exported_symbols())
+    L = ops.lib()                                       # resolves every symbol, checks the ABI version
+    assert L.st_abi_version() == ops.ABI
+    assert L.st_kv_page_bytes(1) == 6400 and L.st_kv_page_bytes(8) == 51200
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    ops = _built()
+    L = ops.lib()
+    assert L.st_dec(None, None, None, 17, 64, None, None) != 0
+    assert b"M % 16" in L.st_last_error()
+    assert L.st_gemv(None, None, None, None, None, None, None, 33, 16, 64, None, 0, None, None) != 0
+    assert b"batch" in L.st_last_error()
+    assert L.st_gemm(None, None, None, None, None, None, 64, 64, 64, None, 0, None, None) != 0
+    assert L.st_gemv_workspace_bytes(100, 64, 1) == -1
+
+
+def test_cpu_tensors_are_rejected():
+    import torch
+    ops = _built()
+    with pytest.raises(RuntimeError):
+        ops.ext().dec(torch.zeros(1, 1, 1552, dtype=torch.uint8), torch.zeros(2, dtype=torch.int32),
+                      torch.zeros(1, dtype=torch.int32), torch.zeros(16, 64, dtype=torch.bfloat16))

@@ -1,0 +1,77 @@
+"""The package's torch encoder / decoder / side tables on CPU against the golden fixtures and the oracle."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import gen_inputs as G
+import oracle
+from statetree_b200 import format as F
+from util import bits_to_torch, torch_to_bits
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.mark.parametrize("name", ["mixed", "heavy", "each", "llm"])
+def test_encode_decode_match_reference_bytes(name):
+    g = np.load(os.path.join(GOLD, "weights_small.npz"))
+    W = bits_to_torch(g[f"{name}_W"])
+    enc = F.encode(W, chunk_rows=32)                     # several row chunks
+    assert np.array_equal(enc["tree"].numpy(), g[f"{name}_tree"])
+    for k in ("esc_rows", "esc_cols", "esc_bits"):
+        assert np.array_equal(enc[k].numpy(), g[f"{name}_{k}"]), k
+    back = F.decode_reference(torch.from_numpy(g[f"{name}_tree"]), enc["esc_rows"], enc["esc_cols"], enc["esc_bits"])
+    assert np.array_equal(torch_to_bits(back), g[f"{name}_W"])
+    assert F.escape_count(W) == g[f"{name}_esc_rows"].size
+
+
+def test_digests_of_larger_cases():
+    with open(os.path.join(GOLD, "weights_digests.json")) as f:
+        dig = json.load(f)
+    for key, d in dig.items():
+        enc = F.encode(bits_to_torch(G.weights(d["M"], d["N"], d["seed"], d["regime"])))
+        assert sha(enc["tree"].numpy()) == d["tree"], key
+        assert sha(enc["esc_bits"].numpy()) == d["esc_bits"], key
+        assert abs(F.bits_per_weight(d["M"], d["N"], d["n_esc"]) - d["bits_per_weight"]) < 1e-12
+
+
+def test_side_tables_are_consistent():
+    g = np.load(os.path.join(GOLD, "weights_small.npz"))
+    for name in ("mixed", "heavy", "each"):
+        W = g[f"{name}_W"]
+        M, N = W.shape
+        er, ec, eb = (torch.from_numpy(g[f"{name}_{k}"]) for k in ("esc_rows", "esc_cols", "esc_bits"))
+        eo, el, blk = F.escape_tables(M, N, er, ec, eb)
+        assert np.array_equal(eo.numpy(), g[f"{name}_eo"])          # same per-record offsets as the reference's lists
+        el_u = el.numpy().view(np.uint32)
+        NG, cpt = N // 64, F.units_per_tile(N)
+        # every entry patches the decoded-without-escapes matrix into the exact one
+        plain = oracle.decode(g[f"{name}_tree"], er[:0].numpy(), ec[:0].numpy(), eb[:0].numpy())
+        for r in range((M // 16) * NG):
+            t, gcol = divmod(r, NG)
+            for e in el_u[eo[r]:eo[r + 1]]:
+                assert (e >> 10) & 7 == gcol % 8
+                plain[t * 16 + ((e >> 6) & 15), gcol * 64 + (e & 63)] = e >> 16
+        assert np.array_equal(plain, W)
+        blk_u = blk.numpy().view(np.uint32)
+        for u in range(blk_u.shape[0]):
+            t, c = divmod(u, cpt)
+            first = t * NG + c * 8
+            last = min(first + 8, (t + 1) * NG)
+            assert blk_u[u, 0] == eo[last] - eo[first] and blk_u[u, 1] == eo[first]
+            n = min(14, int(blk_u[u, 0]))
+            assert np.array_equal(blk_u[u, 2:2 + n], el_u[eo[first]:eo[first] + n])
+
+
+def test_shape_checks():
+    with pytest.raises(AssertionError):
+        F.encode(torch.zeros(8, 64, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError):
+        F.encode(torch.zeros(16, 64))

@@ -1,0 +1,230 @@
+"""GPU parity of the KV page kernels against the CPU oracle: page bytes and decoded values bit-exact, decode attention
+within 1e-3 relative Frobenius error of fp64 on its fp32 split partials."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import gen_inputs as G
+import oracle
+from util import bits_to_torch, rel_fro, torch_to_bits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+H, HQ, PAGE, D = 8, 32, 16, 128
+
+
+def _kx():
+    from statetree_b200.ops import kv_ext
+    return kv_ext()
+
+
+def _fresh(nb, h=H, P=1 << 15):
+    return (torch.zeros(nb, h, 2, 2, 1600, dtype=torch.uint8, device=DEV),
+            torch.zeros(P, 16, dtype=torch.int32, device=DEV), torch.zeros(2, dtype=torch.int32, device=DEV))
+
+
+def test_page_size():
+    assert _kx().page_bytes(1) == 6400 and _kx().version() == 2
+
+
+@pytest.mark.parametrize("name", ["tiny", "chan"])
+def test_records_match_reference_bytes(name):
+    g = np.load(os.path.join(GOLD, "kv_records.npz"))
+    K, V = g[f"{name}_K"], g[f"{name}_V"]
+    n, h, _ = K.shape
+    cache, pool, cnt = _fresh(n // 16, h, 1024)
+    slots = torch.arange(n, device=DEV)
+    Kt, Vt = bits_to_torch(K, DEV), bits_to_torch(V, DEV)
+    for a, b in ((0, 21), (21, n)):                                        # a call boundary inside a page
+        _kx().append(Kt[a:b], Vt[a:b], slots[a:b], cache, pool, cnt)
+    got = cache.cpu().numpy()
+    i = 0
+    for kvi in range(2):
+        for p in range(n // 16):
+            for hh in range(h):
+                for half in range(2):
+                    rec = got[p, hh, kvi, half]
+                    assert np.array_equal(rec[:1552], g[f"{name}_records"][i])
+                    c = int(g[f"{name}_counts"][i])
+                    head = int(rec[1552:1556].view(np.uint32)[0])
+                    assert (head & 15) == min(c, 11) and bool(head & 16) == (c > 11)
+                    assert np.array_equal(rec[1556:1600].view(np.uint32)[:min(c, 11)], g[f"{name}_slots"][i][:min(c, 11)])
+                    i += 1
+
+
+def _write(cache, pool, cnt, lens, pre, maxp, seed, tiny, reuse=True, o_state=None):
+    """chunked prefill (pages split across calls) then batched decode steps with a padding slot -1; the same calls go
+    to the oracle's pages when o_state = (kv, pool, cnt) numpy arrays is given"""
+    rs = np.random.RandomState(seed)
+    nb = cache.shape[0]
+    bt = rs.permutation(nb)[:len(lens) * maxp].reshape(len(lens), maxp).astype(np.int32)
+    data = [G.kv_tokens(L, H, seed=seed * 100 + i, tiny=tiny) for i, L in enumerate(lens)]
+
+    def slots(s, pos):
+        pos = np.asarray(pos)
+        return (bt[s][pos // PAGE].astype(np.int64) * PAGE + pos % PAGE)
+
+    def app(K, V, sl):
+        _kx().append(bits_to_torch(K, DEV), bits_to_torch(V, DEV), torch.from_numpy(sl).to(DEV), cache, pool, cnt, reuse)
+        if o_state is not None:
+            oracle.kv_append(K, V, sl, *o_state, reuse=reuse)
+
+    for s, p0 in enumerate(pre):
+        c = min(p0, (p0 * 3) // 5 + 3)
+        for a, b in ((0, c), (c, p0)):
+            if b > a:
+                app(data[s][0][a:b], data[s][1][a:b], slots(s, np.arange(a, b)))
+    pos = list(pre)
+    while any(p < L for p, L in zip(pos, lens)):
+        ks, vs, sl = [], [], []
+        for s, L in enumerate(lens):
+            if pos[s] < L:
+                ks.append(data[s][0][pos[s]:pos[s] + 1])
+                vs.append(data[s][1][pos[s]:pos[s] + 1])
+                sl.append(slots(s, [pos[s]]))
+                pos[s] += 1
+        ks.append(np.zeros((1, H, D), np.uint16))
+        vs.append(np.zeros((1, H, D), np.uint16))
+        sl.append(np.array([-1], np.int64))
+        app(np.concatenate(ks), np.concatenate(vs), np.concatenate(sl))
+    return bt, data
+
+
+def _wrong(cache, pool, bt, data, lens):
+    n = 0
+    for s, L in enumerate(lens):
+        npg = (L + PAGE - 1) // PAGE
+        Kd = torch.empty(npg, PAGE, H, D, dtype=torch.bfloat16, device=DEV)
+        Vd = torch.empty_like(Kd)
+        _kx().dequant_blocks(cache, pool, torch.from_numpy(bt[s][:npg].copy()).to(DEV), Kd, Vd)
+        n += int((torch_to_bits(Kd).reshape(-1, H, D)[:L] != data[s][0]).sum())
+        n += int((torch_to_bits(Vd).reshape(-1, H, D)[:L] != data[s][1]).sum())
+    return n
+
+
+LENS, PRE, MAXP = [600, 333, 17, 513], [400, 333, 5, 500], 40
+NB = len(LENS) * MAXP + 5
+
+
+def test_pages_exact_with_recycling():
+    cache, pool, cnt = _fresh(NB, H, 1 << 17)
+    used = []
+    for rnd, tiny in enumerate((0.05, 0.12, 0.02, 0.12)):                  # 5-13 % escapes: chains needed
+        bt, data = _write(cache, pool, cnt, LENS, PRE, MAXP, rnd, tiny)
+        assert _wrong(cache, pool, bt, data, LENS) == 0
+        assert int(cnt[1]) == 0
+        used.append(int(cnt[0]))
+    assert used[0] > 0
+    assert used[-1] < 1.6 * used[1], used                                 # chains are recycled, no leak
+
+
+def test_pages_equal_the_oracle_bytes():
+    lens, pre, maxp = [70, 33, 17], [40, 33, 5], 6
+    nb = len(lens) * maxp + 2
+    cache, pool, cnt = _fresh(nb, H, 4096)
+    o = (np.zeros((nb, H, 2, 2, 1600), np.uint8), np.zeros((4096, 16), np.uint32), np.zeros(2, np.int32))
+    bt, data = _write(cache, pool, cnt, lens, pre, maxp, 7, 0.01, reuse=False, o_state=o)
+    got = cache.cpu().numpy()
+    # units without extension chains are byte-identical (chain block numbers depend on allocation order)
+    heads = got[..., 1552:1556].copy().view(np.uint32)[..., 0]
+    plain = (heads & 16) == 0
+    assert plain.mean() > 0.5
+    assert np.array_equal(got[plain], o[0][plain])
+    assert np.array_equal(got[..., :1552], o[0][..., :1552])
+    Kd, Vd = oracle.kv_dequant_blocks(o[0], o[1])
+    Kg = torch.empty(nb, PAGE, H, D, dtype=torch.bfloat16, device=DEV)
+    Vg = torch.empty_like(Kg)
+    _kx().dequant(cache, pool, Kg, Vg)
+    assert np.array_equal(torch_to_bits(Kg), Kd) and np.array_equal(torch_to_bits(Vg), Vd)
+
+
+def test_dequant_blocks_out_of_range_is_zero():
+    cache, pool, cnt = _fresh(NB)
+    _write(cache, pool, cnt, LENS, PRE, MAXP, 1, 0.01)
+    blocks = torch.tensor([-1, NB, 5], dtype=torch.int32, device=DEV)
+    Kd = torch.full((3, PAGE, H, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    Vd = torch.full_like(Kd, 7.0)
+    _kx().dequant_blocks(cache, pool, blocks, Kd, Vd)
+    assert int((Kd[:2] != 0).sum()) == 0 and int((Vd[:2] != 0).sum()) == 0
+    K5, V5 = torch.empty_like(Kd[:1]), torch.empty_like(Vd[:1])
+    _kx().dequant_blocks(cache, pool, blocks[2:].contiguous(), K5, V5)
+    assert torch.equal(Kd[2:], K5) and torch.equal(Vd[2:], V5)
+
+
+def test_pool_exhaustion_is_flagged():
+    cache, pool, cnt = _fresh(2, H, 1)
+    K, V = G.kv_tokens(32, H, seed=5, tiny=0.6)
+    _kx().append(bits_to_torch(K, DEV), bits_to_torch(V, DEV), torch.arange(32, device=DEV), cache, pool, cnt)
+    assert int(cnt[1]) == 1
+
+
+def _merge64(wo, wml, B, S):
+    wo = wo.cpu().numpy().astype(np.float64).reshape(B, HQ, S, D)
+    ml = wml.cpu().numpy().astype(np.float64).reshape(B, HQ, S, 2)
+    m, l = ml[..., 0], ml[..., 1]
+    M = m.max(-1, keepdims=True)
+    f = np.where(np.isfinite(m), np.exp2(m - np.where(np.isfinite(M), M, 0.0)), 0.0)
+    L = (f * l).sum(-1)
+    O = (f[..., None] * wo).sum(-2)
+    return np.where(L[..., None] > 0, O / np.where(L[..., None] > 0, L[..., None], 1.0), 0.0)
+
+
+@pytest.mark.parametrize("tiny,left_pad", [(0.02, False), (0.0, True)])
+def test_decode_attention_matches_fp64(tiny, left_pad):
+    cache, pool, cnt = _fresh(NB)
+    o = (np.zeros((NB, H, 2, 2, 1600), np.uint8), np.zeros((1 << 15, 16), np.uint32), np.zeros(2, np.int32))
+    bt, data = _write(cache, pool, cnt, LENS, PRE, MAXP, 2, tiny, reuse=False, o_state=o)
+    lens_l = LENS + [0]                                                    # an empty sequence
+    B = len(lens_l)
+    bt = np.concatenate([bt, bt[:1]])
+    starts = np.array([37, 0, 3, 500, 0], np.int32) if left_pad else None
+    q = G.to_bf16_bits(np.random.RandomState(9).standard_normal((B, HQ, D)))
+    scale = 1.0 / math.sqrt(D)
+    ref = oracle.kv_attn_f64(q, o[0], o[1], bt, np.array(lens_l, np.int32), scale, starts)
+    qt, btt = bits_to_torch(q, DEV), torch.from_numpy(bt).to(DEV)
+    lens = torch.tensor(lens_l, dtype=torch.int32, device=DEV)
+    st_t = None if starts is None else torch.from_numpy(starts).to(DEV)
+    for S, minpps in ((1, 1), (2, 1), (8, 4), (32, 4)):
+        out = torch.full((B, HQ, D), 7.0, dtype=torch.bfloat16, device=DEV)
+        wo = torch.zeros(B * HQ * S * D, dtype=torch.float32, device=DEV)
+        wml = torch.zeros(B * HQ * S * 2, dtype=torch.float32, device=DEV)
+        _kx().attn(qt, cache, pool, btt, lens, out, wo, wml, scale, S, st_t, minpps)
+        got = out.float().cpu().numpy()
+        assert np.abs(got[:-1] - ref[:-1]).max() / np.abs(ref[:-1]).max() < 1e-2, S   # the reference's own bar
+        assert rel_fro(got[:-1], ref[:-1]) < 5e-3, (S, rel_fro(got[:-1], ref[:-1]))   # BF16 output rounding floor
+        assert not got[-1].any()                                                      # length 0 -> zeros
+        if S > 1:                                                                     # fp32 partials, merged in fp64
+            e = rel_fro(_merge64(wo, wml, B, S)[:-1], ref[:-1])
+            assert e < 1e-3, (S, e)
+        out2 = torch.empty_like(out)
+        _kx().attn(qt, cache, pool, btt, lens, out2, wo, wml, scale, S, st_t, minpps)
+        assert torch.equal(out, out2)
+    from statetree_b200 import ops
+    assert ops.device_status() == 0
+
+
+def test_cache_object_decode_steps():
+    """StateTreeKVCache: prefill + decode steps through update() / attention() against dense fp64 attention"""
+    from statetree_b200.kvcache import StateTreeKVCache
+    B, T0, steps = 3, 37, 5
+    cache = StateTreeKVCache(1, B, 64, H, DEV, pool_blocks=4096)
+    rs = np.random.RandomState(0)
+    Kall = G.to_bf16_bits(rs.standard_normal((B, H, T0 + steps, D)))
+    Vall = G.to_bf16_bits(rs.standard_normal((B, H, T0 + steps, D)))
+    Kt, Vt = bits_to_torch(Kall, DEV), bits_to_torch(Vall, DEV)
+    cache.update(0, Kt[:, :, :T0], Vt[:, :, :T0])
+    for s in range(steps):
+        t = T0 + s
+        cache.update(0, Kt[:, :, t:t + 1], Vt[:, :, t:t + 1])
+        q = torch.randn(B, HQ, D, device=DEV, generator=torch.Generator(DEV).manual_seed(s)).to(torch.bfloat16)
+        out = cache.attention(0, q, 1.0 / math.sqrt(D))
+        k = Kt[:, :, :t + 1].double().repeat_interleave(HQ // H, dim=1)
+        v = Vt[:, :, :t + 1].double().repeat_interleave(HQ // H, dim=1)
+        p = torch.softmax(torch.einsum("bhd,bhld->bhl", q.double(), k) / math.sqrt(D), -1)
+        ref = torch.einsum("bhl,bhld->bhd", p, v)
+        assert float((out.double() - ref).norm() / ref.norm()) < 5e-3
+    cache.check()

@@ -1,0 +1,118 @@
+"""GPU parity of the mixture-of-experts kernels: slot and grouped products, routing-weighted sum, SwiGLU gate."""
+import numpy as np
+import pytest
+import torch
+
+import gen_inputs as G
+from util import bits_to_torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _experts(E, M, N, seed, heavy=None):
+    from statetree_b200 import TreeLinear
+    Ws = []
+    for e in range(E):
+        Ws.append(G.weights(M, N, seed * 1000 + e, "heavy" if e == heavy else "mixed"))
+    mods = [TreeLinear.from_weight(bits_to_torch(W, DEV)) for W in Ws]
+    return Ws, mods
+
+
+def test_slot_and_grouped_products_match_fp64():
+    from statetree_b200.experts import expert_tables, moe_align, moe_gemv, moe_group_gemv, moe_wsum, silu_mul
+    E, M, N = 32, 256, 512
+    Ws, mods = _experts(E, M, N, 1)
+    tabs = expert_tables(mods)
+    Wall = torch.stack([bits_to_torch(W, DEV) for W in Ws]).double()
+    g = torch.Generator(DEV).manual_seed(0)
+    for S, K in ((1, 1), (8, 4), (64, 8), (300, 4)):
+        ids = torch.randint(0, E, (S,), device=DEV, generator=g)
+        x = torch.randn(S // K, N, device=DEV, generator=g).to(torch.bfloat16)
+        ref = torch.einsum("sn,smn->sm", x.repeat_interleave(K, 0).double(), Wall[ids])
+        outs = {"slot": moe_gemv(tabs, x, ids, M, K), "slot_i32": moe_gemv(tabs, x, ids.int(), M, K)}
+        al = moe_align(ids, E, 8)
+        sid = al[0][al[0] < S]
+        assert torch.equal(sid.sort().values, torch.arange(S, device=DEV, dtype=torch.int32))   # every pair once
+        outs["group"] = moe_group_gemv(tabs, x, al, S, M, K)
+        for k, y in outs.items():
+            rel = float((y.double() - ref).norm() / ref.norm())
+            assert rel < 4e-3, (S, k, rel)
+        assert torch.equal(outs["slot"], outs["slot_i32"])
+        bad = ids.int().clone()                          # ids outside [0, E) are clamped in the kernel
+        bad[0] = E + 5
+        if S > 1:
+            bad[-1] = -2
+        assert torch.equal(moe_gemv(tabs, x, bad, M, K), moe_gemv(tabs, x, bad.clamp(0, E - 1), M, K)), S
+        # another rank's experts: negative block ids are skipped and their rows stay untouched
+        bexp = al[1].clone()
+        bexp[bexp % 2 == 1] = -1
+        y = torch.full((S, M), 7.0, dtype=torch.bfloat16, device=DEV)
+        from statetree_b200.linear import _state
+        from statetree_b200.ops import ext
+        st = _state(torch.device(DEV))
+        ws = st.get_ws(ext().moe_group_workspace_bytes(bexp.numel(), M, N))
+        ext().mvg(*tabs, x, al[0], bexp, al[2], y, ws, st.get_cnt(bexp.numel() * (M // 16)), K)
+        odd = (ids % 2 == 1)
+        assert bool((y[odd] == 7.0).all()) and torch.equal(y[~odd], outs["group"][~odd])
+    T, K, Hd = 5, 3, 64
+    y = torch.randn(T * K, Hd, device=DEV, generator=g).to(torch.bfloat16)
+    for w in (torch.rand(T, K, device=DEV), torch.rand(T, K, device=DEV).to(torch.bfloat16)):
+        got = moe_wsum(y, w).float()
+        want = (y.view(T, K, Hd).float() * w.float().unsqueeze(-1)).sum(1)
+        assert (got - want).abs().max().item() < 1e-2
+    gu = torch.randn(7, 2 * 96, device=DEV, generator=g).to(torch.bfloat16)
+    want = (torch.nn.functional.silu(gu[:, :96].float()).to(torch.bfloat16) * gu[:, 96:])
+    assert (silu_mul(gu).float() - want.float()).abs().max().item() < 2e-2
+    from statetree_b200 import ops
+    assert ops.device_status() == 0
+
+
+def test_one_hot_inputs_read_expert_columns_exactly():
+    from statetree_b200.experts import expert_tables, moe_align, moe_gemv, moe_group_gemv
+    E, M = 12, 256
+    for N in (256, 768):
+        Ws, mods = _experts(E, M, N, 2 + N, heavy=3)
+        assert mods[3].esc_rows.numel() > 0.15 * M * N
+        tabs = expert_tables(mods)
+        g = torch.Generator(DEV).manual_seed(N)
+        for S in (1, 8, 37, 200):
+            ids = torch.randint(0, E, (S,), device=DEV, generator=g)
+            ids[: S // 3] = 3                                              # the escape-heavy expert
+            cols = torch.randint(0, N, (S,), device=DEV, generator=g)
+            x = torch.zeros(S, N, device=DEV, dtype=torch.bfloat16)
+            x[torch.arange(S, device=DEV), cols] = 1.0
+            want = torch.stack([bits_to_torch(Ws[int(e)][:, int(c)], DEV) for e, c in zip(ids.tolist(), cols.tolist())])
+            outs = {"slot": moe_gemv(tabs, x, ids, M, 1),
+                    "group": moe_group_gemv(tabs, x, moe_align(ids, E, 8), S, M, 1)}
+            for k, y in outs.items():
+                assert torch.equal(y, want), (N, S, k, (y.float() - want.float()).abs().max().item())
+
+
+def test_tree_experts_block_matches_dense():
+    from statetree_b200.experts import TreeExperts
+    E, Hd, I, K = 16, 256, 128, 4
+    g = torch.Generator(DEV).manual_seed(3)
+    gate_up = (torch.randn(E, 2 * I, Hd, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    down = (torch.randn(E, Hd, I, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    te = TreeExperts.from_weights(gate_up, down)
+    for T in (1, 4, 8, 40):
+        x = torch.randn(T, Hd, device=DEV, generator=g).to(torch.bfloat16)
+        logits = torch.randn(T, E, device=DEV, generator=g)
+        w, ids = torch.softmax(logits, -1).topk(K, -1)
+        got = te(x, ids, w).double()
+        ref = torch.zeros(T, Hd, dtype=torch.float64, device=DEV)
+        for t in range(T):
+            for j in range(K):
+                e = int(ids[t, j])
+                gu = gate_up[e].double() @ x[t].double()
+                act = torch.nn.functional.silu(gu[:I]) * gu[I:]
+                ref[t] += float(w[t, j]) * (down[e].double() @ act)
+        assert float((got - ref).norm() / ref.norm()) < 2e-2, T
+        # expert parallelism: experts split over two ranks, partial outputs add up
+        emap0 = torch.where(torch.arange(E, device=DEV) < E // 2, torch.arange(E, device=DEV), -1).int()
+        emap1 = torch.where(torch.arange(E, device=DEV) >= E // 2, torch.arange(E, device=DEV) - E // 2, -1).int()
+        te0 = TreeExperts(list(te.w13)[:E // 2], list(te.w2)[:E // 2])
+        te1 = TreeExperts(list(te.w13)[E // 2:], list(te.w2)[E // 2:])
+        part = te0(x, ids, w, emap0).double() + te1(x, ids, w, emap1).double()
+        assert float((part - ref).norm() / ref.norm()) < 2e-2, T

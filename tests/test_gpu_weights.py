@@ -1,0 +1,157 @@
+"""GPU parity of the weight kernels (dec, rows, GEMV, tcgen05 GEMM) against the CPU oracle, through the C ABI.
+
+Bars: decoded weights bit-exact; fp32 accumulators within 1e-3 relative Frobenius error of the fp64 product over the
+exactly decoded BF16 values (the BF16 output then carries only its own rounding: it must equal the rounded
+accumulator); one-hot activations read columns of W back bit for bit; reruns are bit-identical.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import gen_inputs as G
+import oracle
+from util import bits_to_torch, layer_from_oracle, rel_fro, torch_to_bits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL = 1e-3            # relative Frobenius error of fp32 accumulators against the fp64 product
+
+
+def _status_ok():
+    from statetree_b200 import ops
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["mixed", "heavy", "each", "llm"])
+def test_dec_of_reference_trees_is_exact(name):
+    from statetree_b200 import TreeLinear
+    g = np.load(os.path.join(GOLD, "weights_small.npz"))
+    W = g[f"{name}_W"]
+    M, N = W.shape
+    tl = TreeLinear(N, M, device="meta", n_esc=g[f"{name}_esc_rows"].size)
+    for k in ("tree", "esc_rows", "esc_cols", "esc_bits"):
+        tl._buffers[k] = torch.from_numpy(g[f"{name}_{k}"]).to(DEV)
+    assert np.array_equal(torch_to_bits(tl.dequantize()), W)
+
+
+@pytest.mark.parametrize("M,N,seed,regime", [(256, 512, 0, "mixed"), (512, 1024, 1, "mixed"), (256, 2048, 5, "heavy"),
+                                             (1024, 512, 6, "each"), (512, 768, 7, "llm"), (16, 64, 8, "mixed")])
+def test_encode_on_gpu_equals_oracle_and_dec_roundtrips(M, N, seed, regime):
+    from statetree_b200 import TreeLinear, format as F
+    W = G.weights(M, N, seed, regime)
+    enc = oracle.encode(W)
+    Wt = bits_to_torch(W, DEV)
+    got = F.encode(Wt)
+    assert np.array_equal(got["tree"].cpu().numpy(), enc["tree"])
+    for k in ("esc_rows", "esc_cols", "esc_bits"):
+        assert np.array_equal(got[k].cpu().numpy(), enc[k])
+    tl = TreeLinear.from_weight(Wt, verify=True)             # verify runs the dec kernel
+    assert np.array_equal(torch_to_bits(tl.dequantize()), W)
+    ids = torch.tensor([[0, M - 1, 17 % M], [5 % M, 5 % M, M // 2]], device=DEV)
+    rows = tl.rows(ids)
+    assert rows.shape == (2, 3, N)
+    assert np.array_equal(torch_to_bits(rows).reshape(-1, N), W[ids.cpu().numpy().reshape(-1)])
+
+
+def _check_linear(tl, W, B, seed, path):
+    from statetree_b200.linear import _state
+    rs = np.random.RandomState(seed)
+    X = G.to_bf16_bits(rs.standard_normal((B, W.shape[1])))
+    x = bits_to_torch(X, DEV)
+    yf = torch.empty(B, W.shape[0], dtype=torch.float32, device=DEV)
+    y = tl._forward(x, yf)
+    torch.cuda.synchronize()
+    ref = oracle.linear_f64(W, X)
+    e32 = rel_fro(yf.cpu().numpy(), ref)
+    assert e32 < TOL, (path, W.shape, B, e32)
+    assert torch.equal(y, yf.to(torch.bfloat16)), (path, "BF16 output is not the rounded accumulator")
+    e16 = rel_fro(y.float().cpu().numpy(), ref)
+    assert e16 < 5e-3, (path, W.shape, B, e16)
+    for _ in range(2):                                                     # bit-identical from run to run
+        assert torch.equal(tl(x), y), (path, W.shape, B, "nondeterministic")
+    st = _state(torch.device(DEV))
+    assert int(st.cnt.abs().sum()) == 0                                   # semaphores left at zero
+    return e32
+
+
+@pytest.mark.parametrize("M,N,regime", [(512, 1024, "mixed"), (1024, 512, "mixed"), (256, 2048, "heavy"),
+                                        (128, 768, "each"), (16, 64, "mixed"), (2048, 4096, "llm")])
+def test_gemv_matches_fp64(M, N, regime):
+    W = G.weights(M, N, M + N, regime)
+    tl, _ = layer_from_oracle(W)
+    for B in (1, 3, 8, 12, 16, 24, 32):
+        _check_linear(tl, W, B, B, "gemv")
+    _status_ok()
+
+
+@pytest.mark.parametrize("M,N,regime", [(512, 1024, "mixed"), (1024, 512, "mixed"), (256, 2048, "heavy"),
+                                        (128, 768, "each"), (2048, 4096, "llm")])
+def test_gemm_matches_fp64(M, N, regime):
+    W = G.weights(M, N, M + N + 1, regime)
+    tl, _ = layer_from_oracle(W)
+    for B in (33, 48, 64, 100, 128, 200, 256, 300, 600):
+        _check_linear(tl, W, B, B, "gemm")
+    _status_ok()
+
+
+def _one_hot_check(tl, W, cols, B):
+    N = W.shape[1]
+    x = torch.zeros(B, N, dtype=torch.bfloat16, device=DEV)
+    for b in range(B):
+        x[b, cols[b % len(cols)]] = 1.0
+    y = tl(x)
+    want = bits_to_torch(np.stack([W[:, cols[b % len(cols)]] for b in range(B)]), DEV)
+    assert torch.equal(y, want), (W.shape, B, (y.float() - want.float()).abs().max().item())
+
+
+@pytest.mark.parametrize("regime", ["mixed", "heavy", "each"])
+def test_one_hot_reads_columns_back_exactly(regime):
+    M, N = 256, 1024
+    W = G.weights(M, N, 3, regime)
+    tl, enc = layer_from_oracle(W)
+    esc_cols = sorted(set(enc["esc_cols"].tolist()))
+    cols = (esc_cols[:40] + list(range(0, N, 37)))[:64]                    # columns that hold escapes first
+    for B in (1, 5, 8, 16, 32, 40, 64, 130):
+        _one_hot_check(tl, W, cols, B)
+    _status_ok()
+
+
+def test_argument_errors_raise():
+    from statetree_b200 import ops
+    W = G.weights(64, 128, 0, "mixed")
+    tl, _ = layer_from_oracle(W)
+    eo, el, eb = tl.tables()
+    x = torch.zeros(40, 128, dtype=torch.bfloat16, device=DEV)
+    y = torch.empty(40, 64, dtype=torch.bfloat16, device=DEV)
+    ws = torch.empty(16, dtype=torch.float32, device=DEV)
+    cnt = torch.zeros(16, dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError, match="batch"):
+        ops.ext().gemv(tl.tree, eo, eb, el, x, y, ws, cnt)
+    with pytest.raises(RuntimeError, match="128"):
+        ops.ext().gemm(tl.tree, eo, el, x, y, ws, cnt)                    # M = 64 is not a multiple of 128
+
+
+def test_benchmark_shape_roundtrip_and_properties():
+    """full-size 4096 x 4096 (the benchmark's q/o projection): lossless round trip on the GPU, one-hot read-back,
+    linearity y(x1 + x2) == y(x1) + y(x2) for one-hot pairs, fp32 accumulators against torch fp64 on the GPU"""
+    from statetree_b200 import TreeLinear
+    W = G.weights(4096, 4096, 0, "llm")
+    Wt = bits_to_torch(W, DEV)
+    tl = TreeLinear.from_weight(Wt, verify=True)
+    assert 0 < tl.esc_rows.numel() < 0.001 * W.size
+    assert abs(tl.bits_per_weight - 12.125) < 0.05
+    cols = list(range(0, 4096, 101))
+    _one_hot_check(tl, W, cols, 8)
+    _one_hot_check(tl, W, cols, 64)
+    for B in (1, 8, 64, 256):
+        x = torch.randn(B, 4096, device=DEV, generator=torch.Generator(DEV).manual_seed(B)).to(torch.bfloat16)
+        yf = torch.empty(B, 4096, dtype=torch.float32, device=DEV)
+        y = tl._forward(x, yf)
+        ref = x.double() @ Wt.double().t()
+        err = float((yf.double() - ref).norm() / ref.norm())
+        assert err < TOL, (B, err)
+        assert torch.equal(y, yf.to(torch.bfloat16))
+    _status_ok()
