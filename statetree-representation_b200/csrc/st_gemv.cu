@@ -15,6 +15,8 @@
 // with one activation row; MODE 2 makes every block of 8 slots of one expert (moe_align_block_size layout) a problem.
 #include "../../include/statetree_b200.h"
 #include "st_common.cuh"
+#include <stdlib.h>
+
 #include "st_host.h"
 
 namespace {
@@ -39,8 +41,19 @@ struct GemvArgs {
   int E, xdiv;
   int NG, CPT, T;                         // column groups, units per tile, tiles per problem
   long long U;                            // units over all problems
-  int nprob, maxcover, stages;
+  int nprob, maxcover, stages, stage_bytes, nxrows;
+#ifdef ST_PROF
+  long long* prof;                        // [CTAs][64] globaltimer stamps (development builds only)
+#endif
 };
+
+#ifdef ST_PROF
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define PROF(slot) do { if (a.prof && (slot) < 64) a.prof[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
+long long* g_prof_buf = nullptr;
+#else
+#define PROF(slot) do {} while (0)
+#endif
 
 struct Prob {                             // what a unit's problem resolves to
   const uint8_t* tree; const int* eo; const uint32_t* eb; const uint32_t* el;
@@ -81,70 +94,221 @@ __device__ __forceinline__ long long out_row(const GemvArgs& a, int p, int n) {
 }
 
 __device__ __forceinline__ int cta_of_unit(long long u, long long U, int C) { return (int)(((u + 1) * C - 1) / U); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Walks a CTA's units without divisions: problem p, tile, unit c inside the tile.  The CTA's range [u0, u1) is
+// visited as two segments: first the units of the trailing tile it shares with the next CTA, then the rest.  Both
+// tiles that a CTA shares with its neighbours are thus finished in its first microsecond, and the cross-CTA
+// hand-over (fence, semaphore, re-read of partial sums) overlaps the streaming instead of forming the kernel's tail.
+template <int MODE>
+struct UnitCursor {
+  int u, end, p, tile, c;
+  int seg, b0, e0, b1, e1;
+  Prob pr;
+  __device__ __forceinline__ void seek(const GemvArgs& a, int ub, int ue) {
+    u = ub; end = ue;
+    if (u >= end) return;
+    const int upp = a.T * a.CPT;
+    p = u / upp;
+    const int ul = u - p * upp;
+    tile = ul / a.CPT; c = ul - tile * a.CPT;
+    enter(a);
+  }
+  __device__ __forceinline__ void enter(const GemvArgs& a) {          // (p, tile, c) just changed problem
+    while (u < end) {
+      pr = resolve<MODE>(a, p);
+      if (MODE != MODE_GROUP || !pr.skip) return;
+      u += a.T * a.CPT - (tile * a.CPT + c);                         // jump over a skipped problem
+      ++p; tile = 0; c = 0;
+    }
+  }
+  __device__ __forceinline__ void init(const GemvArgs& a, int u0, int u1) {
+    const int ts = u1 - u1 % a.CPT;                                   // first unit of the tile that holds u1
+    if (ts > u0 && ts < u1) { b0 = ts; e0 = u1; b1 = u0; e1 = ts; }
+    else { b0 = u0; e0 = u1; b1 = u1; e1 = u1; }
+    seg = 0;
+    seek(a, b0, e0);
+    if (u >= end) { seg = 1; seek(a, b1, e1); }
+  }
+  __device__ __forceinline__ bool valid() const { return u < end; }
+  __device__ __forceinline__ int nrec(const GemvArgs& a) const { return c == a.CPT - 1 ? a.NG - c * CW : CW; }
+  __device__ __forceinline__ bool tile_end(const GemvArgs& a) const { return c == a.CPT - 1 || u + 1 == end; }
+  __device__ __forceinline__ void next(const GemvArgs& a) {
+    ++u;
+    if (++c == a.CPT) {
+      c = 0;
+      if (++tile == a.T) { tile = 0; ++p; enter(a); }
+    }
+    if (u >= end && seg == 0) { seg = 1; seek(a, b1, e1); }
+  }
+};
+
+// 8 consumer warps (one record of the unit each), warp 8 = producer, warp 9 = reducer
 template <int NT, int MODE>
-__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int NB = 8 * NT;                                   // activation columns of the mma
-  constexpr int STAGE = UNIT_BYTES + SIDE_BYTES + NB * XROW;   // bytes per ring stage
   constexpr int EL = 16 * NB;                                  // outputs of one tile
-  const int S = a.stages;
+  const int S = a.stages, STAGE = a.stage_bytes, NX = a.nxrows;
   uint8_t* ring = smem;
-  float* red = reinterpret_cast<float*>(smem + (size_t)S * STAGE);          // [CW][EL]
-  float* tot = red + CW * EL;                                               // [EL]
-  uint64_t* full = reinterpret_cast<uint64_t*>(tot + EL);
+  uint8_t* zrow = smem + (size_t)S * STAGE;                                 // one all-zero activation row
+  float* red = reinterpret_cast<float*>(zrow + XROW);                       // [2][CW][EL]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * CW * EL);
   uint64_t* empty = full + S;
-  int* s_last = reinterpret_cast<int*>(empty + S);
+  uint64_t* done = empty + S;                                               // [2] partials of a tile are in red[buf]
+  uint64_t* freeb = done + 2;                                               // [2] red[buf] may be overwritten
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = gridDim.x;
-  const long long u0 = (long long)blockIdx.x * a.U / C, u1 = (long long)(blockIdx.x + 1) * a.U / C;
-  const int UPP = a.T * a.CPT;                                 // units per problem
+  const int u0 = (int)((long long)blockIdx.x * a.U / C), u1 = (int)((long long)(blockIdx.x + 1) * a.U / C);
 
   if (tid == 0) {
+    PROF(0);
     for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, CW); }
+    for (int b = 0; b < 2; ++b) { mbar_init(done + b, CW); mbar_init(freeb + b, 1); }
     fence_barrier_init();
   }
-  // activation rows that no copy ever fills must not hold NaN patterns
-  for (int i = tid; i < S * NB * (XROW / 16); i += blockDim.x) {
-    const int s = i / (NB * (XROW / 16)), j = i % (NB * (XROW / 16));
-    reinterpret_cast<uint4*>(ring + (size_t)s * STAGE + UNIT_BYTES + SIDE_BYTES)[j] = make_uint4(0, 0, 0, 0);
-  }
-  fence_proxy_async();
+  if (tid < XROW / 16) reinterpret_cast<uint4*>(zrow)[tid] = make_uint4(0, 0, 0, 0);
   __syncthreads();
+  pdl_launch_dependents();                 // the next kernel in the stream may start its own weight prefetch
+  if (MODE != MODE_DENSE) pdl_wait();      // expert ids / slot tables come from earlier kernels: read nothing before
+
+  UnitCursor<MODE> cur;
+  cur.init(a, u0, u1);
+  if (tid == 0) PROF(1);
 
   if (warp == CW) {
-    // ------------------------------------------------------------------ producer: one elected lane drives the ring
-    if (lane == 0) {
-      const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
-      long long it = 0;
-      for (long long u = u0; u < u1; ++u) {
-        const int p = (int)(u / UPP), ul = (int)(u % UPP);
-        const Prob pr = resolve<MODE>(a, p);
-        if (pr.skip) continue;
-        const int tile = ul / a.CPT, c = ul % a.CPT;
-        const int nrec = min(CW, a.NG - c * CW);
-        const int s = (int)(it % S);
-        const long long k = it / S;
-        if (k > 0 && !mbar_wait(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
-        uint8_t* st = ring + (size_t)s * STAGE;
-        int nx = 0;
-        long long rows[NB];
+    // ------------------------------------------------------------------ producer warp.  Lane 0 moves the records,
+    // lane 1 the escape block, lane n activation row n.  Weights never depend on the previous kernel, so the first
+    // ring fill is issued before griddepcontrol.wait; activations (and everything the reducer touches) after it.
+    const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+#ifdef ST_PROF
+    int pcount = 0;
+#endif
+    int lastp = -1;
+    const uint16_t* xrow = nullptr;                           // this lane's activation row of the current problem
+    unsigned nx = 0;
+    auto row_of = [&](const UnitCursor<MODE>& k) {
+      if (k.p != lastp) {
+        lastp = k.p;
+        const long long r = lane < NX ? out_row<MODE>(a, k.p, lane) : -1;
+        xrow = r < 0 ? nullptr : a.X + (MODE == MODE_DENSE ? r : r / a.xdiv) * a.N;
+        nx = __popc(__ballot_sync(FULL, xrow != nullptr));
+      }
+    };
+    auto weights = [&](const UnitCursor<MODE>& k, int s) {
+      const int nrec = k.nrec(a);
+      uint8_t* st = ring + (size_t)s * STAGE;
+      if (lane == 0) {
+        mbar_expect_tx(full + s, (uint32_t)(nrec * REC + SIDE_BYTES) + nx * (uint32_t)(nrec * 128));
+        bulk_g2s(st, k.pr.tree + ((size_t)k.tile * a.NG + (size_t)k.c * CW) * REC, (uint32_t)(nrec * REC), full + s, pol_w);
+      }
+      __syncwarp();
+      if (lane == 1)
+        bulk_g2s(st + UNIT_BYTES, k.pr.eb + ((size_t)k.tile * a.CPT + k.c) * 16, SIDE_BYTES, full + s, pol_w);
+    };
+    auto acts = [&](const UnitCursor<MODE>& k, int s) {
+      if (xrow != nullptr)
+        bulk_g2s(ring + (size_t)s * STAGE + UNIT_BYTES + SIDE_BYTES + lane * XROW, xrow + (size_t)k.c * CW * 64,
+                 (uint32_t)(k.nrec(a) * 128), full + s, pol_x);
+    };
+    // first ring fill: weights, then wait for the previous kernel, then the activations of the same units
+    UnitCursor<MODE> pre = cur;
+    int filled = 0;
+    for (; pre.valid() && filled < S; pre.next(a), ++filled) { row_of(pre); weights(pre, filled); }
+    pdl_wait();
+    lastp = -1;
+    int s = 0;
+    for (int i = 0; i < filled; ++i, cur.next(a)) {
+      row_of(cur);
+      acts(cur, s);
+      ++s;
+#ifdef ST_PROF
+      if (lane == 0) { PROF(40 + pcount); ++pcount; }
+#endif
+    }
+    s = 0;                                                     // filled == S whenever units remain
+    uint32_t ph = 0;
+    for (; cur.valid(); cur.next(a)) {
+      row_of(cur);
+      if (!mbar_wait(empty + s, ph)) {
+        if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
+        break;
+      }
+      weights(cur, s);
+      acts(cur, s);
+      if (++s == S) { s = 0; ph ^= 1u; }
+#ifdef ST_PROF
+      if (lane == 0) { PROF(40 + pcount); ++pcount; }
+#endif
+    }
+    return;
+  }
+
+  if (warp == CW + 1) {
+    // ------------------------------------------------------------------ reducer warp: finishes tiles behind the
+    // consumers (sums the 8 warps in order, stores or hands a partial sum over), so the consumers never wait
+    pdl_wait();                                                // ws, cnt and Y may still be in use by the previous kernel
+    int nf = 0;
+    for (; cur.valid(); cur.next(a)) {
+      if (!cur.tile_end(a)) continue;
+      const int buf = nf & 1;
+      if (!mbar_wait(done + buf, (uint32_t)(nf >> 1) & 1u)) {
+        if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+        return;
+      }
+      ++nf;
+      float sum[EL / 32];
+      const float* rb = red + buf * CW * EL;
 #pragma unroll
-        for (int n = 0; n < NB; ++n) {
-          const long long r = out_row<MODE>(a, p, n);
-          rows[n] = r < 0 ? -1 : (MODE == MODE_DENSE ? r : r / a.xdiv);
-          nx += r >= 0;
+      for (int k = 0; k < EL / 32; ++k) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < CW; ++w) v += rb[w * EL + lane + 32 * k];
+        sum[k] = v;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(freeb + buf);
+      const int tbase = cur.u - cur.c;                          // first unit of the tile
+      const bool owned = tbase >= u0 && tbase + a.CPT <= u1;
+      const long long tg = (long long)cur.p * a.T + cur.tile;
+      bool finish = owned;
+      if (!owned) {
+        const int cfirst = cta_of_unit(tbase, a.U, C), clast = cta_of_unit(tbase + a.CPT - 1, a.U, C);
+        const int ncover = clast - cfirst + 1;
+        float* wsl = a.ws + (size_t)tg * a.maxcover * EL;
+#pragma unroll
+        for (int k = 0; k < EL / 32; ++k) wsl[(size_t)(blockIdx.x - cfirst) * EL + lane + 32 * k] = sum[k];
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(a.cnt + tg, 1) == ncover - 1);
+        last = __shfl_sync(FULL, last, 0);
+        if (last) {
+          __threadfence();
+#pragma unroll
+          for (int k = 0; k < EL / 32; ++k) {
+            float v = 0.f;
+            for (int j = 0; j < ncover; ++j) v += __ldcg(wsl + (size_t)j * EL + lane + 32 * k);
+            sum[k] = v;
+          }
+          if (lane == 0) a.cnt[tg] = 0;
+          finish = true;
         }
-        mbar_expect_tx(full + s, (uint32_t)(nrec * REC + SIDE_BYTES + nx * nrec * 128));
-        bulk_g2s(st, pr.tree + ((size_t)tile * a.NG + (size_t)c * CW) * REC, (uint32_t)(nrec * REC), full + s, pol_w);
-        bulk_g2s(st + UNIT_BYTES, pr.eb + ((size_t)tile * a.CPT + c) * 16, SIDE_BYTES, full + s, pol_w);
+      }
+      if (lane == 0) PROF(24 + nf);
+      if (finish) {
 #pragma unroll
-        for (int n = 0; n < NB; ++n)
-          if (rows[n] >= 0)
-            bulk_g2s(st + UNIT_BYTES + SIDE_BYTES + n * XROW, a.X + rows[n] * a.N + (size_t)c * CW * 64,
-                     (uint32_t)(nrec * 128), full + s, pol_x);
-        ++it;
+        for (int k = 0; k < EL / 32; ++k) {
+          const int idx = lane + 32 * k, n = idx >> 4, r = idx & 15;
+          const long long row = out_row<MODE>(a, cur.p, n);
+          if (row >= 0) {
+            const __nv_bfloat16 hv = __float2bfloat16_rn(sum[k]);
+            a.Y[row * a.M + (size_t)cur.tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+            if (a.Yf) a.Yf[row * a.M + (size_t)cur.tile * 16 + r] = sum[k];
+          }
+        }
       }
     }
     return;
@@ -155,19 +319,24 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvArgs a
   float acc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-  long long it = 0;
-  for (long long u = u0; u < u1; ++u) {
-    const int p = (int)(u / UPP), ul = (int)(u % UPP);
-    const Prob pr = resolve<MODE>(a, p);
-    if (pr.skip) continue;
-    const int tile = ul / a.CPT, c = ul % a.CPT;
-    const int nrec = min(CW, a.NG - c * CW);
-    const int s = (int)(it % S);
-    if (!mbar_wait(full + s, (uint32_t)(it / S) & 1u)) {
+  int s = 0, nf = 0;
+#ifdef ST_PROF
+  int ccount = 0;
+#endif
+  uint32_t ph = 0;
+  // ldmatrix row addresses of this lane: activation row nt * 8 + (lane & 7), or the zero row beyond the batch
+  const uint32_t colo = (uint32_t)(warp * 128 + (lane >> 3) * 16);
+  const uint32_t zaddr = smem_addr(zrow) + colo;
+  uint32_t xo[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+    xo[nt] = (nt * 8 + (lane & 7)) < NX ? (uint32_t)(UNIT_BYTES + SIDE_BYTES + (nt * 8 + (lane & 7)) * XROW) + colo : 0u;
+  for (; cur.valid(); cur.next(a)) {
+    const int nrec = cur.nrec(a);
+    if (!mbar_wait(full + s, ph)) {
       if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
       return;
     }
-    ++it;
     const uint8_t* st = ring + (size_t)s * STAGE;
     if (warp < nrec) {
       uint32_t A[4][4];
@@ -181,32 +350,42 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvArgs a
             if (((e >> 10) & 7u) == (uint32_t)warp) patch_entry(A, e, lane);
           }
         } else {                                               // crowded unit: this record's own list
-          const size_t r = (size_t)tile * a.NG + (size_t)c * CW + warp;
-          const int lo = __ldg(pr.eo + r), hi = __ldg(pr.eo + r + 1);
+          const size_t r = (size_t)cur.tile * a.NG + (size_t)cur.c * CW + warp;
+          const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
           for (int base = lo; base < hi; base += 32) {
             const int n = min(32, hi - base);
-            const uint32_t mine = (lane < n) ? __ldg(pr.el + base + lane) : 0u;
+            const uint32_t mine = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
             for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, mine, i), lane);
           }
         }
       }
-      const uint32_t xs = smem_addr(st + UNIT_BYTES + SIDE_BYTES) + (uint32_t)((lane & 7) * XROW + warp * 128 + (lane >> 3) * 16);
+      const uint32_t sb = smem_addr(st);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         uint32_t b[8];
-        ldmatrix_x4(xs + nt * 8 * XROW, b[0], b[1], b[2], b[3]);
-        ldmatrix_x4(xs + nt * 8 * XROW + 64, b[4], b[5], b[6], b[7]);
+        const uint32_t xa = xo[nt] ? sb + xo[nt] : zaddr;
+        ldmatrix_x4(xa, b[0], b[1], b[2], b[3]);
+        ldmatrix_x4(xa + 64, b[4], b[5], b[6], b[7]);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) mma_bf16(acc[nt], A[ks], b[2 * ks], b[2 * ks + 1]);
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + s);
+    if (++s == S) { s = 0; ph ^= 1u; }
+#ifdef ST_PROF
+    if (warp == 0 && lane == 0) { PROF(2 + ccount); ++ccount; }
+#endif
 
-    // ---- end of this CTA's share of the tile: reduce the warps, then store or hand over a partial sum
-    const bool tile_end = (c == a.CPT - 1) || (u + 1 == u1);
-    if (!tile_end) continue;
-    float* mine = red + warp * EL;
+    if (!cur.tile_end(a)) continue;
+    // ---- end of this CTA's share of the tile: hand the warp's partial sums to the reducer
+    const int buf = nf & 1;
+    if (nf >= 2 && !mbar_wait(freeb + buf, (uint32_t)((nf >> 1) - 1) & 1u)) {
+      if (lane == 0) atomicExch(a.status, ERR_WAIT_ACC);
+      return;
+    }
+    ++nf;
+    float* mine = red + (buf * CW + warp) * EL;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int n0 = nt * 8 + 2 * (lane & 3);
@@ -216,86 +395,69 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvArgs a
       mine[(n0 + 1) * 16 + g + 8] = acc[nt][3];
       acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
     }
-    named_bar_sync(1, CW * 32);
-    const long long tbase = (long long)p * UPP + (long long)tile * a.CPT;      // first unit of the tile
-    const int cfirst = cta_of_unit(tbase, a.U, C), clast = cta_of_unit(tbase + a.CPT - 1, a.U, C);
-    const int ncover = clast - cfirst + 1;
-    const long long tg = (long long)p * a.T + tile;
-    for (int idx = tid; idx < EL; idx += CW * 32) {
-      float sum = 0.f;
-#pragma unroll
-      for (int w = 0; w < CW; ++w) sum += red[w * EL + idx];
-      if (ncover == 1) tot[idx] = sum;
-      else a.ws[((size_t)tg * a.maxcover + (blockIdx.x - cfirst)) * EL + idx] = sum;
-    }
-    bool finish = ncover == 1;
-    if (ncover > 1) {
-      __threadfence();
-      named_bar_sync(1, CW * 32);
-      if (tid == 0) *s_last = (atomicAdd(a.cnt + tg, 1) == ncover - 1);
-      named_bar_sync(1, CW * 32);
-      finish = *s_last != 0;
-      if (finish) {
-        __threadfence();
-        for (int idx = tid; idx < EL; idx += CW * 32) {
-          float sum = 0.f;
-          for (int k = 0; k < ncover; ++k) sum += __ldcg(a.ws + ((size_t)tg * a.maxcover + k) * EL + idx);
-          tot[idx] = sum;
-        }
-        if (tid == 0) a.cnt[tg] = 0;
-      }
-    }
-    if (finish) {
-      for (int idx = tid; idx < EL; idx += CW * 32) {
-        const int n = idx >> 4, r = idx & 15;
-        const long long row = out_row<MODE>(a, p, n);
-        if (row >= 0) {
-          const float v = tot[idx];
-          const __nv_bfloat16 hv = __float2bfloat16_rn(v);
-          a.Y[row * a.M + (size_t)tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-          if (a.Yf) a.Yf[row * a.M + (size_t)tile * 16 + r] = v;
-        }
-      }
-    }
-    named_bar_sync(1, CW * 32);                                  // red / tot / s_last are free again
+    __syncwarp();
+    if (lane == 0) mbar_arrive(done + buf);
   }
 }
 
-struct Plan { int C, stages, maxcover; size_t smem; long long U; int CPT, T, NG, nprob; };
+struct Plan { int C, stages, maxcover, stage_bytes, nxrows; size_t smem; long long U; int CPT, T, NG, nprob; };
 
+bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("STATETREE_PDL");
+    on = (v && v[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+// nx = activation rows staged per unit (the batch for a dense matrix, 1 per slot, 8 per block of slots)
 template <int NT>
-Plan make_plan(long long M, long long N, int nprob) {
+Plan make_plan(long long M, long long N, int nprob, int nx) {
   Plan p;
   p.NG = (int)(N / 64);
   p.CPT = (p.NG + CW - 1) / CW;
   p.T = (int)(M / 16);
   p.nprob = nprob;
   p.U = (long long)nprob * p.T * p.CPT;
-  const int sms = st::sm_count();
-  p.C = (int)(p.U < sms ? p.U : sms);
+  p.nxrows = nx;
+  p.stage_bytes = UNIT_BYTES + SIDE_BYTES + nx * XROW;
+  constexpr int EL = 16 * 8 * NT;
+  const size_t fixed = XROW + (size_t)2 * CW * EL * 4 + (2 * 8 + 4) * 8 + 16;
+  // two CTAs per SM when that still leaves a ring of >= 3 stages each (more warps to hide latency, and room for
+  // the next kernel's CTAs to start while this one drains); else one CTA with the deepest ring that fits
+  int per_sm = 2;
+  int stages = (int)((110 * 1024 - (long long)fixed) / p.stage_bytes);
+  if (NT > 2 || stages < 3) {
+    per_sm = 1;
+    stages = (int)((200 * 1024 - (long long)fixed) / p.stage_bytes);
+  }
+  if (stages > 8) stages = 8;
+  p.stages = stages;
+  p.smem = (size_t)stages * p.stage_bytes + fixed;
+  const long long slots = (long long)st::sm_count() * per_sm;
+  p.C = (int)(p.U < slots ? p.U : slots);
   const long long per = p.U / p.C;
   long long mc = (p.CPT + per - 1) / per + 1;
   if (mc > p.CPT) mc = p.CPT;
   p.maxcover = (int)(mc < 1 ? 1 : mc);
-  constexpr int NB = 8 * NT, STAGE = UNIT_BYTES + SIDE_BYTES + NB * XROW, EL = 16 * NB;
-  const size_t fixed = (size_t)(CW + 1) * EL * 4 + 2 * 16 * 8 + 16;
-  int stages = (int)((200 * 1024 - fixed) / STAGE);
-  if (stages > 8) stages = 8;
-  p.stages = stages;
-  p.smem = (size_t)stages * STAGE + fixed;
   return p;
 }
 
 template <int NT, int MODE>
-int launch(GemvArgs& a, int nprob, long long ws_bytes, cudaStream_t stream, const char* who) {
-  const Plan p = make_plan<NT>(a.M, a.N, nprob);
+int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
+  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx);
   a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages;
+  a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows;
   const long long need = (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
   ST_REQUIRE(p.maxcover == 1 || (a.ws && ws_bytes >= need), "%s: workspace of %lld bytes needed, %lld given", who, need,
              ws_bytes);
   ST_REQUIRE(p.stages >= 2, "%s: internal: ring does not fit", who);
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "%s: no device status word", who);
+#ifdef ST_PROF
+  a.prof = g_prof_buf;
+#endif
   static bool set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -305,21 +467,34 @@ int launch(GemvArgs& a, int nprob, long long ws_bytes, cudaStream_t stream, cons
       return e;
     set[dev] = true;
   }
-  gemv_kernel<NT, MODE><<<p.C, (CW + 1) * 32, p.smem, stream>>>(a);
-  ST_LAUNCH_CHECK(who);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)p.C);
+  cfg.blockDim = dim3((CW + 2) * 32);
+  cfg.dynamicSmemBytes = p.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemv_kernel<NT, MODE>, a), who)) return e;
   return 0;
 }
 
 template <int NT>
-long long ws_need(long long M, long long N, int nprob) {
-  const Plan p = make_plan<NT>(M, N, nprob);
+long long ws_need(long long M, long long N, int nprob, int nx) {
+  const Plan p = make_plan<NT>(M, N, nprob, nx);
   return p.maxcover == 1 ? 0 : (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
 }
 }  // namespace
 
+#ifdef ST_PROF
+extern "C" void st_debug_set_prof(long long* buf) { g_prof_buf = buf; }
+#endif
+
 extern "C" int64_t st_gemv_workspace_bytes(int64_t M, int64_t N, int64_t B) {
   if (M <= 0 || N <= 0 || M % 16 || N % 64 || B < 1 || B > 32) return -1;
-  return B <= 8 ? ws_need<1>(M, N, 1) : (B <= 16 ? ws_need<2>(M, N, 1) : ws_need<4>(M, N, 1));
+  return B <= 8 ? ws_need<1>(M, N, 1, (int)B) : (B <= 16 ? ws_need<2>(M, N, 1, (int)B) : ws_need<4>(M, N, 1, (int)B));
 }
 
 extern "C" int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X,
@@ -336,14 +511,14 @@ extern "C" int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, 
   a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.Yf = Yf32; a.ws = (float*)ws; a.cnt = cnt;
   a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1;
   cudaStream_t s = (cudaStream_t)stream;
-  if (B <= 8) return launch<1, MODE_DENSE>(a, 1, ws_bytes, s, "st_gemv");
-  if (B <= 16) return launch<2, MODE_DENSE>(a, 1, ws_bytes, s, "st_gemv");
-  return launch<4, MODE_DENSE>(a, 1, ws_bytes, s, "st_gemv");
+  if (B <= 8) return launch<1, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
+  if (B <= 16) return launch<2, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
+  return launch<4, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
 }
 
 extern "C" int64_t st_moe_gemv_workspace_bytes(int64_t S, int64_t M, int64_t N) {
   if (M <= 0 || N <= 0 || M % 16 || N % 64 || S < 1) return -1;
-  return ws_need<1>(M, N, (int)S);
+  return ws_need<1>(M, N, (int)S, 1);
 }
 
 static int moe_common_checks(const char* who, const int64_t* tp, const int64_t* eop, const int64_t* ebp,
@@ -368,12 +543,12 @@ extern "C" int st_moe_gemv(const int64_t* tp, const int64_t* eop, const int64_t*
   a.tp = (const long long*)tp; a.eop = (const long long*)eop; a.ebp = (const long long*)ebp; a.elp = (const long long*)elp;
   a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.ws = (float*)ws; a.cnt = cnt; a.ids = ids; a.ids64 = ids64;
   a.M = M; a.N = N; a.B = (int)S; a.E = (int)E; a.xdiv = (int)xdiv;
-  return launch<1, MODE_SLOT>(a, (int)S, ws_bytes, (cudaStream_t)stream, "st_moe_gemv");
+  return launch<1, MODE_SLOT>(a, (int)S, 1, ws_bytes, (cudaStream_t)stream, "st_moe_gemv");
 }
 
 extern "C" int64_t st_moe_group_workspace_bytes(int64_t nblk, int64_t M, int64_t N) {
   if (M <= 0 || N <= 0 || M % 16 || N % 64 || nblk < 1) return -1;
-  return ws_need<1>(M, N, (int)nblk);
+  return ws_need<1>(M, N, (int)nblk, 8);
 }
 
 extern "C" int st_moe_group_gemv(const int64_t* tp, const int64_t* eop, const int64_t* ebp, const int64_t* elp,
@@ -389,5 +564,5 @@ extern "C" int st_moe_group_gemv(const int64_t* tp, const int64_t* eop, const in
   a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.ws = (float*)ws; a.cnt = cnt;
   a.sorted = sorted; a.bexp = bexp; a.npost = npost;
   a.M = M; a.N = N; a.B = (int)S; a.E = (int)E; a.xdiv = (int)xdiv;
-  return launch<1, MODE_GROUP>(a, (int)nblk, ws_bytes, (cudaStream_t)stream, "st_moe_group_gemv");
+  return launch<1, MODE_GROUP>(a, (int)nblk, 8, ws_bytes, (cudaStream_t)stream, "st_moe_group_gemv");
 }
