@@ -55,6 +55,17 @@ int64_t st_gemv_workspace_bytes(int64_t M, int64_t N, int64_t B);
 int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X, void* Y,
             float* Yf32, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);
 
+/* st_gemv for callers that cannot allocate device memory and so have no workspace to pass: code running inside a
+ * host framework that owns the whole device pool, or anywhere cudaMalloc is off limits.  The split partial sums and
+ * tile semaphores live in a 4.06 MiB array built into the library (present on every GPU that loads it, until exit),
+ * so the call takes only inputs and outputs and calls no allocator.  Limits: the shape's partial sums must fit
+ * 4 MiB and M <= 262144, otherwise the call is rejected with a message and nothing is launched.  The first call on
+ * a device looks up the array's device address; make that first call before any stream capture.  All calls on a
+ * device share the array (its semaphores are cleared on the stream at every call), so two calls that overlap on the
+ * GPU - different streams, or different threads - race: serialise them.  No counterpart in the reference. */
+int st_gemv_static(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X, void* Y,
+                   int64_t B, int64_t M, int64_t N, void* stream);
+
 /* Large-batch fused decode + tcgen05 GEMM, B >= 1 (meant for B > 32), M % 128 == 0.  Replaces `_C.tm`, `_C.th`,
  * `_C.tt` (statetree/csrc/kernels.cu:1892-1924, statetree/csrc/hop.cu:864-925, statetree/csrc/tt.cu:508-556).
  * ws / cnt as for st_gemv (cnt: int32 [M/128 * ceil(B/256)]). */

@@ -17,6 +17,8 @@
 #include "st_common.cuh"
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "st_host.h"
 
 namespace {
@@ -514,6 +516,65 @@ extern "C" int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, 
   if (B <= 8) return launch<1, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
   if (B <= 16) return launch<2, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
   return launch<4, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
+}
+
+// ---------------------------------------------------------------------------------------------- st_gemv_static
+// The same GEMV for callers that cannot hand over a workspace because they cannot allocate device memory at all: a
+// plugin running inside a serving process whose memory pool is owned (and fully reserved) by the host framework, or
+// code that runs where cudaMalloc is forbidden.  Its split partial sums and tile semaphores live in the file-scope
+// array below instead of caller buffers.  Every GPU that loads the library carries the array (4.06 MiB) until exit.
+namespace {
+constexpr long long STATIC_WS_BYTES = 4ll << 20;        // fp32 partial sums of tiles shared between CTAs
+constexpr long long STATIC_TILES = 16384;               // one int32 semaphore per 16-row tile: M <= 262144
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_WS_BYTES + STATIC_TILES * 4];
+unsigned char* g_static_addr[64];                       // device address of the array, per device
+std::mutex g_static_mu;
+}  // namespace
+
+extern "C" int st_gemv_static(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X,
+                              void* Y, int64_t B, int64_t M, int64_t N, void* stream) {
+  ST_REQUIRE(M > 0 && N > 0 && M % 16 == 0 && N % 64 == 0,
+             "st_gemv_static: M %% 16 and N %% 64 must be 0 (got %lld x %lld)", (long long)M, (long long)N);
+  ST_REQUIRE(B >= 1 && B <= 32, "st_gemv_static: batch must be in [1, 32] (got %lld)", (long long)B);
+  ST_REQUIRE(tree && eo && eb && el && X && Y, "st_gemv_static: null pointer");
+  ST_REQUIRE(st::aligned16(tree) && st::aligned16(eb) && st::aligned16(X),
+             "st_gemv_static: tree, eb and X must be 16-byte aligned");
+  ST_REQUIRE((M / 16) * ((N / 64 + 7) / 8) < (1ll << 31), "st_gemv_static: too many units");
+  const long long need = B <= 8 ? ws_need<1>(M, N, 1, (int)B) : (B <= 16 ? ws_need<2>(M, N, 1, (int)B)
+                                                                         : ws_need<4>(M, N, 1, (int)B));
+  ST_REQUIRE(need <= STATIC_WS_BYTES && M / 16 <= STATIC_TILES,
+             "st_gemv_static: this shape needs %lld bytes of partial sums and %lld semaphores; the built-in scratch "
+             "holds %lld bytes and %lld semaphores (use st_gemv with a caller workspace)",
+             need, (long long)(M / 16), STATIC_WS_BYTES, STATIC_TILES);
+  int dev = 0;
+  if (int e = st::cuda_fail(cudaGetDevice(&dev), "st_gemv_static: cudaGetDevice")) return e;
+  ST_REQUIRE(dev >= 0 && dev < 64, "st_gemv_static: device index out of range");
+  unsigned char* base = nullptr;
+  {
+    // set-up, once per device, with that device current: the array's name is only a host-side handle here, the
+    // kernel needs its device address
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (g_static_addr[dev] == nullptr) {
+      void* p = nullptr;
+      if (int e = st::cuda_fail(cudaGetSymbolAddress(&p, g_static_scratch), "st_gemv_static: cudaGetSymbolAddress"))
+        return e;
+      ST_REQUIRE(p != nullptr, "st_gemv_static: no device address for the scratch array");
+      g_static_addr[dev] = static_cast<unsigned char*>(p);
+    }
+    base = g_static_addr[dev];
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  int* cnt = reinterpret_cast<int*>(base + STATIC_WS_BYTES);
+  // the array keeps whatever the last call left: the semaphores of this shape's tiles must start at zero
+  if (int e = st::cuda_fail(cudaMemsetAsync(cnt, 0, (size_t)(M / 16) * 4, s), "st_gemv_static: clearing semaphores"))
+    return e;
+  GemvArgs a = {};
+  a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
+  a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.Yf = nullptr; a.ws = reinterpret_cast<float*>(base); a.cnt = cnt;
+  a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1;
+  if (B <= 8) return launch<1, MODE_DENSE>(a, 1, (int)B, STATIC_WS_BYTES, s, "st_gemv_static");
+  if (B <= 16) return launch<2, MODE_DENSE>(a, 1, (int)B, STATIC_WS_BYTES, s, "st_gemv_static");
+  return launch<4, MODE_DENSE>(a, 1, (int)B, STATIC_WS_BYTES, s, "st_gemv_static");
 }
 
 extern "C" int64_t st_moe_gemv_workspace_bytes(int64_t S, int64_t M, int64_t N) {

@@ -23,6 +23,7 @@ _SIGNATURES = {
     "st_rows": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "st_gemv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "st_gemv_static": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "st_gemm_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "st_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_moe_gemv_workspace_bytes": (_i64, [_i64, _i64, _i64]),
@@ -118,6 +119,14 @@ class _Weights:
         with _ctx(T):
             _check(lib().st_gemv(_ptr(T), _ptr(EO), _ptr(EB), _ptr(EL), _ptr(X), _ptr(Y), _ptr(Yf32), B, M, N, _ptr(WS),
                                  WS.numel() * WS.element_size(), _ptr(CNT), _stream(T)))
+
+    @staticmethod
+    def gemv_static(T, EO, EB, EL, X, Y):
+        """the GEMV without caller workspaces (for callers that cannot allocate): scratch built into the library"""
+        B, N = X.shape
+        M = Y.shape[1]
+        with _ctx(T):
+            _check(lib().st_gemv_static(_ptr(T), _ptr(EO), _ptr(EB), _ptr(EL), _ptr(X), _ptr(Y), B, M, N, _stream(T)))
 
     @staticmethod
     def gemm_workspace_bytes(M, N, B):
