@@ -128,6 +128,97 @@ def cpu_reference(steps, warmup, batch):
     return nbytes / dt / 1e9, dt, oracle.threads()
 
 
+def attention_workload(args):
+    """Decode attention over compressed KV pages (32 query / 8 KV heads, head_dim 128, 16-token pages; K = N(0,1) x
+    per-channel LogNormal(0,1), V, q = N(0,1)), contexts 1K/4K/16K x batch 1/8/32/64, L2 flushed between calls, against
+    BF16 attention over the same (exactly decoded) values.  Prints one JSON line with a table."""
+    import math
+
+    import torch
+
+    from statetree_b200 import ops
+    from statetree_b200.kvcache import StateTreeKVLayer, decode_splits
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    Hq, Hkv, D = 32, 8, 128
+    try:
+        from flash_attn import flash_attn_with_kvcache
+        baseline_name = "flash_attn_with_kvcache (FlashAttention-2 %s, dense BF16 cache)" % __import__("flash_attn").__version__
+    except Exception:                                         # noqa: BLE001
+        flash_attn_with_kvcache = None
+        baseline_name = "torch SDPA (enable_gqa) over a dense BF16 cache"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    hbm, _, which = peaks()
+    gen = torch.Generator(device=dev).manual_seed(0)
+    table = []
+    ctxs = [int(c) for c in args.ctx.split(",")]
+    batches = [int(b) for b in args.attn_batch.split(",")]
+
+    def timed(fn, reps):
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    for ctx in ctxs:
+        for B in batches:
+            npg = ctx // 16
+            layer = StateTreeKVLayer(B * npg, Hkv, dev, pool_blocks=1 << 16)
+            bt = torch.randperm(B * npg, device=dev, generator=gen).view(B, npg).to(torch.int32)
+            scale_k = torch.exp(torch.randn(Hkv, D, device=dev, generator=gen))
+            Kd = torch.empty(B, ctx, Hkv, D, dtype=torch.bfloat16, device=dev)
+            Vd = torch.empty_like(Kd)
+            pos = torch.arange(ctx, device=dev)
+            for b in range(B):
+                Kd[b] = (torch.randn(ctx, Hkv, D, device=dev, generator=gen) * scale_k).to(torch.bfloat16)
+                Vd[b] = torch.randn(ctx, Hkv, D, device=dev, generator=gen).to(torch.bfloat16)
+                slots = bt[b].long()[pos // 16] * 16 + pos % 16
+                layer.append(Kd[b], Vd[b], slots)
+            layer.check()
+            q = torch.randn(B, Hq, D, device=dev, generator=gen).to(torch.bfloat16)
+            lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+            S = decode_splits(B, Hkv, npg)
+            sc = 1.0 / math.sqrt(D)
+            out = torch.empty(B, Hq, D, dtype=torch.bfloat16, device=dev)
+            ours = lambda: layer.attention(q, bt, lens, sc, splits=S, min_pages=4, out=out)   # noqa: E731
+            if flash_attn_with_kvcache is not None:
+                q4 = q.view(B, 1, Hq, D)
+                base = lambda: flash_attn_with_kvcache(q4, Kd, Vd, cache_seqlens=lens, softmax_scale=sc)   # noqa: E731
+            else:
+                qs = q.view(B, Hq, 1, D)
+                kt, vt = Kd.transpose(1, 2), Vd.transpose(1, 2)
+                base = lambda: torch.nn.functional.scaled_dot_product_attention(qs, kt, vt, scale=sc, enable_gqa=True)   # noqa: E731
+            for _ in range(3):
+                ours()
+                ref = base()
+            err = float((out.float().view(-1) - ref.float().reshape(-1)).norm() / ref.float().norm())
+            us, us_b = timed(ours, args.steps), timed(base, args.steps)
+            nbytes = B * npg * 16 * Hkv * 400
+            table.append({"batch": B, "ctx": ctx, "splits": S, "us": us, "bf16_us": us_b, "speedup_vs_bf16": us_b / us,
+                          "gbs": nbytes / us / 1e3, "frac_hbm": nbytes / us / 1e3 / hbm, "rel_err_vs_bf16": err})
+            del layer, Kd, Vd
+            torch.cuda.empty_cache()
+    big = table[-1]
+    print(json.dumps({"metric": "decode attention over compressed KV pages, effective GB/s (record bytes / time)",
+                      "value": big["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": 3,
+                      "ms_per_step": big["us"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "compressed-KV decode attention, 32q/8kv heads, d=128, 16-token pages; headline"
+                                             f" row: batch {big['batch']} x ctx {big['ctx']}", "l2": "flushed between calls",
+                                 "bf16_baseline": baseline_name},
+                      "roofline": {"bound": "hbm", "achieved": big["gbs"], "peak": hbm, "unit": "GB/s",
+                                   "frac": big["gbs"] / hbm, "traffic": None, "peak_source": f"of {which}"},
+                      "device_status": ops.device_status(), "table": table}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -137,7 +228,15 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="linear", choices=["linear", "attn"],
+                    help="linear: the Qwen3-8B linear sweep (default, the headline); attn: compressed-KV decode attention")
+    ap.add_argument("--ctx", default="1024,4096,16384")
+    ap.add_argument("--attn-batch", default="1,8,32,64")
     args = ap.parse_args()
+    if args.workload == "attn":
+        if int(os.environ.get("RANK", "0")) == 0:
+            attention_workload(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

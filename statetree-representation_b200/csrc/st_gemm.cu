@@ -213,15 +213,31 @@ __global__ void __launch_bounds__(320, 1) gemm_kernel(const GemmArgs a, const __
       named_bar_sync(1, NDEC * 32);
       if (flags[1]) {
         __threadfence();
+        // the last CTA to arrive adds the KS partial tiles in split order; eight token columns per thread are kept in
+        // flight so the L2 latency of the partial reads overlaps
         const int r = tid & 127;
-        for (int c = tid >> 7; c < NT; c += 2) {
-          const int tok = tok0 + c;
-          if (tok >= a.B) break;
-          float sum = 0.f;
-          for (int p = 0; p < a.KS; ++p) sum += __ldcg(a.ws + (((size_t)unit * a.KS + p) * NT + c) * 128 + r);
-          const __nv_bfloat16 hv = __float2bfloat16_rn(sum);
-          a.Y[(size_t)tok * a.M + rb * 128 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-          if (a.Yf) a.Yf[(size_t)tok * a.M + rb * 128 + r] = sum;
+        const int ncol = min(NT, a.B - tok0);
+        const float* base = a.ws + (size_t)unit * a.KS * NT * 128 + r;
+        for (int c0 = tid >> 7; c0 < ncol; c0 += 16) {
+          float sum[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) sum[u] = 0.f;
+          for (int p = 0; p < a.KS; ++p) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int c = c0 + 2 * u;
+              if (c < ncol) sum[u] += __ldcg(base + ((size_t)p * NT + c) * 128);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int c = c0 + 2 * u;
+            if (c < ncol) {
+              const __nv_bfloat16 hv = __float2bfloat16_rn(sum[u]);
+              a.Y[(size_t)(tok0 + c) * a.M + rb * 128 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+              if (a.Yf) a.Yf[(size_t)(tok0 + c) * a.M + rb * 128 + r] = sum[u];
+            }
+          }
         }
         if (tid == 0) a.cnt[unit] = 0;
       }
@@ -268,7 +284,7 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   for (int ks = 1; ks <= ksmax; ++ks) {
     const long long ctas = units * ks;
     const long long waves = (ctas + sms - 1) / sms;
-    const double score = (double)ctas / (double)(waves * sms) - 0.012 * ks;
+    const double score = (double)ctas / (double)(waves * sms) - 0.03 * ks * p.NT / 256.0;   // partial-sum traffic
     if (score > best_score + 1e-9) { best_score = score; best = ks; }
   }
   p.KS = best;

@@ -43,7 +43,7 @@ struct GemvArgs {
   int E, xdiv;
   int NG, CPT, T;                         // column groups, units per tile, tiles per problem
   long long U;                            // units over all problems
-  int nprob, maxcover, stages, stage_bytes, nxrows;
+  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, ahead;
 #ifdef ST_PROF
   long long* prof;                        // [CTAs][64] globaltimer stamps (development builds only)
 #endif
@@ -146,20 +146,24 @@ struct UnitCursor {
   }
 };
 
-// 8 consumer warps (one record of the unit each), warp 8 = producer, warp 9 = reducer
-template <int NT, int MODE>
-__global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(const GemvArgs a) {
+// G groups of 8 consumer warps (group g takes every G-th unit, warp r of a group takes record r of the unit), then
+// one producer warp and one reducer warp.
+template <int NT, int MODE, int G>
+__global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int NB = 8 * NT;                                   // activation columns of the mma
   constexpr int EL = 16 * NB;                                  // outputs of one tile
+  constexpr int NCW = CW * G;                                  // consumer warps
   const int S = a.stages, STAGE = a.stage_bytes, NX = a.nxrows;
   uint8_t* ring = smem;
   uint8_t* zrow = smem + (size_t)S * STAGE;                                 // one all-zero activation row
-  float* red = reinterpret_cast<float*>(zrow + XROW);                       // [2][CW][EL]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * CW * EL);
+  uint8_t* xw = zrow + XROW;                                                // whole activation rows (xwhole mode)
+  float* red = reinterpret_cast<float*>(xw + a.xw_bytes);                   // [2][NCW][EL]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * NCW * EL);
   uint64_t* empty = full + S;
   uint64_t* done = empty + S;                                               // [2] partials of a tile are in red[buf]
   uint64_t* freeb = done + 2;                                               // [2] red[buf] may be overwritten
+  uint64_t* xbar = freeb + 2;                                               // whole activation rows have landed
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = gridDim.x;
@@ -168,7 +172,8 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
   if (tid == 0) {
     PROF(0);
     for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, CW); }
-    for (int b = 0; b < 2; ++b) { mbar_init(done + b, CW); mbar_init(freeb + b, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(done + b, NCW); mbar_init(freeb + b, 1); }
+    mbar_init(xbar, 1);
     fence_barrier_init();
   }
   if (tid < XROW / 16) reinterpret_cast<uint4*>(zrow)[tid] = make_uint4(0, 0, 0, 0);
@@ -180,7 +185,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
   cur.init(a, u0, u1);
   if (tid == 0) PROF(1);
 
-  if (warp == CW) {
+  if (warp == NCW) {
     // ------------------------------------------------------------------ producer warp.  Lane 0 moves the records,
     // lane 1 the escape block, lane n activation row n.  Weights never depend on the previous kernel, so the first
     // ring fill is issued before griddepcontrol.wait; activations (and everything the reducer touches) after it.
@@ -196,7 +201,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
         lastp = k.p;
         const long long r = lane < NX ? out_row<MODE>(a, k.p, lane) : -1;
         xrow = r < 0 ? nullptr : a.X + (MODE == MODE_DENSE ? r : r / a.xdiv) * a.N;
-        nx = __popc(__ballot_sync(FULL, xrow != nullptr));
+        nx = a.xwhole ? 0u : __popc(__ballot_sync(FULL, xrow != nullptr));
       }
     };
     auto weights = [&](const UnitCursor<MODE>& k, int s) {
@@ -211,15 +216,45 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
         bulk_g2s(st + UNIT_BYTES, k.pr.eb + ((size_t)k.tile * a.CPT + k.c) * 16, SIDE_BYTES, full + s, pol_w);
     };
     auto acts = [&](const UnitCursor<MODE>& k, int s) {
-      if (xrow != nullptr)
+      if (!a.xwhole && xrow != nullptr)
         bulk_g2s(ring + (size_t)s * STAGE + UNIT_BYTES + SIDE_BYTES + lane * XROW, xrow + (size_t)k.c * CW * 64,
                  (uint32_t)(k.nrec(a) * 128), full + s, pol_x);
     };
-    // first ring fill: weights, then wait for the previous kernel, then the activations of the same units
+    // HBM -> L2 prefetch runs AHEAD units in front of the unit being copied into the ring: the depth of the HBM
+    // request queue no longer depends on how much shared memory the ring has, so the ring can stay small
+    auto l2_prefetch = [&](const UnitCursor<MODE>& k) {
+      const uint8_t* src = k.pr.tree + ((size_t)k.tile * a.NG + (size_t)k.c * CW) * REC;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(src), "r"((uint32_t)(k.nrec(a) * REC)) : "memory");
+    };
+    const int AHEAD = a.ahead;
+    UnitCursor<MODE> mine = cur;                               // lane i looks at unit i of this CTA
+    for (int i = 0; i < lane && mine.valid(); ++i) mine.next(a);
+    if (lane < AHEAD && mine.valid()) l2_prefetch(mine);
+    UnitCursor<MODE> pf = cur;
+    for (int i = 0; i < AHEAD && pf.valid(); ++i) pf.next(a);
+    // first ring fill: weights, then wait for the previous kernel, then the activations
     UnitCursor<MODE> pre = cur;
     int filled = 0;
-    for (; pre.valid() && filled < S; pre.next(a), ++filled) { row_of(pre); weights(pre, filled); }
+    if (MODE == MODE_DENSE) {                                  // lane i fills stage i
+      const bool on = lane < S && mine.valid();
+      if (on) {
+        const int nrec = mine.nrec(a);
+        uint8_t* st = ring + (size_t)lane * STAGE;
+        mbar_expect_tx(full + lane, (uint32_t)(nrec * REC + SIDE_BYTES) + (a.xwhole ? 0u : (uint32_t)(NX * nrec * 128)));
+        bulk_g2s(st, mine.pr.tree + ((size_t)mine.tile * a.NG + (size_t)mine.c * CW) * REC, (uint32_t)(nrec * REC),
+                 full + lane, pol_w);
+        bulk_g2s(st + UNIT_BYTES, mine.pr.eb + ((size_t)mine.tile * a.CPT + mine.c) * 16, SIDE_BYTES, full + lane, pol_w);
+      }
+      filled = __popc(__ballot_sync(FULL, on));
+    } else {
+      for (; pre.valid() && filled < S; pre.next(a), ++filled) { row_of(pre); weights(pre, filled); }
+    }
     pdl_wait();
+    if (a.xwhole) {                                            // every activation row once, whole
+      if (lane == 0) mbar_expect_tx(xbar, (uint32_t)(NX * a.N * 2));
+      __syncwarp();
+      if (lane < NX) bulk_g2s(xw + (size_t)lane * a.xw_stride, a.X + (size_t)lane * a.N, (uint32_t)(a.N * 2), xbar, pol_x);
+    }
     lastp = -1;
     int s = 0;
     for (int i = 0; i < filled; ++i, cur.next(a)) {
@@ -234,6 +269,10 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     uint32_t ph = 0;
     for (; cur.valid(); cur.next(a)) {
       row_of(cur);
+      if (AHEAD > 0 && pf.valid()) {
+        if (lane == 2) l2_prefetch(pf);
+        pf.next(a);
+      }
       if (!mbar_wait(empty + s, ph)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
         break;
@@ -248,9 +287,9 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     return;
   }
 
-  if (warp == CW + 1) {
+  if (warp == NCW + 1) {
     // ------------------------------------------------------------------ reducer warp: finishes tiles behind the
-    // consumers (sums the 8 warps in order, stores or hands a partial sum over), so the consumers never wait
+    // consumers (sums the consumer warps in order, stores or hands a partial sum over), so the consumers never wait
     pdl_wait();                                                // ws, cnt and Y may still be in use by the previous kernel
     int nf = 0;
     for (; cur.valid(); cur.next(a)) {
@@ -262,12 +301,12 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       }
       ++nf;
       float sum[EL / 32];
-      const float* rb = red + buf * CW * EL;
+      const float* rb = red + buf * NCW * EL;
 #pragma unroll
       for (int k = 0; k < EL / 32; ++k) {
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < CW; ++w) v += rb[w * EL + lane + 32 * k];
+        for (int w = 0; w < NCW; ++w) v += rb[w * EL + lane + 32 * k];
         sum[k] = v;
       }
       __syncwarp();
@@ -317,67 +356,83 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
   }
 
   // -------------------------------------------------------------------- consumers
-  const int g = lane >> 2;
+  const int g = lane >> 2, grp = warp / CW, rec = warp % CW;
   float acc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-  int s = 0, nf = 0;
+  int s = 0, nf = 0, turn = 0;
 #ifdef ST_PROF
   int ccount = 0;
 #endif
   uint32_t ph = 0;
   // ldmatrix row addresses of this lane: activation row nt * 8 + (lane & 7), or the zero row beyond the batch
-  const uint32_t colo = (uint32_t)(warp * 128 + (lane >> 3) * 16);
+  const uint32_t colo = (uint32_t)(rec * 128 + (lane >> 3) * 16);
   const uint32_t zaddr = smem_addr(zrow) + colo;
   uint32_t xo[NT];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-    xo[nt] = (nt * 8 + (lane & 7)) < NX ? (uint32_t)(UNIT_BYTES + SIDE_BYTES + (nt * 8 + (lane & 7)) * XROW) + colo : 0u;
+  for (int nt = 0; nt < NT; ++nt) {
+    const int n = nt * 8 + (lane & 7);
+    if (n >= NX) xo[nt] = 0u;
+    else if (a.xwhole) xo[nt] = smem_addr(xw) + (uint32_t)(n * a.xw_stride) + colo;
+    else xo[nt] = (uint32_t)(UNIT_BYTES + SIDE_BYTES + n * XROW) + colo;
+  }
+  bool xready = !a.xwhole;
   for (; cur.valid(); cur.next(a)) {
-    const int nrec = cur.nrec(a);
-    if (!mbar_wait(full + s, ph)) {
-      if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
-      return;
-    }
-    const uint8_t* st = ring + (size_t)s * STAGE;
-    if (warp < nrec) {
-      uint32_t A[4][4];
-      decode_frag(load_rec_shared(st + warp * REC, lane), A);
-      const uint32_t* side = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);
-      const uint32_t ne = side[0];
-      if (ne) {
-        if (ne <= 14u) {
-          for (uint32_t i = 0; i < ne; ++i) {
-            const uint32_t e = side[2 + i];
-            if (((e >> 10) & 7u) == (uint32_t)warp) patch_entry(A, e, lane);
-          }
-        } else {                                               // crowded unit: this record's own list
-          const size_t r = (size_t)cur.tile * a.NG + (size_t)cur.c * CW + warp;
-          const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
-          for (int base = lo; base < hi; base += 32) {
-            const int n = min(32, hi - base);
-            const uint32_t mine = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
-            for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, mine, i), lane);
+    const bool mine_unit = (G == 1) || (turn == grp);
+    if (G > 1) turn = turn + 1 == G ? 0 : turn + 1;
+    if (mine_unit) {
+      const int nrec = cur.nrec(a);
+      if (!mbar_wait(full + s, ph)) {
+        if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+        return;
+      }
+      const uint8_t* st = ring + (size_t)s * STAGE;
+      if (rec < nrec) {
+        uint32_t A[4][4];
+        decode_frag(load_rec_shared(st + rec * REC, lane), A);
+        const uint32_t* side = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);
+        const uint32_t ne = side[0];
+        if (ne) {
+          if (ne <= 14u) {
+            for (uint32_t i = 0; i < ne; ++i) {
+              const uint32_t e = side[2 + i];
+              if (((e >> 10) & 7u) == (uint32_t)rec) patch_entry(A, e, lane);
+            }
+          } else {                                             // crowded unit: this record's own list
+            const size_t r = (size_t)cur.tile * a.NG + (size_t)cur.c * CW + rec;
+            const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
+            for (int base = lo; base < hi; base += 32) {
+              const int n = min(32, hi - base);
+              const uint32_t mine = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
+              for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, mine, i), lane);
+            }
           }
         }
-      }
-      const uint32_t sb = smem_addr(st);
+        if (!xready) {                                         // whole activation rows: waited for once
+          if (!mbar_wait(xbar, 0u)) {
+            if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+            return;
+          }
+          xready = true;
+        }
+        const uint32_t sb = a.xwhole ? (uint32_t)(cur.c * (CW * 128)) : smem_addr(st);
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        uint32_t b[8];
-        const uint32_t xa = xo[nt] ? sb + xo[nt] : zaddr;
-        ldmatrix_x4(xa, b[0], b[1], b[2], b[3]);
-        ldmatrix_x4(xa + 64, b[4], b[5], b[6], b[7]);
+        for (int nt = 0; nt < NT; ++nt) {
+          uint32_t b[8];
+          const uint32_t xa = xo[nt] ? sb + xo[nt] : zaddr;
+          ldmatrix_x4(xa, b[0], b[1], b[2], b[3]);
+          ldmatrix_x4(xa + 64, b[4], b[5], b[6], b[7]);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_bf16(acc[nt], A[ks], b[2 * ks], b[2 * ks + 1]);
+          for (int ks = 0; ks < 4; ++ks) mma_bf16(acc[nt], A[ks], b[2 * ks], b[2 * ks + 1]);
+        }
       }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty + s);
-    if (++s == S) { s = 0; ph ^= 1u; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + s);
 #ifdef ST_PROF
-    if (warp == 0 && lane == 0) { PROF(2 + ccount); ++ccount; }
+      if (warp == 0 && lane == 0) { PROF(2 + ccount); ++ccount; }
 #endif
+    }
+    if (++s == S) { s = 0; ph ^= 1u; }
 
     if (!cur.tile_end(a)) continue;
     // ---- end of this CTA's share of the tile: hand the warp's partial sums to the reducer
@@ -387,7 +442,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       return;
     }
     ++nf;
-    float* mine = red + (buf * CW + warp) * EL;
+    float* mine = red + (buf * NCW + warp) * EL;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int n0 = nt * 8 + 2 * (lane & 3);
@@ -402,7 +457,12 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
   }
 }
 
-struct Plan { int C, stages, maxcover, stage_bytes, nxrows; size_t smem; long long U; int CPT, T, NG, nprob; };
+struct Plan {
+  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, groups, ahead;
+  size_t smem;
+  long long U;
+  int CPT, T, NG, nprob;
+};
 
 bool pdl_enabled() {
   static int on = -1;
@@ -413,9 +473,9 @@ bool pdl_enabled() {
   return on == 1;
 }
 
-// nx = activation rows staged per unit (the batch for a dense matrix, 1 per slot, 8 per block of slots)
+// nx = activation rows staged per unit (the batch for a dense matrix, 1 per slot, 8 per block of slots).
 template <int NT>
-Plan make_plan(long long M, long long N, int nprob, int nx) {
+Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   Plan p;
   p.NG = (int)(N / 64);
   p.CPT = (p.NG + CW - 1) / CW;
@@ -423,17 +483,38 @@ Plan make_plan(long long M, long long N, int nprob, int nx) {
   p.nprob = nprob;
   p.U = (long long)nprob * p.T * p.CPT;
   p.nxrows = nx;
-  p.stage_bytes = UNIT_BYTES + SIDE_BYTES + nx * XROW;
+  p.groups = 1;
+  // whole activation rows stay resident when they are small (decode batches of one or two rows)
+  p.xwhole = dense && (long long)nx * (N * 2 + 16) <= 32 * 1024 ? 1 : 0;
+  p.xw_stride = p.xwhole ? (int)(N * 2 + 16) : 0;
+  p.xw_bytes = p.xwhole ? nx * p.xw_stride : 0;
+  p.stage_bytes = UNIT_BYTES + SIDE_BYTES + (p.xwhole ? 0 : nx * XROW);
   constexpr int EL = 16 * 8 * NT;
-  const size_t fixed = XROW + (size_t)2 * CW * EL * 4 + (2 * 8 + 4) * 8 + 16;
-  // two CTAs per SM when that still leaves a ring of >= 3 stages each (more warps to hide latency, and room for
-  // the next kernel's CTAs to start while this one drains); else one CTA with the deepest ring that fits
-  int per_sm = 2;
-  int stages = (int)((110 * 1024 - (long long)fixed) / p.stage_bytes);
-  if (NT > 2 || stages < 3) {
+  const size_t fixed = XROW + p.xw_bytes + (size_t)2 * CW * p.groups * EL * 4 + (2 * 8 + 5) * 8 + 16;
+  // Two CTAs per SM, each with the deepest ring that fits half of the SM's shared memory: the streaming rate is set
+  // by the bytes in flight per SM (measured: 2 x 7 stages = 174 KB in flight sustain ~5.7 TB/s; smaller rings with an
+  // L2 prefetch running ahead of them were slower, the prefetch instruction stalls its issuer once the queue is deep).
+  // Tunables (environment, read once): STATETREE_GEMV_CTAS_PER_SM, STATETREE_GEMV_SMEM_KB, STATETREE_GEMV_STAGES,
+  // STATETREE_GEMV_AHEAD (units of L2 prefetch ahead of the ring, 0 = off).
+  static int slots_per_sm = 0, budget_kb = 0, ahead = 0, max_stages = 0;
+  if (slots_per_sm == 0) {
+    const char* v;
+    slots_per_sm = (v = getenv("STATETREE_GEMV_CTAS_PER_SM")) ? atoi(v) : 2;
+    budget_kb = (v = getenv("STATETREE_GEMV_SMEM_KB")) ? atoi(v) : 113;
+    ahead = (v = getenv("STATETREE_GEMV_AHEAD")) ? atoi(v) : 0;
+    max_stages = (v = getenv("STATETREE_GEMV_STAGES")) ? atoi(v) : 8;
+    if (slots_per_sm < 1) slots_per_sm = 1;
+    if (ahead < 0) ahead = 0;
+    if (ahead > 32) ahead = 32;
+  }
+  p.ahead = ahead;
+  int per_sm = slots_per_sm;
+  int stages = (int)((budget_kb * 1024 - (long long)fixed) / p.stage_bytes);
+  if (stages < 2) {
     per_sm = 1;
     stages = (int)((200 * 1024 - (long long)fixed) / p.stage_bytes);
   }
+  if (stages > max_stages) stages = max_stages;
   if (stages > 8) stages = 8;
   p.stages = stages;
   p.smem = (size_t)stages * p.stage_bytes + fixed;
@@ -448,9 +529,11 @@ Plan make_plan(long long M, long long N, int nprob, int nx) {
 
 template <int NT, int MODE>
 int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
-  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx);
+  constexpr int G = 1;
+  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE);
   a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages;
-  a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows;
+  a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows; a.xwhole = p.xwhole; a.xw_stride = p.xw_stride;
+  a.xw_bytes = p.xw_bytes; a.ahead = p.ahead;
   const long long need = (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
   ST_REQUIRE(p.maxcover == 1 || (a.ws && ws_bytes >= need), "%s: workspace of %lld bytes needed, %lld given", who, need,
              ws_bytes);
@@ -464,14 +547,14 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set[dev]) {
-    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemv_kernel<NT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemv_kernel<NT, MODE, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    200 * 1024), who))
       return e;
     set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)p.C);
-  cfg.blockDim = dim3((CW + 2) * 32);
+  cfg.blockDim = dim3((CW * G + 2) * 32);
   cfg.dynamicSmemBytes = p.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -479,13 +562,13 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
-  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemv_kernel<NT, MODE>, a), who)) return e;
+  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemv_kernel<NT, MODE, G>, a), who)) return e;
   return 0;
 }
 
 template <int NT>
-long long ws_need(long long M, long long N, int nprob, int nx) {
-  const Plan p = make_plan<NT>(M, N, nprob, nx);
+long long ws_need(long long M, long long N, int nprob, int nx, bool dense = true) {
+  const Plan p = make_plan<NT>(M, N, nprob, nx, dense);
   return p.maxcover == 1 ? 0 : (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
 }
 }  // namespace
@@ -579,7 +662,7 @@ extern "C" int st_gemv_static(const void* tree, const int32_t* eo, const uint32_
 
 extern "C" int64_t st_moe_gemv_workspace_bytes(int64_t S, int64_t M, int64_t N) {
   if (M <= 0 || N <= 0 || M % 16 || N % 64 || S < 1) return -1;
-  return ws_need<1>(M, N, (int)S, 1);
+  return ws_need<1>(M, N, (int)S, 1, false);
 }
 
 static int moe_common_checks(const char* who, const int64_t* tp, const int64_t* eop, const int64_t* ebp,
@@ -609,7 +692,7 @@ extern "C" int st_moe_gemv(const int64_t* tp, const int64_t* eop, const int64_t*
 
 extern "C" int64_t st_moe_group_workspace_bytes(int64_t nblk, int64_t M, int64_t N) {
   if (M <= 0 || N <= 0 || M % 16 || N % 64 || nblk < 1) return -1;
-  return ws_need<1>(M, N, (int)nblk, 8);
+  return ws_need<1>(M, N, (int)nblk, 8, false);
 }
 
 extern "C" int st_moe_group_gemv(const int64_t* tp, const int64_t* eop, const int64_t* ebp, const int64_t* elp,

@@ -57,10 +57,10 @@ def test_slot_and_grouped_products_match_fp64():
         assert bool((y[odd] == 7.0).all()) and torch.equal(y[~odd], outs["group"][~odd])
     T, K, Hd = 5, 3, 64
     y = torch.randn(T * K, Hd, device=DEV, generator=g).to(torch.bfloat16)
-    for w in (torch.rand(T, K, device=DEV), torch.rand(T, K, device=DEV).to(torch.bfloat16)):
+    for w in (torch.rand(T, K, device=DEV, generator=g), torch.rand(T, K, device=DEV, generator=g).to(torch.bfloat16)):
         got = moe_wsum(y, w).float()
         want = (y.view(T, K, Hd).float() * w.float().unsqueeze(-1)).sum(1)
-        assert (got - want).abs().max().item() < 1e-2
+        assert bool(((got - want).abs() <= want.abs() * 2.0 ** -8 + 1e-6).all())          # one BF16 rounding
     gu = torch.randn(7, 2 * 96, device=DEV, generator=g).to(torch.bfloat16)
     want = (torch.nn.functional.silu(gu[:, :96].float()).to(torch.bfloat16) * gu[:, 96:])
     assert (silu_mul(gu).float() - want.float()).abs().max().item() < 2e-2
