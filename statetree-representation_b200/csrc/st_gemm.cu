@@ -27,16 +27,26 @@ namespace {
 using namespace st;
 
 constexpr int A_TILE = 128 * 128;            // 128 rows x 64 bf16, one swizzle atom wide
-constexpr int RAW = 13 * 1024;               // 8 records (12416 B) padded to keep stages 1024-byte aligned
 constexpr int NDEC = 8;                      // decode warps = records per k-tile
 
 struct GemmArgs {
   const uint8_t* tree; const int* eo; const uint32_t* el;
   uint16_t* Y; float* Yf; float* ws; int* cnt; int* status;
   long long M, N;
-  int B, NG, NT, KS, RB, TT, stages;
+  int B, NG, NT, KS, RB, TT, stages, rstages, xstages, bar_off;
   uint32_t idesc;
+#ifdef ST_PROF
+  long long* prof;
+#endif
 };
+
+#ifdef ST_PROF
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define GPROF(slot) do { if (a.prof && (slot) < 64) a.prof[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
+long long* g_gemm_prof = nullptr;
+#else
+#define GPROF(slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -70,24 +80,59 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
                : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 // shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 B apart
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-__global__ void __launch_bounds__(320, 1) gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+constexpr int NDW = 2 * NDEC;                // decode warps: two k-tiles are decoded at a time
+constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;     // producer (records), producer (activations), MMA
+constexpr int GEMM_THREADS = (NDW + 3) * 32;
+constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of one k-tile
+
+// Two rings.  The RAW ring (R slots of eight records) faces HBM: its depth sets the bytes in flight.  The TILE ring
+// (S stages of decoded weight tile + activation tile) covers the decode -> MMA hand-over and the L2 latency of the
+// activation loads; one mbarrier per stage counts both operands so the MMA thread waits once and commits once.
+// The KS CTAs that split the k range of one (row block, token tile) form a thread-block cluster (blockIdx.x % KS is
+// the rank).  After its main loop every CTA parks its fp32 accumulator tile in its own shared memory; after a cluster
+// barrier CTA j adds the KS tiles for its share of the token columns through distributed shared memory, in rank
+// order (bit-identical from run to run), and stores BF16.  No partial sums travel through global memory.
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const int NT = a.NT, S = a.stages;
+  const int NT = a.NT, S = a.stages, R = a.rstages;
   const int XT = NT * 128;                       // bytes of an activation tile
-  const int STAGE = A_TILE + XT + RAW;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)S * STAGE);
-  uint64_t* ready = full + S;
-  uint64_t* empty = ready + S;
-  uint64_t* accbar = empty + S;
+  const int STAGE = A_TILE + XT;                 // tile stage: decoded weight tile + activation tile
+  uint8_t* rawring = smem + (size_t)S * STAGE;                       // [R] record slots (deep: covers HBM latency)
+  // one barrier per tile stage collects both operands: 8 decode-warp arrivals + the activation tile's TMA bytes
+  uint64_t* ready = reinterpret_cast<uint64_t*>(smem + a.bar_off);   // [S] both operands of the stage are in place
+  uint64_t* empty = ready + S;                                       // [S] MMAs that read the stage have completed
+  uint64_t* rfull = empty + S;                                       // [R] records landed
+  uint64_t* rempty = rfull + R;                                      // [R] records copied to registers
+  uint64_t* accbar = rempty + R;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accbar + 1);
-  int* flags = reinterpret_cast<int*>(tmem_slot + 1);        // [0] abort, [1] last arriver
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // unit of this CTA
@@ -98,12 +143,13 @@ __global__ void __launch_bounds__(320, 1) gemm_kernel(const GemmArgs a, const __
   const int tok0 = tt * NT;
 
   if (tid == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(ready + s, NDEC); mbar_init(empty + s, 1); }
+    GPROF(0);
+    for (int s = 0; s < S; ++s) { mbar_init(ready + s, NDEC + 1); mbar_init(empty + s, 1); }
+    for (int r = 0; r < R; ++r) { mbar_init(rfull + r, 1); mbar_init(rempty + r, NDEC); }
     mbar_init(accbar, 1);
-    flags[0] = 0; flags[1] = 0;
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == W_MMA) {
     tmem_alloc(tmem_slot, (uint32_t)(NT < 32 ? 32 : NT));
     tmem_relinquish();
   }
@@ -111,61 +157,93 @@ __global__ void __launch_bounds__(320, 1) gemm_kernel(const GemmArgs a, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (tid == 0) GPROF(1);
 
-  if (warp == 8) {
-    // ---------------------------------------------------------------- producer
-    if (lane == 0) {
+  if (warp == W_RAW) {
+    // ---------------------------------------------------------------- record producer: lane w < 8 copies record w
+    // (row tile rb * 8 + w) of every k-tile into the raw ring
+    if (lane < NDEC) {
       const uint64_t pol = policy_evict_first();
+      const uint8_t* myrec = a.tree + ((size_t)(rb * 8 + lane) * a.NG + k0) * REC;
+      for (int i = 0; i < nk; ++i) {
+        const int r = i % R, k = i / R;
+        if (k > 0 && !mbar_wait(rempty + r, (uint32_t)(k - 1) & 1u)) {
+          if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
+          break;
+        }
+        if (lane == 0) mbar_expect_tx(rfull + r, (uint32_t)RAW_SLOT);
+        __syncwarp(0xFFu);
+        bulk_g2s(rawring + (size_t)r * RAW_SLOT + lane * REC, myrec + (size_t)i * REC, REC, rfull + r, pol);
+      }
+    }
+  } else if (warp == W_X) {
+    // ---------------------------------------------------------------- activation producer
+    if (lane == 0) {
       for (int i = 0; i < nk; ++i) {
         const int s = i % S, k = i / S;
         if (k > 0 && !mbar_wait(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
-        uint8_t* st = smem + (size_t)s * STAGE;
-        mbar_expect_tx(full + s, (uint32_t)(NDEC * REC + XT));
-        tma_load_2d(st + A_TILE, &xmap, (k0 + i) * 64, tok0, full + s);
-#pragma unroll
-        for (int w = 0; w < NDEC; ++w)
-          bulk_g2s(st + A_TILE + XT + w * REC, a.tree + ((size_t)(rb * 8 + w) * a.NG + (k0 + i)) * REC, REC, full + s, pol);
+        mbar_expect_tx(ready + s, (uint32_t)XT);
+        tma_load_2d(smem + (size_t)s * STAGE + A_TILE, &xmap, (k0 + i) * 64, tok0, ready + s);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == W_MMA) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      bool ok = true;
-      for (int i = 0; i < nk && ok; ++i) {
+      for (int i = 0; i < nk; ++i) {
         const int s = i % S, k = i / S;
-        if (!mbar_wait(ready + s, (uint32_t)k & 1u)) { atomicExch(a.status, ERR_WAIT_MMA); ok = false; break; }
+        if (!mbar_wait(ready + s, (uint32_t)k & 1u)) {
+          atomicExch(a.status, ERR_WAIT_MMA);
+          break;
+        }
         tc_fence_after();
-        const uint32_t sa = smem_addr(smem + (size_t)s * STAGE), sb = sa + A_TILE;
-        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
+        const uint32_t sa = smem_addr(smem + (size_t)s * STAGE);
+        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TILE);
 #pragma unroll
         for (int j = 0; j < 4; ++j) tc_mma(tmem, da + 2 * j, db + 2 * j, a.idesc, (i | j) ? 1u : 0u);
         tc_commit(empty + s);
+        GPROF(40 + i);
       }
       tc_commit(accbar);                                          // arrives when every MMA above has completed
     }
   } else {
-    // ---------------------------------------------------------------- decode warps
-    const size_t rbase = (size_t)(rb * 8 + warp) * a.NG;
-    int lo = 0, hi = 0;
-    if (nk > 0) { lo = __ldg(a.eo + rbase + k0); hi = __ldg(a.eo + rbase + k0 + 1); }
-    for (int i = 0; i < nk; ++i) {
-      const int s = i % S, k = i / S;
-      int nlo = hi, nhi = hi;
-      if (i + 1 < nk) nhi = __ldg(a.eo + rbase + k0 + i + 2);    // next record's list end (lists are contiguous)
-      if (!mbar_wait(full + s, (uint32_t)k & 1u)) {
+    // ---------------------------------------------------------------- decode warps: group g = warp / 8 takes the
+    // k-tiles i = g, g + 2, ...; warp r of a group decodes record r (rows 16 r .. 16 r + 15 of the block)
+    const int grp = warp / NDEC, rec = warp % NDEC;
+    const size_t rbase = (size_t)(rb * 8 + rec) * a.NG + k0;
+    // escape-list offsets of this warp's records, 32 k-tiles at a time (lane l holds the offsets of k-tile base + l),
+    // so no global load sits between two k-tiles
+    int eo_base = -1, eo_lo = 0, eo_hi = 0;
+    for (int i = grp; i < nk; i += 2) {
+      const int s = i % S, k = i / S, r = i % R;
+      if (eo_base < 0 || i - eo_base >= 32) {
+        eo_base = i;
+        const int j = i + lane;
+        eo_lo = j < nk ? __ldg(a.eo + rbase + j) : 0;
+        eo_hi = j < nk ? __ldg(a.eo + rbase + j + 1) : 0;
+      }
+      const int lo = __shfl_sync(FULL, eo_lo, i - eo_base), hi = __shfl_sync(FULL, eo_hi, i - eo_base);
+      if (!mbar_wait(rfull + r, (uint32_t)(i / R) & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
         break;
       }
-      uint8_t* st = smem + (size_t)s * STAGE;
+      if (tid == 0) GPROF(8 + i + 1);                             // (odd slots: records of k-tile i seen)
+      const RecRegs rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + rec * REC, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rempty + r);                     // the slot can be refilled while we decode
       uint32_t A[4][4];
-      decode_frag(load_rec_shared(st + A_TILE + XT + warp * REC, lane), A);
+      decode_frag(rr, A);
       for (int base = lo; base < hi; base += 32) {
         const int n = min(32, hi - base);
         const uint32_t mine = (lane < n) ? __ldg(a.el + base + lane) : 0u;
         for (int e = 0; e < n; ++e) patch_entry(A, __shfl_sync(FULL, mine, e), lane);
       }
-      // lane l addresses row (l & 7) of matrix (l >> 3): matrices = (rows 0-7 | 8-15) x (16-byte chunk 2ks | 2ks+1)
-      const int mrow = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+      if (k > 0 && !mbar_wait(empty + s, (uint32_t)(k - 1) & 1u)) {   // the MMAs of the stage's last use are done
+        if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
+        break;
+      }
+      uint8_t* st = smem + (size_t)s * STAGE;
+      // lane l addresses row (l & 7) of matrix (l >> 3): matrices = (rows 0-7 | 8-15) x (16-byte chunk 2q | 2q+1)
+      const int mrow = rec * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
       const uint32_t rowaddr = smem_addr(st) + mrow * 128;
       const int chalf = lane >> 4;
 #pragma unroll
@@ -174,78 +252,56 @@ __global__ void __launch_bounds__(320, 1) gemm_kernel(const GemmArgs a, const __
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(ready + s);
-      lo = nlo; hi = nhi;
+      if (tid == 0) GPROF(8 + i);
     }
-    // ---------------------------------------------------------------- epilogue
+    // ---------------------------------------------------------------- epilogue 1: accumulator -> own shared memory
     const bool acc_ok = mbar_wait(accbar, 0u);
     if (!acc_ok && lane == 0) atomicExch(a.status, ERR_WAIT_ACC);
+    if (tid == 0) GPROF(2);
     tc_fence_after();
-    const int q4 = warp & 3, half = warp >> 2;
-    const int row = rb * 128 + q4 * 32 + lane;
-    const int cper = NT / 2;                                      // columns of this warp
-    const int unit = tt * a.RB + rb;
-    if (acc_ok && nk > 0) {
-      for (int c0 = half * cper; c0 < (half + 1) * cper; c0 += 32) {
-        uint32_t v[32];
+    float* stg = reinterpret_cast<float*>(smem);                 // [NT][128] fp32, over the (now idle) ring
+    const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column quarter
+    const int cper = NT / 4;
+    for (int c0 = cg * cper; c0 < (cg + 1) * cper; c0 += 32) {
+      uint32_t v[32];
+      if (cper >= 32) {
         tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
-        if (a.KS == 1) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tok = tok0 + c0 + j;
-            if (tok < a.B) {
-              const float f = __uint_as_float(v[j]);
-              const __nv_bfloat16 hv = __float2bfloat16_rn(f);
-              a.Y[(size_t)tok * a.M + row] = *reinterpret_cast<const uint16_t*>(&hv);
-              if (a.Yf) a.Yf[(size_t)tok * a.M + row] = f;
-            }
-          }
-        } else {
-          float* part = a.ws + ((size_t)unit * a.KS + ks) * NT * 128;
+        for (int j = 0; j < 32; ++j) stg[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
+      } else {                                                   // NT = 64: 16 columns per warp
+        tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) part[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
-        }
+        for (int j = 0; j < 16; ++j) stg[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
       }
     }
-    if (a.KS > 1) {
-      __threadfence();
-      named_bar_sync(1, NDEC * 32);
-      if (tid == 0) flags[1] = (atomicAdd(a.cnt + unit, 1) == a.KS - 1);
-      named_bar_sync(1, NDEC * 32);
-      if (flags[1]) {
-        __threadfence();
-        // the last CTA to arrive adds the KS partial tiles in split order; eight token columns per thread are kept in
-        // flight so the L2 latency of the partial reads overlaps
-        const int r = tid & 127;
-        const int ncol = min(NT, a.B - tok0);
-        const float* base = a.ws + (size_t)unit * a.KS * NT * 128 + r;
-        for (int c0 = tid >> 7; c0 < ncol; c0 += 16) {
-          float sum[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) sum[u] = 0.f;
-          for (int p = 0; p < a.KS; ++p) {
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int c = c0 + 2 * u;
-              if (c < ncol) sum[u] += __ldcg(base + ((size_t)p * NT + c) * 128);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int c = c0 + 2 * u;
-            if (c < ncol) {
-              const __nv_bfloat16 hv = __float2bfloat16_rn(sum[u]);
-              a.Y[(size_t)(tok0 + c) * a.M + rb * 128 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-              if (a.Yf) a.Yf[(size_t)(tok0 + c) * a.M + rb * 128 + r] = sum[u];
-            }
-          }
-        }
-        if (tid == 0) a.cnt[unit] = 0;
-      }
-    }
+    if (tid == 0) GPROF(3);
   }
   tc_fence_before();
-  __syncthreads();
-  if (warp == 9) {
+  __syncwarp();
+  cluster_sync_all();                                            // every CTA of the cluster has parked its tile
+  if (warp < NDW) {
+    // ---------------------------------------------------------------- epilogue 2: add the KS tiles, rank order
+    const int ncol = min(NT, a.B - tok0);
+    const int c_lo = (int)((long long)NT * ks / a.KS), c_hi = (int)((long long)NT * (ks + 1) / a.KS);
+    const uint32_t mine = smem_addr(smem);
+    for (int c = c_lo + warp; c < c_hi && c < ncol; c += NDW) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < a.KS; ++p) {
+        const float4 v = ld_cluster_f4(map_to_cta(mine + (uint32_t)((c * 128 + 4 * lane) * 4), (uint32_t)p));
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      }
+      const size_t o = (size_t)(tok0 + c) * a.M + rb * 128 + 4 * lane;
+      uint2 packed;
+      packed.x = pack_bf16(sum.x, sum.y);
+      packed.y = pack_bf16(sum.z, sum.w);
+      *reinterpret_cast<uint2*>(a.Y + o) = packed;
+      if (a.Yf) *reinterpret_cast<float4*>(a.Yf + o) = sum;
+    }
+  }
+  if (tid == 0) GPROF(4);
+  __syncwarp();
+  cluster_sync_all();                                            // nobody leaves while a peer still reads its tile
+  if (warp == W_MMA) {
     __syncwarp();
     tmem_dealloc(tmem, (uint32_t)(NT < 32 ? 32 : NT));
   }
@@ -269,7 +325,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-struct GemmPlan { int NT, TT, RB, KS, stages; size_t smem; };
+struct GemmPlan { int NT, TT, RB, KS, stages, rstages, xstages, bar_off; size_t smem; };
 
 GemmPlan gemm_plan(long long M, long long N, long long B) {
   GemmPlan p;
@@ -278,28 +334,42 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   p.RB = (int)(M / 128);
   const int NG = (int)(N / 64), sms = st::sm_count();
   const long long units = (long long)p.RB * p.TT;
+  // split of the k range = cluster size (<= 8): fill the SMs, but every extra split costs an accumulator tile of
+  // distributed-shared-memory traffic in the epilogue
   int best = 1;
   double best_score = -1.0;
-  const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 32 ? 32 : NG / 4);
+  const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 8 ? 8 : NG / 4);
   for (int ks = 1; ks <= ksmax; ++ks) {
     const long long ctas = units * ks;
     const long long waves = (ctas + sms - 1) / sms;
-    const double score = (double)ctas / (double)(waves * sms) - 0.03 * ks * p.NT / 256.0;   // partial-sum traffic
+    const double score = (double)ctas / (double)(waves * sms) - 0.01 * ks * p.NT / 256.0;
     if (score > best_score + 1e-9) { best_score = score; best = ks; }
   }
   p.KS = best;
-  const int stage = A_TILE + p.NT * 128 + RAW;
-  int s = (int)((212 * 1024) / stage);
-  p.stages = s > 6 ? 6 : s;
-  p.smem = (size_t)p.stages * stage + 1024 /* alignment slack */ + 256 /* barriers */;
+  // tile stages (decoded weight tile + activation tile): enough to cover the L2 latency of the activation loads;
+  // the rest of the shared memory goes to the record ring, which covers the HBM latency
+  p.stages = p.NT >= 256 ? 3 : 4;
+  p.xstages = 0;
+  const size_t tiles = (size_t)p.stages * (A_TILE + (size_t)p.NT * 128);
+  p.rstages = (int)((212 * 1024 - tiles) / RAW_SLOT);
+  if (p.rstages > 12) p.rstages = 12;
+  size_t ring = tiles + (size_t)p.rstages * RAW_SLOT;
+  ring = (ring + 15) & ~(size_t)15;
+  const size_t stg = (size_t)p.NT * 128 * 4;                    // the parked accumulator tile reuses the rings
+  if (ring < stg) ring = stg;
+  p.bar_off = (int)ring;
+  p.smem = ring + 1024 /* alignment slack */ + 512 /* barriers */;
   return p;
 }
 }  // namespace
 
+#ifdef ST_PROF
+extern "C" void st_debug_set_gemm_prof(long long* buf) { g_gemm_prof = buf; }
+#endif
+
 extern "C" int64_t st_gemm_workspace_bytes(int64_t M, int64_t N, int64_t B) {
   if (M <= 0 || N <= 0 || M % 128 || N % 64 || B < 1) return -1;
-  const GemmPlan p = gemm_plan(M, N, B);
-  return p.KS == 1 ? 0 : (int64_t)p.RB * p.TT * p.KS * p.NT * 128 * 4;
+  return 0;                                                      // split partial sums stay in shared memory
 }
 
 extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, const void* X, void* Y, float* Yf32,
@@ -310,9 +380,7 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   ST_REQUIRE(tree && eo && el && X && Y && cnt, "st_gemm: null pointer");
   ST_REQUIRE(st::aligned16(tree) && st::aligned16(X), "st_gemm: tree and X must be 16-byte aligned");
   const GemmPlan p = gemm_plan(M, N, B);
-  const long long need = p.KS == 1 ? 0 : (long long)p.RB * p.TT * p.KS * p.NT * 128 * 4;
-  ST_REQUIRE(need == 0 || (ws && ws_bytes >= need), "st_gemm: workspace of %lld bytes needed, %lld given", need,
-             (long long)ws_bytes);
+  (void)ws; (void)ws_bytes;
   ST_REQUIRE((long long)p.RB * p.TT * p.KS < (1ll << 31), "st_gemm: grid too large");
   EncodeTiledFn enc = encode_fn();
   ST_REQUIRE(enc != nullptr, "st_gemm: cuTensorMapEncodeTiled is not available from the driver");
@@ -330,7 +398,10 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "st_gemm: no device status word");
   a.M = M; a.N = N; a.B = (int)B; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = p.KS; a.RB = p.RB; a.TT = p.TT;
-  a.stages = p.stages;
+  a.stages = p.stages; a.rstages = p.rstages; a.xstages = p.xstages; a.bar_off = p.bar_off;
+#ifdef ST_PROF
+  a.prof = g_gemm_prof;
+#endif
   // instruction descriptor: D fp32, A and B bf16, both K-major, N = NT, M = 128
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   static bool set[64] = {};
@@ -342,7 +413,18 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
       return e;
     set[dev] = true;
   }
-  gemm_kernel<<<(unsigned)(p.RB * p.TT * p.KS), 320, p.smem, (cudaStream_t)stream>>>(a, xmap);
-  ST_LAUNCH_CHECK("st_gemm launch");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.RB * p.TT * p.KS));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = p.smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)p.KS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel, a, xmap), "st_gemm launch")) return e;
   return 0;
 }

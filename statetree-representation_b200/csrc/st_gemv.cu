@@ -520,6 +520,16 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   p.smem = (size_t)stages * p.stage_bytes + fixed;
   const long long slots = (long long)st::sm_count() * per_sm;
   p.C = (int)(p.U < slots ? p.U : slots);
+  {
+    // Prefer a grid whose CTA boundaries fall on tile boundaries (or cut every tile into equal parts) when one exists
+    // within 20% of the slot count: a tile that is not shared needs no cross-CTA hand-over of partial sums at all.
+    const long long tiles = (long long)nprob * p.T;
+    for (long long c = p.C; c * 5 >= (long long)p.C * 4 && c >= 1; --c) {
+      const bool whole = tiles % c == 0;
+      const bool even = c % tiles == 0 && p.CPT % (c / tiles) == 0;
+      if (whole || even) { p.C = (int)c; break; }
+    }
+  }
   const long long per = p.U / p.C;
   long long mc = (p.CPT + per - 1) / per + 1;
   if (mc > p.CPT) mc = p.CPT;

@@ -10,6 +10,7 @@
 // on mma.m16n8k16 with the decoded K fragments as the B operand and the V fragments transposed in registers;
 // P is fed as a BF16 high part plus a BF16 residual, so the softmax weights keep ~16 mantissa bits.
 #include <math.h>
+#include <stdlib.h>
 
 #include "../../include/statetree_b200.h"
 #include "st_common.cuh"
@@ -253,16 +254,17 @@ struct AttnArgs {
   int* status;
 };
 
-constexpr int ATT_NW = 4;        // warps per CTA
-constexpr int ATT_STG = 3;       // pages in flight per warp
 constexpr int PAGE_BYTES = 4 * RKV;
 
-template <int G>
+// ATT_NW warps per CTA, each with ATT_STG pages in flight.  The per-warp partial results reuse the ring once the
+// loop is over, so a CTA needs only the ring and its barriers (4 warps x 3 stages = 75 KB measured slightly faster
+// than 8 warps x 2 stages = 100 KB; both leave two CTAs per SM).
+template <int G, int ATT_NW, int ATT_STG>
 __global__ void __launch_bounds__(ATT_NW * 32) kv_attn_kernel(const AttnArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;                                                         // [NW][STG][6400]
-  float* red = reinterpret_cast<float*>(smem + ATT_NW * ATT_STG * PAGE_BYTES);  // [NW][G * 128 + 2 G]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(red + ATT_NW * (G * 128 + 2 * G));   // [NW][STG]
+  float* red = reinterpret_cast<float*>(smem);                                  // [NW][G * 128 + 2 G], after the loop
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_NW * ATT_STG * PAGE_BYTES);   // [NW][STG]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int j = blockIdx.x % a.S, bh = blockIdx.x / a.S;
   const int h = bh % a.Hkv, b = bh / a.Hkv, Hq = a.Hkv * G;
@@ -386,8 +388,10 @@ __global__ void __launch_bounds__(ATT_NW * 32) kv_attn_kernel(const AttnArgs a) 
     m = -INFINITY; l = 0.f;
   }
 
-  // merge the warps of the CTA
+  // merge the warps of the CTA (every warp is done with the ring: its partial result goes where the pages were)
+  __syncthreads();
   constexpr int WS = G * 128 + 2 * G;
+  static_assert(ATT_NW * WS * 4 <= ATT_NW * ATT_STG * PAGE_BYTES, "partials must fit the ring");
   float* so = red + warp * WS;
   if (g < G) {
 #pragma unroll
@@ -440,20 +444,30 @@ __global__ void __launch_bounds__(128) kv_merge_kernel(const float* __restrict__
   out[(size_t)(bq / Hq) * os + (size_t)(bq % Hq) * HD + d] = *reinterpret_cast<const uint16_t*>(&v);
 }
 
-template <int G>
-int attn_launch(const AttnArgs& a, int B, cudaStream_t st) {
-  const int smem = ATT_NW * ATT_STG * PAGE_BYTES + ATT_NW * (G * 128 + 2 * G) * 4 + ATT_NW * ATT_STG * 8;
+template <int G, int NW, int STG>
+int attn_launch_cfg(const AttnArgs& a, int B, cudaStream_t st) {
+  const int smem = NW * STG * PAGE_BYTES + NW * STG * 8;
   static bool set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set[dev]) {
-    if (int e = st::cuda_fail(cudaFuncSetAttribute(kv_attn_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                              "st_kv_attn: shared memory attribute"))
+    if (int e = st::cuda_fail(cudaFuncSetAttribute(kv_attn_kernel<G, NW, STG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   smem), "st_kv_attn: shared memory attribute"))
       return e;
     set[dev] = true;
   }
-  kv_attn_kernel<G><<<(unsigned)(B * a.Hkv * a.S), ATT_NW * 32, smem, st>>>(a);
+  kv_attn_kernel<G, NW, STG><<<(unsigned)(B * a.Hkv * a.S), NW * 32, smem, st>>>(a);
   return 0;
+}
+
+template <int G>
+int attn_launch(const AttnArgs& a, int B, cudaStream_t st) {
+  static int cfg = -1;                       // STATETREE_ATTN_CFG: 1 = 4 warps x 3 stages (default), 0 = 8 warps x 2
+  if (cfg < 0) {
+    const char* v = getenv("STATETREE_ATTN_CFG");
+    cfg = v ? atoi(v) : 1;
+  }
+  return cfg == 1 ? attn_launch_cfg<G, 4, 3>(a, B, st) : attn_launch_cfg<G, 8, 2>(a, B, st);
 }
 }  // namespace
 
