@@ -392,11 +392,20 @@ def main():
     ms_e2e = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     status = ops.device_status()
+
+    def leave():
+        """multi-rank exit: the captured graph holds NCCL work, and tearing the process group down under it can block;
+        every rank is past its last collective here, so flush and leave the process directly"""
+        if world > 1:
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
     if world > 1:
         dist.barrier()
+        torch.cuda.synchronize()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        leave()
         return
 
     hbm, tf, which = peaks()
@@ -422,8 +431,7 @@ def main():
         line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
                                 "sample": "the seven linears of one layer, 2 timed passes (1/36 of a GPU step each)"}
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    leave()
 
 
 if __name__ == "__main__":
