@@ -265,7 +265,7 @@ def main():
 
     import statetree_b200 as S
     from statetree_b200 import ops
-    from statetree_b200.linear import _state
+    from statetree_b200.linear import GEMV_MAX, _state
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -317,7 +317,7 @@ def main():
     outs_h = [torch.empty(o.shape, dtype=torch.bfloat16).pin_memory() for o in outs]
     ins = [x, x, x, x_o, x, x, x_d]
     launches = 0
-    use_gemv = B <= 32
+    use_gemv = B <= GEMV_MAX
     st = _state(dev)
     ws_need = max((E.gemv_workspace_bytes if use_gemv else E.gemm_workspace_bytes)(tl.out_features, tl.in_features, B)
                   for tl in layers[0])

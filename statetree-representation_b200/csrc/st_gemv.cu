@@ -43,7 +43,7 @@ struct GemvArgs {
   int E, xdiv;
   int NG, CPT, T;                         // column groups, units per tile, tiles per problem
   long long U;                            // units over all problems
-  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, ahead;
+  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, ahead, slow_s0, slow_ns;
 #ifdef ST_PROF
   long long* prof;                        // [CTAs][64] globaltimer stamps (development builds only)
 #endif
@@ -52,9 +52,11 @@ struct GemvArgs {
 #ifdef ST_PROF
 __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define PROF(slot) do { if (a.prof && (slot) < 64) a.prof[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
+#define CK(n) do { const long long t_ = clock64(); ck[n] += t_ - ckl; ckl = t_; } while (0)
 long long* g_prof_buf = nullptr;
 #else
 #define PROF(slot) do {} while (0)
+#define CK(n) do {} while (0)
 #endif
 
 struct Prob {                             // what a unit's problem resolves to
@@ -136,6 +138,16 @@ struct UnitCursor {
   __device__ __forceinline__ bool valid() const { return u < end; }
   __device__ __forceinline__ int nrec(const GemvArgs& a) const { return c == a.CPT - 1 ? a.NG - c * CW : CW; }
   __device__ __forceinline__ bool tile_end(const GemvArgs& a) const { return c == a.CPT - 1 || u + 1 == end; }
+  // a run = the units of one tile that lie in the current segment, starting at the cursor
+  __device__ __forceinline__ int run_len(const GemvArgs& a) const { return min(a.CPT - c, end - u); }
+  __device__ __forceinline__ void advance(const GemvArgs& a, int len) {
+    u += len; c += len;
+    if (c == a.CPT) {
+      c = 0;
+      if (++tile == a.T) { tile = 0; ++p; enter(a); }
+    }
+    if (u >= end && seg == 0) { seg = 1; seek(a, b1, e1); }
+  }
   __device__ __forceinline__ void next(const GemvArgs& a) {
     ++u;
     if (++c == a.CPT) {
@@ -236,14 +248,24 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
     UnitCursor<MODE> pre = cur;
     int filled = 0;
     if (MODE == MODE_DENSE) {                                  // lane i fills stage i
+      // Slow start: all of a CTA's first copies share the memory system equally and would land together, late.  The
+      // first S0 stages are requested alone and the rest a little later, so the consumers start on the first units
+      // while the others are still in flight.
       const bool on = lane < S && mine.valid();
-      if (on) {
+      const int S0 = (a.xwhole && a.slow_s0 > 0 && a.slow_s0 < S) ? a.slow_s0 : S;
+      auto fill_mine = [&]() {
         const int nrec = mine.nrec(a);
         uint8_t* st = ring + (size_t)lane * STAGE;
         mbar_expect_tx(full + lane, (uint32_t)(nrec * REC + SIDE_BYTES) + (a.xwhole ? 0u : (uint32_t)(NX * nrec * 128)));
         bulk_g2s(st, mine.pr.tree + ((size_t)mine.tile * a.NG + (size_t)mine.c * CW) * REC, (uint32_t)(nrec * REC),
                  full + lane, pol_w);
         bulk_g2s(st + UNIT_BYTES, mine.pr.eb + ((size_t)mine.tile * a.CPT + mine.c) * 16, SIDE_BYTES, full + lane, pol_w);
+      };
+      if (on && lane < S0) fill_mine();
+      if (S0 < S) {
+        if (a.slow_ns > 0) __nanosleep((unsigned)a.slow_ns);
+        else (void)mbar_wait(full + 0, 0u);
+        if (on && lane >= S0) fill_mine();
       }
       filled = __popc(__ballot_sync(FULL, on));
     } else {
@@ -292,8 +314,7 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
     // consumers (sums the consumer warps in order, stores or hands a partial sum over), so the consumers never wait
     pdl_wait();                                                // ws, cnt and Y may still be in use by the previous kernel
     int nf = 0;
-    for (; cur.valid(); cur.next(a)) {
-      if (!cur.tile_end(a)) continue;
+    for (; cur.valid(); cur.advance(a, cur.run_len(a))) {      // one hand-over per run of units of a tile
       const int buf = nf & 1;
       if (!mbar_wait(done + buf, (uint32_t)(nf >> 1) & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
@@ -357,12 +378,15 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
 
   // -------------------------------------------------------------------- consumers
   const int g = lane >> 2, grp = warp / CW, rec = warp % CW;
-  float acc[NT][4];
+  float acc[NT][2][4];                                       // two accumulator chains per column tile
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) acc[nt][h][0] = acc[nt][h][1] = acc[nt][h][2] = acc[nt][h][3] = 0.f;
   int s = 0, nf = 0, turn = 0;
 #ifdef ST_PROF
   int ccount = 0;
+  long long ck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ckl = clock64();
 #endif
   uint32_t ph = 0;
   // ldmatrix row addresses of this lane: activation row nt * 8 + (lane & 7), or the zero row beyond the batch
@@ -377,64 +401,85 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
     else xo[nt] = (uint32_t)(UNIT_BYTES + SIDE_BYTES + n * XROW) + colo;
   }
   bool xready = !a.xwhole;
-  for (; cur.valid(); cur.next(a)) {
-    const bool mine_unit = (G == 1) || (turn == grp);
-    if (G > 1) turn = turn + 1 == G ? 0 : turn + 1;
-    if (mine_unit) {
-      const int nrec = cur.nrec(a);
-      if (!mbar_wait(full + s, ph)) {
-        if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
-        return;
-      }
-      const uint8_t* st = ring + (size_t)s * STAGE;
-      if (rec < nrec) {
-        uint32_t A[4][4];
-        decode_frag(load_rec_shared(st + rec * REC, lane), A);
-        const uint32_t* side = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);
-        const uint32_t ne = side[0];
-        if (ne) {
-          if (ne <= 14u) {
-            for (uint32_t i = 0; i < ne; ++i) {
-              const uint32_t e = side[2 + i];
-              if (((e >> 10) & 7u) == (uint32_t)rec) patch_entry(A, e, lane);
+  const int last_nrec = a.NG - (a.CPT - 1) * CW;
+  while (cur.valid()) {
+    const int len = cur.run_len(a), cbeg = cur.c;
+    for (int j = 0; j < len; ++j) {
+      CK(0);                                                  // loop overhead
+      const int c = cbeg + j;
+      const bool mine_unit = (G == 1) || (turn == grp);
+      if (G > 1) turn = turn + 1 == G ? 0 : turn + 1;
+      if (mine_unit) {
+        const int nrec = c == a.CPT - 1 ? last_nrec : CW;
+        if (!mbar_wait(full + s, ph)) {
+          if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+          return;
+        }
+        const uint8_t* st = ring + (size_t)s * STAGE;
+        CK(1);                                                // wait for the stage
+        if (rec < nrec) {
+          if (!xready) {                                       // whole activation rows: waited for once
+            if (!mbar_wait(xbar, 0u)) {
+              if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+              return;
             }
-          } else {                                             // crowded unit: this record's own list
-            const size_t r = (size_t)cur.tile * a.NG + (size_t)cur.c * CW + rec;
-            const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
-            for (int base = lo; base < hi; base += 32) {
-              const int n = min(32, hi - base);
-              const uint32_t mine = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
-              for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, mine, i), lane);
-            }
+            xready = true;
           }
-        }
-        if (!xready) {                                         // whole activation rows: waited for once
-          if (!mbar_wait(xbar, 0u)) {
-            if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
-            return;
+          // activations first: their shared-memory latency hides behind the decode
+          uint32_t b[NT][8];
+          const uint32_t sb = a.xwhole ? (uint32_t)(c * (CW * 128)) : smem_addr(st);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t xa = xo[nt] ? sb + xo[nt] : zaddr;
+            ldmatrix_x4(xa, b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
+            ldmatrix_x4(xa + 64, b[nt][4], b[nt][5], b[nt][6], b[nt][7]);
           }
-          xready = true;
-        }
-        const uint32_t sb = a.xwhole ? (uint32_t)(cur.c * (CW * 128)) : smem_addr(st);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          uint32_t b[8];
-          const uint32_t xa = xo[nt] ? sb + xo[nt] : zaddr;
-          ldmatrix_x4(xa, b[0], b[1], b[2], b[3]);
-          ldmatrix_x4(xa + 64, b[4], b[5], b[6], b[7]);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) mma_bf16(acc[nt], A[ks], b[2 * ks], b[2 * ks + 1]);
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty + s);
+          const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];   // the escape block
+          uint32_t A[4][4];
+          decode_frag(load_rec_shared(st + rec * REC, lane), A);
 #ifdef ST_PROF
-      if (warp == 0 && lane == 0) { PROF(2 + ccount); ++ccount; }
+          if (A[0][0] == 0x12345u && A[3][3] == 0x54321u) ck[7]++;   // keep the decode before the clock read
 #endif
+          CK(2);                                              // loads + decode
+          const uint32_t ne = __shfl_sync(FULL, sw, 0);
+          if (ne) {
+            if (ne <= 14u) {                                   // lanes 2..15 hold the inline entries: one vote
+              const bool hit = lane >= 2 && lane < 16 && (uint32_t)(lane - 2) < ne && ((sw >> 10) & 7u) == (uint32_t)rec;
+              unsigned m = __ballot_sync(FULL, hit);
+              while (m) {
+                const int src = __ffs(m) - 1;
+                m &= m - 1;
+                patch_entry(A, __shfl_sync(FULL, sw, src), lane);
+              }
+            } else {                                           // crowded unit: this record's own list
+              const size_t r = (size_t)cur.tile * a.NG + (size_t)c * CW + rec;
+              const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
+              for (int base = lo; base < hi; base += 32) {
+                const int n = min(32, hi - base);
+                const uint32_t ent = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
+                for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, ent, i), lane);
+              }
+            }
+          }
+          CK(3);                                              // escapes
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) mma_bf16(acc[nt][ks & 1], A[ks], b[nt][2 * ks], b[nt][2 * ks + 1]);
+#ifdef ST_PROF
+          if (acc[0][0][0] == 1.2345e30f) ck[7]++;             // keep the mma before the clock read
+#endif
+          CK(4);                                              // mma
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+        CK(5);                                                // release
+#ifdef ST_PROF
+        if (warp == 0 && lane == 0) { PROF(2 + ccount); ++ccount; }
+#endif
+      }
+      if (++s == S) { s = 0; ph ^= 1u; }
     }
-    if (++s == S) { s = 0; ph ^= 1u; }
-
-    if (!cur.tile_end(a)) continue;
     // ---- end of this CTA's share of the tile: hand the warp's partial sums to the reducer
     const int buf = nf & 1;
     if (nf >= 2 && !mbar_wait(freeb + buf, (uint32_t)((nf >> 1) - 1) & 1u)) {
@@ -446,19 +491,25 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int n0 = nt * 8 + 2 * (lane & 3);
-      mine[n0 * 16 + g] = acc[nt][0];
-      mine[(n0 + 1) * 16 + g] = acc[nt][1];
-      mine[n0 * 16 + g + 8] = acc[nt][2];
-      mine[(n0 + 1) * 16 + g + 8] = acc[nt][3];
-      acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+      mine[n0 * 16 + g] = acc[nt][0][0] + acc[nt][1][0];
+      mine[(n0 + 1) * 16 + g] = acc[nt][0][1] + acc[nt][1][1];
+      mine[n0 * 16 + g + 8] = acc[nt][0][2] + acc[nt][1][2];
+      mine[(n0 + 1) * 16 + g + 8] = acc[nt][0][3] + acc[nt][1][3];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) acc[nt][h][0] = acc[nt][h][1] = acc[nt][h][2] = acc[nt][h][3] = 0.f;
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(done + buf);
+    cur.advance(a, len);
   }
+#ifdef ST_PROF
+  if (a.prof && warp == 0 && lane == 0)
+    for (int i = 0; i < 8; ++i) a.prof[blockIdx.x * 64 + 56 + i] = ck[i];
+#endif
 }
 
 struct Plan {
-  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, groups, ahead;
+  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, groups, ahead, slow_s0, slow_ns;
   size_t smem;
   long long U;
   int CPT, T, NG, nprob;
@@ -496,18 +547,20 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   // L2 prefetch running ahead of them were slower, the prefetch instruction stalls its issuer once the queue is deep).
   // Tunables (environment, read once): STATETREE_GEMV_CTAS_PER_SM, STATETREE_GEMV_SMEM_KB, STATETREE_GEMV_STAGES,
   // STATETREE_GEMV_AHEAD (units of L2 prefetch ahead of the ring, 0 = off).
-  static int slots_per_sm = 0, budget_kb = 0, ahead = 0, max_stages = 0;
+  static int slots_per_sm = 0, budget_kb = 0, ahead = 0, max_stages = 0, slow_s0 = 0, slow_ns = 0;
   if (slots_per_sm == 0) {
     const char* v;
     slots_per_sm = (v = getenv("STATETREE_GEMV_CTAS_PER_SM")) ? atoi(v) : 2;
     budget_kb = (v = getenv("STATETREE_GEMV_SMEM_KB")) ? atoi(v) : 113;
     ahead = (v = getenv("STATETREE_GEMV_AHEAD")) ? atoi(v) : 0;
     max_stages = (v = getenv("STATETREE_GEMV_STAGES")) ? atoi(v) : 8;
+    slow_s0 = (v = getenv("STATETREE_GEMV_SLOW_S0")) ? atoi(v) : 0;
+    slow_ns = (v = getenv("STATETREE_GEMV_SLOW_NS")) ? atoi(v) : 0;
     if (slots_per_sm < 1) slots_per_sm = 1;
     if (ahead < 0) ahead = 0;
     if (ahead > 32) ahead = 32;
   }
-  p.ahead = ahead;
+  p.ahead = ahead; p.slow_s0 = slow_s0; p.slow_ns = slow_ns;
   int per_sm = slots_per_sm;
   int stages = (int)((budget_kb * 1024 - (long long)fixed) / p.stage_bytes);
   if (stages < 2) {
@@ -543,7 +596,7 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE);
   a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages;
   a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows; a.xwhole = p.xwhole; a.xw_stride = p.xw_stride;
-  a.xw_bytes = p.xw_bytes; a.ahead = p.ahead;
+  a.xw_bytes = p.xw_bytes; a.ahead = p.ahead; a.slow_s0 = p.slow_s0; a.slow_ns = p.slow_ns;
   const long long need = (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
   ST_REQUIRE(p.maxcover == 1 || (a.ws && ws_bytes >= need), "%s: workspace of %lld bytes needed, %lld given", who, need,
              ws_bytes);

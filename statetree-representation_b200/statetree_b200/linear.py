@@ -6,13 +6,15 @@ fused decode GEMV, larger batches the fused decode + tcgen05 GEMM.  Workspaces (
 semaphores) are kept per (device, stream) because callers may run layers on side streams concurrently (the reason
 given at statetree/linear.py:457-466); they are sized once per shape, so steady-state calls allocate only the output.
 """
+import os
+
 import torch
 import torch.nn as nn
 
 from . import format as F
 from .ops import ext
 
-GEMV_MAX = 32                      # rows up to which the GEMV kernel runs
+GEMV_MAX = int(os.environ.get("STATETREE_GEMV_MAX", "32"))     # rows up to which the GEMV kernel runs (<= 32)
 _STATES = {}
 
 
