@@ -219,6 +219,187 @@ def attention_workload(args):
                       "device_status": ops.device_status(), "table": table}))
 
 
+def moe_workload(args):
+    """Routed-expert block of the Qwen3-30B-A3B shape (128 experts, top-8, hidden 2048, expert intermediate 768; all
+    expert weights tree-stored): gate_up product -> SwiGLU gate -> down product -> routing-weighted sum for T tokens,
+    uniform random routing, one CUDA graph per batch size, L2 flushed between replays.  Effective GB/s counts the
+    records of the distinct (expert, projection) pairs actually read."""
+    import torch
+
+    import statetree_b200 as S
+    from statetree_b200 import ops
+    from statetree_b200.experts import TreeExperts
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    E, K, H, I = 128, 8, 2048, 768
+    gen = torch.Generator(device=dev).manual_seed(0)
+    base13 = [S.TreeLinear.from_weight((torch.randn(2 * I, H, device=dev, generator=gen) * 0.02).to(torch.bfloat16),
+                                       verify=(i == 0)) for i in range(4)]
+    base2 = [S.TreeLinear.from_weight((torch.randn(H, I, device=dev, generator=gen) * 0.02).to(torch.bfloat16),
+                                      verify=(i == 0)) for i in range(4)]
+
+    def clone(tl):
+        c = S.TreeLinear(tl.in_features, tl.out_features, device="meta", n_esc=tl.esc_rows.numel())
+        c._buffers["tree"] = tl.tree.clone()
+        for k in ("esc_rows", "esc_cols", "esc_bits"):
+            c._buffers[k] = tl._buffers[k]
+        return c
+
+    te = TreeExperts([clone(base13[e % 4]) for e in range(E)], [clone(base2[e % 4]) for e in range(E)])
+    te.tables()
+    rec13, rec2 = base13[0].record_bytes(), base2[0].record_bytes()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    hbm, _, which = peaks()
+    table = []
+    for T in [int(b) for b in args.moe_batch.split(",")]:
+        x = torch.randn(T, H, device=dev, generator=gen).to(torch.bfloat16)
+        w, ids = torch.softmax(torch.randn(T, E, device=dev, generator=gen), -1).topk(K, -1)
+        w = (w / w.sum(-1, keepdim=True)).float().contiguous()
+        ids = ids.to(torch.int32).contiguous()
+        side = torch.cuda.Stream(dev)
+        torch.cuda.synchronize()                                   # inputs were produced on the default stream
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                out = te(x, ids, w)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = te(x, ids, w)
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(max(5, args.steps)):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        us = ts[len(ts) // 2]
+        # BF16 control: the same block with dense BF16 expert weights gathered per pair (batched matmul)
+        distinct = int(ids.unique().numel())
+        nbytes = distinct * (rec13 + rec2) + T * H * 2 * 2 + T * K * (2 * I + I + H) * 2
+        ref = None
+        if T * K <= 64:
+            W13 = torch.stack([m.dequantize() for m in te.w13])
+            W2 = torch.stack([m.dequantize() for m in te.w2])
+            xe = x.repeat_interleave(K, 0).unsqueeze(2)
+
+            def bf16_block():
+                gu = torch.bmm(W13[ids.view(-1).long()], xe).squeeze(2)
+                act = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+                y = torch.bmm(W2[ids.view(-1).long()], act.unsqueeze(2)).squeeze(2)
+                return (y.view(T, K, H).float() * w.unsqueeze(-1)).sum(1)
+
+            ref = bf16_block()
+            err = float((out.float() - ref).norm() / ref.norm())
+            del W13, W2
+        else:
+            err = None
+        table.append({"tokens": T, "pairs": T * K, "distinct_experts": distinct, "us": us, "gbs": nbytes / us / 1e3,
+                      "frac_hbm": nbytes / us / 1e3 / hbm, "rel_err_vs_bf16": err})
+        del graph
+    big = table[0]
+    print(json.dumps({"metric": "MoE routed-expert block over tree-stored experts, effective GB/s (distinct expert records / time)",
+                      "value": big["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(5, args.steps), "warmup": 2,
+                      "ms_per_step": big["us"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"Qwen3-30B-A3B-shaped expert block: {E} experts top-{K}, hidden {H}, "
+                                             f"intermediate {I}; headline row: {big['tokens']} token(s)",
+                                 "l2": "flushed between replays"},
+                      "roofline": {"bound": "hbm", "achieved": big["gbs"], "peak": hbm, "unit": "GB/s",
+                                   "frac": big["gbs"] / hbm, "traffic": None, "peak_source": f"of {which}"},
+                      "device_status": ops.device_status(), "table": table}))
+
+
+def decode_workload(args):
+    """Greedy decode with a random-init Qwen3-8B-architecture model (36 layers, hidden 4096, 32 q / 8 kv heads,
+    head_dim 128, SwiGLU 12288, vocab 151936; weights N(0, 0.02)): uniform-random prompt tokens fed one step at a time,
+    then greedy tokens, every step one CUDA-graph replay.  Compressed weights + compressed KV against the BF16 control
+    built from the same seeds (dense weights, dense KV, FlashAttention).  Tensor-parallel when launched with N ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from statetree_b200 import ops
+    from statetree_b200.decoder import DecoderConfig, TreeDecoder
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = DecoderConfig(layers=args.layers)
+    B, P, Gn = args.batch, args.prompt, args.gen
+    prompt = torch.randint(0, cfg.vocab, (B, P), generator=torch.Generator().manual_seed(1)).to(dev)
+    res = {}
+    for name, compressed in (("statetree", True), ("bf16", False)):
+        m = TreeDecoder(cfg, dev, B, P + Gn + 16, compressed=compressed, seed=0, rank=rank, world=world)
+        wbytes = m.weight_bytes()
+        m.capture()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        preds = []
+        toks = m.run(prompt, Gn, collect=preds)                   # warm pass (also the token streams that are compared)
+        m.reset()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        for t in range(P):
+            m.tokens.copy_(prompt[:, t])
+            m.graph.replay()
+        e0.record()
+        m.run(prompt[:, :0], Gn)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / Gn
+        if world > 1:
+            t_ = torch.tensor([ms], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            ms = float(t_.item())
+        res[name] = {"ms_per_step": ms, "tok_s": B / (ms * 1e-3), "tokens": toks.cpu(), "weight_bytes_per_rank": wbytes,
+                     "teacher_forced": torch.stack(preds, 1).cpu()}
+        if compressed:
+            m.cache.check()
+        del m
+        torch.cuda.empty_cache()
+    st, bf = res["statetree"], res["bf16"]
+    same = (st["tokens"] == bf["tokens"])
+    first_div = [int((~same[b]).nonzero()[0]) if (~same[b]).any() else Gn for b in range(B)]
+    tf_same = float((st["teacher_forced"] == bf["teacher_forced"]).float().mean())
+    status = ops.device_status()
+    if rank == 0:
+        hbm, _, which = peaks()
+        eff = st["weight_bytes_per_rank"] / (st["ms_per_step"] * 1e-3) / 1e9
+        print(json.dumps({"metric": "greedy decode tokens/s, random-init Qwen3-8B architecture, compressed weights + KV",
+                          "value": st["tok_s"], "unit": "tokens/s", "n_gpus": world, "steps": Gn, "warmup": P,
+                          "ms_per_step": st["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"Qwen3-8B-shape decode, {args.layers} layers, batch {B}, {P} prompt + {Gn} "
+                                                 "greedy tokens", "parallelism": "single GPU" if world == 1 else f"tp{world}"},
+                          "bf16_control": {"tok_s": bf["tok_s"], "ms_per_step": bf["ms_per_step"],
+                                           "what": "same seeds: dense BF16 weights (cuBLAS), dense KV, FlashAttention-2"},
+                          "speedup_vs_bf16": st["tok_s"] / bf["tok_s"],
+                          "agreement_with_bf16": {"teacher_forced_top1": tf_same,
+                                                  "greedy_fraction_equal": float(same.float().mean()),
+                                                  "greedy_first_divergence_step_per_sequence": first_div,
+                                                  "note": "random-init weights give nearly flat logits: a different fp32 "
+                                                          "summation order flips near-ties, after which greedy streams differ"},
+                          "roofline": {"bound": "hbm", "achieved": eff, "peak": hbm, "unit": "GB/s", "frac": eff / hbm,
+                                       "traffic": None, "peak_source": f"of {which}",
+                                       "note": "weight records per rank / step time (KV and activations not counted)"},
+                          "device_status": status}))
+    if world > 1:
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -228,14 +409,20 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="linear", choices=["linear", "attn"],
+    ap.add_argument("--moe-batch", default="1,8,32,64")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--gen", type=int, default=512)
+    ap.add_argument("--workload", default="linear", choices=["linear", "attn", "moe", "decode"],
                     help="linear: the Qwen3-8B linear sweep (default, the headline); attn: compressed-KV decode attention")
     ap.add_argument("--ctx", default="1024,4096,16384")
     ap.add_argument("--attn-batch", default="1,8,32,64")
     args = ap.parse_args()
-    if args.workload == "attn":
+    if args.workload == "decode":
+        decode_workload(args)
+        return
+    if args.workload in ("attn", "moe"):
         if int(os.environ.get("RANK", "0")) == 0:
-            attention_workload(args)
+            (attention_workload if args.workload == "attn" else moe_workload)(args)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

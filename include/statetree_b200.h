@@ -97,6 +97,17 @@ int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int6
  * statetree/csrc/kernels.cu:1327-1333). */
 int st_silu_mul(const void* gu, void* act, int64_t S, int64_t I, void* stream);
 
+/* ---- glue kernels of the decode step (no counterpart in the reference, which leaves them to PyTorch) --------------- */
+/* x[r, :] += delta[r, :] (delta may be NULL), out[r, :] = RMSNorm(x[r, :]) * w; BF16, fp32 arithmetic. */
+int st_add_rmsnorm(void* x, const void* delta, const void* w, void* out, int64_t rows, int64_t cols, double eps,
+                   void* stream);
+/* Per-head RMSNorm (weights wq / wk [128]) + rotary embedding (interleaved pairs; cos_t / sin_t float [max_pos, 64];
+ * the position is the device scalar pos[0]) of the q and k heads of fused qkv rows [B, (hq + 2 hkv) * 128] with row
+ * stride row_stride (elements) -> q_out [B, hq, 128], k_out [B, hkv, 128]. */
+int st_qk_norm_rope(const void* qkv, int64_t row_stride, const void* wq, const void* wk, const float* cos_t,
+                    const float* sin_t, const int64_t* pos, int64_t max_pos, void* q_out, void* k_out, int64_t B,
+                    int64_t hq, int64_t hkv, double eps, void* stream);
+
 /* ---- KV pages --------------------------------------------------------------------------------------------------- */
 /* 6400 * H.  Replaces `_kv.page_bytes` (statetree/csrc/kvcache.cu:295). */
 int64_t st_kv_page_bytes(int64_t H);

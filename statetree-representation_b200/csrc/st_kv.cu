@@ -351,8 +351,10 @@ __global__ void __launch_bounds__(ATT_NW * 32) kv_attn_kernel(const AttnArgs a) 
     ps += __shfl_xor_sync(FULL, ps, 2);
     l = l * al + ps;
     m = mn;
+    if (__any_sync(FULL, al != 1.f)) {                             // after the first pages the maxima rarely move
 #pragma unroll
-    for (int n = 0; n < 16; ++n) { o[n][0] *= al; o[n][1] *= al; }
+      for (int n = 0; n < 16; ++n) { o[n][0] *= al; o[n][1] *= al; }
+    }
     // P = high BF16 part + BF16 residual
     const __nv_bfloat16 h0 = __float2bfloat16_rn(e0), h1 = __float2bfloat16_rn(e1), h2 = __float2bfloat16_rn(e2),
                         h3 = __float2bfloat16_rn(e3);

@@ -1,0 +1,207 @@
+"""A minimal Qwen3-architecture decoder over the tree-stored layers, for decode-throughput measurement with random
+weights: RMSNorm, fused q/k/v and gate/up projections, per-head q/k RMSNorm, RoPE, grouped-query attention over the
+compressed KV pages, SwiGLU, untied lm_head, greedy sampling.  One decode step is captured in a CUDA graph and
+replayed (the measurement method of the reference's statetree/bench.py:74-133 DecodeRunner).  `compressed=False`
+builds the BF16 control from the same seeds: dense weights, a dense BF16 KV cache and FlashAttention.
+
+Tensor parallelism (one process per GPU): q/k/v and gate/up are split by rows (heads / intermediate columns), o and
+down by input columns with an all-reduce of their outputs, the lm_head by vocabulary rows with an all-gather of the
+logits; embeddings and norms are replicated.  Every rank draws the full tensors from the same seeds and keeps its slice,
+so a tensor-parallel run computes the same function as the single-GPU one.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as Fn
+
+from .kvcache import StateTreeKVCache
+from .linear import TreeLinear
+from .ops import ext
+
+
+def _flash():
+    from flash_attn import flash_attn_with_kvcache
+    return flash_attn_with_kvcache
+
+
+@dataclass
+class DecoderConfig:
+    layers: int = 36
+    hidden: int = 4096
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    inter: int = 12288
+    vocab: int = 151936
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+
+
+class _Dense:
+    """BF16 control for a TreeLinear: same call, dense weight"""
+
+    def __init__(self, W):
+        self.W = W
+        self.out_features, self.in_features = W.shape
+
+    def __call__(self, x):
+        return Fn.linear(x, self.W)
+
+    def record_bytes(self):
+        return self.W.numel() * 2
+
+
+class TreeDecoder:
+    def __init__(self, cfg, device, batch, max_len, compressed=True, seed=0, rank=0, world=1, group=None):
+        self.cfg, self.dev, self.B, self.rank, self.world, self.group = cfg, torch.device(device), batch, rank, world, group
+        self.compressed = compressed
+        c = cfg
+        assert c.heads % world == 0 and c.kv_heads % world == 0 and c.inter % (64 * world) == 0 and c.vocab % (16 * world) == 0
+        self.hq, self.hkv = c.heads // world, c.kv_heads // world
+        gen = torch.Generator(device=self.dev)
+        self._tid = 0
+
+        def draw(rows, cols):
+            gen.manual_seed(seed * 100003 + self._tid)
+            self._tid += 1
+            return (torch.randn(rows, cols, device=self.dev, generator=gen) * 0.02).to(torch.bfloat16)
+
+        def make(W):
+            return TreeLinear.from_weight(W.contiguous(), verify=False) if compressed else _Dense(W.contiguous())
+
+        def rows(W, n_parts=1):
+            per = W.shape[0] // world
+            return W[rank * per:(rank + 1) * per]
+
+        D = c.head_dim
+        self.embed = make(draw(c.vocab, c.hidden))
+        self.blocks = []
+        for _ in range(c.layers):
+            q, k, v = draw(c.heads * D, c.hidden), draw(c.kv_heads * D, c.hidden), draw(c.kv_heads * D, c.hidden)
+            qkv = make(torch.cat([rows(q), rows(k), rows(v)]))
+            del q, k, v
+            o = draw(c.hidden, c.heads * D)
+            per = o.shape[1] // world
+            o = make(o[:, rank * per:(rank + 1) * per])
+            g, u = draw(c.inter, c.hidden), draw(c.inter, c.hidden)
+            gu = make(torch.cat([rows(g), rows(u)]))
+            del g, u
+            d = draw(c.hidden, c.inter)
+            per = d.shape[1] // world
+            d = make(d[:, rank * per:(rank + 1) * per])
+            self.blocks.append((qkv, o, gu, d))
+        self.lm_head = make(rows(draw(c.vocab, c.hidden)))
+        ones = torch.ones(c.hidden, dtype=torch.bfloat16, device=self.dev)
+        self.norm_w, self.head_norm_w = ones, torch.ones(D, dtype=torch.bfloat16, device=self.dev)
+        # rotary tables
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, D, 2, device=self.dev, dtype=torch.float32) / D))
+        ang = torch.arange(max_len, device=self.dev, dtype=torch.float32)[:, None] * inv[None]
+        self.cos, self.sin = ang.cos().contiguous(), ang.sin().contiguous()      # float32 [max_len, 64]
+        self.max_len = max_len
+        self.pos_buf = torch.zeros(1, dtype=torch.long, device=self.dev)
+        self.h_buf = torch.empty(batch, c.hidden, dtype=torch.bfloat16, device=self.dev)
+        self.q_buf = torch.empty(batch, self.hq, D, dtype=torch.bfloat16, device=self.dev)
+        self.k_buf = torch.empty(batch, self.hkv, D, dtype=torch.bfloat16, device=self.dev)
+        self.tokens = torch.zeros(batch, dtype=torch.long, device=self.dev)
+        if compressed:
+            self.cache = StateTreeKVCache(c.layers, batch, max_len, self.hkv, self.dev, pool_blocks=1 << 14)
+        else:
+            self.kc = [torch.zeros(batch, max_len, self.hkv, D, dtype=torch.bfloat16, device=self.dev) for _ in range(c.layers)]
+            self.vc = [torch.zeros_like(k) for k in self.kc]
+            self.lens = torch.zeros(batch, dtype=torch.int32, device=self.dev)
+        self.graph = None
+
+    def weight_bytes(self):
+        n = self.lm_head.record_bytes()                          # (the embedding table is read B rows at a time)
+        for blk in self.blocks:
+            n += sum(m.record_bytes() for m in blk)
+        return n
+
+    def _allreduce(self, y):
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
+
+    def _step(self):
+        """one decode step for self.tokens at position self.pos; about ten launches per layer"""
+        c, B, D = self.cfg, self.B, self.cfg.head_dim
+        E = ext()
+        x = self.embed.rows(self.tokens) if self.compressed else self.embed.W[self.tokens]
+        scale = 1.0 / math.sqrt(D)
+        h, qb, kb = self.h_buf, self.q_buf, self.k_buf
+        slots = self.cache.begin_step(B) if self.compressed else None
+        delta = None
+        for li, (qkv, o, gu, d) in enumerate(self.blocks):
+            E.add_rmsnorm(x, delta, self.norm_w, h, c.eps)
+            y = qkv(h)
+            E.qk_norm_rope(y, self.head_norm_w, self.head_norm_w, self.cos, self.sin, self.pos_buf, qb, kb, c.eps)
+            v = y[:, (self.hq + self.hkv) * D:].view(B, self.hkv, D)
+            if self.compressed:
+                layer = self.cache.layers[li]
+                layer.append(kb, v, slots)
+                att = layer.attention(qb, self.cache.bt32[:B], self.cache.lens[:B], scale, self.splits, None, 4)
+            else:
+                att = _flash()(qb.view(B, 1, self.hq, D), self.kc[li], self.vc[li], k=kb.view(B, 1, self.hkv, D),
+                               v=v.unsqueeze(1), cache_seqlens=self.lens, softmax_scale=scale)
+            delta = self._allreduce(o(att.reshape(B, self.hq * D)))
+            E.add_rmsnorm(x, delta, self.norm_w, h, c.eps)
+            y = gu(h)
+            act = torch.empty(B, y.shape[1] // 2, dtype=torch.bfloat16, device=self.dev)
+            E.silu_mul(y, act)
+            delta = self._allreduce(d(act))
+        E.add_rmsnorm(x, delta, self.norm_w, h, c.eps)
+        logits = self.lm_head(h)
+        if self.world > 1:
+            parts = [torch.empty_like(logits) for _ in range(self.world)]
+            dist.all_gather(parts, logits, group=self.group)
+            logits = torch.cat(parts, 1)
+        if self.compressed:
+            self.cache.end_step()
+        else:
+            self.lens += 1
+        self.pos_buf += 1
+        return logits
+
+    def capture(self):
+        from .kvcache import decode_splits
+        self.splits = decode_splits(self.B, self.hkv, (self.max_len + 15) // 16) if self.compressed else 1
+        self.next_tok = torch.zeros(self.B, dtype=torch.long, device=self.dev)
+        side = torch.cuda.Stream(self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))      # weights and buffers were written on that stream
+        with torch.cuda.stream(side):
+            for _ in range(2):                                   # warm-up steps (also sizes every workspace)
+                self.next_tok.copy_(self._step().argmax(-1))
+        side.synchronize()
+        self.reset()
+        torch.cuda.synchronize(self.dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=side):
+            logits = self._step()
+            self.next_tok.copy_(logits.argmax(-1))
+        self.logits = logits
+        self.reset()
+        torch.cuda.synchronize(self.dev)
+
+    def reset(self):
+        self.pos_buf.zero_()
+        if self.compressed:
+            self.cache.reset()
+        else:
+            self.lens.zero_()
+
+    def run(self, prompt, n_new, collect=None):
+        """prompt [B, P] token ids (teacher-forced one step at a time), then n_new greedy tokens -> [B, n_new].
+        collect (optional list): receives the model's prediction after every prompt step (teacher-forced top-1)."""
+        out = []
+        for t in range(prompt.shape[1]):
+            self.tokens.copy_(prompt[:, t])
+            self.graph.replay()
+            if collect is not None:
+                collect.append(self.next_tok.clone())
+        for _ in range(n_new):
+            self.tokens.copy_(self.next_tok)
+            out.append(self.next_tok.clone())
+            self.graph.replay()
+        return torch.stack(out, 1)

@@ -63,7 +63,7 @@ def moe_align(ids, E, bs=8):
     ids = ids.reshape(-1).to(torch.int64)
     S, dev = ids.numel(), ids.device
     nblk = S // bs + min(S, E) + 1
-    per = torch.bincount(ids, minlength=E)[:E]
+    per = torch.zeros(E, dtype=torch.int64, device=dev).scatter_add_(0, ids.clamp(0, E - 1), torch.ones_like(ids))   # no sync
     room = (per + bs - 1) // bs * bs                     # slots reserved per expert
     end = room.cumsum(0)
     begin = end - room

@@ -106,6 +106,16 @@ class StateTreeKVCache:
             self.lens[:B] = (self.cum + T).to(torch.int32)
         return slots
 
+    def begin_step(self, B):
+        """decode step (one token per sequence): the slots every layer appends at, computed once; lens counts the new
+        token.  Graph-safe (positions come from the GPU-side count)."""
+        slots = self.bt64[:B].gather(1, (self.cum // PAGE).expand(B, 1)).view(B) * PAGE + self.cum % PAGE
+        self.lens[:B] = (self.cum + 1).to(torch.int32)
+        return slots
+
+    def end_step(self):
+        self.cum += 1
+
     def attention(self, layer_idx, q, scale, splits=None):
         """decode step: q [B, Hq, 128] against everything stored in the layer (including this step's token)"""
         B = q.shape[0]

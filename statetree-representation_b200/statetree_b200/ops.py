@@ -33,6 +33,8 @@ _SIGNATURES = {
                                  _i64, _vp, _vp]),
     "st_wsum": (_int, [_vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
     "st_silu_mul": (_int, [_vp, _vp, _i64, _i64, _vp]),
+    "st_add_rmsnorm": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _dbl, _vp]),
+    "st_qk_norm_rope": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _dbl, _vp]),
     "st_kv_page_bytes": (_i64, [_i64]),
     "st_kv_append": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _int, _vp]),
     "st_kv_dequant": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
@@ -172,6 +174,20 @@ class _Weights:
         with _ctx(Y):
             _check(lib().st_wsum(_ptr(Y), _ptr(W), 1 if W.dtype == torch.bfloat16 else 0, _ptr(out), T, K, Y.shape[1],
                                  _stream(Y)))
+
+    @staticmethod
+    def add_rmsnorm(x, delta, w, out, eps):
+        """x += delta (in place, delta may be None); out = RMSNorm(x) * w"""
+        rows, cols = x.shape
+        with _ctx(x):
+            _check(lib().st_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(w), _ptr(out), rows, cols, float(eps), _stream(x)))
+
+    @staticmethod
+    def qk_norm_rope(qkv, wq, wk, cos_t, sin_t, pos, q_out, k_out, eps):
+        B, hq, hkv = q_out.shape[0], q_out.shape[1], k_out.shape[1]
+        with _ctx(qkv):
+            _check(lib().st_qk_norm_rope(_ptr(qkv), qkv.stride(0), _ptr(wq), _ptr(wk), _ptr(cos_t), _ptr(sin_t), _ptr(pos),
+                                         cos_t.shape[0], _ptr(q_out), _ptr(k_out), B, hq, hkv, float(eps), _stream(qkv)))
 
     @staticmethod
     def silu_mul(gu, act):
