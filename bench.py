@@ -409,6 +409,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-fused", action="store_true", help="skip the extra pass with fused q/k/v and gate/up trees")
     ap.add_argument("--moe-batch", default="1,8,32,64")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=512)
@@ -578,6 +579,52 @@ def main():
         e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+
+    # ---- the same step with q/k/v and gate/up stored as fused trees (how the reference's model conversion stores
+    # them, statetree/model.py DEFAULT_FUSE, and how its per-layer-kind GEMV table is measured): 4 launches per layer
+    fused = None
+    if world == 1 and use_gemv and not args.no_fused:
+        from statetree_b200 import format as F
+
+        def fuse(tls):
+            M = sum(t.out_features for t in tls)
+            rows, off = [], 0
+            for t in tls:
+                rows.append(t.esc_rows + off)
+                off += t.out_features
+            er, ec, eb_ = torch.cat(rows), torch.cat([t.esc_cols for t in tls]), torch.cat([t.esc_bits for t in tls])
+            return M, F.escape_tables(M, tls[0].in_features, er, ec, eb_)
+
+        Mq, tq = fuse(layers[0][0:3])
+        Mg, tg = fuse(layers[0][4:6])
+        flayers = []
+        for row in layers:
+            flayers.append([(torch.cat([t.tree for t in row[0:3]]), tq, Mq, x), (row[3].tree, row[3]._tables, HIDDEN, x_o),
+                            (torch.cat([t.tree for t in row[4:6]]), tg, Mg, x), (row[6].tree, row[6]._tables, HIDDEN, x_d)])
+        fouts = {m: torch.empty(B, m, dtype=torch.bfloat16, device=dev) for m in (Mq, Mg, HIDDEN)}
+        ws_f = st.get_ws(max(E.gemv_workspace_bytes(m, n, B) for m, n in ((Mq, HIDDEN), (HIDDEN, HIDDEN), (Mg, HIDDEN), (HIDDEN, INTER))))
+        cnt_f = st.get_cnt(Mg // 16)
+
+        def run_fused():
+            for row in flayers:
+                for tree, (eo, el, eb), m, xin in row:
+                    E.gemv(tree, eo, eb, el, xin, fouts[m], ws_f, cnt_f)
+
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            run_fused()
+        side.synchronize()
+        fgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fgraph, stream=side):
+            run_fused()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            fgraph.replay()
+        ms_f = timed(fgraph.replay, args.steps)
+        fused = {"what": "q/k/v and gate/up as fused trees (6144x4096, 24576x4096): 4 launches per layer, same bytes",
+                 "ms_per_step": ms_f, "value": step_bytes / (ms_f * 1e-3) / 1e9, "unit": "GB/s",
+                 "frac": step_bytes / (ms_f * 1e-3) / 1e9 / peaks()[0], "gpu_launches": 4 * args.layers * args.steps}
+        del fgraph, flayers
     status = ops.device_status()
 
     def leave():
@@ -616,6 +663,8 @@ def main():
                     "d2h_bytes_per_step": sum(o.numel() * 2 for o in outs)},
             "gpu_launches": launches * args.steps, "roofline": roof, "device_status": status,
             "bf16_equivalent_gbs": value * 16.0 / 12.125}
+    if fused is not None:
+        line["fused_qkv_gate_up"] = fused
     if not args.no_cpu and world == 1:
         val, dt, cores = cpu_reference(2, 1, B)
         line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
