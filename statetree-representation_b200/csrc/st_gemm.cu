@@ -17,6 +17,8 @@
 // releasing its tensor memory.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "../../include/statetree_b200.h"
@@ -37,20 +39,28 @@ struct GemmArgs {
   uint32_t idesc;
 #ifdef ST_PROF
   long long* prof;
+  int diag;                                 // development only: 1 = reuse the first activation tiles, 2 = issue no MMA
 #endif
 };
 
 #ifdef ST_PROF
 __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define GPROF(slot) do { if (a.prof && (slot) < 64) a.prof[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
+#define GCK(n) do { const long long t_ = clock64(); gck[n] += t_ - gckl; gckl = t_; } while (0)
 long long* g_gemm_prof = nullptr;
+int g_gemm_diag = 0;
 #else
 #define GPROF(slot) do {} while (0)
+#define GCK(n) do {} while (0)
 #endif
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                :: "r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               :: "r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar)) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_addr(slot)), "r"(cols) : "memory");
@@ -107,9 +117,15 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
   return v;
 }
 
-constexpr int NDW = 2 * NDEC;                // decode warps: two k-tiles are decoded at a time
+constexpr int DG = 2;                        // decode groups: this many k-tiles are decoded at a time
+constexpr int NDW = DG * NDEC;               // decode warps
 constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;     // producer (records), producer (activations), MMA
 constexpr int GEMM_THREADS = (NDW + 3) * 32;
+#ifdef ST_GEMM_SPINWAIT
+#define GW mbar_wait_spin
+#else
+#define GW mbar_wait
+#endif
 constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of one k-tile
 
 // Two rings.  The RAW ring (R slots of eight records) faces HBM: its depth sets the bytes in flight.  The TILE ring
@@ -119,7 +135,8 @@ constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of on
 // the rank).  After its main loop every CTA parks its fp32 accumulator tile in its own shared memory; after a cluster
 // barrier CTA j adds the KS tiles for its share of the token columns through distributed shared memory, in rank
 // order (bit-identical from run to run), and stores BF16.  No partial sums travel through global memory.
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap,
+                                                                const __grid_constant__ CUtensorMap wmap) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int NT = a.NT, S = a.stages, R = a.rstages;
@@ -160,20 +177,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
   if (tid == 0) GPROF(1);
 
   if (warp == W_RAW) {
-    // ---------------------------------------------------------------- record producer: lane w < 8 copies record w
-    // (row tile rb * 8 + w) of every k-tile into the raw ring
-    if (lane < NDEC) {
-      const uint64_t pol = policy_evict_first();
-      const uint8_t* myrec = a.tree + ((size_t)(rb * 8 + lane) * a.NG + k0) * REC;
+    // ---------------------------------------------------------------- record producer: one tiled TMA load per k-tile
+    // fetches the eight records (row tiles rb * 8 .. + 7 of column group k0 + i) through a 3-D view of the tree
+    // [row tile][column group][194 x u64]; eight separate 1552-byte bulk copies per k-tile cost ~1 us of issue time
+    if (lane == 0) {
       for (int i = 0; i < nk; ++i) {
         const int r = i % R, k = i / R;
-        if (k > 0 && !mbar_wait(rempty + r, (uint32_t)(k - 1) & 1u)) {
-          if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
-          break;
-        }
-        if (lane == 0) mbar_expect_tx(rfull + r, (uint32_t)RAW_SLOT);
-        __syncwarp(0xFFu);
-        bulk_g2s(rawring + (size_t)r * RAW_SLOT + lane * REC, myrec + (size_t)i * REC, REC, rfull + r, pol);
+        if (k > 0 && !GW(rempty + r, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
+        mbar_expect_tx(rfull + r, (uint32_t)RAW_SLOT);
+        tma_load_3d(rawring + (size_t)r * RAW_SLOT, &wmap, 0, k0 + i, rb * 8, rfull + r);
       }
     }
   } else if (warp == W_X) {
@@ -181,7 +193,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     if (lane == 0) {
       for (int i = 0; i < nk; ++i) {
         const int s = i % S, k = i / S;
-        if (k > 0 && !mbar_wait(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
+        if (k > 0 && !GW(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
+#ifdef ST_PROF
+        if ((a.diag & 1) && i >= S) { mbar_arrive(ready + s); continue; }
+#endif
         mbar_expect_tx(ready + s, (uint32_t)XT);
         tma_load_2d(smem + (size_t)s * STAGE + A_TILE, &xmap, (k0 + i) * 64, tok0, ready + s);
       }
@@ -191,13 +206,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     if (lane == 0) {
       for (int i = 0; i < nk; ++i) {
         const int s = i % S, k = i / S;
-        if (!mbar_wait(ready + s, (uint32_t)k & 1u)) {
+        if (!GW(ready + s, (uint32_t)k & 1u)) {
           atomicExch(a.status, ERR_WAIT_MMA);
           break;
         }
         tc_fence_after();
         const uint32_t sa = smem_addr(smem + (size_t)s * STAGE);
         const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TILE);
+#ifdef ST_PROF
+        if (!(a.diag & 2))
+#endif
 #pragma unroll
         for (int j = 0; j < 4; ++j) tc_mma(tmem, da + 2 * j, db + 2 * j, a.idesc, (i | j) ? 1u : 0u);
         tc_commit(empty + s);
@@ -207,14 +225,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     }
   } else {
     // ---------------------------------------------------------------- decode warps: group g = warp / 8 takes the
-    // k-tiles i = g, g + 2, ...; warp r of a group decodes record r (rows 16 r .. 16 r + 15 of the block)
+    // k-tiles i = g, g + DG, ...; warp r of a group decodes record r (rows 16 r .. 16 r + 15 of the block)
     const int grp = warp / NDEC, rec = warp % NDEC;
     const size_t rbase = (size_t)(rb * 8 + rec) * a.NG + k0;
     // escape-list offsets of this warp's records, 32 k-tiles at a time (lane l holds the offsets of k-tile base + l),
     // so no global load sits between two k-tiles
     int eo_base = -1, eo_lo = 0, eo_hi = 0;
-    for (int i = grp; i < nk; i += 2) {
-      const int s = i % S, k = i / S, r = i % R;
+#ifdef ST_PROF
+    long long gck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gckl = clock64();
+#endif
+    int s = grp % S, k = grp / S, r = grp % R, rk = grp / R;          // tile stage / use count, record slot / use count
+    for (int i = grp; i < nk; i += DG) {
+      GCK(0);
       if (eo_base < 0 || i - eo_base >= 32) {
         eo_base = i;
         const int j = i + lane;
@@ -222,11 +244,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
         eo_hi = j < nk ? __ldg(a.eo + rbase + j + 1) : 0;
       }
       const int lo = __shfl_sync(FULL, eo_lo, i - eo_base), hi = __shfl_sync(FULL, eo_hi, i - eo_base);
-      if (!mbar_wait(rfull + r, (uint32_t)(i / R) & 1u)) {
+      if (!GW(rfull + r, (uint32_t)rk & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
         break;
       }
-      if (tid == 0) GPROF(8 + i + 1);                             // (odd slots: records of k-tile i seen)
+      GCK(1);                                                     // wait for the records
       const RecRegs rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + rec * REC, lane);
       __syncwarp();
       if (lane == 0) mbar_arrive(rempty + r);                     // the slot can be refilled while we decode
@@ -237,10 +259,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
         const uint32_t mine = (lane < n) ? __ldg(a.el + base + lane) : 0u;
         for (int e = 0; e < n; ++e) patch_entry(A, __shfl_sync(FULL, mine, e), lane);
       }
-      if (k > 0 && !mbar_wait(empty + s, (uint32_t)(k - 1) & 1u)) {   // the MMAs of the stage's last use are done
+#ifdef ST_PROF
+      if (A[0][0] == 0x12345u && A[3][3] == 0x54321u) gck[7]++;
+#endif
+      GCK(2);                                                     // load + decode + escapes
+      if (k > 0 && !GW(empty + s, (uint32_t)(k - 1) & 1u)) {   // the MMAs of the stage's last use are done
         if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
         break;
       }
+      GCK(3);                                                     // wait for the tile stage
       uint8_t* st = smem + (size_t)s * STAGE;
       // lane l addresses row (l & 7) of matrix (l >> 3): matrices = (rows 0-7 | 8-15) x (16-byte chunk 2q | 2q+1)
       const int mrow = rec * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
@@ -252,17 +279,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(ready + s);
-      if (tid == 0) GPROF(8 + i);
+      s += DG; while (s >= S) { s -= S; ++k; }
+      r += DG; while (r >= R) { r -= R; ++rk; }
+      GCK(4);                                                     // stmatrix + fence + arrive
     }
+#ifdef ST_PROF
+    if (a.prof && tid == 0) for (int q = 0; q < 5; ++q) a.prof[blockIdx.x * 64 + 8 + q] = gck[q];
+#endif
     // ---------------------------------------------------------------- epilogue 1: accumulator -> own shared memory
-    const bool acc_ok = mbar_wait(accbar, 0u);
+    const bool acc_ok = GW(accbar, 0u);
     if (!acc_ok && lane == 0) atomicExch(a.status, ERR_WAIT_ACC);
     if (tid == 0) GPROF(2);
     tc_fence_after();
     float* stg = reinterpret_cast<float*>(smem);                 // [NT][128] fp32, over the (now idle) ring
-    const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column quarter
+    const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column quarter (warps 0..15)
     const int cper = NT / 4;
-    for (int c0 = cg * cper; c0 < (cg + 1) * cper; c0 += 32) {
+    for (int c0 = cg * cper; warp < 16 && c0 < (cg + 1) * cper; c0 += 32) {
       uint32_t v[32];
       if (cper >= 32) {
         tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
@@ -284,18 +316,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     const int ncol = min(NT, a.B - tok0);
     const int c_lo = (int)((long long)NT * ks / a.KS), c_hi = (int)((long long)NT * (ks + 1) / a.KS);
     const uint32_t mine = smem_addr(smem);
-    for (int c = c_lo + warp; c < c_hi && c < ncol; c += NDW) {
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int p = 0; p < a.KS; ++p) {
-        const float4 v = ld_cluster_f4(map_to_cta(mine + (uint32_t)((c * 128 + 4 * lane) * 4), (uint32_t)p));
-        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    const int c_end = min(c_hi, ncol);
+    // two columns per pass, every partial tile's float4 requested before the first add: distributed-shared-memory
+    // reads have a long latency, so the loads of a pass must all be in flight together
+    for (int c = c_lo + warp; c < c_end; c += 2 * NDW) {
+      const int c2 = c + NDW;
+      float4 v0[8], v1[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        if (p < a.KS) {
+          v0[p] = ld_cluster_f4(map_to_cta(mine + (uint32_t)((c * 128 + 4 * lane) * 4), (uint32_t)p));
+          if (c2 < c_end) v1[p] = ld_cluster_f4(map_to_cta(mine + (uint32_t)((c2 * 128 + 4 * lane) * 4), (uint32_t)p));
+        }
       }
-      const size_t o = (size_t)(tok0 + c) * a.M + rb * 128 + 4 * lane;
-      uint2 packed;
-      packed.x = pack_bf16(sum.x, sum.y);
-      packed.y = pack_bf16(sum.z, sum.w);
-      *reinterpret_cast<uint2*>(a.Y + o) = packed;
-      if (a.Yf) *reinterpret_cast<float4*>(a.Yf + o) = sum;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int cc = h ? c2 : c;
+        if (cc >= c_end) break;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          if (p < a.KS) {
+            const float4 v = h ? v1[p] : v0[p];
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+          }
+        }
+        const size_t o = (size_t)(tok0 + cc) * a.M + rb * 128 + 4 * lane;
+        uint2 packed;
+        packed.x = pack_bf16(sum.x, sum.y);
+        packed.y = pack_bf16(sum.z, sum.w);
+        *reinterpret_cast<uint2*>(a.Y + o) = packed;
+        if (a.Yf) *reinterpret_cast<float4*>(a.Yf + o) = sum;
+      }
     }
   }
   if (tid == 0) GPROF(4);
@@ -336,11 +388,14 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   const long long units = (long long)p.RB * p.TT;
   // split of the k range = cluster size (<= 8): fill the SMs, but every extra split costs an accumulator tile of
   // distributed-shared-memory traffic in the epilogue
+  // one wave only: a second wave pays the start-up and the epilogue again (measured: 288 CTAs in two waves took 72 us
+  // where 96 CTAs in one take ~45), so among the splits that fit the SMs take the one that fills them best
   int best = 1;
   double best_score = -1.0;
   const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 8 ? 8 : NG / 4);
   for (int ks = 1; ks <= ksmax; ++ks) {
     const long long ctas = units * ks;
+    if (ctas > sms && ks > 1) break;
     const long long waves = (ctas + sms - 1) / sms;
     const double score = (double)ctas / (double)(waves * sms) - 0.01 * ks * p.NT / 256.0;
     if (score > best_score + 1e-9) { best_score = score; best = ks; }
@@ -349,6 +404,14 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   // tile stages (decoded weight tile + activation tile): enough to cover the L2 latency of the activation loads;
   // the rest of the shared memory goes to the record ring, which covers the HBM latency
   p.stages = p.NT >= 256 ? 3 : 4;
+  {
+    static int forced = -1;                                      // STATETREE_GEMM_STAGES: tile stages (tuning aid)
+    if (forced < 0) { const char* v = getenv("STATETREE_GEMM_STAGES"); forced = v ? atoi(v) : 0; }
+    if (forced >= 2) {
+      p.stages = forced;
+      while (p.stages > 2 && (size_t)p.stages * (A_TILE + (size_t)p.NT * 128) + 3 * (size_t)RAW_SLOT > 212 * 1024) --p.stages;
+    }
+  }
   p.xstages = 0;
   const size_t tiles = (size_t)p.stages * (A_TILE + (size_t)p.NT * 128);
   p.rstages = (int)((212 * 1024 - tiles) / RAW_SLOT);
@@ -365,6 +428,7 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
 
 #ifdef ST_PROF
 extern "C" void st_debug_set_gemm_prof(long long* buf) { g_gemm_prof = buf; }
+extern "C" void st_debug_set_gemm_diag(int d) { g_gemm_diag = d; }
 #endif
 
 extern "C" int64_t st_gemm_workspace_bytes(int64_t M, int64_t N, int64_t B) {
@@ -393,6 +457,17 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ST_REQUIRE(cr == CUDA_SUCCESS, "st_gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+  CUtensorMap wmap;
+  {
+    const cuuint64_t wd[3] = {194u, (cuuint64_t)(N / 64), (cuuint64_t)(M / 16)};
+    const cuuint64_t wst[2] = {(cuuint64_t)REC, (cuuint64_t)(N / 64) * REC};
+    const cuuint32_t wbox[3] = {194u, 1u, 8u};
+    const cuuint32_t we[3] = {1u, 1u, 1u};
+    const CUresult wr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(tree), wd, wst, wbox, we,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ST_REQUIRE(wr == CUDA_SUCCESS, "st_gemm: cuTensorMapEncodeTiled (tree) failed (%d)", (int)wr);
+  }
   GemmArgs a;
   a.tree = (const uint8_t*)tree; a.eo = eo; a.el = el; a.Y = (uint16_t*)Y; a.Yf = Yf32; a.ws = (float*)ws; a.cnt = cnt;
   a.status = st::status_ptr();
@@ -400,7 +475,7 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   a.M = M; a.N = N; a.B = (int)B; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = p.KS; a.RB = p.RB; a.TT = p.TT;
   a.stages = p.stages; a.rstages = p.rstages; a.xstages = p.xstages; a.bar_off = p.bar_off;
 #ifdef ST_PROF
-  a.prof = g_gemm_prof;
+  a.prof = g_gemm_prof; a.diag = g_gemm_diag;
 #endif
   // instruction descriptor: D fp32, A and B bf16, both K-major, N = NT, M = 128
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -425,6 +500,6 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel, a, xmap), "st_gemm launch")) return e;
+  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel, a, xmap, wmap), "st_gemm launch")) return e;
   return 0;
 }
