@@ -15,8 +15,8 @@
  *   eo, el    escape side table: eo int32 [M/16 * N/64 + 1] offsets per record into el; el uint32 entries
  *             bits << 16 | (record % 8) << 10 | row << 6 | col   (row, col inside the 16 x 64 record)
  *   eb        uint32 [U, 16] per unit of up to 8 consecutive records of one 16-row tile (U = M/16 * ceil(N/512)):
- *             word 0 = escapes in the unit, word 1 = offset of the unit's first entry in el, words 2..15 = the first
- *             14 entries inline (the rest are read from el)
+ *             word 0 = escapes in the unit | (bit r set if record r of the unit has any) << 16, word 1 = offset of the
+ *             unit's first entry in el, words 2..15 = the first 14 entries inline (the rest are read from el)
  *   kv        uint8 [blocks, H, 2, 2, 1600] KV pages; pool uint32 [P, 16]; pool_cnt int32 [2]
  *             (statetree/csrc/kvcache.cu:1-14)
  *   X, Y      BF16 row-major, 16-byte aligned; Y[B, M] = X[B, N] * W[M, N]^T

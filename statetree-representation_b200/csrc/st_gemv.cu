@@ -181,14 +181,17 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
   const int C = gridDim.x;
   const int u0 = (int)((long long)blockIdx.x * a.U / C), u1 = (int)((long long)(blockIdx.x + 1) * a.U / C);
 
-  if (tid == 0) {
-    PROF(0);
-    for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, CW); }
+  if (tid == 0) PROF(0);
+  if (tid < S) {                                               // one thread per ring stage sets its barriers up
+    mbar_init(full + tid, 1);
+    mbar_init(empty + tid, CW);
+    fence_barrier_init();
+  } else if (tid == 32) {
     for (int b = 0; b < 2; ++b) { mbar_init(done + b, NCW); mbar_init(freeb + b, 1); }
     mbar_init(xbar, 1);
     fence_barrier_init();
   }
-  if (tid < XROW / 16) reinterpret_cast<uint4*>(zrow)[tid] = make_uint4(0, 0, 0, 0);
+  if (tid >= 64 && tid < 64 + XROW / 16) reinterpret_cast<uint4*>(zrow)[tid - 64] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   pdl_launch_dependents();                 // the next kernel in the stream may start its own weight prefetch
   if (MODE != MODE_DENSE) pdl_wait();      // expert ids / slot tables come from earlier kernels: read nothing before
@@ -434,16 +437,19 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
             ldmatrix_x4(xa, b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
             ldmatrix_x4(xa + 64, b[nt][4], b[nt][5], b[nt][6], b[nt][7]);
           }
-          const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];   // the escape block
+          const uint32_t sw0 = *reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);            // escape block, word 0
           uint32_t A[4][4];
           decode_frag(load_rec_shared(st + rec * REC, lane), A);
 #ifdef ST_PROF
           if (A[0][0] == 0x12345u && A[3][3] == 0x54321u) ck[7]++;   // keep the decode before the clock read
 #endif
           CK(2);                                              // loads + decode
-          const uint32_t ne = __shfl_sync(FULL, sw, 0);
-          if (ne) {
+          // word 0 = escapes in the unit | (mask of the unit's records that have any) << 16: seven warps in eight
+          // are done after one broadcast load
+          if ((sw0 >> (16 + rec)) & 1u) {
+            const uint32_t ne = sw0 & 0xFFFFu;
             if (ne <= 14u) {                                   // lanes 2..15 hold the inline entries: one vote
+              const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];
               const bool hit = lane >= 2 && lane < 16 && (uint32_t)(lane - 2) < ne && ((sw >> 10) & 7u) == (uint32_t)rec;
               unsigned m = __ballot_sync(FULL, hit);
               while (m) {

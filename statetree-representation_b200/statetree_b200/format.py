@@ -135,7 +135,8 @@ def escape_tables(M, N, esc_rows, esc_cols, esc_bits):
     """Side tables the kernels read (built once per matrix, on the escape lists' device):
       eo int32 [records + 1]   offsets of each record's entries in el (records in memory order: tile * N/64 + group)
       el int32 [max(n, 1)]     entries bits << 16 | (record % 8) << 10 | row << 6 | col, sorted by record
-      eb int32 [units, 16]     per GEMV unit: count, offset into el, the first 14 entries inline
+      eb int32 [units, 16]     per GEMV unit: count | (mask of records with escapes) << 16, offset into el, the first
+                               14 entries inline
     They play the role of the reference's escape_lists / escape_chunks (statetree/format.py:141-154, 189-216)."""
     dev = esc_rows.device
     NG = N // 64
@@ -158,6 +159,9 @@ def escape_tables(M, N, esc_rows, esc_cols, esc_bits):
     if rec.numel():
         unit_s = (tile * cpt + G // 8)[order]
         eb[:, 0] = torch.bincount(unit_s, minlength=nunit)
+        rec_bit = torch.zeros(nunit * 8, dtype=torch.int64, device=dev)
+        rec_bit[unit_s * 8 + (ent_s >> 10 & 7)] = 1                       # which records of the unit have escapes
+        eb[:, 0] |= (rec_bit.view(nunit, 8) << torch.arange(16, 24, device=dev)).sum(1)
         pos = torch.arange(ent_s.numel(), device=dev) - eb[unit_s, 1]
         keep = pos < 14
         eb[unit_s[keep], 2 + pos[keep]] = ent_s[keep]

@@ -65,8 +65,10 @@ def test_side_tables_are_consistent():
             t, c = divmod(u, cpt)
             first = t * NG + c * 8
             last = min(first + 8, (t + 1) * NG)
-            assert blk_u[u, 0] == eo[last] - eo[first] and blk_u[u, 1] == eo[first]
-            n = min(14, int(blk_u[u, 0]))
+            assert (blk_u[u, 0] & 0xFFFF) == eo[last] - eo[first] and blk_u[u, 1] == eo[first]
+            for r in range(first, last):                              # bit 16 + r: record r of the unit has escapes
+                assert bool((blk_u[u, 0] >> (16 + r - first)) & 1) == bool(eo[r + 1] > eo[r])
+            n = min(14, int(blk_u[u, 0] & 0xFFFF))
             assert np.array_equal(blk_u[u, 2:2 + n], el_u[eo[first]:eo[first] + n])
 
 
