@@ -230,9 +230,17 @@ def moe_workload(args):
     from statetree_b200 import ops
     from statetree_b200.experts import TreeExperts
 
+    import torch.distributed as dist
+
+    from statetree_b200.parallel import expert_partition
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     E, K, H, I = 128, 8, 2048, 768
+    e_lo, e_hi, emap = expert_partition(E, rank, world, dev)   # expert parallel: this rank owns experts [e_lo, e_hi)
     gen = torch.Generator(device=dev).manual_seed(0)
     base13 = [S.TreeLinear.from_weight((torch.randn(2 * I, H, device=dev, generator=gen) * 0.02).to(torch.bfloat16),
                                        verify=(i == 0)) for i in range(4)]
@@ -246,8 +254,17 @@ def moe_workload(args):
             c._buffers[k] = tl._buffers[k]
         return c
 
-    te = TreeExperts([clone(base13[e % 4]) for e in range(E)], [clone(base2[e % 4]) for e in range(E)])
+    te = TreeExperts([clone(base13[e % 4]) for e in range(e_lo, e_hi)], [clone(base2[e % 4]) for e in range(e_lo, e_hi)])
     te.tables()
+
+    def block(x, ids, w):
+        """every rank routes all tokens; pairs of other ranks' experts weigh zero; partial outputs are all-reduced"""
+        if world == 1:
+            return te(x, ids, w)
+        out = te(x, ids, w, emap)
+        dist.all_reduce(out)
+        return out
+
     rec13, rec2 = base13[0].record_bytes(), base2[0].record_bytes()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     hbm, _, which = peaks()
@@ -261,15 +278,17 @@ def moe_workload(args):
         torch.cuda.synchronize()                                   # inputs were produced on the default stream
         with torch.cuda.stream(side):
             for _ in range(2):
-                out = te(x, ids, w)
+                out = block(x, ids, w)
         side.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
-            out = te(x, ids, w)
+            out = block(x, ids, w)
         torch.cuda.synchronize()
         ts = []
         for _ in range(max(5, args.steps)):
             flush.zero_()
+            if world > 1:
+                dist.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             graph.replay()
@@ -278,11 +297,15 @@ def moe_workload(args):
             ts.append(e0.elapsed_time(e1) * 1e3)
         ts.sort()
         us = ts[len(ts) // 2]
+        if world > 1:
+            t_ = torch.tensor([us], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            us = float(t_.item())
         # BF16 control: the same block with dense BF16 expert weights gathered per pair (batched matmul)
         distinct = int(ids.unique().numel())
         nbytes = distinct * (rec13 + rec2) + T * H * 2 * 2 + T * K * (2 * I + I + H) * 2
         ref = None
-        if T * K <= 64:
+        if T * K <= 64 and world == 1:
             W13 = torch.stack([m.dequantize() for m in te.w13])
             W2 = torch.stack([m.dequantize() for m in te.w2])
             xe = x.repeat_interleave(K, 0).unsqueeze(2)
@@ -302,13 +325,94 @@ def moe_workload(args):
                       "frac_hbm": nbytes / us / 1e3 / hbm, "rel_err_vs_bf16": err})
         del graph
     big = table[0]
+    status = ops.device_status()
+    if rank != 0:
+        sys.stdout.flush()
+        os._exit(0)
     print(json.dumps({"metric": "MoE routed-expert block over tree-stored experts, effective GB/s (distinct expert records / time)",
-                      "value": big["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(5, args.steps), "warmup": 2,
+                      "value": big["gbs"], "unit": "GB/s", "n_gpus": world, "steps": max(5, args.steps), "warmup": 2,
                       "ms_per_step": big["us"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                       "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": f"Qwen3-30B-A3B-shaped expert block: {E} experts top-{K}, hidden {H}, "
                                              f"intermediate {I}; headline row: {big['tokens']} token(s)",
-                                 "l2": "flushed between replays"},
+                                 "l2": "flushed between replays",
+                                 "parallelism": "single GPU" if world == 1 else f"ep{world} (experts split over ranks, "
+                                                "tokens replicated, all-reduce of the partial outputs)"},
+                      "roofline": {"bound": "hbm", "achieved": big["gbs"], "peak": hbm, "unit": "GB/s",
+                                   "frac": big["gbs"] / hbm, "traffic": None, "peak_source": f"of {which}"},
+                      "device_status": status, "table": table}))
+    if world > 1:
+        sys.stdout.flush()
+        os._exit(0)
+
+
+def aux_workload(args):
+    """The streaming kernels beside the products: tree -> BF16 decode, embedding row gather, KV page append and
+    dequant.  One JSON line with a table (median of L2-flushed calls)."""
+    import torch
+
+    import statetree_b200 as S
+    from statetree_b200 import ops
+    from statetree_b200.kvcache import StateTreeKVLayer
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    hbm, _, which = peaks()
+    gen = torch.Generator(device=dev).manual_seed(0)
+    table = []
+
+    def timed(fn):
+        ts = []
+        for _ in range(max(5, args.steps)):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def row(name, us, nbytes):
+        table.append({"kernel": name, "us": us, "gbs": nbytes / us / 1e3, "frac_hbm": nbytes / us / 1e3 / hbm})
+
+    for M, N in ((4096, 4096), (12288, 4096)):
+        W = (torch.randn(M, N, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        tl = S.TreeLinear.from_weight(W, verify=True)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        eo, el, _ = tl.tables()
+        for _ in range(2):
+            ops.ext().dec(tl.tree, eo, el, out)
+        row(f"dec {M}x{N} (records read + BF16 written)", timed(lambda: ops.ext().dec(tl.tree, eo, el, out)),
+            tl.record_bytes() + 2 * M * N)
+        if M == 12288:
+            ids = torch.randint(0, M, (64,), device=dev, generator=gen)
+            for _ in range(2):
+                tl.rows(ids)
+            row("rows: 64 rows of a 12288x4096 table", timed(lambda: tl.rows(ids)), 64 * (N // 64) * 1552 + 64 * N * 2)
+    H = 8
+    for n_tok, what in ((64, "decode step, batch 64 (one token per sequence)"), (8192, "prefill, 8192 tokens")):
+        layer = StateTreeKVLayer(max(64, n_tok // 16) * 2, H, dev, pool_blocks=1 << 14)
+        K = torch.randn(n_tok, H, 128, device=dev, generator=gen).to(torch.bfloat16)
+        V = torch.randn(n_tok, H, 128, device=dev, generator=gen).to(torch.bfloat16)
+        slots = (torch.arange(n_tok, device=dev) * 16) if n_tok == 64 else torch.arange(n_tok, device=dev)
+        for _ in range(2):
+            layer.append(K, V, slots)
+        row(f"kv_append: {what}", timed(lambda: layer.append(K, V, slots)), n_tok * H * (2 * 128 * 2 + 400))
+        if n_tok == 8192:
+            for _ in range(2):
+                layer.dense()
+            nb = layer.pages.shape[0]
+            row(f"kv_dequant: {nb} pages", timed(lambda: layer.dense()), nb * H * (6400 + 8192))
+        layer.check()
+    big = table[1]
+    print(json.dumps({"metric": "streaming kernels (dec, rows, kv_append, kv_dequant), effective GB/s", "value": big["gbs"],
+                      "unit": "GB/s", "n_gpus": 1, "steps": max(5, args.steps), "warmup": 2, "ms_per_step": big["us"] / 1e3,
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                      "config": {"workload": "dec / rows / kv_append / kv_dequant; headline row: " + big["kernel"],
+                                 "l2": "flushed between calls"},
                       "roofline": {"bound": "hbm", "achieved": big["gbs"], "peak": hbm, "unit": "GB/s",
                                    "frac": big["gbs"] / hbm, "traffic": None, "peak_source": f"of {which}"},
                       "device_status": ops.device_status(), "table": table}))
@@ -413,7 +517,7 @@ def main():
     ap.add_argument("--moe-batch", default="1,8,32,64")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=512)
-    ap.add_argument("--workload", default="linear", choices=["linear", "attn", "moe", "decode"],
+    ap.add_argument("--workload", default="linear", choices=["linear", "attn", "moe", "decode", "aux"],
                     help="linear: the Qwen3-8B linear sweep (default, the headline); attn: compressed-KV decode attention")
     ap.add_argument("--ctx", default="1024,4096,16384")
     ap.add_argument("--attn-batch", default="1,8,32,64")
@@ -421,9 +525,16 @@ def main():
     if args.workload == "decode":
         decode_workload(args)
         return
-    if args.workload in ("attn", "moe"):
+    if args.workload == "moe":
+        moe_workload(args)
+        return
+    if args.workload == "aux":
         if int(os.environ.get("RANK", "0")) == 0:
-            (attention_workload if args.workload == "attn" else moe_workload)(args)
+            aux_workload(args)
+        return
+    if args.workload == "attn":
+        if int(os.environ.get("RANK", "0")) == 0:
+            attention_workload(args)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

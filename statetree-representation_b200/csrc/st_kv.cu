@@ -42,6 +42,7 @@ struct AppendArgs {
   int* pool_cnt;
   long long nblocks;
   int N, H, P, reuse;
+  int gsz;                  // tokens of the call scanned per warp for segment starts (1: decode steps, 16: prefill)
 };
 
 // escape bookkeeping of one record while a warp appends rows to it (lane 0 owns the chain walk)
@@ -85,32 +86,50 @@ __device__ void chain_put(const AppendArgs& a, EscCursor& c, uint32_t* slots, ui
 // One warp per (token, head, K/V, half); only the warp of a segment's first token works: a segment is a run of
 // consecutive slots inside one page, and its warp owns the record for the whole launch (rows g and g+8 share state
 // bytes, and the header is read-modify-write).  Semantics of statetree/csrc/kvcache.cu:62-192.
+// The warp edits the 1600-byte unit in shared memory: the segment's rows are fetched up front (independent loads),
+// encoded row by row with shared-memory byte stores, and the unit goes back to the page as 100 16-byte stores.
 __global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
+  __shared__ __align__(16) uint8_t s_unit[8][RKV];
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int units = a.H * 4;
-  const long long n = w / units;
-  if (n >= a.N) return;
+  const long long grp = w / units;                                // a.gsz consecutive tokens of the call per warp
+  if (grp * a.gsz >= a.N) return;
   const int u = (int)(w % units), h = u >> 2, kvi = (u >> 1) & 1, half = u & 1;
+  const long long n_end = min((long long)a.N, (grp + 1) * a.gsz);
+  for (long long n = grp * a.gsz; n < n_end; ++n) {
   const long long s0 = a.slot[n];
-  if (s0 < 0) return;
+  if (s0 < 0) continue;
   const long long blk = s0 / PAGE;
-  if (blk >= a.nblocks) return;                                   // outside the cache: dropped, no write
+  if (blk >= a.nblocks) continue;                                 // outside the cache: dropped, no write
   if (n > 0) {
     const long long sp = a.slot[n - 1];
-    if (sp >= 0 && sp + 1 == s0 && sp / PAGE == blk) return;      // continues the previous token's segment
+    if (sp >= 0 && sp + 1 == s0 && sp / PAGE == blk) continue;    // continues the previous token's segment
   }
-  uint8_t* const rec = a.kv + unit_off(blk, a.H, h, kvi, half);
+  uint8_t* const grec = a.kv + unit_off(blk, a.H, h, kvi, half);
+  uint8_t* const rec = s_unit[threadIdx.x >> 5];
   uint32_t* const hdr = reinterpret_cast<uint32_t*>(rec + REC);
   uint32_t* const slots = hdr + 1;
+  const int r0 = (int)(s0 % PAGE);
+  // rows of this segment: consecutive slots that stay inside the page
+  int nrow = 1;
+  while (nrow < PAGE - r0 && n + nrow < a.N && a.slot[n + nrow] == s0 + nrow) ++nrow;
+  // fetch every row's pair of values now (independent loads), encode afterwards
+  uint32_t pairs[PAGE];
+#pragma unroll
+  for (int i = 0; i < PAGE; ++i) {
+    if (i < nrow) {
+      const uint16_t* src = (kvi ? a.V + (n + i) * a.vs : a.K + (n + i) * a.ks) + h * HD + half * 64;
+      pairs[i] = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
+    }
+  }
   EscCursor c;
-  if (s0 % PAGE == 0) {                                           // row 0: the page starts over
+  if (r0 == 0) {                                                  // row 0: the page starts over
     int keep = -1;
     if (a.reuse) {
-      const uint32_t old = *reinterpret_cast<volatile uint32_t*>(hdr);
+      const uint32_t old = *reinterpret_cast<const volatile uint32_t*>(grec + REC);
       if ((old & 16u) && (int)(old >> 8) < a.P) keep = (int)(old >> 8);
     }
-    __syncwarp();
     for (int i = lane; i < RKV / 16; i += 32) reinterpret_cast<uint4*>(rec)[i] = make_uint4(0, 0, 0, 0);
     if (keep >= 0 && lane == 0) {                                 // empty the kept chain, links stay
       int b = keep;
@@ -122,20 +141,21 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
     }
     c.cnt = 0;
     c.head = keep;
+  } else {                                                        // continue a page: bring the unit in
+    for (int i = lane; i < RKV / 16; i += 32) reinterpret_cast<uint4*>(rec)[i] = reinterpret_cast<const uint4*>(grec)[i];
     __syncwarp();
-  } else {
-    const uint32_t old = *reinterpret_cast<volatile uint32_t*>(hdr);
+    const uint32_t old = *hdr;
     c.cnt = (int)(old & 15u);
     c.head = (old & 16u) ? (int)(old >> 8) : -1;
   }
+  __syncwarp();
   c.tail = -1;
   c.fill = 0;
-  for (long long m = n; m < a.N; ++m) {
-    const long long sm = a.slot[m];
-    if (m > n && !(sm >= 0 && sm == a.slot[m - 1] + 1 && sm / PAGE == blk)) break;
-    const int r = (int)(sm % PAGE);
-    const uint16_t* src = (kvi ? a.V + m * a.vs : a.K + m * a.ks) + h * HD + half * 64;
-    const uint32_t pr = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
+#pragma unroll
+  for (int i = 0; i < PAGE; ++i) {
+    if (i >= nrow) break;
+    const int r = r0 + i;
+    const uint32_t pr = pairs[i];
     const uint32_t b0 = pr & 0xFFFFu, b1 = pr >> 16;
     const int e0 = (int)((b0 >> 7) & 0xFFu), e1 = (int)((b1 >> 7) & 0xFFu);
     int E = max(e0, e1);
@@ -178,6 +198,10 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
     }
   }
   if (lane == 0) *hdr = (uint32_t)c.cnt | (c.head >= 0 ? (16u | ((uint32_t)c.head << 8)) : 0u);
+  __syncwarp();
+  for (int i = lane; i < RKV / 16; i += 32) reinterpret_cast<uint4*>(grec)[i] = reinterpret_cast<const uint4*>(rec)[i];
+  __syncwarp();                                                   // the staging unit is reused by the next segment
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ record decode
@@ -489,7 +513,10 @@ extern "C" int st_kv_append(const void* K, const void* V, int64_t ks, int64_t vs
   a.K = (const uint16_t*)K; a.V = (const uint16_t*)V; a.ks = ks; a.vs = vs;
   a.slot = (const long long*)slot; a.kv = (uint8_t*)kv; a.pool = pool; a.pool_cnt = pool_cnt;
   a.nblocks = nblocks; a.N = (int)N; a.H = (int)H; a.P = (int)P; a.reuse = reuse ? 1 : 0;
-  const long long warps = N * H * 4;
+  // long calls are mostly whole pages of consecutive tokens: one warp per 16 tokens finds (typically) one segment
+  // and the grid shrinks 16-fold; short calls (decode steps) keep one warp per token
+  a.gsz = N >= 1024 ? 16 : 1;
+  const long long warps = ((N + a.gsz - 1) / a.gsz) * H * 4;
   kv_append_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(a);
   ST_LAUNCH_CHECK("st_kv_append launch");
   return 0;

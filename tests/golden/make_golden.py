@@ -96,4 +96,6 @@ def enc_t(enc, k):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference-checkout")
+    main(sys.argv[1])

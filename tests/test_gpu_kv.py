@@ -142,6 +142,43 @@ def test_pages_equal_the_oracle_bytes():
     assert np.array_equal(torch_to_bits(Kg), Kd) and np.array_equal(torch_to_bits(Vg), Vd)
 
 
+def test_long_append_call_matches_oracle():
+    """one call with thousands of tokens (the grouped mapping of long calls): three sequences back to back, a padding
+    token between them, ragged starts inside pages"""
+    nb, P = 200, 1 << 16
+    cache, pool, cnt = _fresh(nb, H, P)
+    o = (np.zeros((nb, H, 2, 2, 1600), np.uint8), np.zeros((P, 16), np.uint32), np.zeros(2, np.int32))
+    rs = np.random.RandomState(3)
+    perm = rs.permutation(nb)
+    lens = [1203, 517, 899]
+    Ks, Vs, sl, used = [], [], [], 0
+    # a short first call leaves sequence 0 mid-page, so the long call starts inside a page
+    K0, V0 = G.kv_tokens(5, H, seed=90, tiny=0.05)
+    s0 = (perm[0] * 16 + np.arange(5)).astype(np.int64)
+    _kx().append(bits_to_torch(K0, DEV), bits_to_torch(V0, DEV), torch.from_numpy(s0).to(DEV), cache, pool, cnt)
+    oracle.kv_append(K0, V0, s0, *o)
+    for i, L in enumerate(lens):
+        K, V = G.kv_tokens(L, H, seed=91 + i, tiny=0.05)
+        pos = np.arange(L) + (5 if i == 0 else 0)
+        pages = perm[used:used + (pos[-1] // 16 + 1)]
+        used += len(pages)
+        Ks += [K, np.zeros((1, H, D), np.uint16)]
+        Vs += [V, np.zeros((1, H, D), np.uint16)]
+        sl += [(pages[pos // 16] * 16 + pos % 16).astype(np.int64), np.array([-1], np.int64)]
+    K, V, slots = np.concatenate(Ks), np.concatenate(Vs), np.concatenate(sl)
+    assert K.shape[0] >= 1024
+    _kx().append(bits_to_torch(K, DEV), bits_to_torch(V, DEV), torch.from_numpy(slots).to(DEV), cache, pool, cnt)
+    oracle.kv_append(K, V, slots, *o)
+    got = cache.cpu().numpy()
+    assert np.array_equal(got[..., :1552], o[0][..., :1552])
+    Kd, Vd = oracle.kv_dequant_blocks(o[0], o[1])
+    Kg = torch.empty(nb, PAGE, H, D, dtype=torch.bfloat16, device=DEV)
+    Vg = torch.empty_like(Kg)
+    _kx().dequant(cache, pool, Kg, Vg)
+    assert np.array_equal(torch_to_bits(Kg), Kd) and np.array_equal(torch_to_bits(Vg), Vd)
+    assert int(cnt[1]) == 0
+
+
 def test_dequant_blocks_out_of_range_is_zero():
     cache, pool, cnt = _fresh(NB)
     _write(cache, pool, cnt, LENS, PRE, MAXP, 1, 0.01)
