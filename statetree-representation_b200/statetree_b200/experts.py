@@ -77,13 +77,14 @@ def moe_align(ids, E, bs=8):
     return sorted_ids, bexp, end[-1:].to(torch.int32)
 
 
-def moe_group_gemv(tables, x, aligned, S, M, xdiv):
+def moe_group_gemv(tables, x, aligned, S, M, xdiv, zero=False):
     """y[s] = W[expert of s] x[s // xdiv], slots grouped by expert: aligned = moe_align(ids, E, 8).  Rows of blocks
-    whose expert id is negative (another rank's expert) are left untouched."""
+    whose expert id is negative or >= the number of tables (another rank's expert) are left untouched (zero=True:
+    they read as zeros)."""
     sorted_ids, bexp, npost = (t.contiguous() for t in aligned)
     x = _aligned(x)
     N = x.shape[1]
-    y = torch.empty(S, M, dtype=torch.bfloat16, device=x.device)
+    y = (torch.zeros if zero else torch.empty)(S, M, dtype=torch.bfloat16, device=x.device)
     if S == 0:
         return y
     E = ext()
@@ -148,9 +149,18 @@ class TreeExperts(nn.Module):
         ids = topk_ids.reshape(-1)
         w = topk_w
         if expert_map is not None:
+            # expert parallel: pairs of other ranks' experts go to one extra bin whose blocks the kernel skips
             local = expert_map[ids.long()]
             w = torch.where(local.view(T, K) >= 0, topk_w, torch.zeros_like(topk_w))
-            ids = local.clamp(min=0)
+            if S <= SLOT_MAX:                           # a few pairs: cheaper to compute them all (weight 0) than to group
+                ids = local.clamp(min=0)
+                gu = moe_gemv(t13, x, ids, 2 * self.inter, K)
+                return moe_wsum(moe_gemv(t2, silu_mul(gu), ids, self.hidden, 1), w)
+            ids = torch.where(local >= 0, local, torch.full_like(local, self.num_experts))
+            al = moe_align(ids, self.num_experts + 1, 8)
+            gu = moe_group_gemv(t13, x, al, S, 2 * self.inter, K, zero=True)
+            y = moe_group_gemv(t2, silu_mul(gu), al, S, self.hidden, 1, zero=True)
+            return moe_wsum(y, w)
         if S <= SLOT_MAX:
             gu = moe_gemv(t13, x, ids, 2 * self.inter, K)
             y = moe_gemv(t2, silu_mul(gu), ids, self.hidden, 1)
