@@ -35,7 +35,7 @@ struct GemmArgs {
   const uint8_t* tree; const int* eo; const uint32_t* el;
   uint16_t* Y; float* Yf; float* ws; int* cnt; int* status;
   long long M, N;
-  int B, NG, NT, KS, RB, TT, stages, rstages, xstages, bar_off;
+  int B, NG, NT, KS, RB, TT, stages, rstages, nmma, bar_off;
   uint32_t idesc;
 #ifdef ST_PROF
   long long* prof;
@@ -45,8 +45,13 @@ struct GemmArgs {
 
 #ifdef ST_PROF
 __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#ifdef ST_NOTIMERS
+#define GPROF(slot) do {} while (0)
+#define GCK(n) do {} while (0)
+#else
 #define GPROF(slot) do { if (a.prof && (slot) < 64) a.prof[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
 #define GCK(n) do { const long long t_ = clock64(); gck[n] += t_ - gckl; gckl = t_; } while (0)
+#endif
 long long* g_gemm_prof = nullptr;
 int g_gemm_diag = 0;
 #else
@@ -119,13 +124,30 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
 
 constexpr int DG = 2;                        // decode groups: this many k-tiles are decoded at a time
 constexpr int NDW = DG * NDEC;               // decode warps
-constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;     // producer (records), producer (activations), MMA
-constexpr int GEMM_THREADS = (NDW + 3) * 32;
+constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;     // producer (records), producer (activations), MMA issuers
+constexpr int NMMA = 2;                      // MMA issuer warps; a.nmma of them work (issuer m: k-tiles m, m + nmma, ...)
+constexpr int GEMM_THREADS = (NDW + 2 + NMMA) * 32;
 #ifdef ST_GEMM_SPINWAIT
 #define GW mbar_wait_spin
 #else
 #define GW mbar_wait
 #endif
+#ifndef ST_GEMM_BACKOFF_NS
+#define ST_GEMM_BACKOFF_NS 0
+#endif
+// wait of the decode warps: sixteen warps polling a barrier take issue slots from the three single-thread roles that
+// share their schedulers, so a warp that finds the barrier closed sleeps a little before it looks again
+__device__ __forceinline__ bool wait_decode(uint64_t* bar, uint32_t parity) {
+#if ST_GEMM_BACKOFF_NS > 0
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    __nanosleep(ST_GEMM_BACKOFF_NS);
+  }
+  return false;
+#else
+  return GW(bar, parity);
+#endif
+}
 constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of one k-tile
 
 // Two rings.  The RAW ring (R slots of eight records) faces HBM: its depth sets the bytes in flight.  The TILE ring
@@ -163,11 +185,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     GPROF(0);
     for (int s = 0; s < S; ++s) { mbar_init(ready + s, NDEC + 1); mbar_init(empty + s, 1); }
     for (int r = 0; r < R; ++r) { mbar_init(rfull + r, 1); mbar_init(rempty + r, NDEC); }
-    mbar_init(accbar, 1);
+    mbar_init(accbar, NMMA);                                       // every issuer warp arrives, working or not
     fence_barrier_init();
   }
   if (warp == W_MMA) {
-    tmem_alloc(tmem_slot, (uint32_t)(NT < 32 ? 32 : NT));
+    tmem_alloc(tmem_slot, (uint32_t)(a.nmma * NT));              // 64 .. 256 columns: one accumulator per working issuer
     tmem_relinquish();
   }
   tc_fence_before();
@@ -181,18 +203,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     // fetches the eight records (row tiles rb * 8 .. + 7 of column group k0 + i) through a 3-D view of the tree
     // [row tile][column group][194 x u64]; eight separate 1552-byte bulk copies per k-tile cost ~1 us of issue time
     if (lane == 0) {
-      for (int i = 0; i < nk; ++i) {
-        const int r = i % R, k = i / R;
+      for (int i = 0, r = 0, k = 0; i < nk; ++i, r = (r + 1 == R ? 0 : r + 1), k += (r == 0)) {
+#ifdef ST_PROF
+        if (a.diag & 128) break;
+#endif
         if (k > 0 && !GW(rempty + r, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
+#ifdef ST_PROF
+        if ((a.diag & 4) && i >= R) { mbar_arrive(rfull + r); continue; }
+#endif
         mbar_expect_tx(rfull + r, (uint32_t)RAW_SLOT);
         tma_load_3d(rawring + (size_t)r * RAW_SLOT, &wmap, 0, k0 + i, rb * 8, rfull + r);
+        if (i < 24) GPROF(16 + i);
       }
     }
   } else if (warp == W_X) {
     // ---------------------------------------------------------------- activation producer
     if (lane == 0) {
-      for (int i = 0; i < nk; ++i) {
-        const int s = i % S, k = i / S;
+      for (int i = 0, s = 0, k = 0; i < nk; ++i, s = (s + 1 == S ? 0 : s + 1), k += (s == 0)) {
         if (k > 0 && !GW(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
 #ifdef ST_PROF
         if ((a.diag & 1) && i >= S) { mbar_arrive(ready + s); continue; }
@@ -201,15 +228,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
         tma_load_2d(smem + (size_t)s * STAGE + A_TILE, &xmap, (k0 + i) * 64, tok0, ready + s);
       }
     }
-  } else if (warp == W_MMA) {
-    // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      for (int i = 0; i < nk; ++i) {
-        const int s = i % S, k = i / S;
+  } else if (warp >= W_MMA) {
+    // ---------------------------------------------------------------- MMA issuers.  One thread pays ~80 cycles per
+    // tcgen05.mma it issues plus the barrier wait and the commit, about 700 cycles per k-tile: more than the tile's
+    // share of HBM time.  Two issuers alternate k-tiles, each into its own accumulator (the epilogue adds the two in a
+    // fixed order), so the serial cost per k-tile halves and the result does not depend on which issuer ran first.
+    // This needs an even number of tile stages and record slots: then every stage and slot belongs to one decode group
+    // and one issuer, which use it in their own program order.  (A waiter may be at most one phase ahead of an mbarrier:
+    // with shared stages an issuer could ask for use k of a stage whose use k - 1, the other issuer's, has not
+    // completed, and the parity test would pass on use k - 2.)  With three stages (256-token tiles) one issuer works.
+    const int m = warp - W_MMA;
+    if (lane == 0 && m >= a.nmma) mbar_arrive(accbar);
+    if (lane == 0 && m < a.nmma) {
+      const uint32_t acc = tmem + (uint32_t)(m * NT);
+#ifdef ST_PROF
+      long long gck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gckl = clock64();
+#endif
+      int s = m % S, k = m / S;
+      for (int i = m; i < nk; i += a.nmma) {
+        GCK(0);
         if (!GW(ready + s, (uint32_t)k & 1u)) {
           atomicExch(a.status, ERR_WAIT_MMA);
           break;
         }
+        GCK(1);
         tc_fence_after();
         const uint32_t sa = smem_addr(smem + (size_t)s * STAGE);
         const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TILE);
@@ -217,53 +259,106 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
         if (!(a.diag & 2))
 #endif
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tc_mma(tmem, da + 2 * j, db + 2 * j, a.idesc, (i | j) ? 1u : 0u);
+        for (int j = 0; j < 4; ++j) tc_mma(acc, da + 2 * j, db + 2 * j, a.idesc, (i >= a.nmma || j) ? 1u : 0u);
+        GCK(2);
+#ifdef ST_PROF
+        if (a.diag & 64) mbar_arrive(empty + s); else
+#endif
         tc_commit(empty + s);
-        GPROF(40 + i);
+        GCK(3);
+        if (m == 0) GPROF(40 + i / a.nmma);
+        s += a.nmma; while (s >= S) { s -= S; ++k; }
       }
-      tc_commit(accbar);                                          // arrives when every MMA above has completed
+      tc_commit(accbar);                                          // arrives when every MMA of this issuer has completed
+#ifdef ST_PROF
+      if (a.prof && m == 0) for (int q = 0; q < 4; ++q) a.prof[blockIdx.x * 64 + 5 + q - (q == 3 ? -5 : 0)] = gck[q];
+#endif
     }
   } else {
     // ---------------------------------------------------------------- decode warps: group g = warp / 8 takes the
     // k-tiles i = g, g + DG, ...; warp r of a group decodes record r (rows 16 r .. 16 r + 15 of the block)
     const int grp = warp / NDEC, rec = warp % NDEC;
     const size_t rbase = (size_t)(rb * 8 + rec) * a.NG + k0;
-    // escape-list offsets of this warp's records, 32 k-tiles at a time (lane l holds the offsets of k-tile base + l),
-    // so no global load sits between two k-tiles
-    int eo_base = -1, eo_lo = 0, eo_hi = 0;
+    // Escape entries are fetched one k-tile ahead: the list offsets of this warp's records come 32 k-tiles at a time
+    // (lane l holds the offsets of k-tile eo_base + l) and the first 32 entries of the next record are requested before
+    // this record is decoded, so no global-load latency sits between the records landing and the tile being handed
+    // to the tensor core (one record in six has an escape; eight warps must all arrive before the MMA can start)
+    int eo_base = 0, eo_lo = 0, eo_hi = 0;
+    auto load_offsets = [&](int first) {
+      eo_base = first;
+      const int j = first + lane;
+      eo_lo = j < nk ? __ldg(a.eo + rbase + j) : 0;
+      eo_hi = j < nk ? __ldg(a.eo + rbase + j + 1) : 0;
+    };
+    int lo = 0, hi = 0;
+    uint32_t ent = 0u;
+    if (grp < nk) {
+      load_offsets(grp);
+      lo = __shfl_sync(FULL, eo_lo, 0);
+      hi = __shfl_sync(FULL, eo_hi, 0);
+      if (lane < hi - lo) ent = __ldg(a.el + lo + lane);
+    }
 #ifdef ST_PROF
     long long gck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gckl = clock64();
 #endif
     int s = grp % S, k = grp / S, r = grp % R, rk = grp / R;          // tile stage / use count, record slot / use count
     for (int i = grp; i < nk; i += DG) {
       GCK(0);
-      if (eo_base < 0 || i - eo_base >= 32) {
-        eo_base = i;
-        const int j = i + lane;
-        eo_lo = j < nk ? __ldg(a.eo + rbase + j) : 0;
-        eo_hi = j < nk ? __ldg(a.eo + rbase + j + 1) : 0;
+      int nlo = 0, nhi = 0;
+      uint32_t nent = 0u;
+#ifdef ST_PROF
+      if (!(a.diag & 256))
+#endif
+      if (i + DG < nk) {
+        if (i + DG - eo_base >= 32) load_offsets(i + DG);
+        nlo = __shfl_sync(FULL, eo_lo, i + DG - eo_base);
+        nhi = __shfl_sync(FULL, eo_hi, i + DG - eo_base);
+        if (lane < nhi - nlo) nent = __ldg(a.el + nlo + lane);
       }
-      const int lo = __shfl_sync(FULL, eo_lo, i - eo_base), hi = __shfl_sync(FULL, eo_hi, i - eo_base);
-      if (!GW(rfull + r, (uint32_t)rk & 1u)) {
+#ifdef ST_PROF
+      RecRegs rr;
+      if (a.diag & 128) {
+        rr.l0 = rr.l1 = rr.st = make_uint4(i, i, i, i); rr.nodes = i;
+      } else {
+#endif
+      if (!wait_decode(rfull + r, (uint32_t)rk & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
         break;
       }
       GCK(1);                                                     // wait for the records
+#ifdef ST_PROF
+      rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + rec * REC, lane);
+#else
       const RecRegs rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + rec * REC, lane);
+#endif
       __syncwarp();
       if (lane == 0) mbar_arrive(rempty + r);                     // the slot can be refilled while we decode
+#ifdef ST_PROF
+      }
+#endif
       uint32_t A[4][4];
+#ifdef ST_PROF
+      if (a.diag & 8) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) A[q][0] = A[q][1] = A[q][2] = A[q][3] = rr.nodes;
+      } else
+#endif
       decode_frag(rr, A);
-      for (int base = lo; base < hi; base += 32) {
+      {
+        const int n = min(32, hi - lo);
+        for (int e = 0; e < n; ++e) patch_entry(A, __shfl_sync(FULL, ent, e), lane);
+      }
+      for (int base = lo + 32; base < hi; base += 32) {          // a crowded record: the rest of its list
         const int n = min(32, hi - base);
         const uint32_t mine = (lane < n) ? __ldg(a.el + base + lane) : 0u;
         for (int e = 0; e < n; ++e) patch_entry(A, __shfl_sync(FULL, mine, e), lane);
       }
+      lo = nlo; hi = nhi; ent = nent;
 #ifdef ST_PROF
       if (A[0][0] == 0x12345u && A[3][3] == 0x54321u) gck[7]++;
 #endif
       GCK(2);                                                     // load + decode + escapes
-      if (k > 0 && !GW(empty + s, (uint32_t)(k - 1) & 1u)) {   // the MMAs of the stage's last use are done
+      if (k > 0 && !wait_decode(empty + s, (uint32_t)(k - 1) & 1u)) {   // the MMAs of the stage's last use are done
         if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
         break;
       }
@@ -273,9 +368,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
       const int mrow = rec * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
       const uint32_t rowaddr = smem_addr(st) + mrow * 128;
       const int chalf = lane >> 4;
+#ifdef ST_PROF
+      if (!(a.diag & 16))
+#endif
 #pragma unroll
       for (int q = 0; q < 4; ++q)
         stmatrix_x4(rowaddr + (uint32_t)(((2 * q + chalf) ^ (mrow & 7)) << 4), A[q][0], A[q][1], A[q][2], A[q][3]);
+#ifdef ST_PROF
+      if (!(a.diag & 32))
+#endif
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(ready + s);
@@ -294,17 +395,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     float* stg = reinterpret_cast<float*>(smem);                 // [NT][128] fp32, over the (now idle) ring
     const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column quarter (warps 0..15)
     const int cper = NT / 4;
-    for (int c0 = cg * cper; warp < 16 && c0 < (cg + 1) * cper; c0 += 32) {
-      uint32_t v[32];
-      if (cper >= 32) {
-        tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
+    const bool two = a.nmma > 1 && nk > 1;                       // the second issuer had a k-tile
+    for (int c0 = cg * cper; warp < 16 && c0 < (cg + 1) * cper; c0 += 16) {
+      uint32_t v[32], w[32];                                     // (the x16 load fills the first sixteen)
+      const uint32_t t0 = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;
+      tmem_ld16(t0, v);
+      if (two) {
+        tmem_ld16(t0 + (uint32_t)NT, w);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) stg[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
-      } else {                                                   // NT = 64: 16 columns per warp
-        tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) stg[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
+        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
       }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) stg[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
     }
     if (tid == 0) GPROF(3);
   }
@@ -355,7 +457,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
   cluster_sync_all();                                            // nobody leaves while a peer still reads its tile
   if (warp == W_MMA) {
     __syncwarp();
-    tmem_dealloc(tmem, (uint32_t)(NT < 32 ? 32 : NT));
+    tmem_dealloc(tmem, (uint32_t)(a.nmma * NT));
   }
 }
 
@@ -377,7 +479,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-struct GemmPlan { int NT, TT, RB, KS, stages, rstages, xstages, bar_off; size_t smem; };
+struct GemmPlan { int NT, TT, RB, KS, stages, rstages, nmma, bar_off; size_t smem; };
 
 GemmPlan gemm_plan(long long M, long long N, long long B) {
   GemmPlan p;
@@ -412,10 +514,12 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
       while (p.stages > 2 && (size_t)p.stages * (A_TILE + (size_t)p.NT * 128) + 3 * (size_t)RAW_SLOT > 212 * 1024) --p.stages;
     }
   }
-  p.xstages = 0;
   const size_t tiles = (size_t)p.stages * (A_TILE + (size_t)p.NT * 128);
   p.rstages = (int)((212 * 1024 - tiles) / RAW_SLOT);
   if (p.rstages > 12) p.rstages = 12;
+  // two MMA issuers need every stage and record slot owned by one decode group: even counts of both
+  p.nmma = (p.stages % 2 == 0 && p.rstages >= 4) ? 2 : 1;
+  if (p.nmma == 2) p.rstages &= ~1;
   size_t ring = tiles + (size_t)p.rstages * RAW_SLOT;
   ring = (ring + 15) & ~(size_t)15;
   const size_t stg = (size_t)p.NT * 128 * 4;                    // the parked accumulator tile reuses the rings
@@ -473,7 +577,7 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "st_gemm: no device status word");
   a.M = M; a.N = N; a.B = (int)B; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = p.KS; a.RB = p.RB; a.TT = p.TT;
-  a.stages = p.stages; a.rstages = p.rstages; a.xstages = p.xstages; a.bar_off = p.bar_off;
+  a.stages = p.stages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
 #ifdef ST_PROF
   a.prof = g_gemm_prof; a.diag = g_gemm_diag;
 #endif

@@ -21,6 +21,7 @@
 
 #include "st_host.h"
 
+
 namespace {
 using namespace st;
 
@@ -43,7 +44,7 @@ struct GemvArgs {
   int E, xdiv;
   int NG, CPT, T;                         // column groups, units per tile, tiles per problem
   long long U;                            // units over all problems
-  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, ahead, slow_s0, slow_ns;
+  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, ahead;
 #ifdef ST_PROF
   long long* prof;                        // [CTAs][64] globaltimer stamps (development builds only)
 #endif
@@ -251,24 +252,14 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
     UnitCursor<MODE> pre = cur;
     int filled = 0;
     if (MODE == MODE_DENSE) {                                  // lane i fills stage i
-      // Slow start: all of a CTA's first copies share the memory system equally and would land together, late.  The
-      // first S0 stages are requested alone and the rest a little later, so the consumers start on the first units
-      // while the others are still in flight.
       const bool on = lane < S && mine.valid();
-      const int S0 = (a.xwhole && a.slow_s0 > 0 && a.slow_s0 < S) ? a.slow_s0 : S;
-      auto fill_mine = [&]() {
+      if (on) {
         const int nrec = mine.nrec(a);
         uint8_t* st = ring + (size_t)lane * STAGE;
         mbar_expect_tx(full + lane, (uint32_t)(nrec * REC + SIDE_BYTES) + (a.xwhole ? 0u : (uint32_t)(NX * nrec * 128)));
         bulk_g2s(st, mine.pr.tree + ((size_t)mine.tile * a.NG + (size_t)mine.c * CW) * REC, (uint32_t)(nrec * REC),
                  full + lane, pol_w);
         bulk_g2s(st + UNIT_BYTES, mine.pr.eb + ((size_t)mine.tile * a.CPT + mine.c) * 16, SIDE_BYTES, full + lane, pol_w);
-      };
-      if (on && lane < S0) fill_mine();
-      if (S0 < S) {
-        if (a.slow_ns > 0) __nanosleep((unsigned)a.slow_ns);
-        else (void)mbar_wait(full + 0, 0u);
-        if (on && lane >= S0) fill_mine();
       }
       filled = __popc(__ballot_sync(FULL, on));
     } else {
@@ -405,11 +396,42 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
   }
   bool xready = !a.xwhole;
   const int last_nrec = a.NG - (a.CPT - 1) * CW;
+  // escapes of this warp's record: word 0 of the unit's escape block = escapes in the unit | (mask of the unit's records
+  // that have any) << 16, so seven warps in eight are done after one broadcast load
+  auto patch_unit = [&](uint32_t (&A)[4][4], const uint32_t sw0, const uint32_t sw, const int c) {
+    if ((sw0 >> (16 + rec)) & 1u) {
+      const uint32_t ne = sw0 & 0xFFFFu;
+      if (ne <= 14u) {                                       // lanes 2..15 hold the inline entries: one vote
+        const bool hit = lane >= 2 && lane < 16 && (uint32_t)(lane - 2) < ne && ((sw >> 10) & 7u) == (uint32_t)rec;
+        unsigned m = __ballot_sync(FULL, hit);
+        while (m) {
+          const int src = __ffs(m) - 1;
+          m &= m - 1;
+          patch_entry(A, __shfl_sync(FULL, sw, src), lane);
+        }
+      } else {                                               // crowded unit: this record's own list
+        const size_t r = (size_t)cur.tile * a.NG + (size_t)c * CW + rec;
+        const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
+        for (int base = lo; base < hi; base += 32) {
+          const int n = min(32, hi - base);
+          const uint32_t ent = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
+          for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, ent, i), lane);
+        }
+      }
+    }
+  };
   while (cur.valid()) {
     const int len = cur.run_len(a), cbeg = cur.c;
-    for (int j = 0; j < len; ++j) {
+    for (int j = 0; j < len;) {
       CK(0);                                                  // loop overhead
       const int c = cbeg + j;
+      if (!xready) {                                          // whole activation rows: waited for once
+        if (!mbar_wait(xbar, 0u)) {
+          if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+          return;
+        }
+        xready = true;
+      }
       const bool mine_unit = (G == 1) || (turn == grp);
       if (G > 1) turn = turn + 1 == G ? 0 : turn + 1;
       if (mine_unit) {
@@ -421,13 +443,6 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
         const uint8_t* st = ring + (size_t)s * STAGE;
         CK(1);                                                // wait for the stage
         if (rec < nrec) {
-          if (!xready) {                                       // whole activation rows: waited for once
-            if (!mbar_wait(xbar, 0u)) {
-              if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
-              return;
-            }
-            xready = true;
-          }
           // activations first: their shared-memory latency hides behind the decode
           uint32_t b[NT][8];
           const uint32_t sb = a.xwhole ? (uint32_t)(c * (CW * 128)) : smem_addr(st);
@@ -438,35 +453,18 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
             ldmatrix_x4(xa + 64, b[nt][4], b[nt][5], b[nt][6], b[nt][7]);
           }
           const uint32_t sw0 = *reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);            // escape block, word 0
+          const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];   // inline entries
+          const RecRegs raw = load_rec_shared(st + rec * REC, lane);
+          // everything this warp needs from the stage is in registers: hand the slot back before the arithmetic
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty + s);
           uint32_t A[4][4];
-          decode_frag(load_rec_shared(st + rec * REC, lane), A);
+          decode_frag(raw, A);
 #ifdef ST_PROF
           if (A[0][0] == 0x12345u && A[3][3] == 0x54321u) ck[7]++;   // keep the decode before the clock read
 #endif
           CK(2);                                              // loads + decode
-          // word 0 = escapes in the unit | (mask of the unit's records that have any) << 16: seven warps in eight
-          // are done after one broadcast load
-          if ((sw0 >> (16 + rec)) & 1u) {
-            const uint32_t ne = sw0 & 0xFFFFu;
-            if (ne <= 14u) {                                   // lanes 2..15 hold the inline entries: one vote
-              const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];
-              const bool hit = lane >= 2 && lane < 16 && (uint32_t)(lane - 2) < ne && ((sw >> 10) & 7u) == (uint32_t)rec;
-              unsigned m = __ballot_sync(FULL, hit);
-              while (m) {
-                const int src = __ffs(m) - 1;
-                m &= m - 1;
-                patch_entry(A, __shfl_sync(FULL, sw, src), lane);
-              }
-            } else {                                           // crowded unit: this record's own list
-              const size_t r = (size_t)cur.tile * a.NG + (size_t)c * CW + rec;
-              const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
-              for (int base = lo; base < hi; base += 32) {
-                const int n = min(32, hi - base);
-                const uint32_t ent = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
-                for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, ent, i), lane);
-              }
-            }
-          }
+          patch_unit(A, sw0, sw, c);
           CK(3);                                              // escapes
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
@@ -477,14 +475,17 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
 #endif
           CK(4);                                              // mma
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
+        if (rec >= nrec) {                                     // no record of this unit for the warp: release only
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty + s);
+        }
         CK(5);                                                // release
 #ifdef ST_PROF
         if (warp == 0 && lane == 0) { PROF(2 + ccount); ++ccount; }
 #endif
       }
       if (++s == S) { s = 0; ph ^= 1u; }
+      ++j;
     }
     // ---- end of this CTA's share of the tile: hand the warp's partial sums to the reducer
     const int buf = nf & 1;
@@ -515,7 +516,7 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
 }
 
 struct Plan {
-  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, groups, ahead, slow_s0, slow_ns;
+  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, groups, ahead;
   size_t smem;
   long long U;
   int CPT, T, NG, nprob;
@@ -553,20 +554,18 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   // L2 prefetch running ahead of them were slower, the prefetch instruction stalls its issuer once the queue is deep).
   // Tunables (environment, read once): STATETREE_GEMV_CTAS_PER_SM, STATETREE_GEMV_SMEM_KB, STATETREE_GEMV_STAGES,
   // STATETREE_GEMV_AHEAD (units of L2 prefetch ahead of the ring, 0 = off).
-  static int slots_per_sm = 0, budget_kb = 0, ahead = 0, max_stages = 0, slow_s0 = 0, slow_ns = 0;
+  static int slots_per_sm = 0, budget_kb = 0, ahead = 0, max_stages = 0;
   if (slots_per_sm == 0) {
     const char* v;
     slots_per_sm = (v = getenv("STATETREE_GEMV_CTAS_PER_SM")) ? atoi(v) : 2;
     budget_kb = (v = getenv("STATETREE_GEMV_SMEM_KB")) ? atoi(v) : 113;
     ahead = (v = getenv("STATETREE_GEMV_AHEAD")) ? atoi(v) : 0;
     max_stages = (v = getenv("STATETREE_GEMV_STAGES")) ? atoi(v) : 8;
-    slow_s0 = (v = getenv("STATETREE_GEMV_SLOW_S0")) ? atoi(v) : 0;
-    slow_ns = (v = getenv("STATETREE_GEMV_SLOW_NS")) ? atoi(v) : 0;
     if (slots_per_sm < 1) slots_per_sm = 1;
     if (ahead < 0) ahead = 0;
     if (ahead > 32) ahead = 32;
   }
-  p.ahead = ahead; p.slow_s0 = slow_s0; p.slow_ns = slow_ns;
+  p.ahead = ahead;
   int per_sm = slots_per_sm;
   int stages = (int)((budget_kb * 1024 - (long long)fixed) / p.stage_bytes);
   if (stages < 2) {
@@ -602,7 +601,7 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE);
   a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages;
   a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows; a.xwhole = p.xwhole; a.xw_stride = p.xw_stride;
-  a.xw_bytes = p.xw_bytes; a.ahead = p.ahead; a.slow_s0 = p.slow_s0; a.slow_ns = p.slow_ns;
+  a.xw_bytes = p.xw_bytes; a.ahead = p.ahead;
   const long long need = (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
   ST_REQUIRE(p.maxcover == 1 || (a.ws && ws_bytes >= need), "%s: workspace of %lld bytes needed, %lld given", who, need,
              ws_bytes);
