@@ -513,6 +513,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-bf16", action="store_true", help="skip the dense BF16 (cuBLAS) control pass")
     ap.add_argument("--no-fused", action="store_true", help="skip the extra pass with fused q/k/v and gate/up trees")
     ap.add_argument("--moe-batch", default="1,8,32,64")
     ap.add_argument("--prompt", type=int, default=512)
@@ -736,6 +737,33 @@ def main():
                  "ms_per_step": ms_f, "value": step_bytes / (ms_f * 1e-3) / 1e9, "unit": "GB/s",
                  "frac": step_bytes / (ms_f * 1e-3) / 1e9 / peaks()[0], "gpu_launches": 4 * args.layers * args.steps}
         del fgraph, flayers
+    # ---- BF16 control: the same step over dense BF16 copies of the same weights through torch.matmul (cuBLAS), the
+    # comparison the reference's per-layer GEMV table makes (RESULTS.md:176-183); 36 distinct buffers per shape as above
+    control = None
+    if world == 1 and not args.no_bf16:
+        dense = [[tl.dequantize() for tl in row] for row in layers]
+        douts = [torch.empty_like(o) for o in outs]
+
+        def run_dense():
+            for row in dense:
+                for W, xin, y in zip(row, ins, douts):
+                    torch.matmul(xin, W.t(), out=y)
+
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            run_dense()
+        side.synchronize()
+        dgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(dgraph, stream=side):
+            run_dense()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            dgraph.replay()
+        ms_d = timed(dgraph.replay, args.steps)
+        control = {"what": "same step, dense BF16 copies of the same weights, torch.matmul (cuBLAS) in one CUDA graph",
+                   "ms_per_step": ms_d, "speedup_vs_bf16": ms_d / ms,
+                   "speedup_vs_bf16_fused": (ms_d / fused["ms_per_step"]) if fused else None}
+        del dgraph, dense
     status = ops.device_status()
 
     def leave():
@@ -776,6 +804,8 @@ def main():
             "bf16_equivalent_gbs": value * 16.0 / 12.125}
     if fused is not None:
         line["fused_qkv_gate_up"] = fused
+    if control is not None:
+        line["bf16_control"] = control
     if not args.no_cpu and world == 1:
         val, dt, cores = cpu_reference(2, 1, B)
         line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",

@@ -162,6 +162,11 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start while
+// its predecessor in the stream still runs: griddepcontrol.wait blocks until that predecessor has completed and its
+// writes are visible (a no-op for an ordinary launch); launch_dependents lets the successor's CTAs be scheduled early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

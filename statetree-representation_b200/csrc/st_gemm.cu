@@ -85,16 +85,6 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t da, uint64_t db
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                :: "r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-               : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
@@ -271,7 +261,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
       }
       tc_commit(accbar);                                          // arrives when every MMA of this issuer has completed
 #ifdef ST_PROF
-      if (a.prof && m == 0) for (int q = 0; q < 4; ++q) a.prof[blockIdx.x * 64 + 5 + q - (q == 3 ? -5 : 0)] = gck[q];
+      if (a.prof && m == 0) for (int q = 0; q < 4; ++q) a.prof[blockIdx.x * 64 + 5 + q + (q == 3 ? 6 : 0)] = gck[q];
 #endif
     }
   } else {
@@ -321,6 +311,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
         rr.l0 = rr.l1 = rr.st = make_uint4(i, i, i, i); rr.nodes = i;
       } else {
 #endif
+      GCK(5);                                                     // escape prefetch
       if (!wait_decode(rfull + r, (uint32_t)rk & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
         break;
@@ -385,7 +376,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
       GCK(4);                                                     // stmatrix + fence + arrive
     }
 #ifdef ST_PROF
-    if (a.prof && tid == 0) for (int q = 0; q < 5; ++q) a.prof[blockIdx.x * 64 + 8 + q] = gck[q];
+    if (a.prof && tid == 0) for (int q = 0; q < 6; ++q) a.prof[blockIdx.x * 64 + 8 + q] = gck[q];
 #endif
     // ---------------------------------------------------------------- epilogue 1: accumulator -> own shared memory
     const bool acc_ok = GW(accbar, 0u);

@@ -99,8 +99,6 @@ __device__ __forceinline__ long long out_row(const GemvArgs& a, int p, int n) {
 }
 
 __device__ __forceinline__ int cta_of_unit(long long u, long long U, int C) { return (int)(((u + 1) * C - 1) / U); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Walks a CTA's units without divisions: problem p, tile, unit c inside the tile.  The CTA's range [u0, u1) is
 // visited as two segments: first the units of the trailing tile it shares with the next CTA, then the rest.  Both
@@ -522,15 +520,6 @@ struct Plan {
   int CPT, T, NG, nprob;
 };
 
-bool pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* v = getenv("STATETREE_PDL");
-    on = (v && v[0] == '0') ? 0 : 1;
-  }
-  return on == 1;
-}
-
 // nx = activation rows staged per unit (the batch for a dense matrix, 1 per slot, 8 per block of slots).
 template <int NT>
 Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
@@ -629,7 +618,7 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = st::pdl_enabled() ? 1 : 0;
   if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemv_kernel<NT, MODE, G>, a), who)) return e;
   return 0;
 }

@@ -6,6 +6,8 @@
 #include "../../include/statetree_b200.h"
 #include "st_host.h"
 
+#include <stdlib.h>
+
 namespace {
 thread_local char g_err[512] = "";
 __device__ int g_status[8];
@@ -26,6 +28,14 @@ int fail(const char* fmt, ...) {
 int cuda_fail(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return 0;
   return fail("%s: %s", what, cudaGetErrorString(e));
+}
+bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("STATETREE_PDL");
+    on = (v && v[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
 }
 int sm_count() {
   int dev = 0;

@@ -90,6 +90,8 @@ __device__ void chain_put(const AppendArgs& a, EscCursor& c, uint32_t* slots, ui
 // encoded row by row with shared-memory byte stores, and the unit goes back to the page as 100 16-byte stores.
 __global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
   __shared__ __align__(16) uint8_t s_unit[8][RKV];
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int units = a.H * 4;
@@ -292,6 +294,8 @@ __global__ void __launch_bounds__(ATT_NW * 32) kv_attn_kernel(const AttnArgs a) 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int j = blockIdx.x % a.S, bh = blockIdx.x / a.S;
   const int h = bh % a.Hkv, b = bh / a.Hkv, Hq = a.Hkv * G;
+  pdl_wait();                               // queries, lengths and the pages of this step come from earlier kernels
+  pdl_launch_dependents();
   const int len = a.lens[b], st0 = a.starts ? a.starts[b] : 0;
   const int pfirst = st0 / PAGE;
   const int npg = len > st0 ? (int)min((long long)(len + PAGE - 1) / PAGE, a.bts) : 0;
@@ -456,6 +460,8 @@ __global__ void __launch_bounds__(ATT_NW * 32) kv_attn_kernel(const AttnArgs a) 
 __global__ void __launch_bounds__(128) kv_merge_kernel(const float* __restrict__ wo, const float* __restrict__ wml,
                                                        uint16_t* __restrict__ out, long long os, int Hq, int S) {
   const int bq = blockIdx.x, d = threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   float M = -INFINITY;
   for (int j = 0; j < S; ++j) M = fmaxf(M, wml[((size_t)bq * S + j) * 2]);
   float L = 0.f, O = 0.f;
@@ -482,8 +488,8 @@ int attn_launch_cfg(const AttnArgs& a, int B, cudaStream_t st) {
       return e;
     set[dev] = true;
   }
-  kv_attn_kernel<G, NW, STG><<<(unsigned)(B * a.Hkv * a.S), NW * 32, smem, st>>>(a);
-  return 0;
+  return st::launch("st_kv_attn launch", kv_attn_kernel<G, NW, STG>, dim3((unsigned)(B * a.Hkv * a.S)), dim3(NW * 32),
+                    (size_t)smem, st, a);
 }
 
 template <int G>
@@ -517,9 +523,8 @@ extern "C" int st_kv_append(const void* K, const void* V, int64_t ks, int64_t vs
   // and the grid shrinks 16-fold; short calls (decode steps) keep one warp per token
   a.gsz = N >= 1024 ? 16 : 1;
   const long long warps = ((N + a.gsz - 1) / a.gsz) * H * 4;
-  kv_append_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(a);
-  ST_LAUNCH_CHECK("st_kv_append launch");
-  return 0;
+  return st::launch("st_kv_append launch", kv_append_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0,
+                    (cudaStream_t)stream, a);
 }
 
 extern "C" int st_kv_dequant_blocks(const void* kv, int64_t nblocks, int64_t H, const uint32_t* pool, int64_t P,
@@ -569,10 +574,8 @@ extern "C" int st_kv_attn(const void* q, int64_t qs, int64_t B, int64_t Hq, cons
     default: return st::fail("st_kv_attn: query heads per KV head must be 1, 2, 4 or 8 (got %lld)", (long long)(Hq / Hkv));
   }
   if (e) return e;
-  ST_LAUNCH_CHECK("st_kv_attn launch");
-  if (S > 1) {
-    kv_merge_kernel<<<(unsigned)(B * Hq), 128, 0, st_>>>(wo, wml, (uint16_t*)out, os, (int)Hq, (int)S);
-    ST_LAUNCH_CHECK("st_kv_attn merge launch");
-  }
+  if (S > 1)
+    return st::launch("st_kv_attn merge launch", kv_merge_kernel, dim3((unsigned)(B * Hq)), dim3(128), 0, st_,
+                      (const float*)wo, (const float*)wml, (uint16_t*)out, (long long)os, (int)Hq, (int)S);
   return 0;
 }

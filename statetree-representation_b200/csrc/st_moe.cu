@@ -8,6 +8,8 @@ namespace {
 template <bool WBF16>
 __global__ void __launch_bounds__(256) wsum_kernel(const uint4* __restrict__ Y, const void* __restrict__ w,
                                                    uint4* __restrict__ out, long long T, int K, int H8) {
+  st::pdl_wait();
+  st::pdl_launch_dependents();
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= T * H8) return;
   const long long t = i / H8;
@@ -31,14 +33,39 @@ __global__ void __launch_bounds__(256) wsum_kernel(const uint4* __restrict__ Y, 
 }
 
 // act[s, i] = bf16(silu(gate)) * up with gate = gu[s, i], up = gu[s, I + i]
+__device__ __forceinline__ __nv_bfloat16 silu_mul_one(__nv_bfloat16 gate, __nv_bfloat16 up) {
+  const float gte = __bfloat162float(gate);
+  return __hmul(__float2bfloat16_rn(gte / (1.f + __expf(-gte))), up);
+}
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __restrict__ gu,
                                                        __nv_bfloat16* __restrict__ act, long long S, long long I) {
+  st::pdl_wait();
+  st::pdl_launch_dependents();
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= S * I) return;
   const long long s = i / I, c = i % I;
-  const float gte = __bfloat162float(gu[s * 2 * I + c]);
-  const __nv_bfloat16 sg = __float2bfloat16_rn(gte / (1.f + __expf(-gte)));
-  act[i] = __hmul(sg, gu[s * 2 * I + I + c]);
+  act[i] = silu_mul_one(gu[s * 2 * I + c], gu[s * 2 * I + I + c]);
+}
+// eight values per thread, 16-byte loads and stores (I a multiple of 8, 16-byte aligned rows); blockIdx.y = row
+__global__ void __launch_bounds__(256) silu_mul_vec_kernel(const uint4* __restrict__ gu, uint4* __restrict__ act, int I8) {
+  st::pdl_wait();
+  st::pdl_launch_dependents();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= I8) return;
+  const size_t s = blockIdx.y;
+  const uint4 g = gu[s * 2 * I8 + c], u = gu[s * 2 * I8 + I8 + c];
+  const uint32_t gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(&gs[j]);
+    const __nv_bfloat162 uv = *reinterpret_cast<const __nv_bfloat162*>(&us[j]);
+    __nv_bfloat162 r;
+    r.x = silu_mul_one(gv.x, uv.x);
+    r.y = silu_mul_one(gv.y, uv.y);
+    o[j] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  act[s * I8 + c] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 }  // namespace
 
@@ -49,21 +76,18 @@ extern "C" int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int6
   ST_REQUIRE(Y && w && out && st::aligned16(Y) && st::aligned16(out), "st_wsum: null or unaligned pointer");
   const long long n = T * (H / 8);
   const unsigned grid = (unsigned)((n + 255) / 256);
-  if (w_bf16)
-    wsum_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)Y, w, (uint4*)out, T, (int)K, (int)(H / 8));
-  else
-    wsum_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)Y, w, (uint4*)out, T, (int)K, (int)(H / 8));
-  ST_LAUNCH_CHECK("st_wsum launch");
-  return 0;
+  return st::launch("st_wsum launch", w_bf16 ? wsum_kernel<true> : wsum_kernel<false>, dim3(grid), dim3(256), 0,
+                    (cudaStream_t)stream, (const uint4*)Y, w, (uint4*)out, (long long)T, (int)K, (int)(H / 8));
 }
 
 extern "C" int st_silu_mul(const void* gu, void* act, int64_t S, int64_t I, void* stream) {
   ST_REQUIRE(S >= 0 && I > 0, "st_silu_mul: sizes");
   if (S == 0) return 0;
   ST_REQUIRE(gu && act, "st_silu_mul: null pointer");
+  if (I % 8 == 0 && S <= 65535 && st::aligned16(gu) && st::aligned16(act))
+    return st::launch("st_silu_mul launch", silu_mul_vec_kernel, dim3((unsigned)((I / 8 + 255) / 256), (unsigned)S),
+                      dim3(256), 0, (cudaStream_t)stream, (const uint4*)gu, (uint4*)act, (int)(I / 8));
   const long long n = S * I;
-  silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, S, I);
-  ST_LAUNCH_CHECK("st_silu_mul launch");
-  return 0;
+  return st::launch("st_silu_mul launch", silu_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                    (cudaStream_t)stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, (long long)S, (long long)I);
 }
