@@ -494,12 +494,15 @@ int attn_launch_cfg(const AttnArgs& a, int B, cudaStream_t st) {
 
 template <int G>
 int attn_launch(const AttnArgs& a, int B, cudaStream_t st) {
-  static int cfg = -1;                       // STATETREE_ATTN_CFG: 1 = 4 warps x 3 stages (default), 0 = 8 warps x 2
+  // STATETREE_ATTN_CFG (tuning aid): 2 = 4 warps x 2 page stages, three CTAs per SM (default: the kernel is bound by
+  // instruction latency, and twelve warps per SM hide more of it than eight with deeper rings; 4.5 TB/s at batch 32 x 4K
+  // against 4.0), 1 = 4 warps x 3 stages, 0 = 8 warps x 2
+  static int cfg = -1;
   if (cfg < 0) {
     const char* v = getenv("STATETREE_ATTN_CFG");
-    cfg = v ? atoi(v) : 1;
+    cfg = v ? atoi(v) : 2;
   }
-  return cfg == 1 ? attn_launch_cfg<G, 4, 3>(a, B, st) : attn_launch_cfg<G, 8, 2>(a, B, st);
+  return cfg == 1 ? attn_launch_cfg<G, 4, 3>(a, B, st) : (cfg == 2 ? attn_launch_cfg<G, 4, 2>(a, B, st) : attn_launch_cfg<G, 8, 2>(a, B, st));
 }
 }  // namespace
 

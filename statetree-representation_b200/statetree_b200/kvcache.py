@@ -12,11 +12,13 @@ RKV = 1600
 
 
 def decode_splits(B, Hkv, max_pages, sms=148, min_pages=4):
-    """splits of each sequence's pages over CTAs: the power of two nearest (in ratio) to two CTAs per SM, at least
-    min_pages pages per split, at most 64.  A function of the batch size and the longest context only, so one captured
-    graph per batch size serves every step (the role of the reference's statetree/vllm_kv.py:42-50, re-sized for 148
-    SMs; measured on B200: batch 8 is fastest at 4 splits, batch 32 and up at 1, batch 1 at 32)."""
-    want = 2.0 * sms / (B * Hkv)
+    """splits of each sequence's pages over CTAs: a power of two, about one CTA per SM for a single sequence and never
+    fewer than 4 (three CTAs of four warps fit an SM, and CTAs a few times the slot count balance better than one wave
+    of long ones), at least min_pages pages per split, at most 64.  A function of the batch size and the longest
+    context only, so one captured graph per batch size serves every step (the role of the reference's
+    statetree/vllm_kv.py:42-50, re-sized for 148 SMs; measured on B200 at 4K context: batch 1 is fastest at 16 splits,
+    batch 8 at 4-6, batch 32 and 64 at 4)."""
+    want = max(4.0, 1.05 * sms / (B * Hkv))
     s = 1
     while s * 2 <= want * 1.42 and s * 2 <= 64 and max_pages // (s * 2) >= min_pages:
         s *= 2

@@ -100,7 +100,7 @@ def test_moe_align_layout():
 
 def test_decode_split_heuristic():
     from statetree_b200.kvcache import decode_splits
-    assert decode_splits(1, 8, 1024) == 32 and decode_splits(64, 8, 1024) == 1
+    assert decode_splits(1, 8, 1024) == 16 and decode_splits(64, 8, 1024) == 4 and decode_splits(8, 8, 8) == 2
     for B in (1, 8, 32, 64):
         for pages in (64, 256, 1024):
             s = decode_splits(B, 8, pages)
