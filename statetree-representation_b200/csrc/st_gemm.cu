@@ -112,11 +112,14 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
   return v;
 }
 
-constexpr int DG = 2;                        // decode groups: this many k-tiles are decoded at a time
-constexpr int NDW = DG * NDEC;               // decode warps
-constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;     // producer (records), producer (activations), MMA issuers
-constexpr int NMMA = 2;                      // MMA issuer warps; a.nmma of them work (issuer m: k-tiles m, m + nmma, ...)
-constexpr int GEMM_THREADS = (NDW + 2 + NMMA) * 32;
+// DG decode groups of eight warps (group g takes the k-tiles g, g + DG, ...), a record producer, an activation
+// producer and DG MMA issuer warps.  DG = 2: one CTA per SM (any token tile).  DG = 1: 11 warps and at most half an
+// SM's shared memory, so two CTAs share an SM (a tuning aid; slower for the shapes measured).
+template <int DG> struct Roles {
+  static constexpr int NDW = DG * NDEC;                                     // decode warps
+  static constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;         // role warps
+  static constexpr int THREADS = (NDW + 2 + DG) * 32;
+};
 #ifdef ST_GEMM_SPINWAIT
 #define GW mbar_wait_spin
 #else
@@ -147,8 +150,11 @@ constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of on
 // the rank).  After its main loop every CTA parks its fp32 accumulator tile in its own shared memory; after a cluster
 // barrier CTA j adds the KS tiles for its share of the token columns through distributed shared memory, in rank
 // order (bit-identical from run to run), and stores BF16.  No partial sums travel through global memory.
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap,
-                                                                const __grid_constant__ CUtensorMap wmap) {
+template <int DG>
+__global__ void __launch_bounds__(Roles<DG>::THREADS, DG == 1 ? 2 : 1)
+gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
+  constexpr int NDW = Roles<DG>::NDW, W_RAW = Roles<DG>::W_RAW, W_X = Roles<DG>::W_X, W_MMA = Roles<DG>::W_MMA;
+  constexpr int NMMA = DG;                                     // issuer warps; a.nmma of them work
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int NT = a.NT, S = a.stages, R = a.rstages;
@@ -187,6 +193,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   if (tid == 0) GPROF(1);
+  pdl_launch_dependents();
 
   if (warp == W_RAW) {
     // ---------------------------------------------------------------- record producer: one tiled TMA load per k-tile
@@ -207,8 +214,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
       }
     }
   } else if (warp == W_X) {
-    // ---------------------------------------------------------------- activation producer
+    // ---------------------------------------------------------------- activation producer.  The activations are the
+    // only input an earlier kernel of the stream may still be writing: with programmatic dependent launch the CTA
+    // starts (and its record producer streams weights) under the tail of that kernel, and this thread is the one that
+    // waits for it.  Everything that touches the output is downstream of the first activation tile.
     if (lane == 0) {
+      pdl_wait();
       for (int i = 0, s = 0, k = 0; i < nk; ++i, s = (s + 1 == S ? 0 : s + 1), k += (s == 0)) {
         if (k > 0 && !GW(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
 #ifdef ST_PROF
@@ -384,10 +395,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs a,
     if (tid == 0) GPROF(2);
     tc_fence_after();
     float* stg = reinterpret_cast<float*>(smem);                 // [NT][128] fp32, over the (now idle) ring
-    const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column quarter (warps 0..15)
-    const int cper = NT / 4;
+    const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column share of the warp
+    const int cper = NT / (NDW / 4);
     const bool two = a.nmma > 1 && nk > 1;                       // the second issuer had a k-tile
-    for (int c0 = cg * cper; warp < 16 && c0 < (cg + 1) * cper; c0 += 16) {
+    for (int c0 = cg * cper; c0 < (cg + 1) * cper; c0 += 16) {
       uint32_t v[32], w[32];                                     // (the x16 load fills the first sixteen)
       const uint32_t t0 = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;
       tmem_ld16(t0, v);
@@ -470,7 +481,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-struct GemmPlan { int NT, TT, RB, KS, stages, rstages, nmma, bar_off; size_t smem; };
+struct GemmPlan { int NT, TT, RB, KS, DG, stages, rstages, nmma, bar_off; size_t smem; };
 
 GemmPlan gemm_plan(long long M, long long N, long long B) {
   GemmPlan p;
@@ -479,45 +490,88 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   p.RB = (int)(M / 128);
   const int NG = (int)(N / 64), sms = st::sm_count();
   const long long units = (long long)p.RB * p.TT;
-  // split of the k range = cluster size (<= 8): fill the SMs, but every extra split costs an accumulator tile of
-  // distributed-shared-memory traffic in the epilogue
+  // One CTA of two decode groups per SM.  STATETREE_GEMM_DG=1 (tuning aid) runs two CTAs of one group each per SM for
+  // the 64- and 128-token tiles instead; measured slower (6.67 vs 5.22 ms per step at batch 64): twice the k-split
+  // halves every CTA's main loop while its start-up and epilogue stay.
+  static int forced_dg = -1;
+  if (forced_dg < 0) { const char* v = getenv("STATETREE_GEMM_DG"); forced_dg = v ? atoi(v) : 0; }
+  p.DG = (forced_dg == 1 && p.NT < 256) ? 1 : 2;
+  const long long slots = (long long)sms * (p.DG == 1 ? 2 : 1);
+  // split of the k range = cluster size (<= 8): fill the CTA slots, but every extra split costs an accumulator tile
+  // of distributed-shared-memory traffic in the epilogue
   // one wave only: a second wave pays the start-up and the epilogue again (measured: 288 CTAs in two waves took 72 us
-  // where 96 CTAs in one take ~45), so among the splits that fit the SMs take the one that fills them best
+  // where 96 CTAs in one take ~45), so among the splits that fit the slots take the one that fills them best
   int best = 1;
   double best_score = -1.0;
   const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 8 ? 8 : NG / 4);
   for (int ks = 1; ks <= ksmax; ++ks) {
     const long long ctas = units * ks;
-    if (ctas > sms && ks > 1) break;
-    const long long waves = (ctas + sms - 1) / sms;
-    const double score = (double)ctas / (double)(waves * sms) - 0.01 * ks * p.NT / 256.0;
+    if (ctas > slots && ks > 1) break;
+    const long long waves = (ctas + slots - 1) / slots;
+    const double score = (double)ctas / (double)(waves * slots) - 0.01 * ks * p.NT / 256.0;
     if (score > best_score + 1e-9) { best_score = score; best = ks; }
   }
   p.KS = best;
-  // tile stages (decoded weight tile + activation tile): enough to cover the L2 latency of the activation loads;
-  // the rest of the shared memory goes to the record ring, which covers the HBM latency
-  p.stages = p.NT >= 256 ? 3 : 4;
-  {
+  const size_t stage = A_TILE + (size_t)p.NT * 128;
+  const size_t stg = (size_t)p.NT * 128 * 4;                    // the parked accumulator tile reuses the rings
+  if (p.DG == 1) {
+    // half an SM: two tile stages (decode of k-tile i + 1 runs under the MMAs of k-tile i), the rest record slots
+    const size_t budget = 115712 - 1024 - 512;
+    p.stages = 2;
+    p.rstages = (int)((budget - p.stages * stage) / RAW_SLOT);
+    if (p.rstages > 8) p.rstages = 8;
+    p.nmma = 1;
+  } else {
+    // tile stages (decoded weight tile + activation tile): enough to cover the L2 latency of the activation loads;
+    // the rest of the shared memory goes to the record ring, which covers the HBM latency
+    p.stages = p.NT >= 256 ? 3 : 4;
     static int forced = -1;                                      // STATETREE_GEMM_STAGES: tile stages (tuning aid)
     if (forced < 0) { const char* v = getenv("STATETREE_GEMM_STAGES"); forced = v ? atoi(v) : 0; }
     if (forced >= 2) {
       p.stages = forced;
-      while (p.stages > 2 && (size_t)p.stages * (A_TILE + (size_t)p.NT * 128) + 3 * (size_t)RAW_SLOT > 212 * 1024) --p.stages;
+      while (p.stages > 2 && (size_t)p.stages * stage + 3 * (size_t)RAW_SLOT > 212 * 1024) --p.stages;
     }
+    p.rstages = (int)((212 * 1024 - p.stages * stage) / RAW_SLOT);
+    if (p.rstages > 12) p.rstages = 12;
+    // two MMA issuers need every stage and record slot owned by one decode group: even counts of both
+    p.nmma = (p.stages % 2 == 0 && p.rstages >= 4) ? 2 : 1;
+    if (p.nmma == 2) p.rstages &= ~1;
   }
-  const size_t tiles = (size_t)p.stages * (A_TILE + (size_t)p.NT * 128);
-  p.rstages = (int)((212 * 1024 - tiles) / RAW_SLOT);
-  if (p.rstages > 12) p.rstages = 12;
-  // two MMA issuers need every stage and record slot owned by one decode group: even counts of both
-  p.nmma = (p.stages % 2 == 0 && p.rstages >= 4) ? 2 : 1;
-  if (p.nmma == 2) p.rstages &= ~1;
-  size_t ring = tiles + (size_t)p.rstages * RAW_SLOT;
+  size_t ring = (size_t)p.stages * stage + (size_t)p.rstages * RAW_SLOT;
   ring = (ring + 15) & ~(size_t)15;
-  const size_t stg = (size_t)p.NT * 128 * 4;                    // the parked accumulator tile reuses the rings
   if (ring < stg) ring = stg;
   p.bar_off = (int)ring;
   p.smem = ring + 1024 /* alignment slack */ + 512 /* barriers */;
   return p;
+}
+
+template <int DG>
+int gemm_launch(const GemmPlan& p, const GemmArgs& a, const CUtensorMap& xmap, const CUtensorMap& wmap, cudaStream_t stream) {
+  static bool set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !set[dev]) {
+    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemm_kernel<DG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   DG == 1 ? 115712 - 1024 : 220 * 1024),
+                              "st_gemm: shared memory attribute"))
+      return e;
+    set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.RB * p.TT * p.KS));
+  cfg.blockDim = dim3(Roles<DG>::THREADS);
+  cfg.dynamicSmemBytes = p.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)p.KS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = st::pdl_enabled() ? 2 : 1;
+  return st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel<DG>, a, xmap, wmap), "st_gemm launch");
 }
 }  // namespace
 
@@ -574,27 +628,5 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
 #endif
   // instruction descriptor: D fp32, A and B bf16, both K-major, N = NT, M = 128
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-  static bool set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !set[dev]) {
-    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024),
-                              "st_gemm: shared memory attribute"))
-      return e;
-    set[dev] = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(p.RB * p.TT * p.KS));
-  cfg.blockDim = dim3(GEMM_THREADS);
-  cfg.dynamicSmemBytes = p.smem;
-  cfg.stream = (cudaStream_t)stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)p.KS;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel, a, xmap, wmap), "st_gemm launch")) return e;
-  return 0;
+  return p.DG == 1 ? gemm_launch<1>(p, a, xmap, wmap, (cudaStream_t)stream) : gemm_launch<2>(p, a, xmap, wmap, (cudaStream_t)stream);
 }
