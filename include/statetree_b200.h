@@ -131,6 +131,30 @@ int st_kv_attn(const void* q, int64_t qs, int64_t B, int64_t Hq, const void* kv,
                const int32_t* starts, void* out, int64_t os, float* wo, float* wml, double scale, int64_t S,
                int64_t minpps, void* stream);
 
+/* ---- tensor-parallel exchange over NVLink peer memory -------------------------------------------------------------- *
+ * No counterpart in the reference: it has no communication code (under vLLM each rank runs the reference's kernels on
+ * its shard and vLLM all-reduces the outputs of the row-parallel o / down projections with NCCL).  These entry points
+ * do that all-reduce for the small decode-step tensors with plain peer loads and stores.
+ * Set-up, once per process: st_comm_alloc gives this rank's communication buffer (st_comm_bytes() of device memory,
+ * cleared); st_comm_export writes its 64-byte CUDA IPC handle, which the host code sends to the other ranks of the
+ * node (any channel); st_comm_import maps a peer's handle and returns a device pointer valid in this process.  The
+ * calls then take `bufs`, a host array of `world` device pointers indexed by rank (bufs[rank] = the own buffer).
+ * Every rank must make the same sequence of calls with the same sizes.  Waits on peers are bounded (about two
+ * seconds); a call that gives up leaves its output unwritten and sets the device status word (st_device_status). */
+int64_t st_comm_bytes(void);
+int st_comm_alloc(void** buf);
+int st_comm_free(void* buf);
+int st_comm_export(void* buf, void* handle64);
+int st_comm_import(const void* handle64, void** buf);
+int st_comm_close(void* buf);
+/* out[i] = sum over ranks of in[i], BF16, fp32 accumulation in rank order (the same bits on every rank); n a multiple
+ * of 8, at most 524288 values; in / out 16-byte aligned, may be the same buffer. */
+int st_allreduce(void* const* bufs, int rank, int world, const void* in, void* out, int64_t n, void* stream);
+/* st_allreduce of delta [rows, cols] fused with st_add_rmsnorm: x += sum over ranks of delta; out = RMSNorm(x) * w.
+ * rows <= 64, cols <= 8192 and a multiple of 8. */
+int st_allreduce_add_rmsnorm(void* const* bufs, int rank, int world, void* x, const void* delta, const void* w,
+                             void* out, int64_t rows, int64_t cols, double eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,273 @@
+// Tensor-parallel exchange over NVLink peer memory: a one-shot all-reduce of the small BF16 partial outputs of the
+// row-parallel linears (o and down projections: batch x hidden values per call), optionally fused with the residual
+// add and RMSNorm that consume it in a decode step.
+//
+// Every rank owns one communication buffer (plain device memory, exported to its peers as a CUDA IPC handle):
+//     flags  uint32 [MAX_RANKS][MAX_CTAS]   flags[p][c] = last epoch in which rank p's CTA c published its slice
+//     epoch  uint32 [MAX_CTAS]              calls made so far, per CTA slot (all ranks make the same calls)
+//     data   2 x MAX_CTAS x SLOT_BYTES      this rank's partial sums: one region per CTA slot, double-buffered by the
+//                                           parity of that slot's epoch (slots advance independently, so a slot's
+//                                           region is only ever touched by the same slot of the other ranks)
+// One call, CTA c of rank r: copy slice c of the local partials into its region of data[epoch & 1]; system-scope fence; store the
+// epoch into flags[r][c] of every peer (remote stores); wait until flags[p][c] of the own buffer reach the epoch for
+// every p (local loads; bounded); add slice c of every rank's data in rank order (remote loads, fp32) and write the
+// BF16 result.  The double buffer makes a second barrier unnecessary: a rank rewrites data[parity] two calls later,
+// after a barrier that every peer enters only when it has finished reading the earlier call.
+// The wait is bounded by wall time (~2 s); when it runs out the kernel records ERR_WAIT_PEER in the device status word
+// and leaves its output unwritten.  The reference has no communication code (vLLM adds NCCL collectives around it).
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include "../../include/statetree_b200.h"
+#include "st_common.cuh"
+#include "st_host.h"
+
+namespace {
+using namespace st;
+
+constexpr int MAX_RANKS = 8;
+constexpr int MAX_CTAS = 64;
+constexpr long long SLOT_BYTES = 16 << 10;                            // per CTA and call
+constexpr long long MAX_BYTES = MAX_CTAS * SLOT_BYTES;                // per call (1 MiB)
+constexpr size_t OFF_EPOCH = (size_t)MAX_RANKS * MAX_CTAS * 4;
+constexpr size_t OFF_DATA = OFF_EPOCH + MAX_CTAS * 4;                 // 2304: 256-byte aligned
+constexpr size_t COMM_BYTES = OFF_DATA + 2 * (size_t)MAX_BYTES;
+constexpr long long WAIT_NS = 2000000000ll;
+
+struct Peers {
+  uint8_t* buf[MAX_RANKS];                                            // buf[rank] is the local buffer
+};
+
+__device__ __forceinline__ long long now_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {           // never served from a stale local cache line
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint8_t* slot_data(uint8_t* buf, int half, int cta) {
+  return buf + OFF_DATA + (size_t)half * MAX_BYTES + (size_t)cta * SLOT_BYTES;
+}
+
+// Publishes the len bytes at src (16-byte units, len <= SLOT_BYTES) as slot `cta` of this call and returns once every
+// rank has published its slot `cta`.  Called by all threads of the CTA; returns the data half to read from, or -1
+// after a timeout.
+__device__ int publish_and_wait(const Peers& P, int rank, int world, const uint8_t* src, size_t len, int cta, int* status) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  uint8_t* mine = P.buf[rank];
+  if (threadIdx.x == 0) {
+    uint32_t* ep = reinterpret_cast<uint32_t*>(mine + OFF_EPOCH) + cta;
+    s_epoch = *ep + 1u;
+    *ep = s_epoch;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  uint8_t* dst = slot_data(mine, (int)(epoch & 1u), cta);
+  for (size_t i = (size_t)threadIdx.x * 16; i < len; i += (size_t)blockDim.x * 16)
+    *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const int p = threadIdx.x;
+    st_release_sys(reinterpret_cast<uint32_t*>(P.buf[p]) + rank * MAX_CTAS + cta, epoch);      // "rank's slot is there"
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine) + p * MAX_CTAS + cta;
+    const long long t0 = now_ns();
+    // epochs only grow; the signed difference also survives the 32-bit wrap
+    while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
+      if (now_ns() - t0 > WAIT_NS) {
+        atomicExch(status, ERR_WAIT_PEER);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok ? (int)(epoch & 1u) : -1;
+}
+
+// out = sum over ranks of the BF16 vectors `in` (n elements, a multiple of 8); grid <= MAX_CTAS
+__global__ void __launch_bounds__(256) allreduce_kernel(const Peers P, int rank, int world, const uint16_t* in,
+                                                        uint16_t* out, long long n, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long vecs = n / 8, per = (vecs + gridDim.x - 1) / gridDim.x;
+  const long long v0 = (long long)blockIdx.x * per, v1 = min(vecs, v0 + per);
+  const size_t off = (size_t)v0 * 16, len = v1 > v0 ? (size_t)(v1 - v0) * 16 : 0;
+  const int h = publish_and_wait(P, rank, world, reinterpret_cast<const uint8_t*>(in) + off, len, blockIdx.x, status);
+  if (h < 0) return;
+  for (size_t i = (size_t)threadIdx.x * 16; i < len; i += (size_t)blockDim.x * 16) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int p = 0; p < world; ++p) {
+      const uint4 v = ld_peer16(slot_data(P.buf[p], h, blockIdx.x) + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] += __uint_as_float(w[q] << 16);
+        acc[2 * q + 1] += __uint_as_float(w[q] & 0xFFFF0000u);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(out) + off + i) = o;
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* part) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += part[i];
+  return tot;
+}
+
+// One CTA per row: delta_sum = sum over ranks of `delta` rows (rank order, fp32, rounded to BF16 as the separate
+// all-reduce would); x += delta_sum (BF16 residual stream); out = RMSNorm(x) * w.  cols <= 8192, a multiple of 8.
+__global__ void __launch_bounds__(512) allreduce_add_rmsnorm_kernel(const Peers P, int rank, int world, uint16_t* x,
+                                                                    const uint16_t* delta, const uint16_t* w,
+                                                                    uint16_t* out, int cols, float eps, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float part[16];
+  const size_t rowb = (size_t)blockIdx.x * cols * 2;
+  const int h = publish_and_wait(P, rank, world, reinterpret_cast<const uint8_t*>(delta) + rowb, (size_t)cols * 2,
+                                 blockIdx.x, status);
+  if (h < 0) return;
+  float f[2][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int c = (threadIdx.x + k * 512) * 8;
+    if (c < cols) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int p = 0; p < world; ++p) {
+        const uint4 v = ld_peer16(slot_data(P.buf[p], h, blockIdx.x) + (size_t)c * 2);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] += __uint_as_float(u[q] << 16);
+          acc[2 * q + 1] += __uint_as_float(u[q] & 0xFFFF0000u);
+        }
+      }
+      const uint4 xv = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(x) + rowb + (size_t)c * 2);
+      const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+      uint32_t so[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t d = pack_bf16(acc[2 * q], acc[2 * q + 1]);      // the all-reduced delta is a BF16 tensor
+        const uint32_t s = pack_bf16(__uint_as_float(xs[q] << 16) + __uint_as_float(d << 16),
+                                     __uint_as_float(xs[q] & 0xFFFF0000u) + __uint_as_float(d & 0xFFFF0000u));
+        so[q] = s;
+        f[k][2 * q] = __uint_as_float(s << 16);
+        f[k][2 * q + 1] = __uint_as_float(s & 0xFFFF0000u);
+        ss += f[k][2 * q] * f[k][2 * q] + f[k][2 * q + 1] * f[k][2 * q + 1];
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(x) + rowb + (size_t)c * 2) = make_uint4(so[0], so[1], so[2], so[3]);
+    }
+  }
+  const float r = rsqrtf(block_sum(ss, part) / (float)cols + eps);
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int c = (threadIdx.x + k * 512) * 8;
+    if (c < cols) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(w + c);
+      const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t nrm = pack_bf16(f[k][2 * q] * r, f[k][2 * q + 1] * r);        // normalised value rounded, then scaled
+        o[q] = pack_bf16(__uint_as_float(nrm << 16) * __uint_as_float(ws[q] << 16),
+                         __uint_as_float(nrm & 0xFFFF0000u) * __uint_as_float(ws[q] & 0xFFFF0000u));
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(out) + rowb + (size_t)c * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+int fill_peers(Peers& P, void* const* bufs, int rank, int world, const char* who) {
+  ST_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "%s: rank %d of %d (2..%d ranks)", who, rank,
+             world, MAX_RANKS);
+  ST_REQUIRE(bufs != nullptr, "%s: null buffer table", who);
+  for (int p = 0; p < MAX_RANKS; ++p) P.buf[p] = nullptr;
+  for (int p = 0; p < world; ++p) {
+    ST_REQUIRE(bufs[p] != nullptr, "%s: buffer of rank %d missing", who, p);
+    P.buf[p] = (uint8_t*)bufs[p];
+  }
+  return 0;
+}
+}  // namespace
+
+extern "C" int64_t st_comm_bytes(void) { return (int64_t)COMM_BYTES; }
+
+extern "C" int st_comm_alloc(void** buf) {
+  ST_REQUIRE(buf != nullptr, "st_comm_alloc: null pointer");
+  if (int e = st::cuda_fail(cudaMalloc(buf, COMM_BYTES), "st_comm_alloc")) return e;
+  return st::cuda_fail(cudaMemset(*buf, 0, COMM_BYTES), "st_comm_alloc: clear");
+}
+
+extern "C" int st_comm_free(void* buf) { return st::cuda_fail(cudaFree(buf), "st_comm_free"); }
+
+extern "C" int st_comm_export(void* buf, void* handle64) {
+  ST_REQUIRE(buf && handle64, "st_comm_export: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  if (int e = st::cuda_fail(cudaIpcGetMemHandle(&h, buf), "st_comm_export")) return e;
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+
+extern "C" int st_comm_import(const void* handle64, void** buf) {
+  ST_REQUIRE(buf && handle64, "st_comm_import: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return st::cuda_fail(cudaIpcOpenMemHandle(buf, h, cudaIpcMemLazyEnablePeerAccess), "st_comm_import");
+}
+
+extern "C" int st_comm_close(void* buf) { return st::cuda_fail(cudaIpcCloseMemHandle(buf), "st_comm_close"); }
+
+extern "C" int st_allreduce(void* const* bufs, int rank, int world, const void* in, void* out, int64_t n, void* stream) {
+  Peers P;
+  if (int e = fill_peers(P, bufs, rank, world, "st_allreduce")) return e;
+  ST_REQUIRE(n > 0 && n % 8 == 0 && n * 2 <= MAX_BYTES, "st_allreduce: n must be a multiple of 8, at most %lld values",
+             (long long)(MAX_BYTES / 2));
+  ST_REQUIRE(in && out && st::aligned16(in) && st::aligned16(out), "st_allreduce: null or unaligned pointer");
+  int* status = st::status_ptr();
+  ST_REQUIRE(status != nullptr, "st_allreduce: no device status word");
+  const long long vecs = n / 8;
+  long long ctas = (vecs + 255) / 256;                                 // 4 KB per CTA and pass, at most SLOT_BYTES per CTA
+  if (ctas > 16) ctas = 16;
+  while (((vecs + ctas - 1) / ctas) * 16 > SLOT_BYTES) ++ctas;
+  return st::launch("st_allreduce launch", allreduce_kernel, dim3((unsigned)ctas), dim3(256), 0, (cudaStream_t)stream, P,
+                    rank, world, (const uint16_t*)in, (uint16_t*)out, (long long)n, status);
+}
+
+extern "C" int st_allreduce_add_rmsnorm(void* const* bufs, int rank, int world, void* x, const void* delta, const void* w,
+                                        void* out, int64_t rows, int64_t cols, double eps, void* stream) {
+  Peers P;
+  if (int e = fill_peers(P, bufs, rank, world, "st_allreduce_add_rmsnorm")) return e;
+  ST_REQUIRE(rows >= 1 && rows <= MAX_CTAS && cols > 0 && cols % 8 == 0 && cols <= 8192,
+             "st_allreduce_add_rmsnorm: at most %d rows of at most 8192 columns (a multiple of 8)", MAX_CTAS);
+  ST_REQUIRE(x && delta && w && out && st::aligned16(x) && st::aligned16(delta) && st::aligned16(w) && st::aligned16(out),
+             "st_allreduce_add_rmsnorm: null or unaligned pointer");
+  int* status = st::status_ptr();
+  ST_REQUIRE(status != nullptr, "st_allreduce_add_rmsnorm: no device status word");
+  return st::launch("st_allreduce_add_rmsnorm launch", allreduce_add_rmsnorm_kernel, dim3((unsigned)rows), dim3(512), 0,
+                    (cudaStream_t)stream, P, rank, world, (uint16_t*)x, (const uint16_t*)delta, (const uint16_t*)w,
+                    (uint16_t*)out, (int)cols, (float)eps, status);
+}

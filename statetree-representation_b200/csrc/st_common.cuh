@@ -22,7 +22,7 @@ constexpr int XSLOT = 15;          // escape slots of a pool extension block
 constexpr unsigned FULL = 0xFFFFFFFFu;
 
 // status word codes written by kernels that gave up on a bounded wait
-constexpr int ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_MMA = 3, ERR_WAIT_ACC = 4;
+constexpr int ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_MMA = 3, ERR_WAIT_ACC = 4, ERR_WAIT_PEER = 5;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;   // mbarrier try_wait rounds before a kernel gives up (~seconds)
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

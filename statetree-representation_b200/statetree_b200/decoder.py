@@ -111,6 +111,10 @@ class TreeDecoder:
             self.kc = [torch.zeros(batch, max_len, self.hkv, D, dtype=torch.bfloat16, device=self.dev) for _ in range(c.layers)]
             self.vc = [torch.zeros_like(k) for k in self.kc]
             self.lens = torch.zeros(batch, dtype=torch.int32, device=self.dev)
+        self.comm = None
+        if world > 1 and batch <= 64 and c.hidden <= 8192 and c.hidden % 8 == 0:
+            from .parallel import peer_comm
+            self.comm = peer_comm(group)
         self.graph = None
 
     def weight_bytes(self):
@@ -119,10 +123,16 @@ class TreeDecoder:
             n += sum(m.record_bytes() for m in blk)
         return n
 
-    def _allreduce(self, y):
-        if self.world > 1:
-            dist.all_reduce(y, group=self.group)
-        return y
+    def _add_norm(self, x, delta, h):
+        """x += (all-reduced) delta; h = RMSNorm(x) * w.  Under tensor parallelism delta is this rank's partial output of
+        a row-parallel projection: one kernel sums it over the ranks through peer memory and applies add + norm."""
+        c = self.cfg
+        if delta is not None and self.world > 1:
+            if self.comm is not None:
+                self.comm.all_reduce_add_rmsnorm(x, delta, self.norm_w, h, c.eps)
+                return
+            dist.all_reduce(delta, group=self.group)
+        ext().add_rmsnorm(x, delta, self.norm_w, h, c.eps)
 
     def _step(self):
         """one decode step for self.tokens at position self.pos; about ten launches per layer"""
@@ -134,7 +144,7 @@ class TreeDecoder:
         slots = self.cache.begin_step(B) if self.compressed else None
         delta = None
         for li, (qkv, o, gu, d) in enumerate(self.blocks):
-            E.add_rmsnorm(x, delta, self.norm_w, h, c.eps)
+            self._add_norm(x, delta, h)
             y = qkv(h)
             E.qk_norm_rope(y, self.head_norm_w, self.head_norm_w, self.cos, self.sin, self.pos_buf, qb, kb, c.eps)
             v = y[:, (self.hq + self.hkv) * D:].view(B, self.hkv, D)
@@ -145,13 +155,13 @@ class TreeDecoder:
             else:
                 att = _flash()(qb.view(B, 1, self.hq, D), self.kc[li], self.vc[li], k=kb.view(B, 1, self.hkv, D),
                                v=v.unsqueeze(1), cache_seqlens=self.lens, softmax_scale=scale)
-            delta = self._allreduce(o(att.reshape(B, self.hq * D)))
-            E.add_rmsnorm(x, delta, self.norm_w, h, c.eps)
+            delta = o(att.reshape(B, self.hq * D))
+            self._add_norm(x, delta, h)
             y = gu(h)
             act = torch.empty(B, y.shape[1] // 2, dtype=torch.bfloat16, device=self.dev)
             E.silu_mul(y, act)
-            delta = self._allreduce(d(act))
-        E.add_rmsnorm(x, delta, self.norm_w, h, c.eps)
+            delta = d(act)
+        self._add_norm(x, delta, h)
         logits = self.lm_head(h)
         if self.world > 1:
             parts = [torch.empty_like(logits) for _ in range(self.world)]

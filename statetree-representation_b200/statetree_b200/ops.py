@@ -39,6 +39,15 @@ _SIGNATURES = {
     "st_kv_append": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _int, _vp]),
     "st_kv_dequant": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "st_kv_dequant_blocks": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
+    "st_comm_bytes": (_i64, []),
+    "st_comm_alloc": (_int, [ctypes.POINTER(ctypes.c_void_p)]),
+    "st_comm_free": (_int, [_vp]),
+    "st_comm_export": (_int, [_vp, _vp]),
+    "st_comm_import": (_int, [_vp, ctypes.POINTER(ctypes.c_void_p)]),
+    "st_comm_close": (_int, [_vp]),
+    "st_allreduce": (_int, [ctypes.POINTER(ctypes.c_void_p), _int, _int, _vp, _vp, _i64, _vp]),
+    "st_allreduce_add_rmsnorm": (_int, [ctypes.POINTER(ctypes.c_void_p), _int, _int, _vp, _vp, _vp, _vp, _i64, _i64,
+                                        ctypes.c_double, _vp]),
     "st_kv_attn": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp,
                           _dbl, _i64, _i64, _vp]),
 }

@@ -43,9 +43,91 @@ def shard_tree(tree, kind, rank, world):
     return tree.narrow(dim, lo, hi - lo).contiguous()
 
 
+class PeerComm:
+    """Peer-memory exchange between the ranks of one node (one process per GPU): every rank allocates a communication
+    buffer in the kernel library, the 64-byte CUDA IPC handles travel through torch.distributed, and the all-reduce of
+    the small decode-step tensors then runs as one kernel of peer loads and stores per rank (csrc/st_comm.cu) instead of
+    an NCCL call.  Capturable in CUDA graphs (the call sequence must be the same on every rank, as with NCCL).
+    STATETREE_PEER_COMM=0 keeps NCCL."""
+
+    MAX_VALUES = 524288
+
+    def __init__(self, group=None, device=None):
+        import ctypes
+        from . import ops
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if not 2 <= self.world <= 8:
+            raise RuntimeError("PeerComm: 2 to 8 ranks of one node")
+        self.device = torch.device(device if device is not None else torch.cuda.current_device())
+        L = ops.lib()
+        with torch.cuda.device(self.device):
+            own = ctypes.c_void_p()
+            ops._check(L.st_comm_alloc(ctypes.byref(own)))
+            handle = ctypes.create_string_buffer(64)
+            ops._check(L.st_comm_export(own, handle))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(own.value)
+                else:
+                    peer = ctypes.c_void_p()
+                    ops._check(L.st_comm_import(ctypes.create_string_buffer(h, 64), ctypes.byref(peer)))
+                    ptrs.append(peer.value)
+        self._own = own
+        self._bufs = (ctypes.c_void_p * self.world)(*ptrs)
+        self._lib = L
+        dist.barrier(group=group)                              # every buffer is mapped before the first call
+
+    def all_reduce(self, y):
+        """y (BF16, contiguous, a multiple of 8 values) <- sum over ranks, in place"""
+        from . import ops
+        assert y.dtype == torch.bfloat16 and y.is_contiguous() and y.numel() % 8 == 0 and y.numel() <= self.MAX_VALUES
+        with torch.cuda.device(y.device):
+            ops._check(self._lib.st_allreduce(self._bufs, self.rank, self.world, ops._ptr(y), ops._ptr(y), y.numel(),
+                                              ops._stream(y)))
+        return y
+
+    def all_reduce_add_rmsnorm(self, x, delta, w, out, eps):
+        """x += sum over ranks of delta; out = RMSNorm(x) * w  (x, delta, out BF16 [rows, cols])"""
+        from . import ops
+        rows, cols = x.shape
+        with torch.cuda.device(x.device):
+            ops._check(self._lib.st_allreduce_add_rmsnorm(self._bufs, self.rank, self.world, ops._ptr(x), ops._ptr(delta),
+                                                          ops._ptr(w), ops._ptr(out), rows, cols, float(eps),
+                                                          ops._stream(x)))
+        return out
+
+
+_COMMS = {}
+PEER_COMM_DEFAULT = "0"
+
+
+def peer_comm(group=None):
+    """the PeerComm of a process group (created on first use), or None when it is switched off or does not apply"""
+    import os
+    if os.environ.get("STATETREE_PEER_COMM", PEER_COMM_DEFAULT) == "0" or not torch.cuda.is_available():
+        return None
+    if not (dist.is_available() and dist.is_initialized()) or not 2 <= dist.get_world_size(group) <= 8:
+        return None
+    if dist.get_backend(group) != "nccl":
+        return None
+    key = id(group)
+    if key not in _COMMS:
+        _COMMS[key] = PeerComm(group)
+    return _COMMS[key]
+
+
 def reduce_partials(y, group=None):
-    """sum the row-parallel partial outputs over the tensor-parallel group, in place"""
+    """sum the row-parallel partial outputs over the tensor-parallel group, in place: the peer-memory kernel for the
+    small BF16 tensors of a decode step, NCCL otherwise (and on CPU / gloo)"""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        comm = peer_comm(group) if y.is_cuda else None
+        if (comm is not None and y.dtype == torch.bfloat16 and y.is_contiguous() and y.numel() % 8 == 0
+                and y.numel() <= PeerComm.MAX_VALUES):
+            return comm.all_reduce(y)
         dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
     return y
 
