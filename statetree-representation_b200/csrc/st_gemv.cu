@@ -571,6 +571,9 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
     // Prefer a grid whose CTA boundaries fall on tile boundaries (or cut every tile into equal parts) when one exists
     // within 20% of the slot count: a tile that is not shared needs no cross-CTA hand-over of partial sums at all.
     const long long tiles = (long long)nprob * p.T;
+    static int align = -1;                                       // STATETREE_GEMV_ALIGN=0: keep the slot count (tuning aid)
+    if (align < 0) { const char* v = getenv("STATETREE_GEMV_ALIGN"); align = v ? atoi(v) : 1; }
+    if (align)
     for (long long c = p.C; c * 5 >= (long long)p.C * 4 && c >= 1; --c) {
       const bool whole = tiles % c == 0;
       const bool even = c % tiles == 0 && p.CPT % (c / tiles) == 0;

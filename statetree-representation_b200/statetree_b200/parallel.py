@@ -102,7 +102,7 @@ class PeerComm:
 
 
 _COMMS = {}
-PEER_COMM_DEFAULT = "0"
+PEER_COMM_DEFAULT = "1"
 
 
 def peer_comm(group=None):
