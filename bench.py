@@ -106,6 +106,7 @@ def cpu_reference(steps, warmup, batch):
     import gen_inputs as G
     import oracle
     oracle.build()
+    oracle.set_threads(len(os.sched_getaffinity(0)))            # all the cores this process may use (torchrun sets 1)
     encs, xs = [], {}
     rs = np.random.RandomState(0)
     for name, M, N, _ in SHAPES:

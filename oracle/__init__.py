@@ -124,6 +124,11 @@ def threads():
     return int(lib().st_ref_threads())
 
 
+def set_threads(n):
+    """OpenMP threads of the C restatement (launchers export OMP_NUM_THREADS=1; the timed baseline uses the host's cores)"""
+    lib().st_ref_set_threads(int(n))
+
+
 # ------------------------------------------------------------------------------------------------ KV pages
 def kv_append(K, V, slots, kv, pool, pool_cnt, reuse=False):
     """K, V uint16 [N, H, 128]; slots int64 [N] (-1 = skip); kv uint8 [blocks, H, 2, 2, 1600] (in place); pool uint32

@@ -405,6 +405,16 @@ void st_ref_kv_attn_f64(const uint16_t* q, int64_t B, int Hq, const uint8_t* kv,
   }
 }
 
+/* launchers such as torchrun export OMP_NUM_THREADS=1; the timed CPU baseline asks for the cores it is allowed to use */
+void st_ref_set_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int st_ref_threads(void) {
 #ifdef _OPENMP
   extern int omp_get_max_threads(void);
