@@ -67,7 +67,86 @@ __global__ void __launch_bounds__(256) silu_mul_vec_kernel(const uint4* __restri
   }
   act[s * I8 + c] = make_uint4(o[0], o[1], o[2], o[3]);
 }
+// Groups the S (token, expert) pairs by expert in blocks of 8 (the layout vLLM's moe_align_block_size produces and
+// the grouped expert kernel consumes): sorted[nblk * 8] holds pair indices, expert-major, original order inside an
+// expert, every expert's run padded to a multiple of 8 with the value S; bexp[b] = expert of block b; npost = entries
+// in use.  One CTA does the whole job in shared memory: histogram, padded prefix sum, one warp per expert placing its
+// pairs in order with ballots, a binary search per block.  Expert ids outside [0, E) count as E - 1 / 0 (clamped).
+constexpr int ALIGN_MAX_E = 1024;
+template <bool IDS64>
+__global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict__ ids_, int S, int E, int nblk,
+                                                         int* __restrict__ sorted, int* __restrict__ bexp,
+                                                         int* __restrict__ npost) {
+  st::pdl_wait();
+  st::pdl_launch_dependents();
+  __shared__ int cnt[ALIGN_MAX_E], end_[ALIGN_MAX_E], wsum[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  auto id_of = [&](int i) {
+    long long v = IDS64 ? reinterpret_cast<const long long*>(ids_)[i] : (long long)reinterpret_cast<const int*>(ids_)[i];
+    return (int)(v < 0 ? 0 : (v >= E ? E - 1 : v));
+  };
+  for (int e = tid; e < E; e += 1024) cnt[e] = 0;
+  for (int i = tid; i < nblk * 8; i += 1024) sorted[i] = S;                // padding value
+  __syncthreads();
+  for (int i = tid; i < S; i += 1024) atomicAdd(&cnt[id_of(i)], 1);
+  __syncthreads();
+  // inclusive prefix sum of the padded counts: thread e < E (E <= 1024), warp scans + a scan of the warp totals
+  int room = tid < E ? (cnt[tid] + 7) / 8 * 8 : 0;
+  int v = room;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(st::FULL, v, o);
+    if (lane >= o) v += n;
+  }
+  if (lane == 31) wsum[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int w = wsum[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(st::FULL, w, o);
+      if (lane >= o) w += n;
+    }
+    wsum[lane] = w;
+  }
+  __syncthreads();
+  if (tid < E) end_[tid] = v + (warp ? wsum[warp - 1] : 0);
+  __syncthreads();
+  // placement: warp w takes experts w, w + 32, ...; pairs in original order (ballot prefix inside each 32-pair chunk)
+  for (int e = warp; e < E; e += 32) {
+    if (cnt[e] == 0) continue;
+    int at = end_[e] - (cnt[e] + 7) / 8 * 8;
+    for (int base = 0; base < S; base += 32) {
+      const int i = base + lane;
+      const bool hit = i < S && id_of(i) == e;
+      const unsigned m = __ballot_sync(st::FULL, hit);
+      if (hit) sorted[at + __popc(m & ((1u << lane) - 1u))] = i;
+      at += __popc(m);
+    }
+  }
+  // expert of every block: first expert whose end lies beyond the block's first slot (clamped for the unused tail)
+  for (int b = tid; b < nblk; b += 1024) {
+    const int slot = b * 8;
+    int lo = 0, hi = E;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (end_[mid] <= slot) lo = mid + 1; else hi = mid;
+    }
+    bexp[b] = lo < E ? lo : E - 1;
+  }
+  if (tid == 0) npost[0] = end_[E - 1];
+}
 }  // namespace
+
+extern "C" int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int32_t* sorted, int32_t* bexp,
+                            int32_t* npost, int64_t nblk, void* stream) {
+  ST_REQUIRE(S >= 1 && S <= (1 << 20) && E >= 1 && E <= ALIGN_MAX_E, "st_moe_align: 1..%d experts, up to 2^20 pairs",
+             ALIGN_MAX_E);
+  ST_REQUIRE(nblk >= S / 8 + (S < E ? S : E) && nblk * 8 < (1ll << 31), "st_moe_align: nblk must cover S / 8 + min(S, E) blocks");
+  ST_REQUIRE(ids && sorted && bexp && npost, "st_moe_align: null pointer");
+  return st::launch("st_moe_align launch", ids64 ? moe_align_kernel<true> : moe_align_kernel<false>, dim3(1), dim3(1024), 0,
+                    (cudaStream_t)stream, ids, (int)S, (int)E, (int)nblk, (int*)sorted, (int*)bexp, (int*)npost);
+}
 
 extern "C" int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H,
                        void* stream) {

@@ -4,6 +4,8 @@ block (reference 337-519) over the sm_100a kernels.  One kernel serves both slot
 beyond "few pairs: one problem per (token, expert) slot; many pairs: slots grouped by expert, each expert's records
 read once per block of 8 slots".
 """
+import os
+
 import torch
 import torch.nn as nn
 
@@ -57,9 +59,28 @@ def moe_gemv(tables, x, ids, M, xdiv):
     return y
 
 
+ALIGN_KERNEL = os.environ.get("STATETREE_MOE_ALIGN_KERNEL", "0") != "0"
+
+
 def moe_align(ids, E, bs=8):
     """Pairs grouped by expert in blocks of bs (the moe_align_block_size layout), with torch ops and no host sync:
     (sorted_ids int32 [nblk * bs], padded with S; bexp int32 [nblk]; npost int32 [1] = used entries)."""
+    ids = ids.reshape(-1)
+    S, dev = ids.numel(), ids.device
+    nblk = S // bs + min(S, E) + 1
+    if (ALIGN_KERNEL and ids.is_cuda and bs == 8 and 1 <= S <= (1 << 16) and E <= 1024
+            and ids.dtype in (torch.int64, torch.int32)):
+        # one CTA of the kernel library does the whole grouping (the torch formulation below is ~20 small launches)
+        sorted_ids = torch.empty(nblk * bs, dtype=torch.int32, device=dev)
+        bexp = torch.empty(nblk, dtype=torch.int32, device=dev)
+        npost = torch.empty(1, dtype=torch.int32, device=dev)
+        ext().moe_align(ids.contiguous(), E, sorted_ids, bexp, npost)
+        return sorted_ids, bexp, npost
+    return _moe_align_torch(ids, E, bs)
+
+
+def _moe_align_torch(ids, E, bs=8):
+    """the same layout with torch ops (CPU tensors, other block sizes, very long calls); the check for the kernel"""
     ids = ids.reshape(-1).to(torch.int64)
     S, dev = ids.numel(), ids.device
     nblk = S // bs + min(S, E) + 1

@@ -116,3 +116,18 @@ def test_tree_experts_block_matches_dense():
         te1 = TreeExperts(list(te.w13)[E // 2:], list(te.w2)[E // 2:])
         part = te0(x, ids, w, emap0).double() + te1(x, ids, w, emap1).double()
         assert float((part - ref).norm() / ref.norm()) < 2e-2, T
+
+
+@pytest.mark.gpu
+def test_moe_align_kernel_matches_torch_formulation():
+    from statetree_b200.experts import _moe_align_torch, moe_align
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    for S, E, dt in ((1, 8, torch.int64), (8, 128, torch.int64), (64, 128, torch.int32), (512, 128, torch.int64),
+                     (513, 129, torch.int64), (4096, 60, torch.int32), (20000, 1024, torch.int64), (300, 1, torch.int64)):
+        ids = torch.randint(0, E, (S,), device="cuda", generator=gen).to(dt)
+        if S >= 64:
+            ids[: S // 3] = ids[0]                                  # a crowded expert
+        got = moe_align(ids, E, 8)
+        want = _moe_align_torch(ids, E, 8)
+        for g, w, name in zip(got, want, ("sorted_ids", "bexp", "npost")):
+            assert g.dtype == w.dtype and torch.equal(g, w), (S, E, name)
