@@ -59,7 +59,7 @@ def moe_gemv(tables, x, ids, M, xdiv):
     return y
 
 
-ALIGN_KERNEL = os.environ.get("STATETREE_MOE_ALIGN_KERNEL", "0") != "0"
+ALIGN_KERNEL = os.environ.get("STATETREE_MOE_ALIGN_KERNEL", "1") != "0"   # 0: the torch formulation
 
 
 def moe_align(ids, E, bs=8):
