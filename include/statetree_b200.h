@@ -92,10 +92,12 @@ int st_moe_group_gemv(const int64_t* tp, const int64_t* eop, const int64_t* ebp,
                       void* stream);
 /* Pairs grouped by expert in blocks of 8 for st_moe_group_gemv: sorted int32 [nblk * 8] (pair indices, expert-major,
  * original order inside an expert, runs padded to a multiple of 8 with the value S), bexp int32 [nblk], npost int32
- * [1] = entries in use; ids int64 (ids64 = 1) or int32 [S], clamped to [0, E); nblk >= S / 8 + min(S, E); E <= 1024.
- * The reference takes this layout from vLLM's moe_align_block_size (statetree/experts.py:52-120). */
-int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int32_t* sorted, int32_t* bexp, int32_t* npost,
-                 int64_t nblk, void* stream);
+ * [1] = entries of the first used_bins experts (used_bins = E, or E - 1 when the last id collects the pairs of other
+ * ranks' experts, whose blocks the grouped kernel then never visits); ids int64 (ids64 = 1) or int32 [S], clamped to
+ * [0, E); nblk >= S / 8 + min(S, E); E <= 1024.  The reference takes this layout from vLLM's moe_align_block_size
+ * (statetree/experts.py:52-120). */
+int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int64_t used_bins, int32_t* sorted, int32_t* bexp,
+                 int32_t* npost, int64_t nblk, void* stream);
 /* out[t] = sum_j w[t, j] * Y[t * K + j] in fp32, expert order, BF16 out; w float32 (w_bf16 = 0) or BF16 (1).
  * Replaces `_C.wsum` (statetree/csrc/kernels.cu:1489-1535). */
 int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H, void* stream);

@@ -483,6 +483,52 @@ EncodeTiledFn encode_fn() {
 
 struct GemmPlan { int NT, TT, RB, KS, DG, stages, rstages, nmma, bar_off; size_t smem; };
 
+template <int DG>
+int gemm_attr() {                                                // once per device: opt in to the large dynamic shared memory
+  static bool set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !set[dev]) {
+    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemm_kernel<DG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   DG == 1 ? 115712 - 1024 : 220 * 1024),
+                              "st_gemm: shared memory attribute"))
+      return e;
+    set[dev] = true;
+  }
+  return 0;
+}
+
+// CTAs that can be resident at once when launched as clusters of ks (one CTA per SM): a cluster lives inside one GPC,
+// so sizes that do not divide a GPC's SM count strand SMs (clusters of 3 fit 44 times, not 49: a 48-cluster grid then
+// runs as two waves).  Asked from the driver once per (device, cluster size, token tile).
+long long resident_ctas(int ks, int NT, size_t smem, int sms) {
+  static int cache[64][9][3] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int ti = NT <= 64 ? 0 : (NT <= 128 ? 1 : 2);
+  if (ks == 1 || dev < 0 || dev >= 64) return sms;
+  if (cache[dev][ks][ti] == 0) {
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(ks * sms));
+    cfg.blockDim = dim3(Roles<2>::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (gemm_attr<2>() != 0 || cudaOccupancyMaxActiveClusters(&n, gemm_kernel<2>, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = sms / ks;                                              // no answer (no device): assume perfect packing
+    }
+    cache[dev][ks][ti] = n;
+  }
+  return (long long)cache[dev][ks][ti] * ks;
+}
+
 GemmPlan gemm_plan(long long M, long long N, long long B) {
   GemmPlan p;
   p.NT = B <= 64 ? 64 : (B <= 128 ? 128 : 256);
@@ -491,27 +537,11 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   const int NG = (int)(N / 64), sms = st::sm_count();
   const long long units = (long long)p.RB * p.TT;
   // One CTA of two decode groups per SM.  STATETREE_GEMM_DG=1 (tuning aid) runs two CTAs of one group each per SM for
-  // the 64- and 128-token tiles instead; measured slower (6.67 vs 5.22 ms per step at batch 64): twice the k-split
-  // halves every CTA's main loop while its start-up and epilogue stay.
+  // the 64- and 128-token tiles instead; measured slower for every shape (12288 x 4096 at batch 64: 43.7 vs 31.7 us):
+  // twice the k-split halves every CTA's main loop while its start-up and epilogue stay.
   static int forced_dg = -1;
   if (forced_dg < 0) { const char* v = getenv("STATETREE_GEMM_DG"); forced_dg = v ? atoi(v) : 0; }
   p.DG = (forced_dg == 1 && p.NT < 256) ? 1 : 2;
-  const long long slots = (long long)sms * (p.DG == 1 ? 2 : 1);
-  // split of the k range = cluster size (<= 8): fill the CTA slots, but every extra split costs an accumulator tile
-  // of distributed-shared-memory traffic in the epilogue
-  // one wave only: a second wave pays the start-up and the epilogue again (measured: 288 CTAs in two waves took 72 us
-  // where 96 CTAs in one take ~45), so among the splits that fit the slots take the one that fills them best
-  int best = 1;
-  double best_score = -1.0;
-  const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 8 ? 8 : NG / 4);
-  for (int ks = 1; ks <= ksmax; ++ks) {
-    const long long ctas = units * ks;
-    if (ctas > slots && ks > 1) break;
-    const long long waves = (ctas + slots - 1) / slots;
-    const double score = (double)ctas / (double)(waves * slots) - 0.01 * ks * p.NT / 256.0;
-    if (score > best_score + 1e-9) { best_score = score; best = ks; }
-  }
-  p.KS = best;
   const size_t stage = A_TILE + (size_t)p.NT * 128;
   const size_t stg = (size_t)p.NT * 128 * 4;                    // the parked accumulator tile reuses the rings
   if (p.DG == 1) {
@@ -542,21 +572,29 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   if (ring < stg) ring = stg;
   p.bar_off = (int)ring;
   p.smem = ring + 1024 /* alignment slack */ + 512 /* barriers */;
+  // split of the k range = cluster size (<= 8): fill the CTA slots, but every extra split costs an accumulator tile
+  // of distributed-shared-memory traffic in the epilogue
+  // one wave only: a second wave pays the start-up and the epilogue again (measured: 288 CTAs in two waves took 72 us
+  // where 96 CTAs in one take ~45), so among the splits whose clusters are all resident at once take the one that
+  // fills the SMs best
+  int best = 1;
+  double best_score = -1.0;
+  const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 8 ? 8 : NG / 4);
+  for (int ks = 1; ks <= ksmax; ++ks) {
+    const long long ctas = units * ks;
+    const long long slots = p.DG == 1 ? 2ll * sms : resident_ctas(ks, p.NT, p.smem, sms);
+    if (ctas > slots && ks > 1) continue;
+    const long long waves = (ctas + slots - 1) / slots;
+    const double score = (double)ctas / (double)(waves * sms * (p.DG == 1 ? 2 : 1)) - 0.01 * ks * p.NT / 256.0;
+    if (score > best_score + 1e-9) { best_score = score; best = ks; }
+  }
+  p.KS = best;
   return p;
 }
 
 template <int DG>
 int gemm_launch(const GemmPlan& p, const GemmArgs& a, const CUtensorMap& xmap, const CUtensorMap& wmap, cudaStream_t stream) {
-  static bool set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !set[dev]) {
-    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemm_kernel<DG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   DG == 1 ? 115712 - 1024 : 220 * 1024),
-                              "st_gemm: shared memory attribute"))
-      return e;
-    set[dev] = true;
-  }
+  if (int e = gemm_attr<DG>()) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(p.RB * p.TT * p.KS));
   cfg.blockDim = dim3(Roles<DG>::THREADS);

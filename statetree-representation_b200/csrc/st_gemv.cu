@@ -178,7 +178,7 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = gridDim.x;
-  const int u0 = (int)((long long)blockIdx.x * a.U / C), u1 = (int)((long long)(blockIdx.x + 1) * a.U / C);
+  int u0 = (int)((long long)blockIdx.x * a.U / C), u1 = (int)((long long)(blockIdx.x + 1) * a.U / C);
 
   if (tid == 0) PROF(0);
   if (tid < S) {                                               // one thread per ring stage sets its barriers up
@@ -194,6 +194,15 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
   __syncthreads();
   pdl_launch_dependents();                 // the next kernel in the stream may start its own weight prefetch
   if (MODE != MODE_DENSE) pdl_wait();      // expert ids / slot tables come from earlier kernels: read nothing before
+  if (MODE == MODE_GROUP) {
+    // The block table is sized for the worst case on the host; how many blocks the routing filled is known only here.
+    // The CTAs share the tiles of the blocks in use, whole tiles each, so no CTA idles over the unused tail and no
+    // tile is shared (no hand-over of partial sums at all).
+    const int used = min(a.nprob, (a.npost[0] + 7) >> 3);
+    const long long tiles = (long long)used * a.T;
+    u0 = (int)(blockIdx.x * tiles / C) * a.CPT;
+    u1 = (int)((blockIdx.x + 1) * tiles / C) * a.CPT;
+  }
 
   UnitCursor<MODE> cur;
   cur.init(a, u0, u1);

@@ -74,8 +74,8 @@ __global__ void __launch_bounds__(256) silu_mul_vec_kernel(const uint4* __restri
 // pairs in order with ballots, a binary search per block.  Expert ids outside [0, E) count as E - 1 / 0 (clamped).
 constexpr int ALIGN_MAX_E = 1024;
 template <bool IDS64>
-__global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict__ ids_, int S, int E, int nblk,
-                                                         int* __restrict__ sorted, int* __restrict__ bexp,
+__global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict__ ids_, int S, int E, int used_bins,
+                                                         int nblk, int* __restrict__ sorted, int* __restrict__ bexp,
                                                          int* __restrict__ npost) {
   st::pdl_wait();
   st::pdl_launch_dependents();
@@ -134,18 +134,19 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict_
     }
     bexp[b] = lo < E ? lo : E - 1;
   }
-  if (tid == 0) npost[0] = end_[E - 1];
+  if (tid == 0) npost[0] = end_[used_bins - 1];                            // entries of the first used_bins experts
 }
 }  // namespace
 
-extern "C" int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int32_t* sorted, int32_t* bexp,
-                            int32_t* npost, int64_t nblk, void* stream) {
+extern "C" int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int64_t used_bins, int32_t* sorted,
+                            int32_t* bexp, int32_t* npost, int64_t nblk, void* stream) {
   ST_REQUIRE(S >= 1 && S <= (1 << 20) && E >= 1 && E <= ALIGN_MAX_E, "st_moe_align: 1..%d experts, up to 2^20 pairs",
              ALIGN_MAX_E);
   ST_REQUIRE(nblk >= S / 8 + (S < E ? S : E) && nblk * 8 < (1ll << 31), "st_moe_align: nblk must cover S / 8 + min(S, E) blocks");
+  ST_REQUIRE(used_bins >= 1 && used_bins <= E, "st_moe_align: used_bins must be in [1, E]");
   ST_REQUIRE(ids && sorted && bexp && npost, "st_moe_align: null pointer");
   return st::launch("st_moe_align launch", ids64 ? moe_align_kernel<true> : moe_align_kernel<false>, dim3(1), dim3(1024), 0,
-                    (cudaStream_t)stream, ids, (int)S, (int)E, (int)nblk, (int*)sorted, (int*)bexp, (int*)npost);
+                    (cudaStream_t)stream, ids, (int)S, (int)E, (int)used_bins, (int)nblk, (int*)sorted, (int*)bexp, (int*)npost);
 }
 
 extern "C" int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H,

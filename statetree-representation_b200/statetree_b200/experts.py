@@ -62,9 +62,10 @@ def moe_gemv(tables, x, ids, M, xdiv):
 ALIGN_KERNEL = os.environ.get("STATETREE_MOE_ALIGN_KERNEL", "1") != "0"   # 0: the torch formulation
 
 
-def moe_align(ids, E, bs=8):
+def moe_align(ids, E, bs=8, used_bins=None):
     """Pairs grouped by expert in blocks of bs (the moe_align_block_size layout), with torch ops and no host sync:
-    (sorted_ids int32 [nblk * bs], padded with S; bexp int32 [nblk]; npost int32 [1] = used entries)."""
+    (sorted_ids int32 [nblk * bs], padded with S; bexp int32 [nblk]; npost int32 [1] = entries of the first used_bins
+    experts, default all E: the grouped kernel does not visit blocks beyond it)."""
     ids = ids.reshape(-1)
     S, dev = ids.numel(), ids.device
     nblk = S // bs + min(S, E) + 1
@@ -74,12 +75,12 @@ def moe_align(ids, E, bs=8):
         sorted_ids = torch.empty(nblk * bs, dtype=torch.int32, device=dev)
         bexp = torch.empty(nblk, dtype=torch.int32, device=dev)
         npost = torch.empty(1, dtype=torch.int32, device=dev)
-        ext().moe_align(ids.contiguous(), E, sorted_ids, bexp, npost)
+        ext().moe_align(ids.contiguous(), E, E if used_bins is None else used_bins, sorted_ids, bexp, npost)
         return sorted_ids, bexp, npost
-    return _moe_align_torch(ids, E, bs)
+    return _moe_align_torch(ids, E, bs, used_bins)
 
 
-def _moe_align_torch(ids, E, bs=8):
+def _moe_align_torch(ids, E, bs=8, used_bins=None):
     """the same layout with torch ops (CPU tensors, other block sizes, very long calls); the check for the kernel"""
     ids = ids.reshape(-1).to(torch.int64)
     S, dev = ids.numel(), ids.device
@@ -95,7 +96,8 @@ def _moe_align_torch(ids, E, bs=8):
     sorted_ids[begin[e_sorted] + rank] = by_expert.to(torch.int32)
     blk_start = torch.arange(nblk, device=dev) * bs
     bexp = torch.searchsorted(end, blk_start, right=True).clamp(max=E - 1).to(torch.int32)
-    return sorted_ids, bexp, end[-1:].to(torch.int32)
+    nb = E if used_bins is None else used_bins
+    return sorted_ids, bexp, end[nb - 1:nb].to(torch.int32)
 
 
 def moe_group_gemv(tables, x, aligned, S, M, xdiv, zero=False):
@@ -178,7 +180,7 @@ class TreeExperts(nn.Module):
                 gu = moe_gemv(t13, x, ids, 2 * self.inter, K)
                 return moe_wsum(moe_gemv(t2, silu_mul(gu), ids, self.hidden, 1), w)
             ids = torch.where(local >= 0, local, torch.full_like(local, self.num_experts))
-            al = moe_align(ids, self.num_experts + 1, 8)
+            al = moe_align(ids, self.num_experts + 1, 8, used_bins=self.num_experts)   # the last bin = other ranks' pairs
             gu = moe_group_gemv(t13, x, al, S, 2 * self.inter, K, zero=True)
             y = moe_group_gemv(t2, silu_mul(gu), al, S, self.hidden, 1, zero=True)
             return moe_wsum(y, w)

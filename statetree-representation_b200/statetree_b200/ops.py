@@ -39,7 +39,7 @@ _SIGNATURES = {
     "st_kv_append": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _int, _vp]),
     "st_kv_dequant": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "st_kv_dequant_blocks": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
-    "st_moe_align": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "st_moe_align": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "st_comm_bytes": (_i64, []),
     "st_comm_alloc": (_int, [ctypes.POINTER(ctypes.c_void_p)]),
     "st_comm_free": (_int, [_vp]),
@@ -179,10 +179,10 @@ class _Weights:
                                            xdiv, _ptr(WS), WS.numel() * WS.element_size(), _ptr(CNT), _stream(X)))
 
     @staticmethod
-    def moe_align(ids, E, sorted_ids, bexp, npost):
+    def moe_align(ids, E, used_bins, sorted_ids, bexp, npost):
         with _ctx(ids):
-            _check(lib().st_moe_align(_ptr(ids), 1 if ids.dtype == torch.int64 else 0, ids.numel(), E, _ptr(sorted_ids),
-                                      _ptr(bexp), _ptr(npost), bexp.numel(), _stream(ids)))
+            _check(lib().st_moe_align(_ptr(ids), 1 if ids.dtype == torch.int64 else 0, ids.numel(), E, used_bins,
+                                      _ptr(sorted_ids), _ptr(bexp), _ptr(npost), bexp.numel(), _stream(ids)))
 
     @staticmethod
     def wsum(Y, W, out):

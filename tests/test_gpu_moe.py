@@ -127,7 +127,8 @@ def test_moe_align_kernel_matches_torch_formulation():
         ids = torch.randint(0, E, (S,), device="cuda", generator=gen).to(dt)
         if S >= 64:
             ids[: S // 3] = ids[0]                                  # a crowded expert
-        got = moe_align(ids, E, 8)
-        want = _moe_align_torch(ids, E, 8)
-        for g, w, name in zip(got, want, ("sorted_ids", "bexp", "npost")):
-            assert g.dtype == w.dtype and torch.equal(g, w), (S, E, name)
+        for used in (None, max(1, E - 1)):
+            got = moe_align(ids, E, 8, used)
+            want = _moe_align_torch(ids, E, 8, used)
+            for g, w, name in zip(got, want, ("sorted_ids", "bexp", "npost")):
+                assert g.dtype == w.dtype and torch.equal(g, w), (S, E, used, name)
