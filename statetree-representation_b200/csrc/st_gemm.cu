@@ -285,19 +285,23 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
     // this record is decoded, so no global-load latency sits between the records landing and the tile being handed
     // to the tensor core (one record in six has an escape; eight warps must all arrive before the MMA can start)
     int eo_base = 0, eo_lo = 0, eo_hi = 0;
+    unsigned emask = 0u;                                           // bit l: k-tile eo_base + l of this warp has escapes
     auto load_offsets = [&](int first) {
       eo_base = first;
       const int j = first + lane;
       eo_lo = j < nk ? __ldg(a.eo + rbase + j) : 0;
       eo_hi = j < nk ? __ldg(a.eo + rbase + j + 1) : 0;
+      emask = __ballot_sync(FULL, eo_hi > eo_lo);
     };
     int lo = 0, hi = 0;
     uint32_t ent = 0u;
     if (grp < nk) {
       load_offsets(grp);
-      lo = __shfl_sync(FULL, eo_lo, 0);
-      hi = __shfl_sync(FULL, eo_hi, 0);
-      if (lane < hi - lo) ent = __ldg(a.el + lo + lane);
+      if (emask & 1u) {
+        lo = __shfl_sync(FULL, eo_lo, 0);
+        hi = __shfl_sync(FULL, eo_hi, 0);
+        if (lane < hi - lo) ent = __ldg(a.el + lo + lane);
+      }
     }
 #ifdef ST_PROF
     long long gck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gckl = clock64();
@@ -312,9 +316,12 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
 #endif
       if (i + DG < nk) {
         if (i + DG - eo_base >= 32) load_offsets(i + DG);
-        nlo = __shfl_sync(FULL, eo_lo, i + DG - eo_base);
-        nhi = __shfl_sync(FULL, eo_hi, i + DG - eo_base);
-        if (lane < nhi - nlo) nent = __ldg(a.el + nlo + lane);
+        const int off = i + DG - eo_base;
+        if ((emask >> off) & 1u) {                                // five records in six have none: one bit test
+          nlo = __shfl_sync(FULL, eo_lo, off);
+          nhi = __shfl_sync(FULL, eo_hi, off);
+          if (lane < nhi - nlo) nent = __ldg(a.el + nlo + lane);
+        }
       }
 #ifdef ST_PROF
       RecRegs rr;
