@@ -123,7 +123,7 @@ template <int DG> struct Roles {
 #ifdef ST_GEMM_SPINWAIT
 #define GW mbar_wait_spin
 #else
-#define GW mbar_wait
+#define GW mbar_wait_look
 #endif
 #ifndef ST_GEMM_BACKOFF_NS
 #define ST_GEMM_BACKOFF_NS 0
