@@ -105,3 +105,11 @@ def test_decode_split_heuristic():
         for pages in (64, 256, 1024):
             s = decode_splits(B, 8, pages)
             assert s >= 1 and (s & (s - 1)) == 0 and (s == 1 or pages // s >= 4)
+
+
+def test_peer_comm_is_not_used_off_gpu():
+    """the peer-memory all-reduce needs NCCL ranks with CUDA devices; everywhere else reduce_partials stays on the
+    process group's own all-reduce (the gloo ranks above exercise that path)"""
+    from statetree_b200 import parallel
+    assert parallel.peer_comm(None) is None                      # no process group here
+    assert parallel.PeerComm.MAX_VALUES == 524288
