@@ -139,6 +139,16 @@ int st_kv_attn(const void* q, int64_t qs, int64_t B, int64_t Hq, const void* kv,
                const int32_t* starts, void* out, int64_t os, float* wo, float* wml, double scale, int64_t S,
                int64_t minpps, void* stream);
 
+/* Decode step, one new token per sequence: st_qk_norm_rope for the query heads and st_kv_append of the step's K
+ * (normalised and rotated by the appending warps themselves) and V rows, in one launch.  qkv BF16 [B, (hq + 2 hkv) *
+ * 128] with row stride row_stride; slot int64 [B] (negative or outside the cache = no write); the pages are
+ * bit-identical to st_qk_norm_rope followed by st_kv_append.  No single counterpart in the reference (its harness
+ * leaves norm and rotary embedding to PyTorch and then calls `_kv.append`, statetree/csrc/kvcache.cu:297-324). */
+int st_rope_kv_append(const void* qkv, int64_t row_stride, const void* wq, const void* wk, const float* cos_t,
+                      const float* sin_t, const int64_t* pos, int64_t max_pos, void* q_out, int64_t B, int64_t hq,
+                      int64_t hkv, double eps, const int64_t* slot, void* kv, int64_t nblocks, uint32_t* pool, int64_t P,
+                      int32_t* pool_cnt, void* stream);
+
 /* ---- tensor-parallel exchange over NVLink peer memory -------------------------------------------------------------- *
  * No counterpart in the reference: it has no communication code (under vLLM each rank runs the reference's kernels on
  * its shard and vLLM all-reduces the outputs of the row-parallel o / down projections with NCCL).  These entry points

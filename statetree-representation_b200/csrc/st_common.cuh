@@ -175,6 +175,14 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
 // writes are visible (a no-op for an ordinary launch); launch_dependents lets the successor's CTAs be scheduled early.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// pieces of the per-head RMSNorm + rotary embedding shared by the stand-alone kernel and the one fused with the KV
+// append: written with explicit fused multiply-adds so that both produce the same bits
+__device__ __forceinline__ float sumsq4(float a, float b, float c, float d) {
+  return __fmaf_rn(d, d, __fmaf_rn(c, c, __fmaf_rn(b, b, __fmul_rn(a, a))));
+}
+__device__ __forceinline__ uint32_t rope_pair(float n0, float n1, float c, float s) {      // -> packed BF16 pair
+  return pack_bf16(__fmaf_rn(n0, c, -__fmul_rn(n1, s)), __fmaf_rn(n0, s, __fmul_rn(n1, c)));
+}
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

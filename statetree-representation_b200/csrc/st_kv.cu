@@ -83,48 +83,12 @@ __device__ void chain_put(const AppendArgs& a, EscCursor& c, uint32_t* slots, ui
   a.pool[(size_t)c.tail * 16] = (a.pool[(size_t)c.tail * 16] & ~0xFFu) | (uint32_t)c.fill;
 }
 
-// One warp per (token, head, K/V, half); only the warp of a segment's first token works: a segment is a run of
-// consecutive slots inside one page, and its warp owns the record for the whole launch (rows g and g+8 share state
-// bytes, and the header is read-modify-write).  Semantics of statetree/csrc/kvcache.cu:62-192.
-// The warp edits the 1600-byte unit in shared memory: the segment's rows are fetched up front (independent loads),
-// encoded row by row with shared-memory byte stores, and the unit goes back to the page as 100 16-byte stores.
-__global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
-  __shared__ __align__(16) uint8_t s_unit[8][RKV];
-  pdl_wait();
-  pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int units = a.H * 4;
-  const long long grp = w / units;                                // a.gsz consecutive tokens of the call per warp
-  if (grp * a.gsz >= a.N) return;
-  const int u = (int)(w % units), h = u >> 2, kvi = (u >> 1) & 1, half = u & 1;
-  const long long n_end = min((long long)a.N, (grp + 1) * a.gsz);
-  for (long long n = grp * a.gsz; n < n_end; ++n) {
-  const long long s0 = a.slot[n];
-  if (s0 < 0) continue;
-  const long long blk = s0 / PAGE;
-  if (blk >= a.nblocks) continue;                                 // outside the cache: dropped, no write
-  if (n > 0) {
-    const long long sp = a.slot[n - 1];
-    if (sp >= 0 && sp + 1 == s0 && sp / PAGE == blk) continue;    // continues the previous token's segment
-  }
-  uint8_t* const grec = a.kv + unit_off(blk, a.H, h, kvi, half);
-  uint8_t* const rec = s_unit[threadIdx.x >> 5];
+// Encodes nrow consecutive rows (r0 ..) of one record, whose values are pairs[i] (columns 2 lane, 2 lane + 1 of row i),
+// into the 1600-byte unit: staged in `rec` (shared memory, one per warp), written back to `grec` as 100 16-byte stores.
+__device__ __forceinline__ void append_rows(const AppendArgs& a, uint8_t* const grec, uint8_t* const rec, const int r0,
+                                            const int nrow, const uint32_t (&pairs)[PAGE], const int lane) {
   uint32_t* const hdr = reinterpret_cast<uint32_t*>(rec + REC);
   uint32_t* const slots = hdr + 1;
-  const int r0 = (int)(s0 % PAGE);
-  // rows of this segment: consecutive slots that stay inside the page
-  int nrow = 1;
-  while (nrow < PAGE - r0 && n + nrow < a.N && a.slot[n + nrow] == s0 + nrow) ++nrow;
-  // fetch every row's pair of values now (independent loads), encode afterwards
-  uint32_t pairs[PAGE];
-#pragma unroll
-  for (int i = 0; i < PAGE; ++i) {
-    if (i < nrow) {
-      const uint16_t* src = (kvi ? a.V + (n + i) * a.vs : a.K + (n + i) * a.ks) + h * HD + half * 64;
-      pairs[i] = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
-    }
-  }
   EscCursor c;
   if (r0 == 0) {                                                  // row 0: the page starts over
     int keep = -1;
@@ -203,7 +167,129 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
   __syncwarp();
   for (int i = lane; i < RKV / 16; i += 32) reinterpret_cast<uint4*>(grec)[i] = reinterpret_cast<const uint4*>(rec)[i];
   __syncwarp();                                                   // the staging unit is reused by the next segment
+}
+
+// One warp per (token, head, K/V, half); only the warp of a segment's first token works: a segment is a run of
+// consecutive slots inside one page, and its warp owns the record for the whole launch (rows g and g+8 share state
+// bytes, and the header is read-modify-write).  Semantics of statetree/csrc/kvcache.cu:62-192.
+// The warp edits the 1600-byte unit in shared memory: the segment's rows are fetched up front (independent loads),
+// encoded row by row with shared-memory byte stores, and the unit goes back to the page as 100 16-byte stores.
+__global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
+  __shared__ __align__(16) uint8_t s_unit[8][RKV];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int units = a.H * 4;
+  const long long grp = w / units;                                // a.gsz consecutive tokens of the call per warp
+  if (grp * a.gsz >= a.N) return;
+  const int u = (int)(w % units), h = u >> 2, kvi = (u >> 1) & 1, half = u & 1;
+  const long long n_end = min((long long)a.N, (grp + 1) * a.gsz);
+  for (long long n = grp * a.gsz; n < n_end; ++n) {
+  const long long s0 = a.slot[n];
+  if (s0 < 0) continue;
+  const long long blk = s0 / PAGE;
+  if (blk >= a.nblocks) continue;                                 // outside the cache: dropped, no write
+  if (n > 0) {
+    const long long sp = a.slot[n - 1];
+    if (sp >= 0 && sp + 1 == s0 && sp / PAGE == blk) continue;    // continues the previous token's segment
   }
+  uint8_t* const grec = a.kv + unit_off(blk, a.H, h, kvi, half);
+  uint8_t* const rec = s_unit[threadIdx.x >> 5];
+  const int r0 = (int)(s0 % PAGE);
+  // rows of this segment: consecutive slots that stay inside the page
+  int nrow = 1;
+  while (nrow < PAGE - r0 && n + nrow < a.N && a.slot[n + nrow] == s0 + nrow) ++nrow;
+  // fetch every row's pair of values now (independent loads), encode afterwards
+  uint32_t pairs[PAGE];
+#pragma unroll
+  for (int i = 0; i < PAGE; ++i) {
+    if (i < nrow) {
+      const uint16_t* src = (kvi ? a.V + (n + i) * a.vs : a.K + (n + i) * a.ks) + h * HD + half * 64;
+      pairs[i] = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
+    }
+  }
+  append_rows(a, grec, rec, r0, nrow, pairs, lane);
+  }
+}
+
+// Decode step, one new token per sequence: per-head q/k RMSNorm + rotary embedding and the KV append in one launch.
+// Warps [0, B * hq) normalise and rotate a query head into q_out (the arithmetic of qk_norm_rope_kernel, operation for
+// operation); the B * hkv * 4 warps after them each own one (sequence, KV head, K/V, half) record as in
+// kv_append_kernel, and the K warps compute their 64 normalised, rotated values themselves instead of reading them
+// back from a buffer another kernel wrote.  The pages are bit-identical to norm/rope followed by append.
+struct RopeArgs {
+  const uint16_t* qkv; long long row_stride;
+  const uint16_t* wq; const uint16_t* wk;
+  const float* cos_t; const float* sin_t;
+  const long long* pos; long long max_pos;
+  uint16_t* q_out;
+  int B, hq;
+  float eps;
+};
+__device__ __forceinline__ float kv_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+  return v;
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs r, const AppendArgs a) {
+  __shared__ __align__(16) uint8_t s_unit[8][RKV];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long nq = (long long)r.B * r.hq;
+  long long p = r.pos[0];
+  p = p < 0 ? 0 : (p >= r.max_pos ? r.max_pos - 1 : p);
+  if (w < nq) {                                                     // ---- a query head
+    const int b = (int)(w / r.hq), h = (int)(w % r.hq);
+    const uint16_t* src = r.qkv + (size_t)b * r.row_stride + (size_t)h * HD + 4 * lane;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    const float ss = kv_warp_sum(sumsq4(x0.x, x0.y, x1.x, x1.y));
+    const float rn = rsqrtf(__fmaf_rn(ss, 1.f / 128.f, r.eps));
+    const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(r.wq + 4 * lane));
+    const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(r.wq + 4 * lane + 2));
+    const float n00 = bf16_round(bf16_round(x0.x * rn) * g0.x), n01 = bf16_round(bf16_round(x0.y * rn) * g0.y);
+    const float n10 = bf16_round(bf16_round(x1.x * rn) * g1.x), n11 = bf16_round(bf16_round(x1.y * rn) * g1.y);
+    const float c0 = r.cos_t[p * 64 + 2 * lane], s0 = r.sin_t[p * 64 + 2 * lane];
+    const float c1 = r.cos_t[p * 64 + 2 * lane + 1], s1 = r.sin_t[p * 64 + 2 * lane + 1];
+    uint2 o;
+    o.x = rope_pair(n00, n01, c0, s0);
+    o.y = rope_pair(n10, n11, c1, s1);
+    *reinterpret_cast<uint2*>(r.q_out + ((size_t)b * r.hq + h) * HD + 4 * lane) = o;
+    return;
+  }
+  const long long u = w - nq;                                        // ---- a record of the new token
+  const int units = a.H * 4;
+  if (u >= (long long)r.B * units) return;
+  const int b = (int)(u / units), uu = (int)(u % units), h = uu >> 2, kvi = (uu >> 1) & 1, half = uu & 1;
+  const long long s0 = a.slot[b];
+  if (s0 < 0) return;
+  const long long blk = s0 / PAGE;
+  if (blk >= a.nblocks) return;
+  uint32_t pairs[PAGE];
+  if (kvi) {
+    const uint16_t* src = r.qkv + (size_t)b * r.row_stride + (size_t)(r.hq + a.H + h) * HD + half * 64;
+    pairs[0] = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
+  } else {
+    const uint16_t* src = r.qkv + (size_t)b * r.row_stride + (size_t)(r.hq + h) * HD;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + 4 * lane);         // the whole head, for the norm
+    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    const float ss = kv_warp_sum(sumsq4(x0.x, x0.y, x1.x, x1.y));
+    const float rn = rsqrtf(__fmaf_rn(ss, 1.f / 128.f, r.eps));
+    const int d0 = half * 64 + 2 * lane;                                        // this lane's pair of the record row
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + d0));
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(r.wk + d0));
+    const float n0 = bf16_round(bf16_round(v.x * rn) * g.x), n1 = bf16_round(bf16_round(v.y * rn) * g.y);
+    const float c = r.cos_t[p * 64 + (d0 >> 1)], sn = r.sin_t[p * 64 + (d0 >> 1)];
+    pairs[0] = rope_pair(n0, n1, c, sn);
+  }
+  append_rows(a, a.kv + unit_off(blk, a.H, h, kvi, half), s_unit[threadIdx.x >> 5], (int)(s0 % PAGE), 1, pairs, lane);
 }
 
 // ------------------------------------------------------------------------------------------------ record decode
@@ -528,6 +614,31 @@ extern "C" int st_kv_append(const void* K, const void* V, int64_t ks, int64_t vs
   const long long warps = ((N + a.gsz - 1) / a.gsz) * H * 4;
   return st::launch("st_kv_append launch", kv_append_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0,
                     (cudaStream_t)stream, a);
+}
+
+extern "C" int st_rope_kv_append(const void* qkv, int64_t row_stride, const void* wq, const void* wk, const float* cos_t,
+                                 const float* sin_t, const int64_t* pos, int64_t max_pos, void* q_out, int64_t B,
+                                 int64_t hq, int64_t hkv, double eps, const int64_t* slot, void* kv, int64_t nblocks,
+                                 uint32_t* pool, int64_t P, int32_t* pool_cnt, void* stream) {
+  ST_REQUIRE(B >= 0 && hq > 0 && hkv > 0 && max_pos > 0 && nblocks >= 0 && P >= 0, "st_rope_kv_append: sizes");
+  if (B == 0) return 0;
+  ST_REQUIRE(qkv && wq && wk && cos_t && sin_t && pos && q_out && slot && kv && pool && pool_cnt,
+             "st_rope_kv_append: null pointer");
+  ST_REQUIRE(((uintptr_t)qkv & 7u) == 0 && row_stride % 4 == 0 && row_stride >= (hq + 2 * hkv) * 128 &&
+                 ((uintptr_t)q_out & 7u) == 0 && ((uintptr_t)wq & 3u) == 0 && ((uintptr_t)wk & 3u) == 0 && st::aligned16(kv),
+             "st_rope_kv_append: alignment / row stride");
+  ST_REQUIRE(B * (hq + hkv * 4) < (1ll << 31) && P < (1ll << 23), "st_rope_kv_append: too large");
+  RopeArgs r;
+  r.qkv = (const uint16_t*)qkv; r.row_stride = row_stride; r.wq = (const uint16_t*)wq; r.wk = (const uint16_t*)wk;
+  r.cos_t = cos_t; r.sin_t = sin_t; r.pos = (const long long*)pos; r.max_pos = max_pos; r.q_out = (uint16_t*)q_out;
+  r.B = (int)B; r.hq = (int)hq; r.eps = (float)eps;
+  AppendArgs a;
+  a.K = nullptr; a.V = nullptr; a.ks = 0; a.vs = 0;
+  a.slot = (const long long*)slot; a.kv = (uint8_t*)kv; a.pool = pool; a.pool_cnt = pool_cnt;
+  a.nblocks = nblocks; a.N = (int)B; a.H = (int)hkv; a.P = (int)P; a.reuse = 0; a.gsz = 1;
+  const long long warps = B * (hq + hkv * 4);
+  return st::launch("st_rope_kv_append launch", rope_append_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0,
+                    (cudaStream_t)stream, r, a);
 }
 
 extern "C" int st_kv_dequant_blocks(const void* kv, int64_t nblocks, int64_t H, const uint32_t* pool, int64_t P,

@@ -143,8 +143,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const __nv_bfloat16* 
   const uint2 raw = *reinterpret_cast<const uint2*>(src);
   const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
   const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-  const float ss = warp_sum(a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y);
-  const float r = rsqrtf(ss / 128.f + eps);
+  const float ss = warp_sum(st::sumsq4(a.x, a.y, c.x, c.y));
+  const float r = rsqrtf(__fmaf_rn(ss, 1.f / 128.f, eps));
   const __nv_bfloat16* w = (is_k ? wk : wq) + 4 * lane;
   const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w));
   const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + 2));
@@ -158,8 +158,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const __nv_bfloat16* 
   const float c0 = cos_t[p * 64 + 2 * lane], s0 = sin_t[p * 64 + 2 * lane];
   const float c1 = cos_t[p * 64 + 2 * lane + 1], s1 = sin_t[p * 64 + 2 * lane + 1];
   uint2 o;
-  o.x = st::pack_bf16(n0.x * c0 - n0.y * s0, n0.x * s0 + n0.y * c0);
-  o.y = st::pack_bf16(n1.x * c1 - n1.y * s1, n1.x * s1 + n1.y * c1);
+  o.x = st::rope_pair(n0.x, n0.y, c0, s0);
+  o.y = st::rope_pair(n1.x, n1.y, c1, s1);
   __nv_bfloat16* dst = is_k ? k_out + ((size_t)b * hkv + (h - hq)) * 128 : q_out + ((size_t)b * hq + h) * 128;
   *reinterpret_cast<uint2*>(dst + 4 * lane) = o;
 }

@@ -18,7 +18,7 @@ import torch.nn.functional as Fn
 
 from .kvcache import StateTreeKVCache
 from .linear import TreeLinear
-from .ops import ext
+from .ops import ext, kv_ext
 
 
 def _flash():
@@ -146,13 +146,14 @@ class TreeDecoder:
         for li, (qkv, o, gu, d) in enumerate(self.blocks):
             self._add_norm(x, delta, h)
             y = qkv(h)
-            E.qk_norm_rope(y, self.head_norm_w, self.head_norm_w, self.cos, self.sin, self.pos_buf, qb, kb, c.eps)
-            v = y[:, (self.hq + self.hkv) * D:].view(B, self.hkv, D)
             if self.compressed:
-                layer = self.cache.layers[li]
-                layer.append(kb, v, slots)
+                layer = self.cache.layers[li]               # norm + rope of q and k and the append of k, v: one launch
+                kv_ext().rope_append(y, self.head_norm_w, self.head_norm_w, self.cos, self.sin, self.pos_buf, qb,
+                                     self.hq, self.hkv, c.eps, slots, layer.pages, layer.pool, layer.pcnt)
                 att = layer.attention(qb, self.cache.bt32[:B], self.cache.lens[:B], scale, self.splits, None, 4)
             else:
+                E.qk_norm_rope(y, self.head_norm_w, self.head_norm_w, self.cos, self.sin, self.pos_buf, qb, kb, c.eps)
+                v = y[:, (self.hq + self.hkv) * D:].view(B, self.hkv, D)
                 att = _flash()(qb.view(B, 1, self.hq, D), self.kc[li], self.vc[li], k=kb.view(B, 1, self.hkv, D),
                                v=v.unsqueeze(1), cache_seqlens=self.lens, softmax_scale=scale)
             delta = o(att.reshape(B, self.hq * D))

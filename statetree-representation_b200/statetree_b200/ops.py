@@ -39,6 +39,8 @@ _SIGNATURES = {
     "st_kv_append": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _int, _vp]),
     "st_kv_dequant": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "st_kv_dequant_blocks": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
+    "st_rope_kv_append": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _dbl, _vp, _vp, _i64,
+                                 _vp, _i64, _vp, _vp]),
     "st_moe_align": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "st_comm_bytes": (_i64, []),
     "st_comm_alloc": (_int, [ctypes.POINTER(ctypes.c_void_p)]),
@@ -214,6 +216,16 @@ class _Weights:
 
 class _KV:
     """call shapes of the reference's `statetree._kv` module (statetree/csrc/kvcache.cu:588-599)"""
+
+    @staticmethod
+    def rope_append(qkv, wq, wk, cos_t, sin_t, pos, q_out, hq, hkv, eps, slot, kv, pool, pool_cnt):
+        """decode step: q heads of qkv [B, (hq + 2 hkv) * 128] normalised + rotated into q_out, K (normalised + rotated)
+        and V rows appended to the pages at slot [B]"""
+        B = qkv.shape[0]
+        with _ctx(qkv):
+            _check(lib().st_rope_kv_append(_ptr(qkv), qkv.stride(0), _ptr(wq), _ptr(wk), _ptr(cos_t), _ptr(sin_t),
+                                           _ptr(pos), cos_t.shape[0], _ptr(q_out), B, hq, hkv, float(eps), _ptr(slot),
+                                           _ptr(kv), kv.size(0), _ptr(pool), pool.size(0), _ptr(pool_cnt), _stream(qkv)))
 
     @staticmethod
     def version():

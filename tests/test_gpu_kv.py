@@ -265,3 +265,43 @@ def test_cache_object_decode_steps():
         ref = torch.einsum("bhl,bhld->bhd", p, v)
         assert float((out.double() - ref).norm() / ref.norm()) < 5e-3
     cache.check()
+
+
+@pytest.mark.gpu
+def test_fused_rope_append_matches_rope_then_append():
+    """q/k norm + rotary embedding + append in one launch leaves the same q and the same page bytes as the two kernels
+    it replaces (several steps, so rows other than 0 and the page change at row 16 are covered)"""
+    from statetree_b200.kvcache import StateTreeKVLayer
+    from statetree_b200.ops import ext, kv_ext
+    dev = torch.device("cuda")
+    B, hq, hkv, D, max_pos = 3, 8, 2, 128, 64
+    gen = torch.Generator(device=dev).manual_seed(11)
+    wq = (1 + 0.1 * torch.randn(D, device=dev, generator=gen)).to(torch.bfloat16)
+    wk = (1 + 0.1 * torch.randn(D, device=dev, generator=gen)).to(torch.bfloat16)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))
+    ang = torch.arange(max_pos, device=dev, dtype=torch.float32)[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    la, lb = StateTreeKVLayer(8, hkv, dev, pool_blocks=256), StateTreeKVLayer(8, hkv, dev, pool_blocks=256)
+    bt = torch.tensor([[0, 3], [1, 4], [2, 5]], device=dev)
+    pos = torch.zeros(1, dtype=torch.long, device=dev)
+    for step in range(20):
+        y = torch.randn(B, (hq + 2 * hkv) * D, device=dev, generator=gen)
+        y[:, (hq + 1) * D + 5] *= 1e5                                # a channel that escapes
+        y = y.to(torch.bfloat16)
+        slots = bt[:, step // 16] * 16 + step % 16
+        pos.fill_(step)
+        qa, ka = torch.empty(B, hq, D, dtype=torch.bfloat16, device=dev), torch.empty(B, hkv, D, dtype=torch.bfloat16, device=dev)
+        ext().qk_norm_rope(y, wq, wk, cos, sin, pos, qa, ka, 1e-6)
+        la.append(ka, y[:, (hq + hkv) * D:].view(B, hkv, D), slots)
+        qb = torch.empty_like(qa)
+        kv_ext().rope_append(y, wq, wk, cos, sin, pos, qb, hq, hkv, 1e-6, slots, lb.pages, lb.pool, lb.pcnt)
+        assert torch.equal(qa, qb), step
+        # record bytes (leaves, states, nodes) and the in-record slot count are the same; a unit's header also names its
+        # first pool block, and which block a warp draws from the pool depends on the order the warps get there
+        assert torch.equal(la.pages[..., :1552], lb.pages[..., :1552]), step
+        assert torch.equal(la.pages[..., 1552] & 31, lb.pages[..., 1552] & 31), step
+        assert torch.equal(la.pages[..., 1556:], lb.pages[..., 1556:]), step      # the 11 in-record slots
+    assert torch.equal(la.pcnt, lb.pcnt) and int(la.pcnt[0]) > 0     # the escaping channel reached the pool
+    Ka, Va = la.dense()
+    Kb, Vb = lb.dense()
+    assert torch.equal(Ka, Kb) and torch.equal(Va, Vb)               # every stored value, escapes included
