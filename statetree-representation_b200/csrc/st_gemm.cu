@@ -98,20 +98,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-  return v;
-}
-
 // DG decode groups of eight warps (group g takes the k-tiles g, g + DG, ...), a record producer, an activation
 // producer and DG MMA issuer warps.  DG = 2: one CTA per SM (any token tile).  DG = 1: 11 warps and at most half an
 // SM's shared memory, so two CTAs share an SM (a tuning aid; slower for the shapes measured).
