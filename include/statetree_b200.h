@@ -139,6 +139,16 @@ int st_kv_attn(const void* q, int64_t qs, int64_t B, int64_t Hq, const void* kv,
                const int32_t* starts, void* out, int64_t os, float* wo, float* wml, double scale, int64_t S,
                int64_t minpps, void* stream);
 
+/* st_gemv (1 <= B <= 8) of a fused gate/up projection with the SwiGLU gate in the epilogue: the M = 2 I rows of the tree
+ * are the gate and up projections interleaved in 16-row tiles (tile 2j = gate rows 16j .. 16j + 15, tile 2j + 1 = the
+ * same rows of up); act BF16 [B, I] = silu(gate) * up with the rounding points of st_silu_mul (both products to BF16,
+ * silu in fp32 to BF16, BF16 multiply).  Shapes whose work does not divide into whole tile pairs per CTA are rejected
+ * (the caller then runs st_gemv + st_silu_mul).  The reference fuses the same step into its expert kernels only
+ * (`mvwx` / `mvwg`, statetree/csrc/kernels.cu:1159-1279). */
+int st_gemv_swiglu_supported(int64_t M, int64_t N, int64_t B);   /* 1 when st_gemv_swiglu takes the shape on this GPU */
+int st_gemv_swiglu(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X, void* act,
+                   int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);
+
 /* Decode step, one new token per sequence: st_qk_norm_rope for the query heads and st_kv_append of the step's K
  * (normalised and rotated by the appending warps themselves) and V rows, in one launch.  qkv BF16 [B, (hq + 2 hkv) *
  * 128] with row stride row_stride; slot int64 [B] (negative or outside the cache = no write); the pages are

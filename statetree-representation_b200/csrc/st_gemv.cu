@@ -45,6 +45,7 @@ struct GemvArgs {
   int NG, CPT, T;                         // column groups, units per tile, tiles per problem
   long long U;                            // units over all problems
   int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, ahead;
+  int act;                                // dense mode: rows are gate / up tiles in turn, the reducer stores silu(gate) * up
 #ifdef ST_PROF
   long long* prof;                        // [CTAs][64] globaltimer stamps (development builds only)
 #endif
@@ -315,6 +316,9 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
     // consumers (sums the consumer warps in order, stores or hands a partial sum over), so the consumers never wait
     pdl_wait();                                                // ws, cnt and Y may still be in use by the previous kernel
     int nf = 0;
+    float gate[EL / 32];                                       // act mode: the gate tile, until its up tile is done
+#pragma unroll
+    for (int k = 0; k < EL / 32; ++k) gate[k] = 0.f;
     for (; cur.valid(); cur.advance(a, cur.run_len(a))) {      // one hand-over per run of units of a tile
       const int buf = nf & 1;
       if (!mbar_wait(done + buf, (uint32_t)(nf >> 1) & 1u)) {
@@ -361,7 +365,26 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kerne
         }
       }
       if (lane == 0) PROF(24 + nf);
-      if (finish) {
+      if (finish && MODE == MODE_DENSE && a.act) {
+        // SwiGLU epilogue: tiles 2j and 2j + 1 hold rows 16j .. 16j + 15 of the gate and of the up projection; the host
+        // only allows this when every CTA owns whole tiles in pairs, so the gate tile is always the one just before.
+        // Rounding as the separate kernels: both outputs to BF16, silu in fp32 to BF16, BF16 product.
+        if ((cur.tile & 1) == 0) {
+#pragma unroll
+          for (int k = 0; k < EL / 32; ++k) gate[k] = sum[k];
+        } else {
+#pragma unroll
+          for (int k = 0; k < EL / 32; ++k) {
+            const int idx = lane + 32 * k, n = idx >> 4, r = idx & 15;
+            const long long row = out_row<MODE>(a, cur.p, n);
+            if (row >= 0) {
+              const float gte = __bfloat162float(__float2bfloat16_rn(gate[k]));
+              const __nv_bfloat16 hv = __hmul(__float2bfloat16_rn(gte / (1.f + __expf(-gte))), __float2bfloat16_rn(sum[k]));
+              a.Y[row * (a.M >> 1) + (size_t)(cur.tile >> 1) * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+            }
+          }
+        }
+      } else if (finish) {
 #pragma unroll
         for (int k = 0; k < EL / 32; ++k) {
           const int idx = lane + 32 * k, n = idx >> 4, r = idx & 15;
@@ -607,6 +630,9 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   ST_REQUIRE(p.maxcover == 1 || (a.ws && ws_bytes >= need), "%s: workspace of %lld bytes needed, %lld given", who, need,
              ws_bytes);
   ST_REQUIRE(p.stages >= 2, "%s: internal: ring does not fit", who);
+  ST_REQUIRE(!a.act || (p.U % p.C == 0 && (p.U / p.C) % (2 * p.CPT) == 0),
+             "%s: the SwiGLU epilogue needs a grid in which every CTA owns whole tiles in pairs (%lld units on %d CTAs)", who,
+             (long long)p.U, p.C);
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "%s: no device status word", who);
 #ifdef ST_PROF
@@ -668,6 +694,29 @@ extern "C" int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, 
   if (B <= 8) return launch<1, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
   if (B <= 16) return launch<2, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
   return launch<4, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
+}
+
+extern "C" int st_gemv_swiglu_supported(int64_t M, int64_t N, int64_t B) {
+  if (M <= 0 || N <= 0 || M % 32 || N % 64 || B < 1 || B > 8) return 0;
+  const Plan p = make_plan<1>(M, N, 1, (int)B, true);
+  return (p.stages >= 2 && p.U % p.C == 0 && (p.U / p.C) % (2 * p.CPT) == 0) ? 1 : 0;
+}
+
+extern "C" int st_gemv_swiglu(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X,
+                              void* act, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt,
+                              void* stream) {
+  ST_REQUIRE(M > 0 && N > 0 && M % 32 == 0 && N % 64 == 0, "st_gemv_swiglu: M %% 32 and N %% 64 must be 0 (got %lld x %lld)",
+             (long long)M, (long long)N);
+  ST_REQUIRE(B >= 1 && B <= 8, "st_gemv_swiglu: batch must be in [1, 8] (got %lld)", (long long)B);
+  ST_REQUIRE(tree && eo && eb && el && X && act && cnt, "st_gemv_swiglu: null pointer");
+  ST_REQUIRE(st::aligned16(tree) && st::aligned16(eb) && st::aligned16(X),
+             "st_gemv_swiglu: tree, eb and X must be 16-byte aligned");
+  ST_REQUIRE((M / 16) * ((N / 64 + 7) / 8) < (1ll << 31), "st_gemv_swiglu: too many units");
+  GemvArgs a = {};
+  a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
+  a.X = (const uint16_t*)X; a.Y = (uint16_t*)act; a.Yf = nullptr; a.ws = (float*)ws; a.cnt = cnt;
+  a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1; a.act = 1;
+  return launch<1, MODE_DENSE>(a, 1, (int)B, ws_bytes, (cudaStream_t)stream, "st_gemv_swiglu");
 }
 
 // ---------------------------------------------------------------------------------------------- st_gemv_static

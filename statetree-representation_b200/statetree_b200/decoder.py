@@ -10,6 +10,7 @@ logits; embeddings and norms are replicated.  Every rank draws the full tensors 
 so a tensor-parallel run computes the same function as the single-GPU one.
 """
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -17,7 +18,7 @@ import torch.distributed as dist
 import torch.nn.functional as Fn
 
 from .kvcache import StateTreeKVCache
-from .linear import TreeLinear
+from .linear import TreeLinear, interleave_gate_up
 from .ops import ext, kv_ext
 
 
@@ -60,6 +61,11 @@ class TreeDecoder:
         c = cfg
         assert c.heads % world == 0 and c.kv_heads % world == 0 and c.inter % (64 * world) == 0 and c.vocab % (16 * world) == 0
         self.hq, self.hkv = c.heads // world, c.kv_heads // world
+        self.fused_act = False
+        if compressed and batch <= 8 and os.environ.get("STATETREE_FUSED_ACT", "1") != "0":
+            from .ops import lib
+            with torch.cuda.device(self.dev):
+                self.fused_act = bool(lib().st_gemv_swiglu_supported(2 * c.inter // world, c.hidden, batch))
         gen = torch.Generator(device=self.dev)
         self._tid = 0
 
@@ -86,7 +92,10 @@ class TreeDecoder:
             per = o.shape[1] // world
             o = make(o[:, rank * per:(rank + 1) * per])
             g, u = draw(c.inter, c.hidden), draw(c.inter, c.hidden)
-            gu = make(torch.cat([rows(g), rows(u)]))
+            if self.fused_act:                              # gate / up tiles in turn: SwiGLU in the GEMV's epilogue
+                gu = make(interleave_gate_up(rows(g).contiguous(), rows(u).contiguous()))
+            else:
+                gu = make(torch.cat([rows(g), rows(u)]))
             del g, u
             d = draw(c.hidden, c.inter)
             per = d.shape[1] // world
@@ -158,9 +167,12 @@ class TreeDecoder:
                                v=v.unsqueeze(1), cache_seqlens=self.lens, softmax_scale=scale)
             delta = o(att.reshape(B, self.hq * D))
             self._add_norm(x, delta, h)
-            y = gu(h)
-            act = torch.empty(B, y.shape[1] // 2, dtype=torch.bfloat16, device=self.dev)
-            E.silu_mul(y, act)
+            if self.fused_act:
+                act = gu.swiglu(h)
+            else:
+                y = gu(h)
+                act = torch.empty(B, y.shape[1] // 2, dtype=torch.bfloat16, device=self.dev)
+                E.silu_mul(y, act)
             delta = d(act)
         self._add_norm(x, delta, h)
         logits = self.lm_head(h)

@@ -208,6 +208,26 @@ class TreeLinear(nn.Module):
         return y if src == dev else y.to(src)
 
 
+def interleave_gate_up(gate, up):
+    """[2 I, in] weight whose 16-row tiles alternate between the gate and the up projection (tile 2j = gate rows
+    16j .. 16j + 15, tile 2j + 1 = the same rows of up): the layout TreeLinear.swiglu expects"""
+    I, N = gate.shape
+    assert up.shape == gate.shape and I % 16 == 0
+    return torch.stack([gate.view(I // 16, 16, N), up.view(I // 16, 16, N)], 1).reshape(2 * I, N).contiguous()
+
+
+def swiglu(self, x):
+    """x [B, in] BF16, B <= 8 -> silu(gate x) * (up x) [B, I] in one launch, for a TreeLinear built from
+    interleave_gate_up(gate, up); raises RuntimeError for shapes the fused epilogue does not take"""
+    B = x.shape[0]
+    eo, el, eb = self.tables()
+    E, st = ext(), _state(x.device)
+    act = torch.empty(B, self.out_features // 2, dtype=torch.bfloat16, device=x.device)
+    ws = st.get_ws(E.gemv_workspace_bytes(self.out_features, self.in_features, B))
+    E.gemv_swiglu(self.tree, eo, eb, el, x, act, ws, st.get_cnt(self.out_features // 16))
+    return act
+
+
 class TreeSlice(nn.Module):
     """Rows [start, start + size) of a fused TreeLinear (q / k / v of a fused qkv, gate / up of a fused gate_up):
     parts called with the same input object share one product (reference: statetree/linear.py TreeSlice)."""
@@ -244,3 +264,6 @@ class TreeEmbedding(nn.Module):
 
     def forward(self, ids):
         return self.table.rows(ids)
+
+
+TreeLinear.swiglu = swiglu

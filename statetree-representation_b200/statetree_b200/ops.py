@@ -39,6 +39,8 @@ _SIGNATURES = {
     "st_kv_append": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _int, _vp]),
     "st_kv_dequant": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "st_kv_dequant_blocks": (_int, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
+    "st_gemv_swiglu_supported": (_int, [_i64, _i64, _i64]),
+    "st_gemv_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_rope_kv_append": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _dbl, _vp, _vp, _i64,
                                  _vp, _i64, _vp, _vp]),
     "st_moe_align": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
@@ -179,6 +181,15 @@ class _Weights:
             _check(lib().st_moe_group_gemv(_ptr(TP), _ptr(EOP), _ptr(EBP), _ptr(ELP), TP.numel(), _ptr(X),
                                            _ptr(sorted_ids), _ptr(bexp), _ptr(npost), bexp.numel(), _ptr(Y), S, M, N,
                                            xdiv, _ptr(WS), WS.numel() * WS.element_size(), _ptr(CNT), _stream(X)))
+
+    @staticmethod
+    def gemv_swiglu(T, EO, EB, EL, X, act, WS, CNT):
+        """act [B, I] = silu(gate) * up for a tree whose 2 I rows interleave gate and up in 16-row tiles (B <= 8)"""
+        B, N = X.shape
+        M = T.shape[0] * 16
+        with _ctx(T):
+            _check(lib().st_gemv_swiglu(_ptr(T), _ptr(EO), _ptr(EB), _ptr(EL), _ptr(X), _ptr(act), B, M, N, _ptr(WS),
+                                        WS.numel() * WS.element_size(), _ptr(CNT), _stream(T)))
 
     @staticmethod
     def moe_align(ids, E, used_bins, sorted_ids, bexp, npost):

@@ -157,3 +157,31 @@ def test_benchmark_shape_roundtrip_and_properties():
         assert err < TOL, (B, err)
         assert torch.equal(y, yf.to(torch.bfloat16))
     _status_ok()
+
+
+@pytest.mark.gpu
+def test_gemv_swiglu_matches_gemv_then_silu_mul():
+    """the SwiGLU epilogue on a tile-interleaved gate/up tree gives the bits of the plain product followed by st_silu_mul"""
+    import torch
+    import statetree_b200 as S
+    from statetree_b200.linear import interleave_gate_up
+    from statetree_b200.ops import ext, lib
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(21)
+    I, N = 12288, 4096
+    g = (torch.randn(I, N, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    u = (torch.randn(I, N, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    g[:, 7] *= 8
+    plain = S.TreeLinear.from_weight(torch.cat([g, u]), verify=False)
+    inter = S.TreeLinear.from_weight(interleave_gate_up(g, u), verify=False)
+    for B in (1, 3, 8):
+        assert lib().st_gemv_swiglu_supported(2 * I, N, B) == 1
+        x = torch.randn(B, N, device=dev, generator=gen).to(torch.bfloat16)
+        y = plain(x)
+        want = torch.empty(B, I, dtype=torch.bfloat16, device=dev)
+        ext().silu_mul(y, want)
+        got = inter.swiglu(x)
+        assert torch.equal(got, want), B
+    assert lib().st_gemv_swiglu_supported(2 * 48, 64, 1) in (0, 1)      # small shapes: answered, never a crash
+    from statetree_b200 import ops
+    assert ops.device_status() == 0
