@@ -161,7 +161,7 @@ struct UnitCursor {
 // G groups of 8 consumer warps (group g takes every G-th unit, warp r of a group takes record r of the unit), then
 // one producer warp and one reducer warp.
 template <int NT, int MODE, int G>
-__global__ void __launch_bounds__((CW * G + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int NB = 8 * NT;                                   // activation columns of the mma
   constexpr int EL = 16 * NB;                                  // outputs of one tile
@@ -563,13 +563,21 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   p.U = (long long)nprob * p.T * p.CPT;
   p.nxrows = nx;
   p.groups = 1;
+  // STATETREE_GEMV_G2=1 (tuning aid): batches whose rows fit shared memory whole only once per SM (4-8 rows of 4096
+  // columns) run one CTA of two consumer groups per SM on whole rows instead of two CTAs on 512-column slices;
+  // measured slower (batch 8: 4.09 vs 3.78 ms per step, batch 4: 3.89 vs 3.37)
+  static int g2 = -1;
+  if (g2 < 0) { const char* v = getenv("STATETREE_GEMV_G2"); g2 = v ? atoi(v) : 0; }
+  const bool two_groups = g2 == 1 && dense && NT == 1 && (long long)nx * (N * 2 + 16) > 32 * 1024 &&
+                          (long long)nx * (N * 2 + 16) <= 72 * 1024;
+  if (two_groups) p.groups = 2;
   // whole activation rows stay resident when they are small (decode batches of one or two rows)
-  p.xwhole = dense && (long long)nx * (N * 2 + 16) <= 32 * 1024 ? 1 : 0;
+  p.xwhole = (dense && (long long)nx * (N * 2 + 16) <= 32 * 1024) || two_groups ? 1 : 0;
   p.xw_stride = p.xwhole ? (int)(N * 2 + 16) : 0;
   p.xw_bytes = p.xwhole ? nx * p.xw_stride : 0;
   p.stage_bytes = UNIT_BYTES + SIDE_BYTES + (p.xwhole ? 0 : nx * XROW);
   constexpr int EL = 16 * 8 * NT;
-  const size_t fixed = XROW + p.xw_bytes + (size_t)2 * CW * p.groups * EL * 4 + (2 * 8 + 5) * 8 + 16;
+  const size_t fixed = XROW + p.xw_bytes + (size_t)2 * CW * p.groups * EL * 4 + (2 * 16 + 5) * 8 + 16;
   // Two CTAs per SM, each with the deepest ring that fits half of the SM's shared memory: the streaming rate is set
   // by the bytes in flight per SM (measured: 2 x 7 stages = 174 KB in flight sustain ~5.7 TB/s; smaller rings with an
   // L2 prefetch running ahead of them were slower, the prefetch instruction stalls its issuer once the queue is deep).
@@ -587,14 +595,14 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
     if (ahead > 32) ahead = 32;
   }
   p.ahead = ahead;
-  int per_sm = slots_per_sm;
-  int stages = (int)((budget_kb * 1024 - (long long)fixed) / p.stage_bytes);
+  int per_sm = two_groups ? 1 : slots_per_sm;
+  int stages = (int)(((two_groups ? 224 : budget_kb) * 1024 - (long long)fixed) / p.stage_bytes);
   if (stages < 2) {
     per_sm = 1;
     stages = (int)((200 * 1024 - (long long)fixed) / p.stage_bytes);
   }
-  if (stages > max_stages) stages = max_stages;
-  if (stages > 8) stages = 8;
+  if (stages > max_stages && !two_groups) stages = max_stages;
+  if (stages > (two_groups ? 14 : 8)) stages = two_groups ? 14 : 8;
   p.stages = stages;
   p.smem = (size_t)stages * p.stage_bytes + fixed;
   const long long slots = (long long)st::sm_count() * per_sm;
@@ -619,10 +627,8 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   return p;
 }
 
-template <int NT, int MODE>
-int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
-  constexpr int G = 1;
-  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE);
+template <int NT, int MODE, int G>
+int launch_g(GemvArgs& a, const Plan& p, int nprob, long long ws_bytes, cudaStream_t stream, const char* who) {
   a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages;
   a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows; a.xwhole = p.xwhole; a.xw_stride = p.xw_stride;
   a.xw_bytes = p.xw_bytes; a.ahead = p.ahead;
@@ -643,7 +649,7 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set[dev]) {
     if (int e = st::cuda_fail(cudaFuncSetAttribute(gemv_kernel<NT, MODE, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   200 * 1024), who))
+                                                   (G == 1 ? 200 : 227) * 1024), who))
       return e;
     set[dev] = true;
   }
@@ -659,6 +665,13 @@ int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stre
   cfg.numAttrs = st::pdl_enabled() ? 1 : 0;
   if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemv_kernel<NT, MODE, G>, a), who)) return e;
   return 0;
+}
+
+template <int NT, int MODE>
+int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
+  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE);
+  if (NT == 1 && MODE == MODE_DENSE && p.groups == 2) return launch_g<1, MODE_DENSE, 2>(a, p, nprob, ws_bytes, stream, who);
+  return launch_g<NT, MODE, 1>(a, p, nprob, ws_bytes, stream, who);
 }
 
 template <int NT>
