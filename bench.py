@@ -789,9 +789,9 @@ def main():
     hbm, tf, which = peaks()
     value = step_bytes / (ms * 1e-3) / 1e9
     per_gpu = value / world
-    # DRAM bytes per launch from the ncu capture summarised in profiles/ (batch 1, one GPU: 42.65 MB measured per
+    # DRAM bytes per launch from the ncu capture summarised in profiles/ (batch 1, one GPU: 42.59 MB measured per
     # launch on average over the seven shapes, against 41.80 MB algorithmic); null where no capture exists
-    traffic = 42.65e6 if (B == 1 and world == 1 and args.layers == LAYERS) else None
+    traffic = 42.59e6 if (B == 1 and world == 1 and args.layers == LAYERS) else None
     roof = {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s", "frac": per_gpu / hbm,
             "traffic": traffic, "peak_source": f"of {which}", "frac_of_nominal_8TBs": per_gpu / 8000.0,
             "kernel": "gemv_kernel" if use_gemv else "gemm_kernel",
