@@ -77,3 +77,17 @@ def test_shape_checks():
         F.encode(torch.zeros(8, 64, dtype=torch.bfloat16))
     with pytest.raises(AssertionError):
         F.encode(torch.zeros(16, 64))
+
+
+def test_interleave_gate_up_layout():
+    """tile 2j of the fused weight = rows 16j .. 16j + 15 of gate, tile 2j + 1 = the same rows of up"""
+    import torch
+    from statetree_b200.linear import interleave_gate_up
+    I, N = 64, 8
+    g = torch.arange(I * N, dtype=torch.float32).view(I, N)
+    u = -g
+    w = interleave_gate_up(g, u)
+    assert w.shape == (2 * I, N)
+    for j in range(I // 16):
+        assert torch.equal(w[32 * j:32 * j + 16], g[16 * j:16 * j + 16])
+        assert torch.equal(w[32 * j + 16:32 * j + 32], u[16 * j:16 * j + 16])
