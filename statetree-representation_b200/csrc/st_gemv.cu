@@ -568,11 +568,18 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   // measured slower (batch 8: 4.09 vs 3.78 ms per step, batch 4: 3.89 vs 3.37)
   static int g2 = -1;
   if (g2 < 0) { const char* v = getenv("STATETREE_GEMV_G2"); g2 = v ? atoi(v) : 0; }
-  const bool two_groups = g2 == 1 && dense && NT == 1 && (long long)nx * (N * 2 + 16) > 32 * 1024 &&
+  const long long xw_kb_g2 = 66;
+  const bool two_groups = g2 == 1 && dense && NT == 1 && (long long)nx * (N * 2 + 16) > (long long)xw_kb_g2 * 1024 &&
                           (long long)nx * (N * 2 + 16) <= 72 * 1024;
   if (two_groups) p.groups = 2;
-  // whole activation rows stay resident when they are small (decode batches of one or two rows)
-  p.xwhole = (dense && (long long)nx * (N * 2 + 16) <= 32 * 1024) || two_groups ? 1 : 0;
+  // whole activation rows stay resident when they fit next to a ring of at least two stages
+  // Whole rows win over 512-column slices even when they leave room for three ring stages only (measured, ms per step of
+  // the Qwen3-8B linears: batch 4 3.36 -> 3.12, batch 6 3.59 -> 3.25, batch 8 3.78 -> 3.39): a slice costs eight more
+  // bulk copies per stage and re-reads the activations from L2 for every 16-row tile.  Limit: 66 KB = 8 rows of 4096
+  // columns.  STATETREE_GEMV_XWHOLE_KB overrides it (tuning aid).
+  static int xw_kb = -1;
+  if (xw_kb < 0) { const char* v = getenv("STATETREE_GEMV_XWHOLE_KB"); xw_kb = v ? atoi(v) : 66; }
+  p.xwhole = (dense && (long long)nx * (N * 2 + 16) <= (long long)xw_kb * 1024) || two_groups ? 1 : 0;
   p.xw_stride = p.xwhole ? (int)(N * 2 + 16) : 0;
   p.xw_bytes = p.xwhole ? nx * p.xw_stride : 0;
   p.stage_bytes = UNIT_BYTES + SIDE_BYTES + (p.xwhole ? 0 : nx * XROW);
