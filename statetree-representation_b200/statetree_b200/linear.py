@@ -15,8 +15,8 @@ from . import format as F
 from .ops import ext
 
 GEMV_MAX = int(os.environ.get("STATETREE_GEMV_MAX", "10"))     # rows up to which the GEMV kernel runs (<= 32);
-# measured on B200 (Qwen3-8B shapes, ms per step of 252 linears): GEMV 3.76 at 8 rows, 4.22 at 9, 4.54 at 12, 4.95 at
-# 16; tcgen05 GEMM 4.41-4.44 at 9-16 and 4.49 at 32
+# measured on B200 (Qwen3-8B shapes, ms per step of 252 linears): GEMV 3.39 at 8 rows, 4.22 at 9, 4.54 at 12, 4.95 at
+# 16; tcgen05 GEMM 4.41-4.44 at 9-16 and 4.32 at 32
 _STATES = {}
 
 
