@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define ST_ABI_VERSION 1
+#define ST_ABI_VERSION 2
 
 /* replaces the `ABI` attribute check of statetree/ops.py:12 */
 int st_abi_version(void);
@@ -48,20 +48,22 @@ int st_rows(const void* tree, const int32_t* eo, const uint32_t* el, int64_t M, 
 
 /* Small-batch fused decode + GEMV, 1 <= B <= 32.  Replaces the reference's mv / mvs / mvh / mvc / mvt entry points
  * (statetree/csrc/kernels.cu:243-254, 370-400, 548-599, 771-808; statetree/csrc/hop.cu:993-1019).
- * ws: fp32 workspace of st_gemv_workspace_bytes() bytes; cnt: int32 [M/16] semaphores, zero on entry and on exit
- * (MoE: cnt int32 [problems * M/16], problems = S slots or nblk blocks).
+ * ws: workspace of st_gemv_workspace_bytes() bytes whose 32-bit words all hold 0xFFFFFFFF on entry and are left so
+ * (fill it once after allocating it; the kernels use the words as exchange slots for tiles shared between CTAs and put
+ * the all-ones sentinel back).  cnt: int32 [M/16] (MoE: [problems * M/16], problems = S slots or nblk blocks), zero
+ * on entry and on exit; kept in the signature for callers of the reference's layout, the GEMV no longer touches it.
  * Yf32 (optional, may be NULL): the fp32 accumulators [B, M] before BF16 rounding, for verification. */
 int64_t st_gemv_workspace_bytes(int64_t M, int64_t N, int64_t B);
 int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X, void* Y,
             float* Yf32, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);
 
 /* st_gemv for callers that cannot allocate device memory and so have no workspace to pass: code running inside a
- * host framework that owns the whole device pool, or anywhere cudaMalloc is off limits.  The split partial sums and
- * tile semaphores live in a 4.06 MiB array built into the library (present on every GPU that loads it, until exit),
+ * host framework that owns the whole device pool, or anywhere cudaMalloc is off limits.  The exchange slots of tiles
+ * shared between CTAs live in a 4.06 MiB array built into the library (present on every GPU that loads it, until exit),
  * so the call takes only inputs and outputs and calls no allocator.  Limits: the shape's partial sums must fit
  * 4 MiB and M <= 262144, otherwise the call is rejected with a message and nothing is launched.  The first call on
  * a device looks up the array's device address; make that first call before any stream capture.  All calls on a
- * device share the array (its semaphores are cleared on the stream at every call), so two calls that overlap on the
+ * device share the array (the slots a shape uses are reset on the stream at every call), so two calls that overlap on the
  * GPU - different streams, or different threads - race: serialise them.  No counterpart in the reference. */
 int st_gemv_static(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X, void* Y,
                    int64_t B, int64_t M, int64_t N, void* stream);

@@ -30,6 +30,7 @@ constexpr int UNIT_BYTES = CW * REC;      // 12416
 constexpr int SIDE_BYTES = 64;            // escape block of a unit
 constexpr int XROW = CW * 128 + 16;       // bytes per staged activation row (512 columns + pad: conflict-free ldmatrix)
 constexpr int MODE_DENSE = 0, MODE_SLOT = 1, MODE_GROUP = 2;
+constexpr uint32_t EMPTY_SLOT = 0xFFFFFFFFu;  // what every word of the workspace holds between launches
 
 struct GemvArgs {
   // dense: one matrix; MoE: per-expert device address tables
@@ -44,22 +45,9 @@ struct GemvArgs {
   int E, xdiv;
   int NG, CPT, T;                         // column groups, units per tile, tiles per problem
   long long U;                            // units over all problems
-  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, ahead;
+  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
   int act;                                // dense mode: rows are gate / up tiles in turn, the reducer stores silu(gate) * up
-#ifdef ST_PROF
-  long long* prof;                        // [CTAs][64] globaltimer stamps (development builds only)
-#endif
 };
-
-#ifdef ST_PROF
-__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define PROF(slot) do { if (a.prof && (slot) < 64) a.prof[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
-#define CK(n) do { const long long t_ = clock64(); ck[n] += t_ - ckl; ckl = t_; } while (0)
-long long* g_prof_buf = nullptr;
-#else
-#define PROF(slot) do {} while (0)
-#define CK(n) do {} while (0)
-#endif
 
 struct Prob {                             // what a unit's problem resolves to
   const uint8_t* tree; const int* eo; const uint32_t* eb; const uint32_t* el;
@@ -158,36 +146,34 @@ struct UnitCursor {
   }
 };
 
-// G groups of 8 consumer warps (group g takes every G-th unit, warp r of a group takes record r of the unit), then
-// one producer warp and one reducer warp.
-template <int NT, int MODE, int G>
-__global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1) gemv_kernel(const GemvArgs a) {
+// Eight consumer warps (warp r takes record r of every unit), then one producer warp and one reducer warp.
+template <int NT, int MODE>
+__global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int NB = 8 * NT;                                   // activation columns of the mma
   constexpr int EL = 16 * NB;                                  // outputs of one tile
-  constexpr int NCW = CW * G;                                  // consumer warps
+  constexpr int NRED = NT == 1 ? 4 : 2;                        // tile results in flight between consumers and reducer
   const int S = a.stages, STAGE = a.stage_bytes, NX = a.nxrows;
   uint8_t* ring = smem;
   uint8_t* zrow = smem + (size_t)S * STAGE;                                 // one all-zero activation row
   uint8_t* xw = zrow + XROW;                                                // whole activation rows (xwhole mode)
-  float* red = reinterpret_cast<float*>(xw + a.xw_bytes);                   // [2][NCW][EL]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * NCW * EL);
+  float* red = reinterpret_cast<float*>(xw + a.xw_bytes);                   // [NRED][CW][EL]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + NRED * CW * EL);
   uint64_t* empty = full + S;
-  uint64_t* done = empty + S;                                               // [2] partials of a tile are in red[buf]
-  uint64_t* freeb = done + 2;                                               // [2] red[buf] may be overwritten
-  uint64_t* xbar = freeb + 2;                                               // whole activation rows have landed
+  uint64_t* done = empty + S;                                               // [NRED] partials of a tile are in red[buf]
+  uint64_t* freeb = done + NRED;                                            // [NRED] red[buf] may be overwritten
+  uint64_t* xbar = freeb + NRED;                                            // whole activation rows have landed
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = gridDim.x;
   int u0 = (int)((long long)blockIdx.x * a.U / C), u1 = (int)((long long)(blockIdx.x + 1) * a.U / C);
 
-  if (tid == 0) PROF(0);
   if (tid < S) {                                               // one thread per ring stage sets its barriers up
     mbar_init(full + tid, 1);
     mbar_init(empty + tid, CW);
     fence_barrier_init();
   } else if (tid == 32) {
-    for (int b = 0; b < 2; ++b) { mbar_init(done + b, NCW); mbar_init(freeb + b, 1); }
+    for (int b = 0; b < NRED; ++b) { mbar_init(done + b, CW); mbar_init(freeb + b, 1); }
     mbar_init(xbar, 1);
     fence_barrier_init();
   }
@@ -207,16 +193,12 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
 
   UnitCursor<MODE> cur;
   cur.init(a, u0, u1);
-  if (tid == 0) PROF(1);
 
-  if (warp == NCW) {
+  if (warp == CW) {
     // ------------------------------------------------------------------ producer warp.  Lane 0 moves the records,
     // lane 1 the escape block, lane n activation row n.  Weights never depend on the previous kernel, so the first
     // ring fill is issued before griddepcontrol.wait; activations (and everything the reducer touches) after it.
     const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
-#ifdef ST_PROF
-    int pcount = 0;
-#endif
     int lastp = -1;
     const uint16_t* xrow = nullptr;                           // this lane's activation row of the current problem
     unsigned nx = 0;
@@ -244,18 +226,8 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
         bulk_g2s(ring + (size_t)s * STAGE + UNIT_BYTES + SIDE_BYTES + lane * XROW, xrow + (size_t)k.c * CW * 64,
                  (uint32_t)(k.nrec(a) * 128), full + s, pol_x);
     };
-    // HBM -> L2 prefetch runs AHEAD units in front of the unit being copied into the ring: the depth of the HBM
-    // request queue no longer depends on how much shared memory the ring has, so the ring can stay small
-    auto l2_prefetch = [&](const UnitCursor<MODE>& k) {
-      const uint8_t* src = k.pr.tree + ((size_t)k.tile * a.NG + (size_t)k.c * CW) * REC;
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(src), "r"((uint32_t)(k.nrec(a) * REC)) : "memory");
-    };
-    const int AHEAD = a.ahead;
     UnitCursor<MODE> mine = cur;                               // lane i looks at unit i of this CTA
     for (int i = 0; i < lane && mine.valid(); ++i) mine.next(a);
-    if (lane < AHEAD && mine.valid()) l2_prefetch(mine);
-    UnitCursor<MODE> pf = cur;
-    for (int i = 0; i < AHEAD && pf.valid(); ++i) pf.next(a);
     // first ring fill: weights, then wait for the previous kernel, then the activations
     UnitCursor<MODE> pre = cur;
     int filled = 0;
@@ -285,18 +257,11 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
       row_of(cur);
       acts(cur, s);
       ++s;
-#ifdef ST_PROF
-      if (lane == 0) { PROF(40 + pcount); ++pcount; }
-#endif
     }
     s = 0;                                                     // filled == S whenever units remain
     uint32_t ph = 0;
     for (; cur.valid(); cur.next(a)) {
       row_of(cur);
-      if (AHEAD > 0 && pf.valid()) {
-        if (lane == 2) l2_prefetch(pf);
-        pf.next(a);
-      }
       if (!mbar_wait(empty + s, ph)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
         break;
@@ -304,68 +269,82 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
       weights(cur, s);
       acts(cur, s);
       if (++s == S) { s = 0; ph ^= 1u; }
-#ifdef ST_PROF
-      if (lane == 0) { PROF(40 + pcount); ++pcount; }
-#endif
     }
     return;
   }
 
-  if (warp == NCW + 1) {
+  if (warp == CW + 1) {
     // ------------------------------------------------------------------ reducer warp: finishes tiles behind the
-    // consumers (sums the consumer warps in order, stores or hands a partial sum over), so the consumers never wait
-    pdl_wait();                                                // ws, cnt and Y may still be in use by the previous kernel
+    // consumers (sums the consumer warps in order, then stores or meets the other CTAs of the tile), so the consumers
+    // never wait.
+    //
+    // A tile cut by CTA boundaries is finished without semaphores, word by word, through exchange slots in `ws` that
+    // hold a sentinel (all ones, a NaN pattern no arithmetic produces) between launches.  For a tile in n parts the
+    // sums are folded left to right, ((p0 + p1) + p2) + ...: slot level L is where the fold of parts < L meets part L.
+    // Each of the two parties swaps its value into the slot (atomicExch); the one that finds the sentinel is done, the
+    // one that finds the other's value adds it (fp32 addition is commutative, so who came second does not matter),
+    // restores the sentinel and either stores the result (last level) or carries the fold to the next level.  The
+    // result has one fixed summation order, and the usual two-part tile costs its second arriver a single round trip.
+    pdl_wait();                                                // ws and Y may still be in use by the previous kernel
     int nf = 0;
     float gate[EL / 32];                                       // act mode: the gate tile, until its up tile is done
 #pragma unroll
     for (int k = 0; k < EL / 32; ++k) gate[k] = 0.f;
     for (; cur.valid(); cur.advance(a, cur.run_len(a))) {      // one hand-over per run of units of a tile
-      const int buf = nf & 1;
-      if (!mbar_wait(done + buf, (uint32_t)(nf >> 1) & 1u)) {
+      const int buf = nf % NRED;
+      if (!mbar_wait(done + buf, (uint32_t)(nf / NRED) & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
         return;
       }
       ++nf;
       float sum[EL / 32];
-      const float* rb = red + buf * NCW * EL;
+      const float* rb = red + buf * CW * EL;
 #pragma unroll
       for (int k = 0; k < EL / 32; ++k) {
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) v += rb[w * EL + lane + 32 * k];
+        for (int w = 0; w < CW; ++w) v += rb[w * EL + lane + 32 * k];
         sum[k] = v;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(freeb + buf);
       const int tbase = cur.u - cur.c;                          // first unit of the tile
       const bool owned = tbase >= u0 && tbase + a.CPT <= u1;
-      const long long tg = (long long)cur.p * a.T + cur.tile;
-      bool finish = owned;
+      long long orow[EL / 32];                                  // output row of each of this lane's values, -1 = none
+#pragma unroll
+      for (int k = 0; k < EL / 32; ++k) orow[k] = out_row<MODE>(a, cur.p, (lane + 32 * k) >> 4);
       if (!owned) {
+        const long long tg = (long long)cur.p * a.T + cur.tile;
         const int cfirst = cta_of_unit(tbase, a.U, C), clast = cta_of_unit(tbase + a.CPT - 1, a.U, C);
-        const int ncover = clast - cfirst + 1;
-        float* wsl = a.ws + (size_t)tg * a.maxcover * EL;
+        const int last_level = clast - cfirst;                  // parts - 1
+        const int part = blockIdx.x - cfirst;
+        uint32_t* slots = reinterpret_cast<uint32_t*>(a.ws) + (size_t)tg * a.maxcover * EL;
+        const int level0 = part > 0 ? part : 1;
+        uint32_t old[EL / 32];
 #pragma unroll
-        for (int k = 0; k < EL / 32; ++k) wsl[(size_t)(blockIdx.x - cfirst) * EL + lane + 32 * k] = sum[k];
-        __threadfence();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) last = (atomicAdd(a.cnt + tg, 1) == ncover - 1);
-        last = __shfl_sync(FULL, last, 0);
-        if (last) {
-          __threadfence();
+        for (int k = 0; k < EL / 32; ++k)                       // all swaps of the first level in flight together
+          old[k] = orow[k] >= 0 ? atomicExch(slots + (size_t)(level0 - 1) * EL + lane + 32 * k, __float_as_uint(sum[k]))
+                                : EMPTY_SLOT;
 #pragma unroll
-          for (int k = 0; k < EL / 32; ++k) {
-            float v = 0.f;
-            for (int j = 0; j < ncover; ++j) v += __ldcg(wsl + (size_t)j * EL + lane + 32 * k);
-            sum[k] = v;
+        for (int k = 0; k < EL / 32; ++k) {
+          uint32_t o = old[k];
+          int level = level0;
+          float v = sum[k];
+          while (o != EMPTY_SLOT) {                             // met the other party of this level
+            slots[(size_t)(level - 1) * EL + lane + 32 * k] = EMPTY_SLOT;
+            v += __uint_as_float(o);
+            if (level == last_level) {
+              const int r = (lane + 32 * k) & 15;
+              const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+              a.Y[orow[k] * a.M + (size_t)cur.tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+              if (a.Yf) a.Yf[orow[k] * a.M + (size_t)cur.tile * 16 + r] = v;
+              break;
+            }
+            ++level;
+            o = atomicExch(slots + (size_t)(level - 1) * EL + lane + 32 * k, __float_as_uint(v));
           }
-          if (lane == 0) a.cnt[tg] = 0;
-          finish = true;
         }
-      }
-      if (lane == 0) PROF(24 + nf);
-      if (finish && MODE == MODE_DENSE && a.act) {
+      } else if (MODE == MODE_DENSE && a.act) {
         // SwiGLU epilogue: tiles 2j and 2j + 1 hold rows 16j .. 16j + 15 of the gate and of the up projection; the host
         // only allows this when every CTA owns whole tiles in pairs, so the gate tile is always the one just before.
         // Rounding as the separate kernels: both outputs to BF16, silu in fp32 to BF16, BF16 product.
@@ -375,24 +354,22 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
         } else {
 #pragma unroll
           for (int k = 0; k < EL / 32; ++k) {
-            const int idx = lane + 32 * k, n = idx >> 4, r = idx & 15;
-            const long long row = out_row<MODE>(a, cur.p, n);
-            if (row >= 0) {
+            const int r = (lane + 32 * k) & 15;
+            if (orow[k] >= 0) {
               const float gte = __bfloat162float(__float2bfloat16_rn(gate[k]));
               const __nv_bfloat16 hv = __hmul(__float2bfloat16_rn(gte / (1.f + __expf(-gte))), __float2bfloat16_rn(sum[k]));
-              a.Y[row * (a.M >> 1) + (size_t)(cur.tile >> 1) * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+              a.Y[orow[k] * (a.M >> 1) + (size_t)(cur.tile >> 1) * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
             }
           }
         }
-      } else if (finish) {
+      } else {
 #pragma unroll
         for (int k = 0; k < EL / 32; ++k) {
-          const int idx = lane + 32 * k, n = idx >> 4, r = idx & 15;
-          const long long row = out_row<MODE>(a, cur.p, n);
-          if (row >= 0) {
+          const int r = (lane + 32 * k) & 15;
+          if (orow[k] >= 0) {
             const __nv_bfloat16 hv = __float2bfloat16_rn(sum[k]);
-            a.Y[row * a.M + (size_t)cur.tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-            if (a.Yf) a.Yf[row * a.M + (size_t)cur.tile * 16 + r] = sum[k];
+            a.Y[orow[k] * a.M + (size_t)cur.tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+            if (a.Yf) a.Yf[orow[k] * a.M + (size_t)cur.tile * 16 + r] = sum[k];
           }
         }
       }
@@ -401,17 +378,18 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
   }
 
   // -------------------------------------------------------------------- consumers
-  const int g = lane >> 2, grp = warp / CW, rec = warp % CW;
-  float acc[NT][2][4];                                       // two accumulator chains per column tile
+  const int g = lane >> 2, rec = warp;
+#ifdef ST_V3
+  constexpr int NCH = NT == 1 ? 4 : 2;                       // independent accumulator chains per column tile
+#else
+  constexpr int NCH = 2;
+#endif
+  float acc[NT][NCH][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) acc[nt][h][0] = acc[nt][h][1] = acc[nt][h][2] = acc[nt][h][3] = 0.f;
-  int s = 0, nf = 0, turn = 0;
-#ifdef ST_PROF
-  int ccount = 0;
-  long long ck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ckl = clock64();
-#endif
+    for (int h = 0; h < NCH; ++h) acc[nt][h][0] = acc[nt][h][1] = acc[nt][h][2] = acc[nt][h][3] = 0.f;
+  int s = 0, nf = 0;
   uint32_t ph = 0;
   // ldmatrix row addresses of this lane: activation row nt * 8 + (lane & 7), or the zero row beyond the batch
   const uint32_t colo = (uint32_t)(rec * 128 + (lane >> 3) * 16);
@@ -452,8 +430,7 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
   };
   while (cur.valid()) {
     const int len = cur.run_len(a), cbeg = cur.c;
-    for (int j = 0; j < len;) {
-      CK(0);                                                  // loop overhead
+    for (int j = 0; j < len; ++j) {
       const int c = cbeg + j;
       if (!xready) {                                          // whole activation rows: waited for once
         if (!mbar_wait(xbar, 0u)) {
@@ -462,99 +439,97 @@ __global__ void __launch_bounds__((CW * G + 2) * 32, (NT <= 2 && G == 1) ? 2 : 1
         }
         xready = true;
       }
-      const bool mine_unit = (G == 1) || (turn == grp);
-      if (G > 1) turn = turn + 1 == G ? 0 : turn + 1;
-      if (mine_unit) {
-        const int nrec = c == a.CPT - 1 ? last_nrec : CW;
-        if (!mbar_wait(full + s, ph)) {
-          if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
-          return;
-        }
-        const uint8_t* st = ring + (size_t)s * STAGE;
-        CK(1);                                                // wait for the stage
-        if (rec < nrec) {
-          // activations first: their shared-memory latency hides behind the decode
-          uint32_t b[NT][8];
-          const uint32_t sb = a.xwhole ? (uint32_t)(c * (CW * 128)) : smem_addr(st);
+      const int nrec = c == a.CPT - 1 ? last_nrec : CW;
+      if (!mbar_wait(full + s, ph)) {
+        if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+        return;
+      }
+      const uint8_t* st = ring + (size_t)s * STAGE;
+      if (rec < nrec) {
+        // activations first: their shared-memory latency hides behind the decode
+        uint32_t b[NT][8];
+        const uint32_t sb = a.xwhole ? (uint32_t)(c * (CW * 128)) : smem_addr(st);
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t xa = xo[nt] ? sb + xo[nt] : zaddr;
-            ldmatrix_x4(xa, b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
-            ldmatrix_x4(xa + 64, b[nt][4], b[nt][5], b[nt][6], b[nt][7]);
-          }
-          const uint32_t sw0 = *reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);            // escape block, word 0
-          const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];   // inline entries
-          const RecRegs raw = load_rec_shared(st + rec * REC, lane);
-          // everything this warp needs from the stage is in registers: hand the slot back before the arithmetic
-          __syncwarp();
-          if (lane == 0) mbar_arrive(empty + s);
-          uint32_t A[4][4];
-          decode_frag(raw, A);
-#ifdef ST_PROF
-          if (A[0][0] == 0x12345u && A[3][3] == 0x54321u) ck[7]++;   // keep the decode before the clock read
-#endif
-          CK(2);                                              // loads + decode
-          patch_unit(A, sw0, sw, c);
-          CK(3);                                              // escapes
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) mma_bf16(acc[nt][ks & 1], A[ks], b[nt][2 * ks], b[nt][2 * ks + 1]);
-#ifdef ST_PROF
-          if (acc[0][0][0] == 1.2345e30f) ck[7]++;             // keep the mma before the clock read
-#endif
-          CK(4);                                              // mma
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t xa = xo[nt] ? sb + xo[nt] : zaddr;
+          ldmatrix_x4(xa, b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
+          ldmatrix_x4(xa + 64, b[nt][4], b[nt][5], b[nt][6], b[nt][7]);
         }
-        if (rec >= nrec) {                                     // no record of this unit for the warp: release only
-          __syncwarp();
-          if (lane == 0) mbar_arrive(empty + s);
-        }
-        CK(5);                                                // release
-#ifdef ST_PROF
-        if (warp == 0 && lane == 0) { PROF(2 + ccount); ++ccount; }
+        const uint32_t sw0 = *reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);            // escape block, word 0
+#ifdef ST_V5
+        uint32_t sw = 0u;                                     // inline entries: read only when this record has escapes
+        if ((sw0 >> (16 + rec)) & 1u) sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];
+#else
+        const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];   // inline entries
 #endif
+        const RecRegs raw = load_rec_shared(st + rec * REC, lane);
+        // everything this warp needs from the stage is in registers: hand the slot back before the arithmetic
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+        uint32_t A[4][4];
+        decode_frag(raw, A);
+        patch_unit(A, sw0, sw, c);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) mma_bf16(acc[nt][ks % NCH], A[ks], b[nt][2 * ks], b[nt][2 * ks + 1]);
+      } else {                                                // no record of this unit for the warp: release only
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
       }
       if (++s == S) { s = 0; ph ^= 1u; }
-      ++j;
     }
     // ---- end of this CTA's share of the tile: hand the warp's partial sums to the reducer
-    const int buf = nf & 1;
-    if (nf >= 2 && !mbar_wait(freeb + buf, (uint32_t)((nf >> 1) - 1) & 1u)) {
+    const int buf = nf % NRED;
+    if (nf >= NRED && !mbar_wait(freeb + buf, (uint32_t)(nf / NRED - 1) & 1u)) {
       if (lane == 0) atomicExch(a.status, ERR_WAIT_ACC);
       return;
     }
     ++nf;
-    float* mine = red + (buf * NCW + warp) * EL;
+    float* mine = red + (buf * CW + warp) * EL;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int n0 = nt * 8 + 2 * (lane & 3);
-      mine[n0 * 16 + g] = acc[nt][0][0] + acc[nt][1][0];
-      mine[(n0 + 1) * 16 + g] = acc[nt][0][1] + acc[nt][1][1];
-      mine[n0 * 16 + g + 8] = acc[nt][0][2] + acc[nt][1][2];
-      mine[(n0 + 1) * 16 + g + 8] = acc[nt][0][3] + acc[nt][1][3];
+      float t4[4];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) acc[nt][h][0] = acc[nt][h][1] = acc[nt][h][2] = acc[nt][h][3] = 0.f;
+      for (int q = 0; q < 4; ++q) {
+        t4[q] = acc[nt][0][q] + acc[nt][1][q];
+        if (NCH == 4) t4[q] += acc[nt][2][q] + acc[nt][3][q];
+      }
+      mine[n0 * 16 + g] = t4[0];
+      mine[(n0 + 1) * 16 + g] = t4[1];
+      mine[n0 * 16 + g + 8] = t4[2];
+      mine[(n0 + 1) * 16 + g + 8] = t4[3];
+#pragma unroll
+      for (int h = 0; h < NCH; ++h) acc[nt][h][0] = acc[nt][h][1] = acc[nt][h][2] = acc[nt][h][3] = 0.f;
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(done + buf);
     cur.advance(a, len);
   }
-#ifdef ST_PROF
-  if (a.prof && warp == 0 && lane == 0)
-    for (int i = 0; i < 8; ++i) a.prof[blockIdx.x * 64 + 56 + i] = ck[i];
-#endif
 }
 
 struct Plan {
-  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes, groups, ahead;
+  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
   size_t smem;
   long long U;
   int CPT, T, NG, nprob;
 };
 
+// development builds (-DST_TUNE) read a few planning constants from the environment; the shipped library does not
+static int tune(const char* name, int dflt) {
+#ifdef ST_TUNE
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+#else
+  (void)name;
+  return dflt;
+#endif
+}
+
 // nx = activation rows staged per unit (the batch for a dense matrix, 1 per slot, 8 per block of slots).
 template <int NT>
-Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
+Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act = false) {
   Plan p;
   p.NG = (int)(N / 64);
   p.CPT = (p.NG + CW - 1) / CW;
@@ -562,65 +537,48 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   p.nprob = nprob;
   p.U = (long long)nprob * p.T * p.CPT;
   p.nxrows = nx;
-  p.groups = 1;
-  // STATETREE_GEMV_G2=1 (tuning aid): batches whose rows fit shared memory whole only once per SM (4-8 rows of 4096
-  // columns) run one CTA of two consumer groups per SM on whole rows instead of two CTAs on 512-column slices;
-  // measured slower (batch 8: 4.09 vs 3.78 ms per step, batch 4: 3.89 vs 3.37)
-  static int g2 = -1;
-  if (g2 < 0) { const char* v = getenv("STATETREE_GEMV_G2"); g2 = v ? atoi(v) : 0; }
-  const long long xw_kb_g2 = 66;
-  const bool two_groups = g2 == 1 && dense && NT == 1 && (long long)nx * (N * 2 + 16) > (long long)xw_kb_g2 * 1024 &&
-                          (long long)nx * (N * 2 + 16) <= 72 * 1024;
-  if (two_groups) p.groups = 2;
-  // whole activation rows stay resident when they fit next to a ring of at least two stages
-  // Whole rows win over 512-column slices even when they leave room for three ring stages only (measured, ms per step of
-  // the Qwen3-8B linears: batch 4 3.36 -> 3.12, batch 6 3.59 -> 3.25, batch 8 3.78 -> 3.39): a slice costs eight more
-  // bulk copies per stage and re-reads the activations from L2 for every 16-row tile.  Limit: 66 KB = 8 rows of 4096
-  // columns.  STATETREE_GEMV_XWHOLE_KB overrides it (tuning aid).
-  static int xw_kb = -1;
-  if (xw_kb < 0) { const char* v = getenv("STATETREE_GEMV_XWHOLE_KB"); xw_kb = v ? atoi(v) : 66; }
-  p.xwhole = (dense && (long long)nx * (N * 2 + 16) <= (long long)xw_kb * 1024) || two_groups ? 1 : 0;
+  // Whole activation rows stay resident in shared memory when they fit in 66 KB (8 rows of 4096 columns), which leaves
+  // at least three ring stages; beyond that every stage carries the matching 512-column slice of each row.
+  static const int xw_kb = tune("STATETREE_GEMV_XWHOLE_KB", 66);
+  p.xwhole = (dense && (long long)nx * (N * 2 + 16) <= (long long)xw_kb * 1024) ? 1 : 0;
   p.xw_stride = p.xwhole ? (int)(N * 2 + 16) : 0;
   p.xw_bytes = p.xwhole ? nx * p.xw_stride : 0;
   p.stage_bytes = UNIT_BYTES + SIDE_BYTES + (p.xwhole ? 0 : nx * XROW);
   constexpr int EL = 16 * 8 * NT;
-  const size_t fixed = XROW + p.xw_bytes + (size_t)2 * CW * p.groups * EL * 4 + (2 * 16 + 5) * 8 + 16;
-  // Two CTAs per SM, each with the deepest ring that fits half of the SM's shared memory: the streaming rate is set
-  // by the bytes in flight per SM (measured: 2 x 7 stages = 174 KB in flight sustain ~5.7 TB/s; smaller rings with an
-  // L2 prefetch running ahead of them were slower, the prefetch instruction stalls its issuer once the queue is deep).
-  // Tunables (environment, read once): STATETREE_GEMV_CTAS_PER_SM, STATETREE_GEMV_SMEM_KB, STATETREE_GEMV_STAGES,
-  // STATETREE_GEMV_AHEAD (units of L2 prefetch ahead of the ring, 0 = off).
-  static int slots_per_sm = 0, budget_kb = 0, ahead = 0, max_stages = 0;
-  if (slots_per_sm == 0) {
-    const char* v;
-    slots_per_sm = (v = getenv("STATETREE_GEMV_CTAS_PER_SM")) ? atoi(v) : 2;
-    budget_kb = (v = getenv("STATETREE_GEMV_SMEM_KB")) ? atoi(v) : 113;
-    ahead = (v = getenv("STATETREE_GEMV_AHEAD")) ? atoi(v) : 0;
-    max_stages = (v = getenv("STATETREE_GEMV_STAGES")) ? atoi(v) : 8;
-    if (slots_per_sm < 1) slots_per_sm = 1;
-    if (ahead < 0) ahead = 0;
-    if (ahead > 32) ahead = 32;
+  const size_t fixed = XROW + p.xw_bytes + (size_t)(NT == 1 ? 4 : 2) * CW * EL * 4 + (2 * 16 + 9) * 8 + 16;
+  // Two CTAs per SM, each with the deepest ring (at most 8 stages) that fits half of the SM's shared memory; one CTA
+  // when even two stages do not fit twice (32 activation rows).  Measured alternatives that lost: three CTAs of four
+  // stages at 64 registers per thread, and grids that cut tiles when a tile-aligned grid exists.
+  static const int want_per_sm = tune("STATETREE_GEMV_CTAS_PER_SM", 2), max_stages = tune("STATETREE_GEMV_STAGES", 8),
+                   align = tune("STATETREE_GEMV_ALIGN", 1), min_units = tune("STATETREE_GEMV_MIN_UNITS", 2);
+  int per_sm = want_per_sm < 1 ? 1 : (want_per_sm > 2 ? 2 : want_per_sm);
+  int stages = 0;
+  for (; per_sm >= 1; --per_sm) {
+    // shared memory of an SM with 1 KB per CTA reserved; a single CTA is capped at the 200 KB the kernel opts in to
+    const long long budget = per_sm == 1 ? 200 * 1024 : 233472 / per_sm - 1024;
+    stages = (int)((budget - (long long)fixed) / p.stage_bytes);
+    if (stages >= 2 || per_sm == 1) break;
   }
-  p.ahead = ahead;
-  int per_sm = two_groups ? 1 : slots_per_sm;
-  int stages = (int)(((two_groups ? 224 : budget_kb) * 1024 - (long long)fixed) / p.stage_bytes);
-  if (stages < 2) {
-    per_sm = 1;
-    stages = (int)((200 * 1024 - (long long)fixed) / p.stage_bytes);
-  }
-  if (stages > max_stages && !two_groups) stages = max_stages;
-  if (stages > (two_groups ? 14 : 8)) stages = two_groups ? 14 : 8;
+  if (stages > max_stages) stages = max_stages;
+  if (stages > 16) stages = 16;
   p.stages = stages;
   p.smem = (size_t)stages * p.stage_bytes + fixed;
   const long long slots = (long long)st::sm_count() * per_sm;
-  p.C = (int)(p.U < slots ? p.U : slots);
-  {
-    // Prefer a grid whose CTA boundaries fall on tile boundaries (or cut every tile into equal parts) when one exists
-    // within 20% of the slot count: a tile that is not shared needs no cross-CTA hand-over of partial sums at all.
+  long long want = p.U / (min_units < 1 ? 1 : min_units);     // small matrices: no CTA with less than min_units units
+  if (want < 1) want = 1;
+  p.C = (int)(want < slots ? want : slots);
+  // Cutting tiles at arbitrary unit boundaries fills every slot with the same amount of work, but the CTA that meets
+  // its neighbour last on a cut tile pays a round trip at its tail.  That pays off when a CTA has many units (measured
+  // from about 12: 12288 x 4096 takes 15.6 us cut against 16.5 us on 256 whole-tile CTAs, 4096 x 4096 8.9 against
+  // 7.6).  Shorter CTAs prefer a grid whose boundaries fall on tile boundaries (or that cuts every tile into equal
+  // parts) when one exists within 20% of the slot count.
+  static const int cut_from = tune("STATETREE_GEMV_CUT_FROM", 12);
+  if (act) {                                                   // SwiGLU epilogue: every CTA owns whole gate / up tile pairs
+    const long long pairs = (long long)nprob * p.T / 2;
+    for (long long c = p.C; c >= 1; --c)
+      if (pairs % c == 0) { p.C = (int)c; break; }
+  } else if (align && p.U / p.C < cut_from) {
     const long long tiles = (long long)nprob * p.T;
-    static int align = -1;                                       // STATETREE_GEMV_ALIGN=0: keep the slot count (tuning aid)
-    if (align < 0) { const char* v = getenv("STATETREE_GEMV_ALIGN"); align = v ? atoi(v) : 1; }
-    if (align)
     for (long long c = p.C; c * 5 >= (long long)p.C * 4 && c >= 1; --c) {
       const bool whole = tiles % c == 0;
       const bool even = c % tiles == 0 && p.CPT % (c / tiles) == 0;
@@ -634,11 +592,12 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense) {
   return p;
 }
 
-template <int NT, int MODE, int G>
-int launch_g(GemvArgs& a, const Plan& p, int nprob, long long ws_bytes, cudaStream_t stream, const char* who) {
+template <int NT, int MODE>
+int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
+  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE, a.act != 0);
   a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages;
   a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows; a.xwhole = p.xwhole; a.xw_stride = p.xw_stride;
-  a.xw_bytes = p.xw_bytes; a.ahead = p.ahead;
+  a.xw_bytes = p.xw_bytes;
   const long long need = (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
   ST_REQUIRE(p.maxcover == 1 || (a.ws && ws_bytes >= need), "%s: workspace of %lld bytes needed, %lld given", who, need,
              ws_bytes);
@@ -648,37 +607,16 @@ int launch_g(GemvArgs& a, const Plan& p, int nprob, long long ws_bytes, cudaStre
              (long long)p.U, p.C);
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "%s: no device status word", who);
-#ifdef ST_PROF
-  a.prof = g_prof_buf;
-#endif
   static bool set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set[dev]) {
-    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemv_kernel<NT, MODE, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   (G == 1 ? 200 : 227) * 1024), who))
+    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemv_kernel<NT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   200 * 1024), who))
       return e;
     set[dev] = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)p.C);
-  cfg.blockDim = dim3((CW * G + 2) * 32);
-  cfg.dynamicSmemBytes = p.smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = st::pdl_enabled() ? 1 : 0;
-  if (int e = st::cuda_fail(cudaLaunchKernelEx(&cfg, gemv_kernel<NT, MODE, G>, a), who)) return e;
-  return 0;
-}
-
-template <int NT, int MODE>
-int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
-  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE);
-  if (NT == 1 && MODE == MODE_DENSE && p.groups == 2) return launch_g<1, MODE_DENSE, 2>(a, p, nprob, ws_bytes, stream, who);
-  return launch_g<NT, MODE, 1>(a, p, nprob, ws_bytes, stream, who);
+  return st::launch(who, gemv_kernel<NT, MODE>, dim3((unsigned)p.C), dim3((CW + 2) * 32), p.smem, stream, a);
 }
 
 template <int NT>
@@ -686,11 +624,32 @@ long long ws_need(long long M, long long N, int nprob, int nx, bool dense = true
   const Plan p = make_plan<NT>(M, N, nprob, nx, dense);
   return p.maxcover == 1 ? 0 : (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
 }
-}  // namespace
 
-#ifdef ST_PROF
-extern "C" void st_debug_set_prof(long long* buf) { g_prof_buf = buf; }
-#endif
+int shape_checks(const char* who, int64_t M, int64_t N, int64_t B) {
+  ST_REQUIRE(M > 0 && N > 0 && M % 16 == 0 && N % 64 == 0, "%s: M %% 16 and N %% 64 must be 0 (got %lld x %lld)", who,
+             (long long)M, (long long)N);
+  ST_REQUIRE(B >= 1 && B <= 32, "%s: batch must be in [1, 32] (got %lld)", who, (long long)B);
+  ST_REQUIRE((M / 16) * ((N / 64 + 7) / 8) < (1ll << 31), "%s: too many units", who);
+  return 0;
+}
+
+int dense_gemv(const char* who, const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el,
+               const void* X, void* Y, float* Yf32, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes,
+               int32_t* cnt, int act, cudaStream_t s) {
+  if (int e = shape_checks(who, M, N, B)) return e;
+  ST_REQUIRE(!act || (M % 32 == 0 && B <= 8 && Yf32 == nullptr),
+             "%s: the SwiGLU epilogue needs M %% 32 == 0, batch <= 8 and no fp32 output", who);
+  ST_REQUIRE(tree && eo && eb && el && X && Y && cnt, "%s: null pointer", who);
+  ST_REQUIRE(st::aligned16(tree) && st::aligned16(eb) && st::aligned16(X), "%s: tree, eb and X must be 16-byte aligned", who);
+  GemvArgs a = {};
+  a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
+  a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.Yf = Yf32; a.ws = (float*)ws; a.cnt = cnt;
+  a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1; a.act = act ? 1 : 0;
+  if (B <= 8) return launch<1, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, who);
+  if (B <= 16) return launch<2, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, who);
+  return launch<4, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, who);
+}
+}  // namespace
 
 extern "C" int64_t st_gemv_workspace_bytes(int64_t M, int64_t N, int64_t B) {
   if (M <= 0 || N <= 0 || M % 16 || N % 64 || B < 1 || B > 32) return -1;
@@ -700,43 +659,20 @@ extern "C" int64_t st_gemv_workspace_bytes(int64_t M, int64_t N, int64_t B) {
 extern "C" int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X,
                        void* Y, float* Yf32, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt,
                        void* stream) {
-  ST_REQUIRE(M > 0 && N > 0 && M % 16 == 0 && N % 64 == 0, "st_gemv: M %% 16 and N %% 64 must be 0 (got %lld x %lld)",
-             (long long)M, (long long)N);
-  ST_REQUIRE(B >= 1 && B <= 32, "st_gemv: batch must be in [1, 32] (got %lld)", (long long)B);
-  ST_REQUIRE(tree && eo && eb && el && X && Y && cnt, "st_gemv: null pointer");
-  ST_REQUIRE(st::aligned16(tree) && st::aligned16(eb) && st::aligned16(X), "st_gemv: tree, eb and X must be 16-byte aligned");
-  ST_REQUIRE((M / 16) * ((N / 64 + 7) / 8) < (1ll << 31), "st_gemv: too many units");
-  GemvArgs a = {};
-  a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
-  a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.Yf = Yf32; a.ws = (float*)ws; a.cnt = cnt;
-  a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1;
-  cudaStream_t s = (cudaStream_t)stream;
-  if (B <= 8) return launch<1, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
-  if (B <= 16) return launch<2, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
-  return launch<4, MODE_DENSE>(a, 1, (int)B, ws_bytes, s, "st_gemv");
+  return dense_gemv("st_gemv", tree, eo, eb, el, X, Y, Yf32, B, M, N, ws, ws_bytes, cnt, 0, (cudaStream_t)stream);
 }
 
 extern "C" int st_gemv_swiglu_supported(int64_t M, int64_t N, int64_t B) {
   if (M <= 0 || N <= 0 || M % 32 || N % 64 || B < 1 || B > 8) return 0;
-  const Plan p = make_plan<1>(M, N, 1, (int)B, true);
-  return (p.stages >= 2 && p.U % p.C == 0 && (p.U / p.C) % (2 * p.CPT) == 0) ? 1 : 0;
+  const Plan p = make_plan<1>(M, N, 1, (int)B, true, true);
+  return (p.stages >= 2 && p.C * 2 >= st::sm_count() && p.U % p.C == 0 && (p.U / p.C) % (2 * p.CPT) == 0) ? 1 : 0;
 }
 
 extern "C" int st_gemv_swiglu(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X,
                               void* act, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt,
                               void* stream) {
-  ST_REQUIRE(M > 0 && N > 0 && M % 32 == 0 && N % 64 == 0, "st_gemv_swiglu: M %% 32 and N %% 64 must be 0 (got %lld x %lld)",
-             (long long)M, (long long)N);
-  ST_REQUIRE(B >= 1 && B <= 8, "st_gemv_swiglu: batch must be in [1, 8] (got %lld)", (long long)B);
-  ST_REQUIRE(tree && eo && eb && el && X && act && cnt, "st_gemv_swiglu: null pointer");
-  ST_REQUIRE(st::aligned16(tree) && st::aligned16(eb) && st::aligned16(X),
-             "st_gemv_swiglu: tree, eb and X must be 16-byte aligned");
-  ST_REQUIRE((M / 16) * ((N / 64 + 7) / 8) < (1ll << 31), "st_gemv_swiglu: too many units");
-  GemvArgs a = {};
-  a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
-  a.X = (const uint16_t*)X; a.Y = (uint16_t*)act; a.Yf = nullptr; a.ws = (float*)ws; a.cnt = cnt;
-  a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1; a.act = 1;
-  return launch<1, MODE_DENSE>(a, 1, (int)B, ws_bytes, (cudaStream_t)stream, "st_gemv_swiglu");
+  return dense_gemv("st_gemv_swiglu", tree, eo, eb, el, X, act, nullptr, B, M, N, ws, ws_bytes, cnt, 1,
+                    (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------- st_gemv_static
@@ -786,9 +722,10 @@ extern "C" int st_gemv_static(const void* tree, const int32_t* eo, const uint32_
   }
   cudaStream_t s = (cudaStream_t)stream;
   int* cnt = reinterpret_cast<int*>(base + STATIC_WS_BYTES);
-  // the array keeps whatever the last call left: the semaphores of this shape's tiles must start at zero
-  if (int e = st::cuda_fail(cudaMemsetAsync(cnt, 0, (size_t)(M / 16) * 4, s), "st_gemv_static: clearing semaphores"))
-    return e;
+  // the array keeps whatever the last call left: the exchange slots this shape uses must hold the sentinel (all ones)
+  if (need > 0)
+    if (int e = st::cuda_fail(cudaMemsetAsync(base, 0xFF, (size_t)need, s), "st_gemv_static: resetting exchange slots"))
+      return e;
   GemvArgs a = {};
   a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
   a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.Yf = nullptr; a.ws = reinterpret_cast<float*>(base); a.cnt = cnt;

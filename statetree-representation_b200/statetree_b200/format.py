@@ -14,7 +14,10 @@ golden fixtures).  The side tables the kernels of this package read are built by
 import torch
 
 RECORD_BYTES = 1552
-LEAF_FORMAT = 2
+LEAF_FORMAT = 2                      # leaf byte = mantissa << 1 | partner's sign; format 1 was sign << 7 | mantissa
+# column (0..63) that thread-in-quad t of a lane holds at byte position p of its 16 leaf bytes of one record half-row:
+# k-step p // 4, upper half of the k-step (p // 2) % 2, element of the pair p % 2 (the reference's format.PERM)
+PERM = [16 * (p >> 2) + 8 * ((p >> 1) & 1) + 2 * t + (p & 1) for t in range(4) for p in range(16)]
 _LUT = {}
 
 
@@ -120,6 +123,30 @@ def decode_reference(tree, esc_rows, esc_cols, esc_bits):
     return bits.view(torch.bfloat16)
 
 
+@torch.no_grad()
+def leaves_v1_to_v2(tree):
+    """records written with leaf format 1 (sign << 7 | mantissa, checkpoints of version < 3) -> leaf format 2; the
+    two bytes of a BF16 pair sit next to each other, states and nodes are untouched
+    (reference: statetree/format.py:36-40)"""
+    out = tree.clone()
+    old = out[..., :1024].to(torch.int32)
+    pairs = old.reshape(*old.shape[:-1], 512, 2)
+    new = ((pairs & 0x7F) << 1) | (pairs.flip(-1) >> 7)
+    out[..., :1024] = new.reshape(old.shape).to(torch.uint8)
+    return out
+
+
+@torch.no_grad()
+def leaves_v2_to_v1(tree):
+    """inverse of leaves_v1_to_v2 (used to write version-2 files for the migration test)"""
+    out = tree.clone()
+    new = out[..., :1024].to(torch.int32)
+    pairs = new.reshape(*new.shape[:-1], 512, 2)
+    old = ((pairs.flip(-1) & 1) << 7) | (pairs >> 1)
+    out[..., :1024] = old.reshape(new.shape).to(torch.uint8)
+    return out
+
+
 def _u32(x):
     """int64 values in [0, 2^32) -> the same bit patterns as int32"""
     return torch.where(x >= 2 ** 31, x - 2 ** 32, x).to(torch.int32).contiguous()
@@ -167,6 +194,77 @@ def escape_tables(M, N, esc_rows, esc_cols, esc_bits):
         eb[unit_s[keep], 2 + pos[keep]] = ent_s[keep]
     el = _u32(ent_s) if ent_s.numel() else torch.zeros(1, dtype=torch.int32, device=dev)
     return eo.to(torch.int32).contiguous(), el, _u32(eb.view(-1)).view(nunit, 16)
+
+
+# ---- the reference's side-table builders (statetree/format.py:141-216), kept for callers of its format module.  The
+# kernels of this package read escape_tables() above; these produce the reference's tables bit for bit.
+def _fragment_entry(esc_rows, esc_cols, esc_bits):
+    """per escape: (tile, column group, k-step, entry) with entry = bits << 16 | lane << 5 | k-step << 3 | reg << 1 |
+    half, i.e. where the value sits in the mma.m16n8k16 A fragment of its record"""
+    r, c = esc_rows.long(), esc_cols.long()
+    row, col = r % 16, c % 64
+    kstep, k = col // 16, col % 16
+    lane = (row % 8) * 4 + (k % 8) // 2
+    reg = row // 8 + 2 * (k // 8)
+    ent = ((esc_bits.to(torch.int64) & 0xFFFF) << 16) | (lane << 5) | (kstep << 3) | (reg << 1) | (k % 2)
+    return r // 16, c // 64, kstep, ent
+
+
+def _unit_blocks(unit, slot, kstep, ent, n_units):
+    """64-byte blocks per unit of 8 records: words 0-1 = bit (slot * 4 + k-step) per escape, word 2 = count, words
+    3..15 = the first 13 entries (entry | slot << 10); plus offsets per unit and the full sorted list"""
+    dev = unit.device
+    ent = ent | (slot << 10)
+    order = torch.argsort(unit, stable=True)
+    u_s, e_s = unit[order], ent[order]
+    count = torch.bincount(unit, minlength=n_units) if unit.numel() else torch.zeros(n_units, dtype=torch.int64, device=dev)
+    offs = torch.zeros(n_units + 1, dtype=torch.int64, device=dev)
+    offs[1:] = count.cumsum(0)
+    blocks = torch.zeros(n_units, 16, dtype=torch.int64, device=dev)
+    blocks[:, 2] = count
+    if unit.numel():
+        bit = slot * 4 + kstep
+        flags = torch.zeros(n_units, 64, dtype=torch.int64, device=dev)
+        flags[unit, bit] = 1
+        weights = torch.ones(32, dtype=torch.int64, device=dev) << torch.arange(32, device=dev)
+        blocks[:, 0] = (flags[:, :32] * weights).sum(1)
+        blocks[:, 1] = (flags[:, 32:] * weights).sum(1)
+        rank = torch.arange(u_s.numel(), device=dev) - offs[u_s]
+        inline = rank < 13
+        blocks[u_s[inline], 3 + rank[inline]] = e_s[inline]
+    full = _u32(e_s) if e_s.numel() else torch.zeros(1, dtype=torch.int32, device=dev)
+    return _u32(blocks.view(-1)), offs.to(torch.int32).contiguous(), full
+
+
+@torch.no_grad()
+def escape_lists(M, N, esc_rows, esc_cols, esc_bits):
+    """(EO int32 [records + 1], EL int32): per record (tile * N/64 + group) its fragment entries"""
+    NG, nrec = N // 64, (M // 16) * (N // 64)
+    tile, grp, _, ent = _fragment_entry(esc_rows, esc_cols, esc_bits)
+    rec = tile * NG + grp
+    eo = torch.zeros(nrec + 1, dtype=torch.int64, device=esc_rows.device)
+    if rec.numel():
+        eo[1:] = torch.bincount(rec, minlength=nrec).cumsum(0)
+    ent = ent[torch.argsort(rec, stable=True)]
+    el = _u32(ent) if ent.numel() else torch.zeros(1, dtype=torch.int32, device=esc_rows.device)
+    return eo.to(torch.int32).contiguous(), el
+
+
+@torch.no_grad()
+def escape_blocks(M, N, RT, esc_rows, esc_cols, esc_bits):
+    """(EB int32 [U * 16], EOU int32 [U + 1], EALL int32) for units = (block of RT row tiles, column group)"""
+    NG = N // 64
+    tile, grp, kstep, ent = _fragment_entry(esc_rows, esc_cols, esc_bits)
+    return _unit_blocks((tile // RT) * NG + grp, tile % RT, kstep, ent, (M // 16 // RT) * NG)
+
+
+@torch.no_grad()
+def escape_chunks(M, N, esc_rows, esc_cols, esc_bits):
+    """the same blocks for units of 8 consecutive records in memory order"""
+    NG = N // 64
+    tile, grp, kstep, ent = _fragment_entry(esc_rows, esc_cols, esc_bits)
+    rec = tile * NG + grp
+    return _unit_blocks(rec // 8, rec % 8, kstep, ent, (M // 16) * NG // 8)
 
 
 def bits_per_weight(M, N, n_esc, esc_bytes=10):

@@ -25,20 +25,29 @@ class EscapeHeavy(RuntimeError):
 
 
 class _DevState:
-    """per (device, stream): fp32 workspace (grown on demand) and the semaphore array (zero between calls)"""
+    """per (device, stream): the fp32 workspace of the small-batch kernels and the semaphore array.  The kernels expect
+    every workspace word to hold 0xFFFFFFFF between launches (their exchange-slot sentinel) and every semaphore to be
+    zero, and leave them so.  Buffers only ever grow, and a buffer that was handed out is never freed: a CUDA graph
+    captured earlier keeps replaying into the old one."""
 
     def __init__(self, device):
         self.device = device
-        self.ws = torch.empty(1 << 20, dtype=torch.float32, device=device)
+        self._retired = []
+        self.ws = self._new_ws(1 << 20)
         self.cnt = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+
+    def _new_ws(self, words):
+        return torch.full((words,), -1, dtype=torch.int32, device=self.device).view(torch.float32)
 
     def get_ws(self, nbytes):
         if self.ws.numel() * 4 < nbytes:
-            self.ws = torch.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.device)
+            self._retired.append(self.ws)
+            self.ws = self._new_ws((nbytes + 3) // 4)
         return self.ws
 
     def get_cnt(self, n):
         if self.cnt.numel() < n:
+            self._retired.append(self.cnt)
             self.cnt = torch.zeros(n, dtype=torch.int32, device=self.device)
         return self.cnt
 

@@ -9,8 +9,10 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libstatetree_b200.so")
-ABI = 1
+# STATETREE_B200_LIB names another build of the same library (the reference accepts a prebuilt extension the same way,
+# statetree/ops.py:7-27); the ABI version is checked either way
+LIB_PATH = os.environ.get("STATETREE_B200_LIB") or os.path.join(_HERE, "libstatetree_b200.so")
+ABI = 2
 _LIB = None
 
 _i64, _int, _vp, _dbl = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_double

@@ -22,7 +22,7 @@ def test_static_scratch_entry_matches_workspace_entry(M, N, B):
     E = ops.ext()
     x = bits_to_torch(G.to_bf16_bits(np.random.RandomState(B).standard_normal((B, N))), DEV)
     want = torch.empty(B, M, dtype=torch.bfloat16, device=DEV)
-    ws = torch.empty(max(1, E.gemv_workspace_bytes(M, N, B) // 4), dtype=torch.float32, device=DEV)
+    ws = torch.full((max(1, E.gemv_workspace_bytes(M, N, B) // 4),), -1, dtype=torch.int32, device=DEV).view(torch.float32)
     cnt = torch.zeros(M // 16, dtype=torch.int32, device=DEV)
     E.gemv(tl.tree, eo, eb, el, x, want, ws, cnt)
     for call in range(2):                                   # the second call reuses what the first left in the scratch
