@@ -7,12 +7,15 @@ N(0, 0.02) with 1% of the columns scaled x8.
 One step = every linear of all 36 layers once at batch M (default 1), captured in one CUDA graph.  All 36 layers own
 distinct record buffers (10.5 GB in total, far beyond the 126 MB L2), so every step streams the records from HBM.
 value    = algorithmic bytes (records + activations in + out) / device time, inputs resident in HBM
-e2e      = the same through the module API with pinned host activations copied in and results copied out every step
+e2e      = the same through the C-ABI shim (statetree_b200.ops.ext().gemv / .gemm, the call TreeLinear.forward makes) with
+           pinned host activations copied in and results copied out every step
 roofline = the GEMV (or GEMM) kernel's achieved algorithmic GB/s against the measured HBM copy bandwidth
 cpu_baseline / --impl reference = the reference's CPU path (decode + BF16 matmul) restated in C, on the host cores,
 on a bounded sample (the linears of one layer).
-With N > 1 ranks (torchrun) the linears are tensor-parallel: q/k/v/gate/up split by rows, o/down split by columns
-and followed by an NCCL all-reduce of their [M, 4096] outputs; total work is fixed (strong scaling).
+With N > 1 ranks (torchrun) the linears are tensor-parallel: q/k/v and gate/up split by rows and stored per rank as
+fused trees (four launches per layer), o/down split by columns and followed by an all-reduce of their [M, 4096] outputs
+over NVLink peer memory; total work is fixed (strong scaling).  Before timing, the all-reduced outputs of one layer
+are checked against the fp64 product over the unsharded weights (`tp_check`).
 """
 import argparse
 import json
@@ -48,6 +51,24 @@ def peaks():
             p = json.load(f)
         return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
     return 6650.0, 1590.0, "fallback"
+
+
+def measured_traffic(batch, world, layers):
+    """DRAM bytes per launch of the dominant kernel from the tracked ncu summary (a JSON next to the text summary that
+    also names the kernel source it was captured from); (None, reason) when there is none for this workload or the
+    kernel source has changed since the capture"""
+    import hashlib
+    path = os.path.join(ROOT, "profiles", "gemv_qwen3_8b_linears_b1.json")
+    if not (batch == 1 and world == 1 and layers == LAYERS and os.path.exists(path)):
+        return None, "no capture for this workload"
+    with open(path) as f:
+        rec = json.load(f)
+    src = os.path.join(ROOT, "statetree-representation_b200", "csrc", "st_gemv.cu")
+    with open(src, "rb") as f:
+        sha = hashlib.sha256(f.read()).hexdigest()[:16]
+    if rec.get("kernel_source_sha256_16") != sha:
+        return None, "kernel source changed since the capture"
+    return rec["dram_bytes_per_launch"], f"ncu capture of {rec.get('captured', '?')}"
 
 
 class ClockSampler:
@@ -546,8 +567,9 @@ def main():
                           f" x {args.layers} layers, batch M={args.batch}, seeds per shape, N(0,0.02) + 1% columns x8",
               "batch": args.batch, "layers": args.layers,
               "l2": "inputs larger than L2: 10.5 GB of distinct record buffers per step",
-              "parallelism": "single GPU" if world == 1 else f"tp{world} (col/row parallel + all-reduce of the row-parallel "
-                                                              "outputs over NVLink peer memory, one kernel per rank)"}
+              "parallelism": "single GPU, one launch per linear" if world == 1 else
+              f"tp{world} (q/k/v and gate/up of a rank as fused trees, o/down column shards + all-reduce of their outputs "
+              "over NVLink peer memory, one kernel per rank)"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -580,23 +602,44 @@ def main():
     B = args.batch
     assert 1 <= B <= 4096
 
-    # ---- weights: one encoded set per shape (this rank's shard), cloned into `layers` distinct buffers
+    # ---- weights: the seven matrices from their seeds; one encoded set per launch (this rank's shard), cloned into
+    # `layers` distinct record buffers.  One GPU: the seven linears as seven launches.  Tensor parallel: q/k/v and
+    # gate/up of a rank stored as fused trees (four launches per layer), o and down split by columns.
     gen = torch.Generator(device=dev)
-    layers = []
-    shard = []
+    full = {}
     for i, (name, M, N, kind) in enumerate(SHAPES):
         gen.manual_seed(i)
         W = torch.randn(M, N, device=dev, generator=gen) * 0.02
         cols = torch.randperm(N, device=dev, generator=gen)[:N // 100]
         W[:, cols] *= 8.0
-        W = W.to(torch.bfloat16)
-        if world > 1:                                  # each rank encodes its own shard, on 16-row / 64-col boundaries
-            if kind == "col":
-                W = W[rank * (M // world):(rank + 1) * (M // world)].contiguous()
-            else:
-                W = W[:, rank * (N // world):(rank + 1) * (N // world)].contiguous()
-        shard.append(S.TreeLinear.from_weight(W, verify=(i == 0)))
+        full[name] = W.to(torch.bfloat16)
         del W
+
+    def rows_of(name):
+        W = full[name]
+        per = W.shape[0] // world
+        return W[rank * per:(rank + 1) * per]
+
+    def cols_of(name):
+        W = full[name]
+        per = W.shape[1] // world
+        return W[:, rank * per:(rank + 1) * per].contiguous()
+
+    Hs, Is = HIDDEN // world, INTER // world                 # o's / down's input columns on this rank
+    x_h = torch.randn(B, HIDDEN, generator=torch.Generator().manual_seed(100)).to(torch.bfloat16).pin_memory()
+    x2_h = torch.randn(B, INTER, generator=torch.Generator().manual_seed(101)).to(torch.bfloat16).pin_memory()
+    x = x_h.to(dev)
+    x_o = x_h[:, rank * Hs:(rank + 1) * Hs].contiguous().to(dev)
+    x_d = x2_h[:, rank * Is:(rank + 1) * Is].contiguous().to(dev)
+    if world == 1:
+        plan = [(n, full[n], {"o": x_o, "down": x_d}.get(n, x), k) for n, _, _, k in SHAPES]
+    else:
+        plan = [("qkv", torch.cat([rows_of("q"), rows_of("k"), rows_of("v")]), x, "col"), ("o", cols_of("o"), x_o, "row"),
+                ("gate_up", torch.cat([rows_of("gate"), rows_of("up")]), x, "col"), ("down", cols_of("down"), x_d, "row")]
+    shard = [S.TreeLinear.from_weight(W.contiguous(), verify=(i == 0)) for i, (_, W, _, _) in enumerate(plan)]
+    ins = [xin for _, _, xin, _ in plan]
+    kinds = [k for _, _, _, k in plan]
+    layers = []
     for _ in range(args.layers):
         row = []
         for tl in shard:
@@ -607,20 +650,10 @@ def main():
             c._tables = tl.tables()
             row.append(c)
         layers.append(row)
-    del shard
     torch.cuda.synchronize()
 
-    # ---- static buffers
-    Hs = HIDDEN // world if world > 1 else HIDDEN          # o's input columns on this rank
-    Is = INTER // world if world > 1 else INTER
-    x_h = torch.randn(B, HIDDEN, generator=torch.Generator().manual_seed(100)).to(torch.bfloat16).pin_memory()
-    x2_h = torch.randn(B, INTER, generator=torch.Generator().manual_seed(101)).to(torch.bfloat16).pin_memory()
-    x = x_h.to(dev)
-    x_o = x_h[:, rank * Hs:(rank + 1) * Hs].contiguous().to(dev)
-    x_d = x2_h[:, rank * Is:(rank + 1) * Is].contiguous().to(dev)
     outs = [torch.empty(B, tl.out_features, dtype=torch.bfloat16, device=dev) for tl in layers[0]]
     outs_h = [torch.empty(o.shape, dtype=torch.bfloat16).pin_memory() for o in outs]
-    ins = [x, x, x, x_o, x, x, x_d]
     launches = 0
     use_gemv = B <= GEMV_MAX
     st = _state(dev)
@@ -629,18 +662,47 @@ def main():
     ws = st.get_ws(ws_need)
     cnt = st.get_cnt(4096)
 
+    def one(tl, xin, y):
+        eo, el, eb = tl._tables
+        if use_gemv:
+            E.gemv(tl.tree, eo, eb, el, xin, y, ws, cnt)
+        else:
+            E.gemm(tl.tree, eo, el, xin, y, ws, cnt)
+
+    # ---- tensor-parallel check (before any timing): the all-reduced outputs of the row-parallel projections of one
+    # layer against the fp64 product over the unsharded weights, and the same bits on every rank
+    tp_check = None
+    if world > 1:
+        worst = 0.0
+        for (name, _, xin, kind), tl, y in zip(plan, shard, outs):
+            if kind != "row":
+                continue
+            one(tl, xin, y)
+            reduce_partials(y)
+            xf = (x_h if name == "o" else x2_h).to(dev).double()
+            ref = xf @ full[name].double().t()
+            err = float((y.double() - ref).norm() / ref.norm())
+            worst = max(worst, err)
+            gathered = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(gathered, y)
+            same = all(torch.equal(g.view(torch.int16), y.view(torch.int16)) for g in gathered)
+            if not (err < 5e-3 and same):
+                raise RuntimeError(f"tensor-parallel check failed for {name}: rel. error {err:.2e} vs fp64, identical on "
+                                   f"all ranks: {same}")
+        tp_check = {"result": "ok", "max_rel_err_vs_fp64": worst, "bar": 5e-3,
+                    "what": "all-reduced o and down outputs of one layer (BF16) against the fp64 product over the "
+                            "unsharded weights; bit-identical on every rank"}
+    del shard
+
     def run_layers():
         n = 0
         for row in layers:
-            for tl, xin, y, (_, _, _, kind) in zip(row, ins, outs, SHAPES):
-                eo, el, eb = tl._tables
-                if use_gemv:
-                    E.gemv(tl.tree, eo, eb, el, xin, y, ws, cnt)
-                else:
-                    E.gemm(tl.tree, eo, el, xin, y, ws, cnt)
+            for tl, xin, y, kind in zip(row, ins, outs, kinds):
+                one(tl, xin, y)
                 n += 1
                 if world > 1 and kind == "row":
                     reduce_partials(y)
+                    n += 1                                   # the peer-memory all-reduce is one kernel of this library
         return n
 
     side = torch.cuda.Stream(dev)
@@ -789,11 +851,10 @@ def main():
     hbm, tf, which = peaks()
     value = step_bytes / (ms * 1e-3) / 1e9
     per_gpu = value / world
-    # DRAM bytes per launch from the ncu capture summarised in profiles/ (batch 1, one GPU: 42.59 MB measured per
-    # launch on average over the seven shapes, against 41.80 MB algorithmic); null where no capture exists
-    traffic = 42.59e6 if (B == 1 and world == 1 and args.layers == LAYERS) else None
+    traffic, traffic_source = measured_traffic(B, world, args.layers)
     roof = {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s", "frac": per_gpu / hbm,
-            "traffic": traffic, "peak_source": f"of {which}", "frac_of_nominal_8TBs": per_gpu / 8000.0,
+            "traffic": traffic, "traffic_source": traffic_source, "peak_source": f"of {which}",
+            "frac_of_nominal_8TBs": per_gpu / 8000.0,
             "kernel": "gemv_kernel" if use_gemv else "gemm_kernel",
             "bytes_per_launch": step_bytes / world / launches, "us_per_launch": ms * 1e3 / launches}
     if not use_gemv:
@@ -807,6 +868,8 @@ def main():
                     "d2h_bytes_per_step": sum(o.numel() * 2 for o in outs)},
             "gpu_launches": launches * args.steps, "roofline": roof, "device_status": status,
             "bf16_equivalent_gbs": value * 16.0 / 12.125}
+    if tp_check is not None:
+        line["tp_check"] = tp_check
     if fused is not None:
         line["fused_qkv_gate_up"] = fused
     if control is not None:
