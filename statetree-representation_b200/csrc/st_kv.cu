@@ -4,11 +4,7 @@
 // one 1600-byte unit = a 1552-byte record of 16 tokens x 64 dims (token = row) + a header word + 11 escape slots
 // (bits << 16 | row << 6 | col); further escapes chain through 16-word blocks of a pool.
 //
-// Attention design: grid = B x Hkv x S; each of the 4 warps of a CTA walks its own pages of the split through a
-// private 3-stage ring of 6400-byte bulk copies (one page of one KV head = K half 0/1, V half 0/1, contiguous), so a
-// CTA keeps up to 12 pages (75 KB) in flight with no block-level barrier inside the loop.  S = q K^T and O += P V run
-// on mma.m16n8k16 with the decoded K fragments as the B operand and the V fragments transposed in registers;
-// P is fed as a BF16 high part plus a BF16 residual, so the softmax weights keep ~16 mantissa bits.
+// The attention kernel's design is described above kv_attn_kernel.
 #include <math.h>
 #include <stdlib.h>
 
@@ -353,242 +349,309 @@ __global__ void __launch_bounds__(256) kv_dequant_kernel(const uint8_t* __restri
 }
 
 // ------------------------------------------------------------------------------------------------ attention
-struct AttnArgs {
-  const uint16_t* q; long long qs;
-  const uint8_t* kv; long long nblocks;
-  const uint32_t* pool; int P;
-  const int* bt; long long bts;
-  const int* lens; const int* starts;
-  uint16_t* out; long long os;
-  float* wo; float* wml;
-  float sl2;
-  int Hkv, S, minpps;
+// Decode attention over the pages, one query token per sequence.
+//
+// Orientation.  A record is stored in mma.m16n8k16 A-fragment order with tokens as rows, and a decode step has only
+// G = Hq / Hkv (1..8) query heads per KV head.  So the heads go on the 8-wide N side of the tensor-core shape and the
+// big dimensions on the 16-wide M side:
+//     S^T [16 tokens x 8 heads]  = K [16 tokens x 128 dims] . Q^T      8 MMAs per page; the decoded K record is the A
+//                                                                      operand as it comes out of the decoder
+//     O^T [128 dims x 8 heads]  += V^T [128 dims x 16 tokens] . P^T    8 MMAs per page (16 with the residual of P);
+//                                                                      V^T fragments are the V record's 8 x 8 blocks
+//                                                                      transposed in registers (movmatrix), P^T is the
+//                                                                      probability fragment transposed the same way
+// With G = 4 half of each MMA is useful (a quarter when the heads sit on the M side), 24 MMAs per page in all.
+//
+// Softmax.  Scores live in the exp2 domain.  Each head keeps a reference maximum m that is raised only when a page
+// holds a score more than 8 above it (one warp vote per page finds out; raising costs the cross-lane reduction and a
+// rescale of the accumulators), so probabilities stay below 2^8 and the common page pays no reduction at all.  The
+// row sums are kept per lane and reduced once at the end.  P is fed to the tensor cores as a BF16 value plus the BF16
+// of its rounding residual (~16 mantissa bits), which keeps the fp32 partial results within 1e-3 of fp64.
+//
+// Work split.  Grid = sequences x KV heads x splits; a CTA's pages are dealt round-robin to its warps, and every warp
+// streams its own pages through a private ring of 6400-byte bulk copies (one page of one KV head = K half 0/1, V
+// half 0/1, contiguous), so there is no block-level barrier inside the loop.
+struct AttnLaunch {
+  const uint16_t* q; long long q_stride;          // [B][Hq][128] BF16, elements between sequences
+  const uint8_t* pages; long long n_pages;
+  const uint32_t* pool; int pool_blocks;
+  const int* table; long long table_stride;       // block table [B][table_stride]
+  const int* seq_len; const int* seq_start;       // tokens [seq_start, seq_len) of each sequence take part
+  uint16_t* out; long long out_stride;
+  float* part_o; float* part_ml;                  // split partials: [B][Hq][splits][128], [B][Hq][splits][2] = (m, l)
+  float scale_log2;                               // softmax scale * log2(e)
+  int kv_heads, group, splits, min_pages;
   int* status;
 };
 
 constexpr int PAGE_BYTES = 4 * RKV;
+constexpr float RAISE_MARGIN = 8.f;               // a head's reference maximum is raised when a score exceeds it by this
 
-// ATT_NW warps per CTA, each with ATT_STG pages in flight.  The per-warp partial results reuse the ring once the
-// loop is over, so a CTA needs only the ring and its barriers (4 warps x 3 stages = 75 KB measured slightly faster
-// than 8 warps x 2 stages = 100 KB; both leave two CTAs per SM).
-template <int G, int ATT_NW, int ATT_STG>
-__global__ void __launch_bounds__(ATT_NW * 32) kv_attn_kernel(const AttnArgs a) {
+// exact bits of one element of a decoded record; the entry is the same in every lane, so the register it lands in is
+// warp-uniform and only the lane that owns the element takes the (single) branch
+__device__ __forceinline__ void put_exact(uint32_t (&R)[4][4], uint32_t entry, int lane) {
+  const int row = (int)((entry >> 6) & 15u), col = (int)(entry & 63u);
+  if (lane != (row & 7) * 4 + ((col & 7) >> 1)) return;
+  const uint32_t sh = 16u * (uint32_t)(col & 1), keep = ~(0xFFFFu << sh), val = (entry >> 16) << sh;
+  switch ((col >> 4) * 4 + (row >> 3) + 2 * ((col >> 3) & 1)) {
+#define ST_PUT(i) case i: R[(i) >> 2][(i) & 3] = (R[(i) >> 2][(i) & 3] & keep) | val; break;
+    ST_PUT(0) ST_PUT(1) ST_PUT(2) ST_PUT(3) ST_PUT(4) ST_PUT(5) ST_PUT(6) ST_PUT(7)
+    ST_PUT(8) ST_PUT(9) ST_PUT(10) ST_PUT(11) ST_PUT(12) ST_PUT(13) ST_PUT(14) ST_PUT(15)
+#undef ST_PUT
+  }
+}
+
+// one 1600-byte unit in shared memory -> the lane's fragment registers, escapes (in-record slots, then the pool chain)
+// applied
+__device__ __forceinline__ void unit_to_frag(const uint8_t* unit, const uint32_t* pool, int pool_blocks, int lane,
+                                             uint32_t (&R)[4][4]) {
+  decode_frag(load_rec_shared(unit, lane), R);
+  const uint32_t head = *reinterpret_cast<const uint32_t*>(unit + REC);
+  if ((head & 31u) == 0u) return;
+  const uint32_t* slot = reinterpret_cast<const uint32_t*>(unit + REC + 4);
+  const int used = min((int)(head & 15u), NSLOT);
+  for (int i = 0; i < used; ++i) put_exact(R, slot[i], lane);
+  if (head & 16u) {
+    int blk = (int)(head >> 8);
+    for (int hops = 0; blk >= 0 && blk < pool_blocks && hops < 4096; ++hops) {
+      const uint32_t w0 = __ldg(pool + (size_t)blk * 16);
+      const int n = min((int)(w0 & 0xFFu), XSLOT);
+      for (int i = 0; i < n; ++i) put_exact(R, __ldg(pool + (size_t)blk * 16 + 1 + i), lane);
+      blk = (int)(w0 >> 8) - 1;
+    }
+  }
+}
+
+__device__ __forceinline__ float max_over_rows(float v) {        // lanes that differ in g (bits 2..4) hold other tokens
+  v = fmaxf(v, __shfl_xor_sync(FULL, v, 4));
+  v = fmaxf(v, __shfl_xor_sync(FULL, v, 8));
+  return fmaxf(v, __shfl_xor_sync(FULL, v, 16));
+}
+__device__ __forceinline__ float sum_over_rows(float v) {
+  v += __shfl_xor_sync(FULL, v, 4);
+  v += __shfl_xor_sync(FULL, v, 8);
+  return v + __shfl_xor_sync(FULL, v, 16);
+}
+
+template <int NW, int STG>
+__global__ void __launch_bounds__(NW * 32) kv_attn_kernel(const AttnLaunch a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* ring = smem;                                                         // [NW][STG][6400]
-  float* red = reinterpret_cast<float*>(smem);                                  // [NW][G * 128 + 2 G], after the loop
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_NW * ATT_STG * PAGE_BYTES);   // [NW][STG]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NW * STG * PAGE_BYTES);      // [NW][STG]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-  const int j = blockIdx.x % a.S, bh = blockIdx.x / a.S;
-  const int h = bh % a.Hkv, b = bh / a.Hkv, Hq = a.Hkv * G;
-  pdl_wait();                               // queries, lengths and the pages of this step come from earlier kernels
+  const int G = a.group, Hq = a.kv_heads * G;
+  const int split = blockIdx.x % a.splits, bh = blockIdx.x / a.splits;
+  const int kvh = bh % a.kv_heads, seq = bh / a.kv_heads;
+  pdl_wait();                               // queries, lengths and this step's pages come from earlier kernels
   pdl_launch_dependents();
-  const int len = a.lens[b], st0 = a.starts ? a.starts[b] : 0;
-  const int pfirst = st0 / PAGE;
-  const int npg = len > st0 ? (int)min((long long)(len + PAGE - 1) / PAGE, a.bts) : 0;
-  const int pps = max(a.minpps, (npg - pfirst + a.S - 1) / a.S);
-  const int p0 = pfirst + j * pps, p1 = min(npg, p0 + pps);
-  const int mine = p1 > p0 + warp ? (p1 - p0 - warp + ATT_NW - 1) / ATT_NW : 0;   // pages of this warp
 
-  uint64_t* mybar = bars + warp * ATT_STG;
-  uint8_t* myring = ring + (size_t)warp * ATT_STG * PAGE_BYTES;
+  // ---- this warp's pages
+  const int len = a.seq_len[seq], start = a.seq_start ? a.seq_start[seq] : 0;
+  const int first_page = start / PAGE;
+  const int end_page = len > start ? (int)min((long long)(len + PAGE - 1) / PAGE, a.table_stride) : 0;
+  const int per_split = max(a.min_pages, (end_page - first_page + a.splits - 1) / a.splits);
+  const int lo_page = first_page + split * per_split, hi_page = min(end_page, lo_page + per_split);
+  const int my_first = lo_page + warp;
+  const int my_count = hi_page > my_first ? (hi_page - my_first + NW - 1) / NW : 0;
+
+  uint8_t* ring = smem + (size_t)warp * STG * PAGE_BYTES;
+  uint64_t* bar = bars + warp * STG;
   if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < ATT_STG; ++s) mbar_init(mybar + s, 1);
+    for (int s = 0; s < STG; ++s) mbar_init(bar + s, 1);
     fence_barrier_init();
   }
   __syncwarp();
-  uint64_t pol = 0;
-  auto issue = [&](int i) {                        // lane 0: page i of this warp -> stage i % STG
-    const int p = p0 + warp + i * ATT_NW;
-    long long blk = a.bt[(size_t)b * a.bts + p];
-    blk = blk < 0 ? 0 : (blk >= a.nblocks ? a.nblocks - 1 : blk);
-    const int s = i % ATT_STG;
-    mbar_expect_tx(mybar + s, PAGE_BYTES);
-    bulk_g2s(myring + (size_t)s * PAGE_BYTES, a.kv + ((size_t)blk * a.Hkv + h) * PAGE_BYTES, PAGE_BYTES, mybar + s, pol);
+  const uint64_t stream_policy = policy_evict_first();
+  auto fetch = [&](int i) {                        // lane 0: this warp's i-th page -> stage i % STG
+    long long blk = a.table[(size_t)seq * a.table_stride + my_first + i * NW];
+    blk = blk < 0 ? 0 : (blk >= a.n_pages ? a.n_pages - 1 : blk);
+    const int s = i % STG;
+    mbar_expect_tx(bar + s, PAGE_BYTES);
+    bulk_g2s(ring + (size_t)s * PAGE_BYTES, a.pages + ((size_t)blk * a.kv_heads + kvh) * PAGE_BYTES, PAGE_BYTES, bar + s,
+             stream_policy);
   };
-  if (lane == 0) {
-    pol = policy_evict_first();
-    for (int i = 0; i < min(mine, ATT_STG); ++i) issue(i);
-  }
+  if (lane == 0)
+    for (int i = 0; i < min(my_count, STG); ++i) fetch(i);
 
-  uint32_t qa[8][2];
+  // ---- Q^T as the B operand: lane (g, t) holds head g, dims 16 ks + 2t, +1 and 16 ks + 8 + 2t, +1
+  uint32_t qf[8][2];
+  {
+    const uint16_t* qrow = a.q + (size_t)seq * a.q_stride + (size_t)(kvh * G + (g < G ? g : 0)) * HD;
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
-    if (g < G) {
-      const uint16_t* qp = a.q + (size_t)b * a.qs + (size_t)(h * G + g) * HD;
-      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 2 * t);
-      qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 8 + 2 * t);
-    } else {
-      qa[ks][0] = qa[ks][1] = 0u;
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint32_t v0 = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t);
+      const uint32_t v1 = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 8 + 2 * t);
+      qf[ks][0] = g < G ? v0 : 0u;
+      qf[ks][1] = g < G ? v1 : 0u;
     }
   }
-  float o[16][4];
+  // ---- running state.  This lane's score columns are heads 2t and 2t + 1; heads beyond G never take part: their
+  // scores are masked to -inf and their reference maximum stays 0, so their probabilities are exactly 0
+  const bool head0 = 2 * t < G, head1 = 2 * t + 1 < G;
+  float m0 = head0 ? -INFINITY : 0.f, m1 = head1 ? -INFINITY : 0.f, l0 = 0.f, l1 = 0.f;
+  float acc[8][4];                                 // O^T: tile j = dims 16j .. 16j + 15; [0],[1] dim 16j + g, [2],[3] + 8
 #pragma unroll
-  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  float m = -INFINITY, l = 0.f;
-  int dead_at = -1;
+  for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  bool gave_up = false;
 
-  for (int i = 0; i < mine; ++i) {
-    const int p = p0 + warp + i * ATT_NW, s = i % ATT_STG;
-    if (!mbar_wait(mybar + s, (uint32_t)(i / ATT_STG) & 1u)) {
+  for (int i = 0; i < my_count; ++i) {
+    const int s = i % STG, page = my_first + i * NW;
+    if (!mbar_wait(bar + s, (uint32_t)(i / STG) & 1u)) {
       if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
-      dead_at = i;
+      for (int k = i + 1; k < min(my_count, i + STG); ++k)           // let the copies still in flight land
+        (void)mbar_wait(bar + k % STG, (uint32_t)(k / STG) & 1u);
+      gave_up = true;
       break;
     }
-    const uint8_t* pg = myring + (size_t)s * PAGE_BYTES;
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint8_t* pg = ring + (size_t)s * PAGE_BYTES;
+    // ---- S^T = K Q^T
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      uint32_t A[4][4];
-      const uint8_t* rec = pg + hf * RKV;
-      decode_frag(load_rec_shared(rec, lane), A);
-      apply_kv_escapes(A, rec, a.pool, a.P, lane);
+    for (int half = 0; half < 2; ++half) {
+      uint32_t R[4][4];
+      unit_to_frag(pg + half * RKV, a.pool, a.pool_blocks, lane, R);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) mma_bf16(sc, R[ks], qf[half * 4 + ks][0], qf[half * 4 + ks][1]);
+    }
+    // this lane: tokens g and g + 8 of the page; valid tokens of the sequence are [start, len)
+    const int tok = page * PAGE + g;
+    const bool v_lo = tok >= start && tok < len, v_hi = tok + 8 >= start && tok + 8 < len;
+    const float x00 = (v_lo && head0) ? sc[0] * a.scale_log2 : -INFINITY;
+    const float x01 = (v_lo && head1) ? sc[1] * a.scale_log2 : -INFINITY;
+    const float x10 = (v_hi && head0) ? sc[2] * a.scale_log2 : -INFINITY;
+    const float x11 = (v_hi && head1) ? sc[3] * a.scale_log2 : -INFINITY;
+    const float top0 = fmaxf(x00, x10), top1 = fmaxf(x01, x11);
+    if (__any_sync(FULL, top0 > m0 + RAISE_MARGIN || top1 > m1 + RAISE_MARGIN)) {
+      // raise the reference maxima to the page's true maxima and bring the accumulators along
+      const float n0 = fmaxf(m0, max_over_rows(top0)), n1 = fmaxf(m1, max_over_rows(top1));
+      const float f0 = n0 == m0 ? 1.f : exp2f(m0 - n0), f1 = n1 == m1 ? 1.f : exp2f(m1 - n1);
+      l0 *= f0;
+      l1 *= f1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { acc[j][0] *= f0; acc[j][1] *= f1; acc[j][2] *= f0; acc[j][3] *= f1; }
+      m0 = n0;
+      m1 = n1;
+    }
+    const float p00 = exp2f(x00 - m0), p01 = exp2f(x01 - m1), p10 = exp2f(x10 - m0), p11 = exp2f(x11 - m1);
+    l0 += p00 + p10;
+    l1 += p01 + p11;
+    // P^T as the B operand: the score fragment is [token][head]; transposed it is [head g][tokens 2t, 2t + 1]
+    const uint32_t hi_lo = pack_bf16(p00, p01), hi_hi = pack_bf16(p10, p11);
+    const float2 r_lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi_lo));
+    const float2 r_hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi_hi));
+    const uint32_t pb0 = movmatrix_t(hi_lo), pb1 = movmatrix_t(hi_hi);
+    const uint32_t rb0 = movmatrix_t(pack_bf16(p00 - r_lo.x, p01 - r_lo.y));
+    const uint32_t rb1 = movmatrix_t(pack_bf16(p10 - r_hi.x, p11 - r_hi.y));
+    // ---- O^T += V^T P^T
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t R[4][4];
+      unit_to_frag(pg + (2 + half) * RKV, a.pool, a.pool_blocks, lane, R);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
-        mma_bf16_r(s0, qa[hf * 4 + ks][0], 0u, qa[hf * 4 + ks][1], 0u, A[ks][0], A[ks][2]);   // tokens 0..7
-        mma_bf16_r(s1, qa[hf * 4 + ks][0], 0u, qa[hf * 4 + ks][1], 0u, A[ks][1], A[ks][3]);   // tokens 8..15
+        // 8 x 8 blocks of the record (tokens x dims) transposed: rows become dims, the k index becomes tokens
+        const uint32_t a0 = movmatrix_t(R[ks][0]), a1 = movmatrix_t(R[ks][2]);
+        const uint32_t a2 = movmatrix_t(R[ks][1]), a3 = movmatrix_t(R[ks][3]);
+        mma_bf16_r(acc[half * 4 + ks], a0, a1, a2, a3, pb0, pb1);
+        mma_bf16_r(acc[half * 4 + ks], a0, a1, a2, a3, rb0, rb1);
       }
     }
-    const int hiv = len - p * PAGE, lov = st0 - p * PAGE;          // valid rows of this page: [lov, hiv)
-    const float x0 = (2 * t < hiv && 2 * t >= lov) ? s0[0] * a.sl2 : -INFINITY;
-    const float x1 = (2 * t + 1 < hiv && 2 * t + 1 >= lov) ? s0[1] * a.sl2 : -INFINITY;
-    const float x2 = (8 + 2 * t < hiv && 8 + 2 * t >= lov) ? s1[0] * a.sl2 : -INFINITY;
-    const float x3 = (9 + 2 * t < hiv && 9 + 2 * t >= lov) ? s1[1] * a.sl2 : -INFINITY;
-    float mp = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
-    mp = fmaxf(mp, __shfl_xor_sync(FULL, mp, 1));
-    mp = fmaxf(mp, __shfl_xor_sync(FULL, mp, 2));
-    const float mn = fmaxf(m, mp);                                // finite: every page here holds a valid token
-    const float al = exp2f(m - mn);
-    const float e0 = exp2f(x0 - mn), e1 = exp2f(x1 - mn), e2 = exp2f(x2 - mn), e3 = exp2f(x3 - mn);
-    float ps = (e0 + e1) + (e2 + e3);
-    ps += __shfl_xor_sync(FULL, ps, 1);
-    ps += __shfl_xor_sync(FULL, ps, 2);
-    l = l * al + ps;
-    m = mn;
-    if (__any_sync(FULL, al != 1.f)) {                             // after the first pages the maxima rarely move
-#pragma unroll
-      for (int n = 0; n < 16; ++n) { o[n][0] *= al; o[n][1] *= al; }
-    }
-    // P = high BF16 part + BF16 residual
-    const __nv_bfloat16 h0 = __float2bfloat16_rn(e0), h1 = __float2bfloat16_rn(e1), h2 = __float2bfloat16_rn(e2),
-                        h3 = __float2bfloat16_rn(e3);
-    const uint32_t ph0 = pack_bf16(e0, e1), ph2 = pack_bf16(e2, e3);
-    const uint32_t pl0 = pack_bf16(e0 - __bfloat162float(h0), e1 - __bfloat162float(h1));
-    const uint32_t pl2 = pack_bf16(e2 - __bfloat162float(h2), e3 - __bfloat162float(h3));
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      uint32_t A[4][4];
-      const uint8_t* rec = pg + (2 + hf) * RKV;
-      decode_frag(load_rec_shared(rec, lane), A);
-      apply_kv_escapes(A, rec, a.pool, a.P, lane);
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const int nt = 2 * (4 * hf + ks);
-        const uint32_t v0 = movmatrix_t(A[ks][0]), v1 = movmatrix_t(A[ks][1]);
-        const uint32_t v2 = movmatrix_t(A[ks][2]), v3 = movmatrix_t(A[ks][3]);
-        mma_bf16_r(o[nt], ph0, 0u, ph2, 0u, v0, v1);               // dims 16 ks .. + 7
-        mma_bf16_r(o[nt], pl0, 0u, pl2, 0u, v0, v1);
-        mma_bf16_r(o[nt + 1], ph0, 0u, ph2, 0u, v2, v3);           // dims 16 ks + 8 .. + 15
-        mma_bf16_r(o[nt + 1], pl0, 0u, pl2, 0u, v2, v3);
-      }
-    }
-    __syncwarp();                                                  // every lane is done with this stage
-    if (lane == 0 && i + ATT_STG < mine) {
+    __syncwarp();                                  // every lane has read this stage
+    if (lane == 0 && i + STG < my_count) {
       fence_proxy_async();
-      issue(i + ATT_STG);
+      fetch(i + STG);
     }
   }
-  if (dead_at >= 0) {                                              // drain this warp's copies still in flight
-    for (int k = dead_at; k < min(mine, dead_at + ATT_STG); ++k)
-      (void)mbar_wait(mybar + k % ATT_STG, (uint32_t)(k / ATT_STG) & 1u);
-    m = -INFINITY; l = 0.f;
-  }
+  if (gave_up) { m0 = head0 ? -INFINITY : 0.f; m1 = head1 ? -INFINITY : 0.f; l0 = l1 = 0.f; }
+  l0 = sum_over_rows(l0);
+  l1 = sum_over_rows(l1);
 
-  // merge the warps of the CTA (every warp is done with the ring: its partial result goes where the pages were)
+  // ---- combine the warps of the CTA.  The rings are idle now; each warp parks (O^T, m, l) of its G heads there.
   __syncthreads();
-  constexpr int WS = G * 128 + 2 * G;
-  static_assert(ATT_NW * WS * 4 <= ATT_NW * ATT_STG * PAGE_BYTES, "partials must fit the ring");
-  float* so = red + warp * WS;
-  if (g < G) {
+  float* park = reinterpret_cast<float*>(smem);
+  constexpr int PER_WARP = 8 * (HD + 2);           // per head: 128 values of O, then m, l
+  static_assert(NW * PER_WARP * 4 <= NW * STG * PAGE_BYTES, "parked partials must fit in the ring");
+  float* mine = park + warp * PER_WARP;
 #pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      so[g * 128 + n * 8 + 2 * t] = o[n][0];
-      so[g * 128 + n * 8 + 2 * t + 1] = o[n][1];
-    }
-    if (t == 0) { so[G * 128 + 2 * g] = m; so[G * 128 + 2 * g + 1] = l; }
+  for (int j = 0; j < 8; ++j) {
+    if (head0) { mine[(2 * t) * (HD + 2) + 16 * j + g] = acc[j][0]; mine[(2 * t) * (HD + 2) + 16 * j + 8 + g] = acc[j][2]; }
+    if (head1) { mine[(2 * t + 1) * (HD + 2) + 16 * j + g] = acc[j][1]; mine[(2 * t + 1) * (HD + 2) + 16 * j + 8 + g] = acc[j][3]; }
+  }
+  if (g == 0) {
+    if (head0) { mine[(2 * t) * (HD + 2) + HD] = m0; mine[(2 * t) * (HD + 2) + HD + 1] = l0; }
+    if (head1) { mine[(2 * t + 1) * (HD + 2) + HD] = m1; mine[(2 * t + 1) * (HD + 2) + HD + 1] = l1; }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < G * 128; i += ATT_NW * 32) {
-    const int r = i >> 7, d = i & 127;
-    float M = -INFINITY;
+  for (int e = threadIdx.x; e < G * HD; e += NW * 32) {
+    const int h = e / HD, d = e % HD;
+    float top = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < ATT_NW; ++w) M = fmaxf(M, red[w * WS + G * 128 + 2 * r]);
-    float L = 0.f, O = 0.f;
+    for (int w = 0; w < NW; ++w) top = fmaxf(top, park[w * PER_WARP + h * (HD + 2) + HD]);
+    float den = 0.f, num = 0.f;
 #pragma unroll
-    for (int w = 0; w < ATT_NW; ++w) {
-      const float mw = red[w * WS + G * 128 + 2 * r];
-      if (mw == -INFINITY) continue;
-      const float f = exp2f(mw - M);
-      L += f * red[w * WS + G * 128 + 2 * r + 1];
-      O += f * red[w * WS + r * 128 + d];
+    for (int w = 0; w < NW; ++w) {
+      const float* pw = park + w * PER_WARP + h * (HD + 2);
+      if (pw[HD] == -INFINITY) continue;           // a warp without pages
+      const float f = exp2f(pw[HD] - top);
+      den += f * pw[HD + 1];
+      num += f * pw[d];
     }
-    if (a.S == 1) {
-      const __nv_bfloat16 v = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-      a.out[(size_t)b * a.os + (size_t)(h * G + r) * HD + d] = *reinterpret_cast<const uint16_t*>(&v);
+    const int hq = kvh * G + h;
+    if (a.splits == 1) {
+      const __nv_bfloat16 v = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      a.out[(size_t)seq * a.out_stride + (size_t)hq * HD + d] = *reinterpret_cast<const uint16_t*>(&v);
     } else {
-      const size_t ix = (size_t)(b * Hq + h * G + r) * a.S + j;
-      a.wo[ix * HD + d] = O;
-      if (d == 0) { a.wml[ix * 2] = M; a.wml[ix * 2 + 1] = L; }
+      const size_t ix = ((size_t)seq * Hq + hq) * a.splits + split;
+      a.part_o[ix * HD + d] = num;
+      if (d == 0) { a.part_ml[ix * 2] = top; a.part_ml[ix * 2 + 1] = den; }
     }
   }
 }
 
-__global__ void __launch_bounds__(128) kv_merge_kernel(const float* __restrict__ wo, const float* __restrict__ wml,
-                                                       uint16_t* __restrict__ out, long long os, int Hq, int S) {
-  const int bq = blockIdx.x, d = threadIdx.x;
+// One warp per (sequence, query head): weighs the split partials by exp2(m_j - max m) and normalises.
+__global__ void __launch_bounds__(128) kv_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                       uint16_t* __restrict__ out, long long out_stride, int Hq,
+                                                       int splits, long long rows) {
   pdl_wait();
   pdl_launch_dependents();
-  float M = -INFINITY;
-  for (int j = 0; j < S; ++j) M = fmaxf(M, wml[((size_t)bq * S + j) * 2]);
-  float L = 0.f, O = 0.f;
-  for (int j = 0; j < S; ++j) {
-    const float mj = wml[((size_t)bq * S + j) * 2];
-    if (mj == -INFINITY) continue;
-    const float f = exp2f(mj - M);
-    L += f * wml[((size_t)bq * S + j) * 2 + 1];
-    O += f * wo[((size_t)bq * S + j) * HD + d];
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* ml = part_ml + (size_t)row * splits * 2;
+  float top = -INFINITY;
+  for (int j = lane; j < splits; j += 32) top = fmaxf(top, ml[2 * j]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) top = fmaxf(top, __shfl_xor_sync(FULL, top, o));
+  float den = 0.f;
+  float4 num = make_float4(0.f, 0.f, 0.f, 0.f);    // this lane's four dims
+  for (int j = 0; j < splits; ++j) {
+    const float mj = ml[2 * j];
+    if (mj == -INFINITY) continue;                  // a split without tokens
+    const float f = exp2f(mj - top);
+    den += f * ml[2 * j + 1];
+    const float4 o = *reinterpret_cast<const float4*>(part_o + ((size_t)row * splits + j) * HD + 4 * lane);
+    num.x += f * o.x; num.y += f * o.y; num.z += f * o.z; num.w += f * o.w;
   }
-  const __nv_bfloat16 v = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-  out[(size_t)(bq / Hq) * os + (size_t)(bq % Hq) * HD + d] = *reinterpret_cast<const uint16_t*>(&v);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  uint2 packed;
+  packed.x = pack_bf16(num.x * inv, num.y * inv);
+  packed.y = pack_bf16(num.z * inv, num.w * inv);
+  *reinterpret_cast<uint2*>(out + (size_t)(row / Hq) * out_stride + (size_t)(row % Hq) * HD + 4 * lane) = packed;
 }
 
-template <int G, int NW, int STG>
-int attn_launch_cfg(const AttnArgs& a, int B, cudaStream_t st) {
+template <int NW, int STG>
+int attn_launch(const AttnLaunch& a, int B, cudaStream_t st) {
   const int smem = NW * STG * PAGE_BYTES + NW * STG * 8;
   static bool set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set[dev]) {
-    if (int e = st::cuda_fail(cudaFuncSetAttribute(kv_attn_kernel<G, NW, STG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int e = st::cuda_fail(cudaFuncSetAttribute(kv_attn_kernel<NW, STG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    smem), "st_kv_attn: shared memory attribute"))
       return e;
     set[dev] = true;
   }
-  return st::launch("st_kv_attn launch", kv_attn_kernel<G, NW, STG>, dim3((unsigned)(B * a.Hkv * a.S)), dim3(NW * 32),
-                    (size_t)smem, st, a);
-}
-
-template <int G>
-int attn_launch(const AttnArgs& a, int B, cudaStream_t st) {
-  // STATETREE_ATTN_CFG (tuning aid): 2 = 4 warps x 2 page stages, three CTAs per SM (default: the kernel is bound by
-  // instruction latency, and twelve warps per SM hide more of it than eight with deeper rings; 4.5 TB/s at batch 32 x 4K
-  // against 4.0), 1 = 4 warps x 3 stages, 0 = 8 warps x 2
-  static int cfg = -1;
-  if (cfg < 0) {
-    const char* v = getenv("STATETREE_ATTN_CFG");
-    cfg = v ? atoi(v) : 2;
-  }
-  return cfg == 1 ? attn_launch_cfg<G, 4, 3>(a, B, st) : (cfg == 2 ? attn_launch_cfg<G, 4, 2>(a, B, st) : attn_launch_cfg<G, 8, 2>(a, B, st));
+  return st::launch("st_kv_attn launch", kv_attn_kernel<NW, STG>, dim3((unsigned)(B * a.kv_heads * a.splits)),
+                    dim3(NW * 32), (size_t)smem, st, a);
 }
 }  // namespace
 
@@ -664,32 +727,31 @@ extern "C" int st_kv_attn(const void* q, int64_t qs, int64_t B, int64_t Hq, cons
                           const int32_t* lens, const int32_t* starts, void* out, int64_t os, float* wo, float* wml,
                           double scale, int64_t S, int64_t minpps, void* stream) {
   ST_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "st_kv_attn: heads");
+  ST_REQUIRE(Hq / Hkv <= 8, "st_kv_attn: at most 8 query heads per KV head (got %lld)", (long long)(Hq / Hkv));
   ST_REQUIRE(S >= 1 && S <= 1024, "st_kv_attn: splits must be in [1, 1024]");
   if (B == 0) return 0;
   ST_REQUIRE(q && kv && pool && bt && lens && out, "st_kv_attn: null pointer");
   ST_REQUIRE(S == 1 || (wo && wml), "st_kv_attn: split workspace (wo, wml) missing");
   ST_REQUIRE(nblocks > 0, "st_kv_attn: empty cache");
   ST_REQUIRE(((uintptr_t)q & 3u) == 0 && qs % 2 == 0 && st::aligned16(kv), "st_kv_attn: alignment");
+  ST_REQUIRE(S == 1 || (((uintptr_t)wo & 15u) == 0 && ((uintptr_t)out & 7u) == 0 && os % 4 == 0),
+             "st_kv_attn: wo must be 16-byte aligned, out 8-byte aligned with a row stride that is a multiple of 4");
   ST_REQUIRE(B * Hkv * S < (1ll << 31), "st_kv_attn: grid too large");
-  AttnArgs a;
-  a.q = (const uint16_t*)q; a.qs = qs; a.kv = (const uint8_t*)kv; a.nblocks = nblocks; a.pool = pool; a.P = (int)P;
-  a.bt = bt; a.bts = bts; a.lens = lens; a.starts = starts; a.out = (uint16_t*)out; a.os = os; a.wo = wo; a.wml = wml;
-  a.sl2 = (float)(scale * 1.4426950408889634);
-  a.Hkv = (int)Hkv; a.S = (int)S; a.minpps = (int)(minpps < 1 ? 1 : minpps);
+  AttnLaunch a;
+  a.q = (const uint16_t*)q; a.q_stride = qs; a.pages = (const uint8_t*)kv; a.n_pages = nblocks;
+  a.pool = pool; a.pool_blocks = (int)P; a.table = bt; a.table_stride = bts; a.seq_len = lens; a.seq_start = starts;
+  a.out = (uint16_t*)out; a.out_stride = os; a.part_o = wo; a.part_ml = wml;
+  a.scale_log2 = (float)(scale * 1.4426950408889634);
+  a.kv_heads = (int)Hkv; a.group = (int)(Hq / Hkv); a.splits = (int)S; a.min_pages = (int)(minpps < 1 ? 1 : minpps);
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "st_kv_attn: no device status word");
   cudaStream_t st_ = (cudaStream_t)stream;
-  int e = 0;
-  switch (Hq / Hkv) {
-    case 1: e = attn_launch<1>(a, (int)B, st_); break;
-    case 2: e = attn_launch<2>(a, (int)B, st_); break;
-    case 4: e = attn_launch<4>(a, (int)B, st_); break;
-    case 8: e = attn_launch<8>(a, (int)B, st_); break;
-    default: return st::fail("st_kv_attn: query heads per KV head must be 1, 2, 4 or 8 (got %lld)", (long long)(Hq / Hkv));
+  // four warps with two pages in flight each (51 KB): several CTAs share an SM and hide each other's latencies
+  if (int e = attn_launch<4, 2>(a, (int)B, st_)) return e;
+  if (S > 1) {
+    const long long rows = B * Hq;
+    return st::launch("st_kv_attn merge launch", kv_merge_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, st_,
+                      (const float*)wo, (const float*)wml, (uint16_t*)out, (long long)os, (int)Hq, (int)S, rows);
   }
-  if (e) return e;
-  if (S > 1)
-    return st::launch("st_kv_attn merge launch", kv_merge_kernel, dim3((unsigned)(B * Hq)), dim3(128), 0, st_,
-                      (const float*)wo, (const float*)wml, (uint16_t*)out, (long long)os, (int)Hq, (int)S);
   return 0;
 }

@@ -12,25 +12,15 @@ RKV = 1600
 
 
 def decode_splits(B, Hkv, max_pages, sms=148, min_pages=4):
-    """splits of each sequence's pages over CTAs, 1..16: the count that minimises a two-parameter cost model fitted to
-    measurements on B200 -- waves x (pages per split + 4), where waves = CTAs / (3 CTAs of four warps per SM) rounded up
-    and 4 pages stand for a split's start-up and its share of the merge.  It avoids grids just above a whole number of
-    waves (batch 16 at 4 splits: 512 CTAs on 444 slots, 201 us at 16K against 165-179 us at 3 or 16 splits) and gives
-    short contexts few splits and long ones many.  At least 3 splits (one-wave grids of long CTAs lose to finer ones) and
-    at least min_pages pages per split.  A function of the batch size
-    and the longest context only, so one captured graph per batch size serves every step (the role of the reference's
-    statetree/vllm_kv.py:42-50, re-sized for 148 SMs)."""
-    slots = 3 * sms
-    allowed = max(1, min(16, max_pages // min_pages))
-    if 2 * B * Hkv >= slots:                            # batch 32 and up: measured fastest at 4 (several waves of
-        return min(4, allowed)                          # short CTAs balance themselves)
-    best, best_cost = min(3, allowed), None
-    for s in range(min(3, allowed), allowed + 1):
-        ctas = B * Hkv * s
-        cost = ((ctas + slots - 1) // slots) * ((max_pages + s - 1) // s + 4)
-        if best_cost is None or cost < best_cost:
-            best, best_cost = s, cost
-    return best
+    """How many CTAs share each (sequence, KV head) of the decode attention kernel.  Two bounds: the split that
+    balances a split's own pages against the cost of merging the partial results grows like the square root of the
+    page count, and no more splits are needed than fill the GPU about three CTAs deep.  At least min_pages pages
+    per split.  A function of the batch size and the longest context only, so one captured graph per batch size
+    serves every step (the role of the reference's statetree/vllm_kv.py:42-50, re-sized for 148 SMs)."""
+    by_length = int(round(max_pages ** 0.5))
+    by_fill = -(-3 * sms // max(1, B * Hkv))
+    most = max(1, max_pages // max(1, min_pages))
+    return min(most, max(2, min(by_length, by_fill, 64)))               # two splits at least: several waves of CTAs
 
 
 class StateTreeKVLayer:

@@ -244,6 +244,39 @@ def test_decode_attention_matches_fp64(tiny, left_pad):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 4), (16, 2), (6, 2)])
+def test_decode_attention_other_group_sizes(hq, hkv):
+    """1, 2, 8 and 3 query heads per KV head (the kernel puts up to 8 heads on the N side of the tensor-core shape)"""
+    from statetree_b200.kvcache import StateTreeKVLayer
+    B, ctx = 3, 333
+    npg = (ctx + 15) // 16
+    gen = torch.Generator(device=DEV).manual_seed(hq * 10 + hkv)
+    layer = StateTreeKVLayer(B * npg, hkv, DEV, pool_blocks=1 << 12)
+    bt = torch.randperm(B * npg, device=DEV, generator=gen).view(B, npg).to(torch.int32)
+    pos = torch.arange(ctx, device=DEV)
+    Ks, Vs = [], []
+    for b in range(B):
+        K = torch.randn(ctx, hkv, D, device=DEV, generator=gen).to(torch.bfloat16)
+        V = torch.randn(ctx, hkv, D, device=DEV, generator=gen).to(torch.bfloat16)
+        layer.append(K, V, bt[b].long()[pos // 16] * 16 + pos % 16)
+        Ks.append(K)
+        Vs.append(V)
+    q = torch.randn(B, hq, D, device=DEV, generator=gen).to(torch.bfloat16)
+    lens = torch.tensor([ctx, ctx - 17, 5], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    for S in (1, 3):
+        out = layer.attention(q, bt, lens, scale, splits=S, min_pages=2)
+        for b in range(B):
+            L = int(lens[b])
+            k = Ks[b][:L].double().permute(1, 0, 2).repeat_interleave(hq // hkv, 0)
+            v = Vs[b][:L].double().permute(1, 0, 2).repeat_interleave(hq // hkv, 0)
+            p = torch.softmax(torch.einsum("hd,hld->hl", q[b].double(), k) * scale, -1)
+            ref = torch.einsum("hl,hld->hd", p, v)
+            assert float((out[b].double() - ref).norm() / ref.norm()) < 5e-3, (hq, hkv, S, b)
+    from statetree_b200 import ops
+    assert ops.device_status() == 0
+
+
 def test_cache_object_decode_steps():
     """StateTreeKVCache: prefill + decode steps through update() / attention() against dense fp64 attention"""
     from statetree_b200.kvcache import StateTreeKVCache
