@@ -222,10 +222,22 @@ def attention_workload(args):
                 ours()
                 ref = base()
             err = float((out.float().view(-1) - ref.float().reshape(-1)).norm() / ref.float().norm())
+            # correctness gate: the first two sequences against fp64 attention over the exactly decoded values
+            worst = 0.0
+            for b in range(min(B, 2)):
+                k64 = Kd[b].double().permute(1, 0, 2).repeat_interleave(Hq // Hkv, 0)
+                v64 = Vd[b].double().permute(1, 0, 2).repeat_interleave(Hq // Hkv, 0)
+                p64 = torch.softmax(torch.einsum("hd,hld->hl", q[b].double(), k64) * sc, -1)
+                r64 = torch.einsum("hl,hld->hd", p64, v64)
+                worst = max(worst, float((out[b].double() - r64).norm() / r64.norm()))
+                del k64, v64, p64, r64
+            if not worst < 5e-3:
+                raise RuntimeError(f"attention output off by {worst:.2e} (relative) from fp64 at batch {B}, context {ctx}")
             us, us_b = timed(ours, args.steps), timed(base, args.steps)
             nbytes = B * npg * 16 * Hkv * 400
             table.append({"batch": B, "ctx": ctx, "splits": S, "us": us, "bf16_us": us_b, "speedup_vs_bf16": us_b / us,
-                          "gbs": nbytes / us / 1e3, "frac_hbm": nbytes / us / 1e3 / hbm, "rel_err_vs_bf16": err})
+                          "gbs": nbytes / us / 1e3, "frac_hbm": nbytes / us / 1e3 / hbm, "rel_err_vs_bf16": err,
+                          "rel_err_vs_fp64": worst})
             del layer, Kd, Vd
             torch.cuda.empty_cache()
     big = table[-1]
@@ -345,7 +357,8 @@ def moe_workload(args):
         else:
             err = None
         table.append({"tokens": T, "pairs": T * K, "distinct_experts": distinct, "us": us, "gbs": nbytes / us / 1e3,
-                      "frac_hbm": nbytes / us / 1e3 / hbm, "rel_err_vs_bf16": err})
+                      "frac_hbm": nbytes / us / 1e3 / hbm, "rel_err_vs_bf16": err,
+                          "rel_err_vs_fp64": worst})
         del graph
     big = table[0]
     status = ops.device_status()
