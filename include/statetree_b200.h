@@ -92,14 +92,31 @@ int st_moe_group_gemv(const int64_t* tp, const int64_t* eop, const int64_t* ebp,
                       const void* X, const int32_t* sorted, const int32_t* bexp, const int32_t* npost, int64_t nblk,
                       void* Y, int64_t S, int64_t M, int64_t N, int64_t xdiv, void* ws, int64_t ws_bytes, int32_t* cnt,
                       void* stream);
-/* Pairs grouped by expert in blocks of 8 for st_moe_group_gemv: sorted int32 [nblk * 8] (pair indices, expert-major,
- * original order inside an expert, runs padded to a multiple of 8 with the value S), bexp int32 [nblk], npost int32
- * [1] = entries of the first used_bins experts (used_bins = E, or E - 1 when the last id collects the pairs of other
- * ranks' experts, whose blocks the grouped kernel then never visits); ids int64 (ids64 = 1) or int32 [S], clamped to
- * [0, E); nblk >= S / 8 + min(S, E); E <= 1024.  The reference takes this layout from vLLM's moe_align_block_size
- * (statetree/experts.py:52-120). */
-int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int64_t used_bins, int32_t* sorted, int32_t* bexp,
-                 int32_t* npost, int64_t nblk, void* stream);
+/* Pairs grouped by expert in blocks of bs (8 for st_moe_group_gemv, 64 or 128 for st_moe_group_gemm): sorted int32
+ * [nblk * bs] (pair indices, expert-major, original order inside an expert, runs padded to a multiple of bs with the
+ * value S), bexp int32 [nblk], npost int32 [1] = entries of the first used_bins experts (used_bins = E, or E - 1 when
+ * the last id collects the pairs of other ranks' experts, whose blocks the grouped kernels then never visit); ids
+ * int64 (ids64 = 1) or int32 [S], clamped to [0, E); nblk >= S / bs + min(S, E); E <= 1024.  The reference takes
+ * this layout from vLLM's moe_align_block_size (statetree/experts.py:52-120). */
+int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int64_t used_bins, int64_t bs, int32_t* sorted,
+                 int32_t* bexp, int32_t* npost, int64_t nblk, void* stream);
+
+/* Grouped fused decode + tcgen05 GEMM over per-expert trees, for many pairs per expert (prefill-sized calls):
+ * y[pair] = W[expert of pair] x[pair / xdiv].  Replaces `_C.gtt` (statetree/csrc/gtt.cu:80-299, 322-368).
+ *   st_moe_tensor_maps  writes one weight tensor map (st_moe_tensor_map_bytes() bytes each, 64-byte aligned) per
+ *                       expert tree into maps_dev; trees_host is a HOST array of E device addresses.  Once per
+ *                       expert set, outside graph capture.
+ *   st_moe_gather       Xg[i, :] = X[sorted[i] / xdiv, :] for the used entries of sorted (rows = nblk * bs)
+ *   st_moe_group_gemm   one CTA per (block of bs pairs, 128 rows of M): Y[sorted[i], :] = W[bexp[block]] Xg[i, :];
+ *                       rows of padding entries and of blocks with a negative expert are not written; eop / elp as
+ *                       for st_moe_gemv; M % 128 == 0, bs = 64 or 128.  Yf32 optional as for st_gemv. */
+int64_t st_moe_tensor_map_bytes(void);
+int st_moe_tensor_maps(const int64_t* trees_host, int64_t E, int64_t M, int64_t N, void* maps_dev, void* stream);
+int st_moe_gather(const void* X, const int32_t* sorted, const int32_t* npost, int64_t rows, int64_t S, int64_t xdiv,
+                  int64_t N, void* Xg, void* stream);
+int st_moe_group_gemm(const void* maps, const int64_t* eop, const int64_t* elp, int64_t E, const void* Xg,
+                      const int32_t* sorted, const int32_t* bexp, const int32_t* npost, int64_t nblk, int64_t bs,
+                      void* Y, float* Yf32, int64_t S, int64_t M, int64_t N, void* stream);
 /* out[t] = sum_j w[t, j] * Y[t * K + j] in fp32, expert order, BF16 out; w float32 (w_bf16 = 0) or BF16 (1).
  * Replaces `_C.wsum` (statetree/csrc/kernels.cu:1489-1535). */
 int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H, void* stream);

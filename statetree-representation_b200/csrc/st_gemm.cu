@@ -2,22 +2,29 @@
 //   Y[B, M] = X[B, N] W[M, N]^T,  W as state-tree records, fp32 accumulation in tensor memory, BF16 output.
 //
 // One CTA computes a 128-row block of W against one tile of NT tokens (NT = 64, 128 or 256) over a contiguous range
-// of 64-column k-tiles.  Warp roles (10 warps):
-//   warp 8   producer: per k-tile, eight 1552-byte bulk copies (the records of the block's eight 16-row tiles) and
-//            one tiled TMA load of the activation tile X[tok0 .. tok0+NT, 64 cols] with the 128-byte swizzle
-//   warps 0-7 decode: each turns one record into its mma-fragment registers (five integer ops per four weights),
-//            patches escapes, and writes the 16 x 64 BF16 sub-tile into the K-major, 128-byte-swizzled A tile with
-//            stmatrix; fence.proxy.async hands the tile to the tensor core
-//   warp 9   MMA: one elected thread issues four tcgen05.mma (128 x NT x 16, kind::f16) per k-tile, A and B read
-//            from shared memory through descriptors, D in TMEM; tcgen05.commit releases the stage
-// Epilogue: warps 0-7 read the accumulator with tcgen05.ld (32 lanes x 32 columns per instruction) and either store
-// BF16 results or, when the k range is split over several CTAs, store fp32 partials; the last CTA to arrive for a
-// tile adds the partials in split order (deterministic) and stores the result.
+// of 64-column k-tiles.  Warp roles (20 warps):
+//   warps 0-15  decode, in two groups of eight (group g takes every second k-tile): each warp turns one record into
+//               its mma-fragment registers (five integer ops per four weights), patches escapes, and writes the
+//               16 x 64 BF16 sub-tile into the K-major, 128-byte-swizzled A tile with stmatrix; fence.proxy.async
+//               hands the tile to the tensor core
+//   warp 16     record producer: one 3-D tiled TMA load per k-tile brings the eight 1552-byte records of the block's
+//               eight 16-row tiles into a deep ring
+//   warp 17     activation producer: one tiled TMA load of X[tok0 .. tok0 + NT, 64 cols] with the 128-byte swizzle
+//   warps 18-19 MMA issuers: one elected thread each issues four tcgen05.mma (128 x NT x 16, kind::f16) per k-tile of
+//               its decode group, A and B read from shared memory through descriptors, D in its own TMEM
+//               accumulator; tcgen05.commit releases the stage
+// Epilogue: the decode warps read the accumulators with tcgen05.ld, add the two issuers' tiles in a fixed order and
+// park the fp32 tile in shared memory; the CTAs that split a k range form a thread-block cluster and add their tiles
+// through distributed shared memory in rank order (deterministic), then store BF16.
+// The grouped (mixture-of-experts) variant runs the same pipeline per (block of NT routed pairs, 128-row block): the
+// block's expert selects the weight tensor map and escape tables, the activation tile comes from rows gathered in
+// block order, and the result rows are scattered back to their pair indices.
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word and the CTA leaves after
 // releasing its tensor memory.
 #include <cuda.h>
 
 #include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 
@@ -33,31 +40,14 @@ constexpr int NDEC = 8;                      // decode warps = records per k-til
 
 struct GemmArgs {
   const uint8_t* tree; const int* eo; const uint32_t* el;
-  uint16_t* Y; float* Yf; float* ws; int* cnt; int* status;
+  uint16_t* Y; float* Yf; int* status;
+  // grouped (mixture of experts): per-expert weight tensor maps and escape tables, pairs in moe_align layout
+  const CUtensorMap* maps; const long long* eop; const long long* elp;
+  const int* sorted; const int* bexp; const int* npost; int E;
   long long M, N;
   int B, NG, NT, KS, RB, TT, stages, rstages, nmma, bar_off;
   uint32_t idesc;
-#ifdef ST_PROF
-  long long* prof;
-  int diag;                                 // development only: 1 = reuse the first activation tiles, 2 = issue no MMA
-#endif
 };
-
-#ifdef ST_PROF
-__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#ifdef ST_NOTIMERS
-#define GPROF(slot) do {} while (0)
-#define GCK(n) do {} while (0)
-#else
-#define GPROF(slot) do { if (a.prof && (slot) < 64) a.prof[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
-#define GCK(n) do { const long long t_ = clock64(); gck[n] += t_ - gckl; gckl = t_; } while (0)
-#endif
-long long* g_gemm_prof = nullptr;
-int g_gemm_diag = 0;
-#else
-#define GPROF(slot) do {} while (0)
-#define GCK(n) do {} while (0)
-#endif
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -98,35 +88,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-// DG decode groups of eight warps (group g takes the k-tiles g, g + DG, ...), a record producer, an activation
-// producer and DG MMA issuer warps.  DG = 2: one CTA per SM (any token tile).  DG = 1: 11 warps and at most half an
-// SM's shared memory, so two CTAs share an SM (a tuning aid; slower for the shapes measured).
-template <int DG> struct Roles {
-  static constexpr int NDW = DG * NDEC;                                     // decode warps
-  static constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;         // role warps
-  static constexpr int THREADS = (NDW + 2 + DG) * 32;
-};
-#ifdef ST_GEMM_SPINWAIT
-#define GW mbar_wait_spin
-#else
+// Two decode groups of eight warps (group g takes the k-tiles g, g + 2, ...), a record producer, an activation
+// producer and two MMA issuer warps: one CTA per SM.
+constexpr int DG = 2;
+constexpr int NDW = DG * NDEC;                                              // decode warps
+constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;                  // role warps
+constexpr int THREADS = (NDW + 2 + DG) * 32;
 #define GW mbar_wait_look
-#endif
-#ifndef ST_GEMM_BACKOFF_NS
-#define ST_GEMM_BACKOFF_NS 0
-#endif
-// wait of the decode warps: sixteen warps polling a barrier take issue slots from the three single-thread roles that
-// share their schedulers, so a warp that finds the barrier closed sleeps a little before it looks again
-__device__ __forceinline__ bool wait_decode(uint64_t* bar, uint32_t parity) {
-#if ST_GEMM_BACKOFF_NS > 0
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    if (mbar_try(bar, parity)) return true;
-    __nanosleep(ST_GEMM_BACKOFF_NS);
-  }
-  return false;
-#else
-  return GW(bar, parity);
-#endif
-}
+__device__ __forceinline__ bool wait_decode(uint64_t* bar, uint32_t parity) { return GW(bar, parity); }
 constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of one k-tile
 
 // Two rings.  The RAW ring (R slots of eight records) faces HBM: its depth sets the bytes in flight.  The TILE ring
@@ -136,10 +105,9 @@ constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of on
 // the rank).  After its main loop every CTA parks its fp32 accumulator tile in its own shared memory; after a cluster
 // barrier CTA j adds the KS tiles for its share of the token columns through distributed shared memory, in rank
 // order (bit-identical from run to run), and stores BF16.  No partial sums travel through global memory.
-template <int DG>
-__global__ void __launch_bounds__(Roles<DG>::THREADS, DG == 1 ? 2 : 1)
+template <bool GROUPED>
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
-  constexpr int NDW = Roles<DG>::NDW, W_RAW = Roles<DG>::W_RAW, W_X = Roles<DG>::W_X, W_MMA = Roles<DG>::W_MMA;
   constexpr int NMMA = DG;                                     // issuer warps; a.nmma of them work
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -162,9 +130,21 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
   const int k0 = (int)((long long)a.NG * ks / a.KS), k1 = (int)((long long)a.NG * (ks + 1) / a.KS);
   const int nk = k1 - k0;
   const int tok0 = tt * NT;
+  // the matrix this CTA multiplies by: the one of the call, or (grouped) the expert of pair block tt
+  const int* eo = a.eo;
+  const uint32_t* el = a.el;
+  const CUtensorMap* wm = &wmap;
+  if (GROUPED) {
+    pdl_wait();                                                  // the block table comes from an earlier kernel
+    if (tok0 >= a.npost[0]) return;                              // beyond the blocks the routing filled
+    const int expert = a.bexp[tt];
+    if (expert < 0 || expert >= a.E) return;                     // another rank's expert
+    eo = reinterpret_cast<const int*>(a.eop[expert]);
+    el = reinterpret_cast<const uint32_t*>(a.elp[expert]);
+    wm = a.maps + expert;
+  }
 
   if (tid == 0) {
-    GPROF(0);
     for (int s = 0; s < S; ++s) { mbar_init(ready + s, NDEC + 1); mbar_init(empty + s, 1); }
     for (int r = 0; r < R; ++r) { mbar_init(rfull + r, 1); mbar_init(rempty + r, NDEC); }
     mbar_init(accbar, NMMA);                                       // every issuer warp arrives, working or not
@@ -178,7 +158,6 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (tid == 0) GPROF(1);
   pdl_launch_dependents();
 
   if (warp == W_RAW) {
@@ -187,16 +166,9 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
     // [row tile][column group][194 x u64]; eight separate 1552-byte bulk copies per k-tile cost ~1 us of issue time
     if (lane == 0) {
       for (int i = 0, r = 0, k = 0; i < nk; ++i, r = (r + 1 == R ? 0 : r + 1), k += (r == 0)) {
-#ifdef ST_PROF
-        if (a.diag & 128) break;
-#endif
         if (k > 0 && !GW(rempty + r, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
-#ifdef ST_PROF
-        if ((a.diag & 4) && i >= R) { mbar_arrive(rfull + r); continue; }
-#endif
         mbar_expect_tx(rfull + r, (uint32_t)RAW_SLOT);
-        tma_load_3d(rawring + (size_t)r * RAW_SLOT, &wmap, 0, k0 + i, rb * 8, rfull + r);
-        if (i < 24) GPROF(16 + i);
+        tma_load_3d(rawring + (size_t)r * RAW_SLOT, wm, 0, k0 + i, rb * 8, rfull + r);
       }
     }
   } else if (warp == W_X) {
@@ -208,9 +180,6 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
       pdl_wait();
       for (int i = 0, s = 0, k = 0; i < nk; ++i, s = (s + 1 == S ? 0 : s + 1), k += (s == 0)) {
         if (k > 0 && !GW(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
-#ifdef ST_PROF
-        if ((a.diag & 1) && i >= S) { mbar_arrive(ready + s); continue; }
-#endif
         mbar_expect_tx(ready + s, (uint32_t)XT);
         tma_load_2d(smem + (size_t)s * STAGE + A_TILE, &xmap, (k0 + i) * 64, tok0, ready + s);
       }
@@ -228,38 +197,21 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
     if (lane == 0 && m >= a.nmma) mbar_arrive(accbar);
     if (lane == 0 && m < a.nmma) {
       const uint32_t acc = tmem + (uint32_t)(m * NT);
-#ifdef ST_PROF
-      long long gck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gckl = clock64();
-#endif
       int s = m % S, k = m / S;
       for (int i = m; i < nk; i += a.nmma) {
-        GCK(0);
         if (!GW(ready + s, (uint32_t)k & 1u)) {
           atomicExch(a.status, ERR_WAIT_MMA);
           break;
         }
-        GCK(1);
         tc_fence_after();
         const uint32_t sa = smem_addr(smem + (size_t)s * STAGE);
         const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TILE);
-#ifdef ST_PROF
-        if (!(a.diag & 2))
-#endif
 #pragma unroll
         for (int j = 0; j < 4; ++j) tc_mma(acc, da + 2 * j, db + 2 * j, a.idesc, (i >= a.nmma || j) ? 1u : 0u);
-        GCK(2);
-#ifdef ST_PROF
-        if (a.diag & 64) mbar_arrive(empty + s); else
-#endif
         tc_commit(empty + s);
-        GCK(3);
-        if (m == 0) GPROF(40 + i / a.nmma);
         s += a.nmma; while (s >= S) { s -= S; ++k; }
       }
       tc_commit(accbar);                                          // arrives when every MMA of this issuer has completed
-#ifdef ST_PROF
-      if (a.prof && m == 0) for (int q = 0; q < 4; ++q) a.prof[blockIdx.x * 64 + 5 + q + (q == 3 ? 6 : 0)] = gck[q];
-#endif
     }
   } else {
     // ---------------------------------------------------------------- decode warps: group g = warp / 8 takes the
@@ -275,8 +227,8 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
     auto load_offsets = [&](int first) {
       eo_base = first;
       const int j = first + lane;
-      eo_lo = j < nk ? __ldg(a.eo + rbase + j) : 0;
-      eo_hi = j < nk ? __ldg(a.eo + rbase + j + 1) : 0;
+      eo_lo = j < nk ? __ldg(eo + rbase + j) : 0;
+      eo_hi = j < nk ? __ldg(eo + rbase + j + 1) : 0;
       emask = __ballot_sync(FULL, eo_hi > eo_lo);
     };
     int lo = 0, hi = 0;
@@ -286,58 +238,30 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
       if (emask & 1u) {
         lo = __shfl_sync(FULL, eo_lo, 0);
         hi = __shfl_sync(FULL, eo_hi, 0);
-        if (lane < hi - lo) ent = __ldg(a.el + lo + lane);
+        if (lane < hi - lo) ent = __ldg(el + lo + lane);
       }
     }
-#ifdef ST_PROF
-    long long gck[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gckl = clock64();
-#endif
     int s = grp % S, k = grp / S, r = grp % R, rk = grp / R;          // tile stage / use count, record slot / use count
     for (int i = grp; i < nk; i += DG) {
-      GCK(0);
       int nlo = 0, nhi = 0;
       uint32_t nent = 0u;
-#ifdef ST_PROF
-      if (!(a.diag & 256))
-#endif
       if (i + DG < nk) {
         if (i + DG - eo_base >= 32) load_offsets(i + DG);
         const int off = i + DG - eo_base;
         if ((emask >> off) & 1u) {                                // five records in six have none: one bit test
           nlo = __shfl_sync(FULL, eo_lo, off);
           nhi = __shfl_sync(FULL, eo_hi, off);
-          if (lane < nhi - nlo) nent = __ldg(a.el + nlo + lane);
+          if (lane < nhi - nlo) nent = __ldg(el + nlo + lane);
         }
       }
-#ifdef ST_PROF
-      RecRegs rr;
-      if (a.diag & 128) {
-        rr.l0 = rr.l1 = rr.st = make_uint4(i, i, i, i); rr.nodes = i;
-      } else {
-#endif
-      GCK(5);                                                     // escape prefetch
       if (!wait_decode(rfull + r, (uint32_t)rk & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
         break;
       }
-      GCK(1);                                                     // wait for the records
-#ifdef ST_PROF
-      rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + rec * REC, lane);
-#else
       const RecRegs rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + rec * REC, lane);
-#endif
       __syncwarp();
       if (lane == 0) mbar_arrive(rempty + r);                     // the slot can be refilled while we decode
-#ifdef ST_PROF
-      }
-#endif
       uint32_t A[4][4];
-#ifdef ST_PROF
-      if (a.diag & 8) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) A[q][0] = A[q][1] = A[q][2] = A[q][3] = rr.nodes;
-      } else
-#endif
       decode_frag(rr, A);
       {
         const int n = min(32, hi - lo);
@@ -345,47 +269,31 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
       }
       for (int base = lo + 32; base < hi; base += 32) {          // a crowded record: the rest of its list
         const int n = min(32, hi - base);
-        const uint32_t mine = (lane < n) ? __ldg(a.el + base + lane) : 0u;
+        const uint32_t mine = (lane < n) ? __ldg(el + base + lane) : 0u;
         for (int e = 0; e < n; ++e) patch_entry(A, __shfl_sync(FULL, mine, e), lane);
       }
       lo = nlo; hi = nhi; ent = nent;
-#ifdef ST_PROF
-      if (A[0][0] == 0x12345u && A[3][3] == 0x54321u) gck[7]++;
-#endif
-      GCK(2);                                                     // load + decode + escapes
       if (k > 0 && !wait_decode(empty + s, (uint32_t)(k - 1) & 1u)) {   // the MMAs of the stage's last use are done
         if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
         break;
       }
-      GCK(3);                                                     // wait for the tile stage
       uint8_t* st = smem + (size_t)s * STAGE;
       // lane l addresses row (l & 7) of matrix (l >> 3): matrices = (rows 0-7 | 8-15) x (16-byte chunk 2q | 2q+1)
       const int mrow = rec * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
       const uint32_t rowaddr = smem_addr(st) + mrow * 128;
       const int chalf = lane >> 4;
-#ifdef ST_PROF
-      if (!(a.diag & 16))
-#endif
 #pragma unroll
       for (int q = 0; q < 4; ++q)
         stmatrix_x4(rowaddr + (uint32_t)(((2 * q + chalf) ^ (mrow & 7)) << 4), A[q][0], A[q][1], A[q][2], A[q][3]);
-#ifdef ST_PROF
-      if (!(a.diag & 32))
-#endif
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(ready + s);
       s += DG; while (s >= S) { s -= S; ++k; }
       r += DG; while (r >= R) { r -= R; ++rk; }
-      GCK(4);                                                     // stmatrix + fence + arrive
     }
-#ifdef ST_PROF
-    if (a.prof && tid == 0) for (int q = 0; q < 6; ++q) a.prof[blockIdx.x * 64 + 8 + q] = gck[q];
-#endif
     // ---------------------------------------------------------------- epilogue 1: accumulator -> own shared memory
     const bool acc_ok = GW(accbar, 0u);
     if (!acc_ok && lane == 0) atomicExch(a.status, ERR_WAIT_ACC);
-    if (tid == 0) GPROF(2);
     tc_fence_after();
     float* stg = reinterpret_cast<float*>(smem);                 // [NT][128] fp32, over the (now idle) ring
     const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column share of the warp
@@ -403,14 +311,13 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
 #pragma unroll
       for (int j = 0; j < 16; ++j) stg[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
     }
-    if (tid == 0) GPROF(3);
   }
   tc_fence_before();
   __syncwarp();
   cluster_sync_all();                                            // every CTA of the cluster has parked its tile
   if (warp < NDW) {
     // ---------------------------------------------------------------- epilogue 2: add the KS tiles, rank order
-    const int ncol = min(NT, a.B - tok0);
+    const int ncol = GROUPED ? NT : min(NT, a.B - tok0);        // grouped: padding pairs are filtered per column
     const int c_lo = (int)((long long)NT * ks / a.KS), c_hi = (int)((long long)NT * (ks + 1) / a.KS);
     const uint32_t mine = smem_addr(smem);
     const int c_end = min(c_hi, ncol);
@@ -438,7 +345,12 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
             sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
           }
         }
-        const size_t o = (size_t)(tok0 + cc) * a.M + rb * 128 + 4 * lane;
+        long long row = tok0 + cc;
+        if (GROUPED) {                                            // result rows go back to their pair index
+          row = a.sorted[tok0 + cc];
+          if (row < 0 || row >= a.B) continue;
+        }
+        const size_t o = (size_t)row * a.M + rb * 128 + 4 * lane;
         uint2 packed;
         packed.x = pack_bf16(sum.x, sum.y);
         packed.y = pack_bf16(sum.z, sum.w);
@@ -447,7 +359,6 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
       }
     }
   }
-  if (tid == 0) GPROF(4);
   __syncwarp();
   cluster_sync_all();                                            // nobody leaves while a peer still reads its tile
   if (warp == W_MMA) {
@@ -474,17 +385,16 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-struct GemmPlan { int NT, TT, RB, KS, DG, stages, rstages, nmma, bar_off; size_t smem; };
+struct GemmPlan { int NT, TT, RB, KS, stages, rstages, nmma, bar_off; size_t smem; };
 
-template <int DG>
+template <bool GROUPED>
 int gemm_attr() {                                                // once per device: opt in to the large dynamic shared memory
   static bool set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set[dev]) {
-    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemm_kernel<DG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   DG == 1 ? 115712 - 1024 : 220 * 1024),
-                              "st_gemm: shared memory attribute"))
+    if (int e = st::cuda_fail(cudaFuncSetAttribute(gemm_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   220 * 1024), "st_gemm: shared memory attribute"))
       return e;
     set[dev] = true;
   }
@@ -504,7 +414,7 @@ long long resident_ctas(int ks, int NT, size_t smem, int sms) {
     int n = 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(ks * sms));
-    cfg.blockDim = dim3(Roles<2>::THREADS);
+    cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -513,13 +423,39 @@ long long resident_ctas(int ks, int NT, size_t smem, int sms) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (gemm_attr<2>() != 0 || cudaOccupancyMaxActiveClusters(&n, gemm_kernel<2>, &cfg) != cudaSuccess || n <= 0) {
+    if (gemm_attr<false>() != 0 || cudaOccupancyMaxActiveClusters(&n, gemm_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
       (void)cudaGetLastError();
       n = sms / ks;                                              // no answer (no device): assume perfect packing
     }
     cache[dev][ks][ti] = n;
   }
   return (long long)cache[dev][ks][ti] * ks;
+}
+
+// rings and issuers for a token tile of NT
+void gemm_rings(GemmPlan& p) {
+  const size_t stage = A_TILE + (size_t)p.NT * 128;
+  const size_t stg = (size_t)p.NT * 128 * 4;                      // the parked accumulator tile reuses the rings
+  // tile stages (decoded weight tile + activation tile): enough to cover the L2 latency of the activation loads; the
+  // rest of the shared memory goes to the record ring, which covers the HBM latency
+  p.stages = p.NT >= 256 ? 3 : 4;
+  p.rstages = (int)((212 * 1024 - p.stages * stage) / RAW_SLOT);
+  if (p.rstages > 12) p.rstages = 12;
+  // The two decode groups alternate k-tiles.  A decode warp waits for the fill of a record slot by the parity of that
+  // slot's use count, and an mbarrier tells only the current phase from the previous one, so a waiter must never be
+  // two fills ahead.  With an even slot count every slot belongs to one group, whose own program order guarantees
+  // that; with an odd count the groups share slots, and a group that runs ahead while a bulk copy of the other
+  // group's k-tile is still in flight passes its wait on the stale phase, reads old records and releases the slot a
+  // second time.  So: always an even number of record slots.  (Tile stages may be odd: their waits are on the
+  // previous use of a stage.)
+  p.rstages &= ~1;
+  // two MMA issuers need every tile stage owned by one decode group as well: an even count of stages
+  p.nmma = (p.stages % 2 == 0 && p.rstages >= 4) ? 2 : 1;
+  size_t ring = (size_t)p.stages * stage + (size_t)p.rstages * RAW_SLOT;
+  ring = (ring + 15) & ~(size_t)15;
+  if (ring < stg) ring = stg;
+  p.bar_off = (int)ring;
+  p.smem = ring + 1024 /* alignment slack */ + 512 /* barriers */;
 }
 
 GemmPlan gemm_plan(long long M, long long N, long long B) {
@@ -529,68 +465,31 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   p.RB = (int)(M / 128);
   const int NG = (int)(N / 64), sms = st::sm_count();
   const long long units = (long long)p.RB * p.TT;
-  // One CTA of two decode groups per SM.  STATETREE_GEMM_DG=1 (tuning aid) runs two CTAs of one group each per SM for
-  // the 64- and 128-token tiles instead; measured slower for every shape (12288 x 4096 at batch 64: 43.7 vs 31.7 us):
-  // twice the k-split halves every CTA's main loop while its start-up and epilogue stay.
-  static int forced_dg = -1;
-  if (forced_dg < 0) { const char* v = getenv("STATETREE_GEMM_DG"); forced_dg = v ? atoi(v) : 0; }
-  p.DG = (forced_dg == 1 && p.NT < 256) ? 1 : 2;
-  const size_t stage = A_TILE + (size_t)p.NT * 128;
-  const size_t stg = (size_t)p.NT * 128 * 4;                    // the parked accumulator tile reuses the rings
-  if (p.DG == 1) {
-    // half an SM: two tile stages (decode of k-tile i + 1 runs under the MMAs of k-tile i), the rest record slots
-    const size_t budget = 115712 - 1024 - 512;
-    p.stages = 2;
-    p.rstages = (int)((budget - p.stages * stage) / RAW_SLOT);
-    if (p.rstages > 8) p.rstages = 8;
-    p.nmma = 1;
-  } else {
-    // tile stages (decoded weight tile + activation tile): enough to cover the L2 latency of the activation loads;
-    // the rest of the shared memory goes to the record ring, which covers the HBM latency
-    p.stages = p.NT >= 256 ? 3 : 4;
-    static int forced = -1;                                      // STATETREE_GEMM_STAGES: tile stages (tuning aid)
-    if (forced < 0) { const char* v = getenv("STATETREE_GEMM_STAGES"); forced = v ? atoi(v) : 0; }
-    if (forced >= 2) {
-      p.stages = forced;
-      while (p.stages > 2 && (size_t)p.stages * stage + 3 * (size_t)RAW_SLOT > 212 * 1024) --p.stages;
-    }
-    p.rstages = (int)((212 * 1024 - p.stages * stage) / RAW_SLOT);
-    if (p.rstages > 12) p.rstages = 12;
-    // two MMA issuers need every stage and record slot owned by one decode group: even counts of both
-    p.nmma = (p.stages % 2 == 0 && p.rstages >= 4) ? 2 : 1;
-    if (p.nmma == 2) p.rstages &= ~1;
-  }
-  size_t ring = (size_t)p.stages * stage + (size_t)p.rstages * RAW_SLOT;
-  ring = (ring + 15) & ~(size_t)15;
-  if (ring < stg) ring = stg;
-  p.bar_off = (int)ring;
-  p.smem = ring + 1024 /* alignment slack */ + 512 /* barriers */;
+  gemm_rings(p);
   // split of the k range = cluster size (<= 8): fill the CTA slots, but every extra split costs an accumulator tile
-  // of distributed-shared-memory traffic in the epilogue
-  // one wave only: a second wave pays the start-up and the epilogue again (measured: 288 CTAs in two waves took 72 us
-  // where 96 CTAs in one take ~45), so among the splits whose clusters are all resident at once take the one that
-  // fills the SMs best
+  // of distributed-shared-memory traffic in the epilogue, and a second wave pays the start-up and the epilogue again:
+  // among the splits whose clusters are all resident at once take the one that fills the SMs best
   int best = 1;
   double best_score = -1.0;
   const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 8 ? 8 : NG / 4);
   for (int ks = 1; ks <= ksmax; ++ks) {
     const long long ctas = units * ks;
-    const long long slots = p.DG == 1 ? 2ll * sms : resident_ctas(ks, p.NT, p.smem, sms);
+    const long long slots = resident_ctas(ks, p.NT, p.smem, sms);
     if (ctas > slots && ks > 1) continue;
     const long long waves = (ctas + slots - 1) / slots;
-    const double score = (double)ctas / (double)(waves * sms * (p.DG == 1 ? 2 : 1)) - 0.01 * ks * p.NT / 256.0;
+    const double score = (double)ctas / (double)(waves * sms) - 0.01 * ks * p.NT / 256.0;
     if (score > best_score + 1e-9) { best_score = score; best = ks; }
   }
   p.KS = best;
   return p;
 }
 
-template <int DG>
+template <bool GROUPED>
 int gemm_launch(const GemmPlan& p, const GemmArgs& a, const CUtensorMap& xmap, const CUtensorMap& wmap, cudaStream_t stream) {
-  if (int e = gemm_attr<DG>()) return e;
+  if (int e = gemm_attr<GROUPED>()) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(p.RB * p.TT * p.KS));
-  cfg.blockDim = dim3(Roles<DG>::THREADS);
+  cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = p.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -602,14 +501,42 @@ int gemm_launch(const GemmPlan& p, const GemmArgs& a, const CUtensorMap& xmap, c
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = st::pdl_enabled() ? 2 : 1;
-  return st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel<DG>, a, xmap, wmap), "st_gemm launch");
+  return st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel<GROUPED>, a, xmap, wmap), GROUPED ? "st_moe_group_gemm launch" : "st_gemm launch");
 }
-}  // namespace
 
-#ifdef ST_PROF
-extern "C" void st_debug_set_gemm_prof(long long* buf) { g_gemm_prof = buf; }
-extern "C" void st_debug_set_gemm_diag(int d) { g_gemm_diag = d; }
-#endif
+// activations [rows, N] BF16 as 64-column x NT-row boxes with the 128-byte swizzle
+int make_xmap(CUtensorMap* map, const void* X, long long rows, long long N, int NT, const char* who) {
+  EncodeTiledFn enc = encode_fn();
+  ST_REQUIRE(enc != nullptr, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)NT};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult cr = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(X), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  ST_REQUIRE(cr == CUDA_SUCCESS, "%s: cuTensorMapEncodeTiled failed (%d)", who, (int)cr);
+  return 0;
+}
+
+// a tree [M/16][N/64][1552 B] as 194 x u64 rows, boxes of eight row tiles of one column group
+int make_wmap(CUtensorMap* map, const void* tree, long long M, long long N, const char* who) {
+  EncodeTiledFn enc = encode_fn();
+  ST_REQUIRE(enc != nullptr, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+  const cuuint64_t wd[3] = {194u, (cuuint64_t)(N / 64), (cuuint64_t)(M / 16)};
+  const cuuint64_t wst[2] = {(cuuint64_t)REC, (cuuint64_t)(N / 64) * REC};
+  const cuuint32_t wbox[3] = {194u, 1u, 8u};
+  const cuuint32_t we[3] = {1u, 1u, 1u};
+  const CUresult wr = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(tree), wd, wst, wbox, we,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  ST_REQUIRE(wr == CUDA_SUCCESS, "%s: cuTensorMapEncodeTiled (tree) failed (%d)", who, (int)wr);
+  return 0;
+}
+
+// instruction descriptor: D fp32, A and B bf16, both K-major, N = NT, M = 128
+uint32_t mma_idesc(int NT) { return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24); }
+}  // namespace
 
 extern "C" int64_t st_gemm_workspace_bytes(int64_t M, int64_t N, int64_t B) {
   if (M <= 0 || N <= 0 || M % 128 || N % 64 || B < 1) return -1;
@@ -626,38 +553,65 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   const GemmPlan p = gemm_plan(M, N, B);
   (void)ws; (void)ws_bytes;
   ST_REQUIRE((long long)p.RB * p.TT * p.KS < (1ll << 31), "st_gemm: grid too large");
-  EncodeTiledFn enc = encode_fn();
-  ST_REQUIRE(enc != nullptr, "st_gemm: cuTensorMapEncodeTiled is not available from the driver");
-  CUtensorMap xmap;
-  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)B};
-  const cuuint64_t strides[1] = {(cuuint64_t)N * 2};
-  const cuuint32_t box[2] = {64u, (cuuint32_t)p.NT};
-  const cuuint32_t estr[2] = {1u, 1u};
-  const CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(X), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  ST_REQUIRE(cr == CUDA_SUCCESS, "st_gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
-  CUtensorMap wmap;
-  {
-    const cuuint64_t wd[3] = {194u, (cuuint64_t)(N / 64), (cuuint64_t)(M / 16)};
-    const cuuint64_t wst[2] = {(cuuint64_t)REC, (cuuint64_t)(N / 64) * REC};
-    const cuuint32_t wbox[3] = {194u, 1u, 8u};
-    const cuuint32_t we[3] = {1u, 1u, 1u};
-    const CUresult wr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(tree), wd, wst, wbox, we,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    ST_REQUIRE(wr == CUDA_SUCCESS, "st_gemm: cuTensorMapEncodeTiled (tree) failed (%d)", (int)wr);
-  }
-  GemmArgs a;
-  a.tree = (const uint8_t*)tree; a.eo = eo; a.el = el; a.Y = (uint16_t*)Y; a.Yf = Yf32; a.ws = (float*)ws; a.cnt = cnt;
+  CUtensorMap xmap, wmap;
+  if (int e = make_xmap(&xmap, X, B, N, p.NT, "st_gemm")) return e;
+  if (int e = make_wmap(&wmap, tree, M, N, "st_gemm")) return e;
+  GemmArgs a = {};
+  a.tree = (const uint8_t*)tree; a.eo = eo; a.el = el; a.Y = (uint16_t*)Y; a.Yf = Yf32;
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "st_gemm: no device status word");
   a.M = M; a.N = N; a.B = (int)B; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = p.KS; a.RB = p.RB; a.TT = p.TT;
   a.stages = p.stages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
-#ifdef ST_PROF
-  a.prof = g_gemm_prof; a.diag = g_gemm_diag;
-#endif
-  // instruction descriptor: D fp32, A and B bf16, both K-major, N = NT, M = 128
-  a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-  return p.DG == 1 ? gemm_launch<1>(p, a, xmap, wmap, (cudaStream_t)stream) : gemm_launch<2>(p, a, xmap, wmap, (cudaStream_t)stream);
+  a.idesc = mma_idesc(p.NT);
+  return gemm_launch<false>(p, a, xmap, wmap, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------- grouped (MoE)
+extern "C" int64_t st_moe_tensor_map_bytes(void) { return (int64_t)sizeof(CUtensorMap); }
+
+extern "C" int st_moe_tensor_maps(const int64_t* trees_host, int64_t E, int64_t M, int64_t N, void* maps_dev,
+                                  void* stream) {
+  ST_REQUIRE(E >= 1 && E <= 4096 && M > 0 && N > 0 && M % 128 == 0 && N % 64 == 0,
+             "st_moe_tensor_maps: 1..4096 experts of M %% 128 == 0 rows and N %% 64 == 0 columns");
+  ST_REQUIRE(trees_host && maps_dev && ((uintptr_t)maps_dev & 63u) == 0, "st_moe_tensor_maps: null or unaligned pointer");
+  static thread_local CUtensorMap staging[4096];
+  for (int64_t e = 0; e < E; ++e) {
+    const void* tree = reinterpret_cast<const void*>(trees_host[e]);
+    ST_REQUIRE(tree != nullptr && st::aligned16(tree), "st_moe_tensor_maps: tree %lld is null or unaligned", (long long)e);
+    if (int r = make_wmap(&staging[e], tree, M, N, "st_moe_tensor_maps")) return r;
+  }
+  // pageable source: the copy is staged by the driver before the call returns, so `staging` may be reused at once
+  return st::cuda_fail(cudaMemcpyAsync(maps_dev, staging, (size_t)E * sizeof(CUtensorMap), cudaMemcpyHostToDevice,
+                                       (cudaStream_t)stream), "st_moe_tensor_maps: copy");
+}
+
+extern "C" int st_moe_group_gemm(const void* maps, const int64_t* eop, const int64_t* elp, int64_t E, const void* Xg,
+                                 const int32_t* sorted, const int32_t* bexp, const int32_t* npost, int64_t nblk,
+                                 int64_t bs, void* Y, float* Yf32, int64_t S, int64_t M, int64_t N, void* stream) {
+  ST_REQUIRE(M > 0 && N > 0 && M % 128 == 0 && N % 64 == 0, "st_moe_group_gemm: M %% 128 and N %% 64 must be 0");
+  ST_REQUIRE(bs == 64 || bs == 128, "st_moe_group_gemm: block size must be 64 or 128 (got %lld)", (long long)bs);
+  ST_REQUIRE(E >= 1 && S >= 0 && nblk >= 0, "st_moe_group_gemm: sizes");
+  if (S == 0 || nblk == 0) return 0;
+  ST_REQUIRE(maps && eop && elp && Xg && sorted && bexp && npost && Y, "st_moe_group_gemm: null pointer");
+  ST_REQUIRE(((uintptr_t)maps & 63u) == 0 && st::aligned16(Xg), "st_moe_group_gemm: maps 64-byte, Xg 16-byte aligned");
+  GemmPlan p;
+  p.NT = (int)bs;
+  p.TT = (int)nblk;
+  p.RB = (int)(M / 128);
+  p.KS = 1;
+  gemm_rings(p);
+  ST_REQUIRE((long long)p.RB * p.TT < (1ll << 31), "st_moe_group_gemm: grid too large");
+  CUtensorMap xmap, unused;
+  if (int e = make_xmap(&xmap, Xg, nblk * bs, N, p.NT, "st_moe_group_gemm")) return e;
+  memset(&unused, 0, sizeof(unused));
+  GemmArgs a = {};
+  a.Y = (uint16_t*)Y; a.Yf = Yf32;
+  a.maps = reinterpret_cast<const CUtensorMap*>(maps); a.eop = (const long long*)eop; a.elp = (const long long*)elp;
+  a.sorted = sorted; a.bexp = bexp; a.npost = npost; a.E = (int)E;
+  a.status = st::status_ptr();
+  ST_REQUIRE(a.status != nullptr, "st_moe_group_gemm: no device status word");
+  a.M = M; a.N = N; a.B = (int)S; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = 1; a.RB = p.RB; a.TT = p.TT;
+  a.stages = p.stages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
+  a.idesc = mma_idesc(p.NT);
+  return gemm_launch<true>(p, a, xmap, unused, (cudaStream_t)stream);
 }

@@ -67,16 +67,17 @@ __global__ void __launch_bounds__(256) silu_mul_vec_kernel(const uint4* __restri
   }
   act[s * I8 + c] = make_uint4(o[0], o[1], o[2], o[3]);
 }
-// Groups the S (token, expert) pairs by expert in blocks of 8 (the layout vLLM's moe_align_block_size produces and
-// the grouped expert kernel consumes): sorted[nblk * 8] holds pair indices, expert-major, original order inside an
-// expert, every expert's run padded to a multiple of 8 with the value S; bexp[b] = expert of block b; npost = entries
+// Groups the S (token, expert) pairs by expert in blocks of bs (8 for the grouped GEMV, 64 / 128 for the grouped
+// tcgen05 GEMM; the layout vLLM's moe_align_block_size produces and
+// the grouped expert kernels consume): sorted[nblk * bs] holds pair indices, expert-major, original order inside an
+// expert, every expert's run padded to a multiple of bs with the value S; bexp[b] = expert of block b; npost = entries
 // in use.  One CTA does the whole job in shared memory: histogram, padded prefix sum, one warp per expert placing its
 // pairs in order with ballots, a binary search per block.  Expert ids outside [0, E) count as E - 1 / 0 (clamped).
 constexpr int ALIGN_MAX_E = 1024;
 template <bool IDS64>
 __global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict__ ids_, int S, int E, int used_bins,
-                                                         int nblk, int* __restrict__ sorted, int* __restrict__ bexp,
-                                                         int* __restrict__ npost) {
+                                                         int nblk, int bs, int* __restrict__ sorted,
+                                                         int* __restrict__ bexp, int* __restrict__ npost) {
   st::pdl_wait();
   st::pdl_launch_dependents();
   __shared__ int cnt[ALIGN_MAX_E], end_[ALIGN_MAX_E], wsum[32];
@@ -86,12 +87,12 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict_
     return (int)(v < 0 ? 0 : (v >= E ? E - 1 : v));
   };
   for (int e = tid; e < E; e += 1024) cnt[e] = 0;
-  for (int i = tid; i < nblk * 8; i += 1024) sorted[i] = S;                // padding value
+  for (int i = tid; i < nblk * bs; i += 1024) sorted[i] = S;               // padding value
   __syncthreads();
   for (int i = tid; i < S; i += 1024) atomicAdd(&cnt[id_of(i)], 1);
   __syncthreads();
   // inclusive prefix sum of the padded counts: thread e < E (E <= 1024), warp scans + a scan of the warp totals
-  int room = tid < E ? (cnt[tid] + 7) / 8 * 8 : 0;
+  int room = tid < E ? (cnt[tid] + bs - 1) / bs * bs : 0;
   int v = room;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict_
   // placement: warp w takes experts w, w + 32, ...; pairs in original order (ballot prefix inside each 32-pair chunk)
   for (int e = warp; e < E; e += 32) {
     if (cnt[e] == 0) continue;
-    int at = end_[e] - (cnt[e] + 7) / 8 * 8;
+    int at = end_[e] - (cnt[e] + bs - 1) / bs * bs;
     for (int base = 0; base < S; base += 32) {
       const int i = base + lane;
       const bool hit = i < S && id_of(i) == e;
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict_
   }
   // expert of every block: first expert whose end lies beyond the block's first slot (clamped for the unused tail)
   for (int b = tid; b < nblk; b += 1024) {
-    const int slot = b * 8;
+    const int slot = b * bs;
     int lo = 0, hi = E;
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
@@ -136,17 +137,46 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const void* __restrict_
   }
   if (tid == 0) npost[0] = end_[used_bins - 1];                            // entries of the first used_bins experts
 }
+
+// Xg[i, :] = X[sorted[i] / xdiv, :] for the used entries of sorted (padding entries are skipped: their columns of the
+// grouped product are never stored).  One warp per row, 16-byte vectors.
+__global__ void __launch_bounds__(256) moe_gather_kernel(const uint4* __restrict__ X, const int* __restrict__ sorted,
+                                                         const int* __restrict__ npost, int S, int xdiv, int n16,
+                                                         long long rows, uint4* __restrict__ Xg) {
+  st::pdl_wait();
+  st::pdl_launch_dependents();
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows || r >= npost[0]) return;
+  const int src = sorted[r];
+  if (src < 0 || src >= S) return;
+  const uint4* in = X + (size_t)(src / xdiv) * n16;
+  uint4* out = Xg + (size_t)r * n16;
+  for (int c = threadIdx.x & 31; c < n16; c += 32) out[c] = in[c];
+}
 }  // namespace
 
-extern "C" int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int64_t used_bins, int32_t* sorted,
-                            int32_t* bexp, int32_t* npost, int64_t nblk, void* stream) {
+extern "C" int st_moe_align(const void* ids, int ids64, int64_t S, int64_t E, int64_t used_bins, int64_t bs,
+                            int32_t* sorted, int32_t* bexp, int32_t* npost, int64_t nblk, void* stream) {
   ST_REQUIRE(S >= 1 && S <= (1 << 20) && E >= 1 && E <= ALIGN_MAX_E, "st_moe_align: 1..%d experts, up to 2^20 pairs",
              ALIGN_MAX_E);
-  ST_REQUIRE(nblk >= S / 8 + (S < E ? S : E) && nblk * 8 < (1ll << 31), "st_moe_align: nblk must cover S / 8 + min(S, E) blocks");
+  ST_REQUIRE(bs >= 1 && bs <= 1024, "st_moe_align: block size in [1, 1024]");
+  ST_REQUIRE(nblk >= S / bs + (S < E ? S : E) && nblk * bs < (1ll << 31),
+             "st_moe_align: nblk must cover S / bs + min(S, E) blocks");
   ST_REQUIRE(used_bins >= 1 && used_bins <= E, "st_moe_align: used_bins must be in [1, E]");
   ST_REQUIRE(ids && sorted && bexp && npost, "st_moe_align: null pointer");
   return st::launch("st_moe_align launch", ids64 ? moe_align_kernel<true> : moe_align_kernel<false>, dim3(1), dim3(1024), 0,
-                    (cudaStream_t)stream, ids, (int)S, (int)E, (int)used_bins, (int)nblk, (int*)sorted, (int*)bexp, (int*)npost);
+                    (cudaStream_t)stream, ids, (int)S, (int)E, (int)used_bins, (int)nblk, (int)bs, (int*)sorted, (int*)bexp,
+                    (int*)npost);
+}
+
+extern "C" int st_moe_gather(const void* X, const int32_t* sorted, const int32_t* npost, int64_t rows, int64_t S,
+                             int64_t xdiv, int64_t N, void* Xg, void* stream) {
+  ST_REQUIRE(rows >= 0 && S >= 0 && xdiv >= 1 && N > 0 && N % 8 == 0, "st_moe_gather: sizes (N %% 8 == 0)");
+  if (rows == 0 || S == 0) return 0;
+  ST_REQUIRE(X && sorted && npost && Xg && st::aligned16(X) && st::aligned16(Xg), "st_moe_gather: null or unaligned pointer");
+  return st::launch("st_moe_gather launch", moe_gather_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0,
+                    (cudaStream_t)stream, (const uint4*)X, sorted, npost, (int)S, (int)xdiv, (int)(N / 8), (long long)rows,
+                    (uint4*)Xg);
 }
 
 extern "C" int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H,

@@ -13,6 +13,9 @@ from .linear import TreeLinear, _state
 from .ops import ext
 
 SLOT_MAX = 32                       # (token, expert) pairs up to which the ungrouped kernel runs
+GEMM_PAIRS_PER_EXPERT = 8           # average pairs per expert from which the grouped tcgen05 GEMM takes over: the
+#                                     grouped GEMV re-reads an expert's records for every 8 of its pairs, the GEMM
+#                                     reads them once per 64 (128 from 64 pairs per expert on)
 
 
 def _aligned(x):
@@ -69,13 +72,13 @@ def moe_align(ids, E, bs=8, used_bins=None):
     ids = ids.reshape(-1)
     S, dev = ids.numel(), ids.device
     nblk = S // bs + min(S, E) + 1
-    if (ALIGN_KERNEL and ids.is_cuda and bs == 8 and 1 <= S <= (1 << 16) and E <= 1024
+    if (ALIGN_KERNEL and ids.is_cuda and 1 <= S <= (1 << 20) and E <= 1024
             and ids.dtype in (torch.int64, torch.int32)):
         # one CTA of the kernel library does the whole grouping (the torch formulation below is ~20 small launches)
         sorted_ids = torch.empty(nblk * bs, dtype=torch.int32, device=dev)
         bexp = torch.empty(nblk, dtype=torch.int32, device=dev)
         npost = torch.empty(1, dtype=torch.int32, device=dev)
-        ext().moe_align(ids.contiguous(), E, E if used_bins is None else used_bins, sorted_ids, bexp, npost)
+        ext().moe_align(ids.contiguous(), E, E if used_bins is None else used_bins, sorted_ids, bexp, npost, bs)
         return sorted_ids, bexp, npost
     return _moe_align_torch(ids, E, bs, used_bins)
 
@@ -118,6 +121,22 @@ def moe_group_gemv(tables, x, aligned, S, M, xdiv, zero=False):
     return y
 
 
+def moe_group_gemm(tables, maps, x, aligned, bs, S, M, xdiv, zero=False, yf32=None):
+    """The same product through the grouped fused decode + tcgen05 GEMM: aligned = moe_align(ids, E, bs), bs = 64 or
+    128; maps = ext().moe_tensor_maps(trees, M, N).  The activation rows are first gathered into block order (one
+    small kernel), each CTA then multiplies one block of pairs by 128 rows of its expert's matrix."""
+    sorted_ids, bexp, npost = (t.contiguous() for t in aligned)
+    x = _aligned(x)
+    y = (torch.zeros if zero else torch.empty)(S, M, dtype=torch.bfloat16, device=x.device)
+    if S == 0:
+        return y
+    E = ext()
+    xg = torch.empty(sorted_ids.numel(), x.shape[1], dtype=torch.bfloat16, device=x.device)
+    E.moe_gather(x, sorted_ids, npost, S, xdiv, xg)
+    E.gtt(maps, tables[1], tables[3], xg, sorted_ids, bexp, npost, bs, y, yf32)
+    return y
+
+
 def moe_wsum(y, w):
     """out[t] = sum_j w[t, j] y[t * k + j] (fp32 sum in expert order, BF16 out); w [T, k] float32 or BF16"""
     T, K = w.shape
@@ -147,6 +166,7 @@ class TreeExperts(nn.Module):
         self.num_experts = len(w13)
         self.hidden, self.inter = w13[0].in_features, w13[0].out_features // 2
         self._tabs = None
+        self._maps = None
 
     @classmethod
     @torch.no_grad()
@@ -159,6 +179,17 @@ class TreeExperts(nn.Module):
         if self._tabs is None:
             self._tabs = (expert_tables(list(self.w13)), expert_tables(list(self.w2)))
         return self._tabs
+
+    def tensor_maps(self):
+        """weight tensor maps of the grouped tcgen05 GEMM, or None when the shapes do not fit it (rows % 128)"""
+        if self._maps is None:
+            if (2 * self.inter) % 128 or self.hidden % 128:
+                self._maps = False
+            else:
+                E = ext()
+                self._maps = (E.moe_tensor_maps([m.tree for m in self.w13], 2 * self.inter, self.hidden),
+                              E.moe_tensor_maps([m.tree for m in self.w2], self.hidden, self.inter))
+        return self._maps or None
 
     def record_bytes(self):
         return sum(m.record_bytes() for m in self.w13) + sum(m.record_bytes() for m in self.w2)
@@ -187,6 +218,12 @@ class TreeExperts(nn.Module):
         if S <= SLOT_MAX:
             gu = moe_gemv(t13, x, ids, 2 * self.inter, K)
             y = moe_gemv(t2, silu_mul(gu), ids, self.hidden, 1)
+        elif S >= GEMM_PAIRS_PER_EXPERT * self.num_experts and self.tensor_maps() is not None:
+            bs = 128 if S >= 64 * self.num_experts else 64
+            m13, m2 = self.tensor_maps()
+            al = moe_align(ids, self.num_experts, bs)
+            gu = moe_group_gemm(t13, m13, x, al, bs, S, 2 * self.inter, K)
+            y = moe_group_gemm(t2, m2, silu_mul(gu), al, bs, S, self.hidden, 1)
         else:
             al = moe_align(ids, self.num_experts, 8)
             gu = moe_group_gemv(t13, x, al, S, 2 * self.inter, K)

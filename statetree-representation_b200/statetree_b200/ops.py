@@ -45,7 +45,11 @@ _SIGNATURES = {
     "st_gemv_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_rope_kv_append": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _dbl, _vp, _vp, _i64,
                                  _vp, _i64, _vp, _vp]),
-    "st_moe_align": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "st_moe_align": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "st_moe_tensor_map_bytes": (_i64, []),
+    "st_moe_tensor_maps": (_int, [_vp, _i64, _i64, _i64, _vp, _vp]),
+    "st_moe_gather": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "st_moe_group_gemm": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
     "st_comm_bytes": (_i64, []),
     "st_comm_alloc": (_int, [ctypes.POINTER(ctypes.c_void_p)]),
     "st_comm_free": (_int, [_vp]),
@@ -194,10 +198,38 @@ class _Weights:
                                         WS.numel() * WS.element_size(), _ptr(CNT), _stream(T)))
 
     @staticmethod
-    def moe_align(ids, E, used_bins, sorted_ids, bexp, npost):
+    def moe_align(ids, E, used_bins, sorted_ids, bexp, npost, bs=8):
         with _ctx(ids):
-            _check(lib().st_moe_align(_ptr(ids), 1 if ids.dtype == torch.int64 else 0, ids.numel(), E, used_bins,
+            _check(lib().st_moe_align(_ptr(ids), 1 if ids.dtype == torch.int64 else 0, ids.numel(), E, used_bins, bs,
                                       _ptr(sorted_ids), _ptr(bexp), _ptr(npost), bexp.numel(), _stream(ids)))
+
+    @staticmethod
+    def moe_tensor_maps(trees, M, N):
+        """uint8 device buffer holding one weight tensor map per expert tree (built on the host, copied once)"""
+        E = len(trees)
+        nb = int(lib().st_moe_tensor_map_bytes())
+        dev = trees[0].device
+        maps = torch.empty(E * nb + 64, dtype=torch.uint8, device=dev)
+        maps = maps[(-maps.data_ptr()) % 64:][:E * nb]                       # 64-byte aligned view
+        host = (ctypes.c_int64 * E)(*[t.data_ptr() for t in trees])
+        with _ctx(trees[0]):
+            _check(lib().st_moe_tensor_maps(host, E, M, N, _ptr(maps), _stream(trees[0])))
+        return maps
+
+    @staticmethod
+    def moe_gather(X, sorted_ids, npost, S, xdiv, Xg):
+        with _ctx(X):
+            _check(lib().st_moe_gather(_ptr(X), _ptr(sorted_ids), _ptr(npost), Xg.shape[0], S, xdiv, X.shape[1], _ptr(Xg),
+                                       _stream(X)))
+
+    @staticmethod
+    def gtt(maps, EOP, ELP, Xg, sorted_ids, bexp, npost, bs, Y, Yf32=None):
+        """grouped fused decode + tcgen05 GEMM (the place of the reference's `_C.gtt`)"""
+        S, M = Y.shape
+        with _ctx(Xg):
+            _check(lib().st_moe_group_gemm(_ptr(maps), _ptr(EOP), _ptr(ELP), EOP.numel(), _ptr(Xg), _ptr(sorted_ids),
+                                           _ptr(bexp), _ptr(npost), bexp.numel(), bs, _ptr(Y), _ptr(Yf32), S, M,
+                                           Xg.shape[1], _stream(Xg)))
 
     @staticmethod
     def wsum(Y, W, out):

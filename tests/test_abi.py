@@ -44,8 +44,10 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert L.st_allreduce(None, 0, 1, None, None, 8, None) != 0
     assert b"ranks" in L.st_last_error()
     assert L.st_allreduce_add_rmsnorm(None, 3, 2, None, None, None, None, 1, 4096, 1e-6, None) != 0
-    assert L.st_moe_align(None, 1, 0, 8, 8, None, None, None, 4, None) != 0
-    assert L.st_moe_align(None, 1, 8, 2048, 2048, None, None, None, 16, None) != 0 and b"experts" in L.st_last_error()
+    assert L.st_moe_align(None, 1, 0, 8, 8, 8, None, None, None, 4, None) != 0
+    assert L.st_moe_align(None, 1, 8, 2048, 2048, 8, None, None, None, 16, None) != 0 and b"experts" in L.st_last_error()
+    assert L.st_moe_group_gemm(None, None, None, 4, None, None, None, None, 4, 32, None, None, 8, 128, 64, None) != 0
+    assert b"block size" in L.st_last_error()
 
 
 def test_cpu_tensors_are_rejected():

@@ -132,3 +132,69 @@ def test_moe_align_kernel_matches_torch_formulation():
             want = _moe_align_torch(ids, E, 8, used)
             for g, w, name in zip(got, want, ("sorted_ids", "bexp", "npost")):
                 assert g.dtype == w.dtype and torch.equal(g, w), (S, E, used, name)
+
+
+@pytest.mark.parametrize("bs", [64, 128])
+def test_grouped_tcgen05_gemm_matches_fp64(bs):
+    """the grouped fused decode + tcgen05 GEMM against fp64, after the reference's gtt test (tests/test_moe.py:282-315):
+    escapes (one expert with a fifth of its weights escaping), an expert without pairs, experts with several blocks,
+    padded blocks, one row per token (xdiv = k) and one row per pair, one-hot rows read exact weights back, other
+    ranks' blocks skipped, repeat runs bit-identical"""
+    from statetree_b200.experts import expert_tables, moe_align, moe_group_gemm, moe_group_gemv
+    from statetree_b200.ops import ext
+    E, M, N = 12, 256, 320
+    Ws, mods = _experts(E, M, N, 5, heavy=3)
+    tabs = expert_tables(mods)
+    maps = ext().moe_tensor_maps([m.tree for m in mods], M, N)
+    Wall = torch.stack([bits_to_torch(W, DEV) for W in Ws]).double()
+    g = torch.Generator(DEV).manual_seed(bs)
+    for S, K in ((5, 1), (96, 4), (1000, 4), (777, 1)):
+        ids = torch.randint(0, E - 1, (S,), device=DEV, generator=g)       # expert E - 1 gets no pairs
+        ids[:S // 3] = 7                                                    # one expert with several blocks
+        ids[S // 3:S // 3 + min(S, 50)] = 3                                 # the escape-heavy one
+        x = torch.randn(-(-S // K), N, device=DEV, generator=g).to(torch.bfloat16)
+        ref = torch.einsum("sn,smn->sm", x.repeat_interleave(K, 0)[:S].double(), Wall[ids])
+        al = moe_align(ids, E, bs)
+        yf = torch.zeros(S, M, dtype=torch.float32, device=DEV)
+        y = moe_group_gemm(tabs, maps, x, al, bs, S, M, K, yf32=yf)
+        assert float((yf.double() - ref).norm() / ref.norm()) < 1e-3, (S, K)           # fp32 accumulators
+        assert torch.equal(y, yf.to(torch.bfloat16)), (S, K)
+        assert float((y.double() - ref).norm() / ref.norm()) < 5e-3, (S, K)
+        assert torch.equal(moe_group_gemm(tabs, maps, x, al, bs, S, M, K), y), (S, K)  # deterministic
+        # other ranks' experts: blocks with a negative expert are skipped, their rows stay as they were
+        bexp = al[1].clone()
+        bexp[bexp % 2 == 1] = -1
+        part = moe_group_gemm(tabs, maps, x, (al[0], bexp, al[2]), bs, S, M, K, zero=True)
+        odd = ids % 2 == 1
+        assert int((part[odd] != 0).sum()) == 0 and torch.equal(part[~odd], y[~odd])
+    # one-hot rows: the exact weights come back, escapes included
+    S = 300
+    ids = torch.randint(0, E, (S,), device=DEV, generator=g)
+    ids[:100] = 3
+    cols = torch.randint(0, N, (S,), device=DEV, generator=g)
+    x = torch.zeros(S, N, device=DEV, dtype=torch.bfloat16)
+    x[torch.arange(S, device=DEV), cols] = 1.0
+    want = torch.stack([bits_to_torch(Ws[int(e)][:, int(c)], DEV) for e, c in zip(ids.tolist(), cols.tolist())])
+    got = moe_group_gemm(tabs, maps, x, moe_align(ids, E, bs), bs, S, M, 1)
+    assert torch.equal(got, want)
+    assert torch.equal(got, moe_group_gemv(tabs, x, moe_align(ids, E, 8), S, M, 1))
+    from statetree_b200 import ops
+    assert ops.device_status() == 0
+
+
+def test_tree_experts_prefill_sized_call_uses_the_grouped_gemm():
+    from statetree_b200 import experts as X
+    E, Hd, I, K = 8, 256, 128, 2
+    g = torch.Generator(DEV).manual_seed(9)
+    gate_up = (torch.randn(E, 2 * I, Hd, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    down = (torch.randn(E, Hd, I, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    te = X.TreeExperts.from_weights(gate_up, down)
+    T = 300                                                                # 600 pairs on 8 experts: the GEMM regime
+    assert T * K >= X.GEMM_PAIRS_PER_EXPERT * E and te.tensor_maps() is not None
+    x = torch.randn(T, Hd, device=DEV, generator=g).to(torch.bfloat16)
+    w, ids = torch.softmax(torch.randn(T, E, device=DEV, generator=g), -1).topk(K, -1)
+    got = te(x, ids, w).double()
+    gu = torch.einsum("tkmh,th->tkm", gate_up[ids].double(), x.double())
+    act = torch.nn.functional.silu(gu[..., :I]) * gu[..., I:]
+    ref = (torch.einsum("tkhi,tki->tkh", down[ids].double(), act) * w.double().unsqueeze(-1)).sum(1)
+    assert float((got - ref).norm() / ref.norm()) < 2e-2
