@@ -186,9 +186,12 @@ int st_rope_kv_append(const void* qkv, int64_t row_stride, const void* wq, const
  * cleared); st_comm_export writes its 64-byte CUDA IPC handle, which the host code sends to the other ranks of the
  * node (any channel); st_comm_import maps a peer's handle and returns a device pointer valid in this process.  The
  * calls then take `bufs`, a host array of `world` device pointers indexed by rank (bufs[rank] = the own buffer).
- * Every rank must make the same sequence of calls with the same sizes.  Waits on peers are bounded (about two
- * seconds); a call that gives up leaves its output unwritten and sets the device status word (st_device_status). */
+ * Every rank must make the same sequence of calls with the same sizes.  Waits on peers are bounded by wall time
+ * (st_comm_set_timeout_ms; 20 s unless set, long enough for a peer held up by a lazy module load or a graph capture);
+ * a call that gives up leaves its output unwritten and sets the device status word: the step's result is then
+ * invalid, so check st_device_status() at the step's sync point and redo the step (or fall back to NCCL). */
 int64_t st_comm_bytes(void);
+int st_comm_set_timeout_ms(int64_t ms);
 int st_comm_alloc(void** buf);
 int st_comm_free(void* buf);
 int st_comm_export(void* buf, void* handle64);

@@ -3,18 +3,21 @@
 // add and RMSNorm that consume it in a decode step.
 //
 // Every rank owns one communication buffer (plain device memory, exported to its peers as a CUDA IPC handle):
-//     flags  uint32 [MAX_RANKS][MAX_CTAS]   flags[p][c] = last epoch in which rank p's CTA c published its slice
+//     flags  uint32 [MAX_RANKS][MAX_CTAS]   flags[p][c] = last epoch in which rank p's CTA c delivered its slice here
 //     epoch  uint32 [MAX_CTAS]              calls made so far, per CTA slot (all ranks make the same calls)
-//     data   2 x MAX_CTAS x SLOT_BYTES      this rank's partial sums: one region per CTA slot, double-buffered by the
-//                                           parity of that slot's epoch (slots advance independently, so a slot's
-//                                           region is only ever touched by the same slot of the other ranks)
-// One call, CTA c of rank r: copy slice c of the local partials into its region of data[epoch & 1]; system-scope fence; store the
-// epoch into flags[r][c] of every peer (remote stores); wait until flags[p][c] of the own buffer reach the epoch for
-// every p (local loads; bounded); add slice c of every rank's data in rank order (remote loads, fp32) and write the
-// BF16 result.  The double buffer makes a second barrier unnecessary: a rank rewrites data[parity] two calls later,
-// after a barrier that every peer enters only when it has finished reading the earlier call.
-// The wait is bounded by wall time (~2 s); when it runs out the kernel records ERR_WAIT_PEER in the device status word
-// and leaves its output unwritten.  The reference has no communication code (vLLM adds NCCL collectives around it).
+//     data   2 x MAX_RANKS x MAX_CTAS x SLOT_BYTES   the partial sums of every rank: one region per (source rank, CTA
+//                                           slot), double-buffered by the parity of that slot's epoch
+// One call, CTA c of rank r: PUSH slice c of the local partials into region (r, c) of every rank's buffer (remote
+// stores; the own copy is a local store), system-scope fence, store the epoch into flags[r][c] of every peer; wait until
+// flags[p][c] of the own buffer reach the epoch for every p (local loads; bounded); add the world copies of slice c in
+// rank order from the OWN buffer (local loads, fp32) and write the BF16 result.  The data crosses NVLink once, as
+// stores, and nobody waits on a remote load.  The double buffer makes a second barrier unnecessary: a rank overwrites
+// region (r, c) of a peer two calls later, after a wait that the peer satisfies only at the start of its next call,
+// when it has finished reading the earlier one.
+// The wait is bounded by wall time (st_comm_set_timeout_ms, 20 s unless set); when it runs out the kernel records
+// ERR_WAIT_PEER in the device status word and leaves its output unwritten: the step's result is then invalid and the
+// host must check st_device_status() before it trusts it.  The reference has no communication code (vLLM adds NCCL
+// collectives around it).
 #include <cuda_runtime.h>
 #include <string.h>
 
@@ -31,8 +34,8 @@ constexpr long long SLOT_BYTES = 16 << 10;                            // per CTA
 constexpr long long MAX_BYTES = MAX_CTAS * SLOT_BYTES;                // per call (1 MiB)
 constexpr size_t OFF_EPOCH = (size_t)MAX_RANKS * MAX_CTAS * 4;
 constexpr size_t OFF_DATA = OFF_EPOCH + MAX_CTAS * 4;                 // 2304: 256-byte aligned
-constexpr size_t COMM_BYTES = OFF_DATA + 2 * (size_t)MAX_BYTES;
-constexpr long long WAIT_NS = 2000000000ll;
+constexpr size_t COMM_BYTES = OFF_DATA + 2 * (size_t)MAX_RANKS * (size_t)MAX_BYTES;
+long long g_wait_ns = 20000000000ll;                                  // st_comm_set_timeout_ms
 
 struct Peers {
   uint8_t* buf[MAX_RANKS];                                            // buf[rank] is the local buffer
@@ -57,14 +60,15 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {           // never s
   return v;
 }
 
-__device__ __forceinline__ uint8_t* slot_data(uint8_t* buf, int half, int cta) {
-  return buf + OFF_DATA + (size_t)half * MAX_BYTES + (size_t)cta * SLOT_BYTES;
+__device__ __forceinline__ uint8_t* slot_data(uint8_t* buf, int half, int src_rank, int cta) {
+  return buf + OFF_DATA + ((size_t)half * MAX_RANKS + src_rank) * MAX_BYTES + (size_t)cta * SLOT_BYTES;
 }
 
-// Publishes the len bytes at src (16-byte units, len <= SLOT_BYTES) as slot `cta` of this call and returns once every
-// rank has published its slot `cta`.  Called by all threads of the CTA; returns the data half to read from, or -1
-// after a timeout.
-__device__ int publish_and_wait(const Peers& P, int rank, int world, const uint8_t* src, size_t len, int cta, int* status) {
+// Delivers the len bytes at src (16-byte units, len <= SLOT_BYTES) as slot `cta` of this call to every rank and returns
+// once every rank's slot `cta` has arrived here.  Called by all threads of the CTA; returns the data half to read from
+// (in the own buffer), or -1 after a timeout.
+__device__ int publish_and_wait(const Peers& P, int rank, int world, const uint8_t* src, size_t len, int cta, int* status,
+                                long long wait_ns) {
   __shared__ uint32_t s_epoch;
   __shared__ int s_ok;
   uint8_t* mine = P.buf[rank];
@@ -76,9 +80,11 @@ __device__ int publish_and_wait(const Peers& P, int rank, int world, const uint8
   }
   __syncthreads();
   const uint32_t epoch = s_epoch;
-  uint8_t* dst = slot_data(mine, (int)(epoch & 1u), cta);
-  for (size_t i = (size_t)threadIdx.x * 16; i < len; i += (size_t)blockDim.x * 16)
-    *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+  const int half = (int)(epoch & 1u);
+  for (size_t i = (size_t)threadIdx.x * 16; i < len; i += (size_t)blockDim.x * 16) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src + i);
+    for (int p = 0; p < world; ++p) *reinterpret_cast<uint4*>(slot_data(P.buf[p], half, rank, cta) + i) = v;
+  }
   __threadfence_system();
   __syncthreads();
   if ((int)threadIdx.x < world) {
@@ -88,7 +94,7 @@ __device__ int publish_and_wait(const Peers& P, int rank, int world, const uint8
     const long long t0 = now_ns();
     // epochs only grow; the signed difference also survives the 32-bit wrap
     while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
-      if (now_ns() - t0 > WAIT_NS) {
+      if (now_ns() - t0 > wait_ns) {
         atomicExch(status, ERR_WAIT_PEER);
         s_ok = 0;
         break;
@@ -96,23 +102,24 @@ __device__ int publish_and_wait(const Peers& P, int rank, int world, const uint8
     }
   }
   __syncthreads();
-  return s_ok ? (int)(epoch & 1u) : -1;
+  return s_ok ? half : -1;
 }
 
 // out = sum over ranks of the BF16 vectors `in` (n elements, a multiple of 8); grid <= MAX_CTAS
 __global__ void __launch_bounds__(256) allreduce_kernel(const Peers P, int rank, int world, const uint16_t* in,
-                                                        uint16_t* out, long long n, int* status) {
+                                                        uint16_t* out, long long n, int* status, long long wait_ns) {
   pdl_wait();
   pdl_launch_dependents();
   const long long vecs = n / 8, per = (vecs + gridDim.x - 1) / gridDim.x;
   const long long v0 = (long long)blockIdx.x * per, v1 = min(vecs, v0 + per);
   const size_t off = (size_t)v0 * 16, len = v1 > v0 ? (size_t)(v1 - v0) * 16 : 0;
-  const int h = publish_and_wait(P, rank, world, reinterpret_cast<const uint8_t*>(in) + off, len, blockIdx.x, status);
+  const int h = publish_and_wait(P, rank, world, reinterpret_cast<const uint8_t*>(in) + off, len, blockIdx.x, status, wait_ns);
+  uint8_t* mine = P.buf[rank];
   if (h < 0) return;
   for (size_t i = (size_t)threadIdx.x * 16; i < len; i += (size_t)blockDim.x * 16) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int p = 0; p < world; ++p) {
-      const uint4 v = ld_peer16(slot_data(P.buf[p], h, blockIdx.x) + i);
+      const uint4 v = ld_peer16(slot_data(mine, h, p, blockIdx.x) + i);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -141,14 +148,16 @@ __device__ __forceinline__ float block_sum(float v, float* part) {
 // all-reduce would); x += delta_sum (BF16 residual stream); out = RMSNorm(x) * w.  cols <= 8192, a multiple of 8.
 __global__ void __launch_bounds__(512) allreduce_add_rmsnorm_kernel(const Peers P, int rank, int world, uint16_t* x,
                                                                     const uint16_t* delta, const uint16_t* w,
-                                                                    uint16_t* out, int cols, float eps, int* status) {
+                                                                    uint16_t* out, int cols, float eps, int* status,
+                                                                    long long wait_ns) {
   pdl_wait();
   pdl_launch_dependents();
   __shared__ float part[16];
   const size_t rowb = (size_t)blockIdx.x * cols * 2;
   const int h = publish_and_wait(P, rank, world, reinterpret_cast<const uint8_t*>(delta) + rowb, (size_t)cols * 2,
-                                 blockIdx.x, status);
+                                 blockIdx.x, status, wait_ns);
   if (h < 0) return;
+  uint8_t* mine = P.buf[rank];
   float f[2][8];
   float ss = 0.f;
 #pragma unroll
@@ -157,7 +166,7 @@ __global__ void __launch_bounds__(512) allreduce_add_rmsnorm_kernel(const Peers 
     if (c < cols) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int p = 0; p < world; ++p) {
-        const uint4 v = ld_peer16(slot_data(P.buf[p], h, blockIdx.x) + (size_t)c * 2);
+        const uint4 v = ld_peer16(slot_data(mine, h, p, blockIdx.x) + (size_t)c * 2);
         const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -215,6 +224,12 @@ int fill_peers(Peers& P, void* const* bufs, int rank, int world, const char* who
 
 extern "C" int64_t st_comm_bytes(void) { return (int64_t)COMM_BYTES; }
 
+extern "C" int st_comm_set_timeout_ms(int64_t ms) {
+  ST_REQUIRE(ms >= 1 && ms <= 3600000, "st_comm_set_timeout_ms: 1 ms .. 1 h");
+  g_wait_ns = ms * 1000000ll;
+  return 0;
+}
+
 extern "C" int st_comm_alloc(void** buf) {
   ST_REQUIRE(buf != nullptr, "st_comm_alloc: null pointer");
   if (int e = st::cuda_fail(cudaMalloc(buf, COMM_BYTES), "st_comm_alloc")) return e;
@@ -254,7 +269,7 @@ extern "C" int st_allreduce(void* const* bufs, int rank, int world, const void* 
   if (ctas > 16) ctas = 16;
   while (((vecs + ctas - 1) / ctas) * 16 > SLOT_BYTES) ++ctas;
   return st::launch("st_allreduce launch", allreduce_kernel, dim3((unsigned)ctas), dim3(256), 0, (cudaStream_t)stream, P,
-                    rank, world, (const uint16_t*)in, (uint16_t*)out, (long long)n, status);
+                    rank, world, (const uint16_t*)in, (uint16_t*)out, (long long)n, status, g_wait_ns);
 }
 
 extern "C" int st_allreduce_add_rmsnorm(void* const* bufs, int rank, int world, void* x, const void* delta, const void* w,
@@ -269,5 +284,5 @@ extern "C" int st_allreduce_add_rmsnorm(void* const* bufs, int rank, int world, 
   ST_REQUIRE(status != nullptr, "st_allreduce_add_rmsnorm: no device status word");
   return st::launch("st_allreduce_add_rmsnorm launch", allreduce_add_rmsnorm_kernel, dim3((unsigned)rows), dim3(512), 0,
                     (cudaStream_t)stream, P, rank, world, (uint16_t*)x, (const uint16_t*)delta, (const uint16_t*)w,
-                    (uint16_t*)out, (int)cols, (float)eps, status);
+                    (uint16_t*)out, (int)cols, (float)eps, status, g_wait_ns);
 }

@@ -206,6 +206,16 @@ class TreeDecoder:
         self.logits = logits
         self.reset()
         torch.cuda.synchronize(self.dev)
+        self._check_status("capture")
+
+    def _check_status(self, where):
+        """a kernel that gave up on a bounded wait (a peer that never arrived) leaves its output unwritten: fail loudly"""
+        from .ops import device_status
+        with torch.cuda.device(self.dev):
+            code = device_status()
+        if code != 0:
+            raise RuntimeError(f"TreeDecoder.{where}: a kernel gave up on a bounded wait (device status {code}); the "
+                               "results of this call are invalid")
 
     def reset(self):
         self.pos_buf.zero_()
@@ -217,6 +227,10 @@ class TreeDecoder:
     def run(self, prompt, n_new, collect=None):
         """prompt [B, P] token ids (teacher-forced one step at a time), then n_new greedy tokens -> [B, n_new].
         collect (optional list): receives the model's prediction after every prompt step (teacher-forced top-1)."""
+        start = int(self.pos_buf.item())
+        if start + prompt.shape[1] + n_new > self.max_len:       # beyond it the page lookup would leave the block table
+            raise ValueError(f"TreeDecoder.run: {prompt.shape[1]} prompt + {n_new} new tokens from position {start} "
+                             f"exceed the cache capacity of {self.max_len} tokens")
         out = []
         for t in range(prompt.shape[1]):
             self.tokens.copy_(prompt[:, t])
@@ -227,4 +241,7 @@ class TreeDecoder:
             self.tokens.copy_(self.next_tok)
             out.append(self.next_tok.clone())
             self.graph.replay()
-        return torch.stack(out, 1)
+        res = torch.stack(out, 1) if out else torch.empty(self.B, 0, dtype=torch.long, device=self.dev)
+        if self.world > 1:
+            self._check_status("run")
+        return res

@@ -91,10 +91,15 @@ class StateTreeKVCache:
         self.bt64 = self.bt32.long()
         self.lens = torch.zeros(batch_size, dtype=torch.int32, device=device)
         self.cum = torch.zeros((), dtype=torch.long, device=device)      # tokens stored (same for every sequence)
+        self._stored = 0                                                  # the same count on the host, for capacity checks
 
     def update(self, layer_idx, key_states, value_states):
         """key/value_states [B, H, T, 128]; positions continue from the GPU-side count; returns the slots used"""
         B, H, T, D = key_states.shape
+        self._stored += T if layer_idx == len(self.layers) - 1 else 0
+        if self._stored + (T if layer_idx != len(self.layers) - 1 else 0) > self.max_len:
+            raise ValueError(f"StateTreeKVCache.update: position {self._stored + T} exceeds the capacity of "
+                             f"{self.max_len} tokens")
         cp = torch.arange(T, device=self.device) + self.cum
         slots = (self.bt64[:B][:, cp // PAGE] * PAGE + (cp % PAGE)).reshape(-1)
         K = key_states.transpose(1, 2).reshape(B * T, H, D)
@@ -110,8 +115,10 @@ class StateTreeKVCache:
     def begin_step(self, B):
         """decode step (one token per sequence): the slots every layer appends at, computed once; lens counts the new
         token.  Graph-safe (positions come from the GPU-side count)."""
-        slots = self.bt64[:B].gather(1, (self.cum // PAGE).expand(B, 1)).view(B) * PAGE + self.cum % PAGE
-        self.lens[:B] = (self.cum + 1).to(torch.int32)
+        page = (self.cum // PAGE).clamp(max=self.max_pages - 1)            # a full cache never indexes past the table:
+        slots = self.bt64[:B].gather(1, page.expand(B, 1)).view(B) * PAGE + self.cum % PAGE
+        slots = torch.where(self.cum < self.max_len, slots, torch.full_like(slots, -1))   # ... the token is dropped
+        self.lens[:B] = (self.cum + 1).clamp(max=self.max_len).to(torch.int32)
         return slots
 
     def end_step(self):
@@ -129,6 +136,7 @@ class StateTreeKVCache:
             layer.check()
 
     def reset(self):
+        self._stored = 0
         self.cum.zero_()
         self.lens.zero_()
         for layer in self.layers:

@@ -51,6 +51,7 @@ _SIGNATURES = {
     "st_moe_gather": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "st_moe_group_gemm": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
     "st_comm_bytes": (_i64, []),
+    "st_comm_set_timeout_ms": (_int, [_i64]),
     "st_comm_alloc": (_int, [ctypes.POINTER(ctypes.c_void_p)]),
     "st_comm_free": (_int, [_vp]),
     "st_comm_export": (_int, [_vp, _vp]),

@@ -40,7 +40,8 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert L.st_gemm(None, None, None, None, None, None, 64, 64, 64, None, 0, None, None) != 0
     assert L.st_gemv_workspace_bytes(100, 64, 1) == -1
     # the exchange entry points check rank / world and sizes before anything touches a GPU
-    assert L.st_comm_bytes() == 8 * 64 * 4 + 64 * 4 + 2 * 64 * 16384
+    assert L.st_comm_bytes() == 8 * 64 * 4 + 64 * 4 + 2 * 8 * 64 * 16384
+    assert L.st_comm_set_timeout_ms(0) != 0
     assert L.st_allreduce(None, 0, 1, None, None, 8, None) != 0
     assert b"ranks" in L.st_last_error()
     assert L.st_allreduce_add_rmsnorm(None, 3, 2, None, None, None, None, 1, 4096, 1e-6, None) != 0

@@ -23,8 +23,8 @@ def test_peer_allreduce_two_gpus():
 
 @pytest.mark.gpu
 def test_wait_on_absent_peer_runs_out_and_reports():
-    """One GPU, a second buffer standing in for a rank that never arrives: the kernel's bounded wait (about two
-    seconds) runs out, the output stays unwritten, the status word says so and the context remains usable."""
+    """One GPU, a second buffer standing in for a rank that never arrives: the kernel's bounded wait (set to 300 ms
+    here) runs out, the output stays unwritten, the status word says so and the context remains usable."""
     import ctypes
     import sys
     sys.path.insert(0, os.path.join(os.path.dirname(HERE), "statetree-representation_b200"))
@@ -32,6 +32,7 @@ def test_wait_on_absent_peer_runs_out_and_reports():
     L = ops.lib()
     torch.cuda.set_device(0)
     assert ops.device_status() == 0
+    ops._check(L.st_comm_set_timeout_ms(300))
     own, absent = ctypes.c_void_p(), ctypes.c_void_p()
     ops._check(L.st_comm_alloc(ctypes.byref(own)))
     ops._check(L.st_comm_alloc(ctypes.byref(absent)))
@@ -47,5 +48,6 @@ def test_wait_on_absent_peer_runs_out_and_reports():
         assert ops.device_status() == 0                              # read-and-clear; the context still works
         assert float((y + y).float().sum()) == 2 * 4096
     finally:
+        ops._check(L.st_comm_set_timeout_ms(20000))
         ops._check(L.st_comm_free(own))
         ops._check(L.st_comm_free(absent))
