@@ -1,12 +1,14 @@
 """TreeLinear / TreeSlice / TreeEmbedding: drop-in modules over the sm_100a kernels, with the buffers and call
-surface of the reference's statetree/linear.py (TreeLinear 595-1018, TreeSlice / TreeEmbedding below it).
+surface of the reference's statetree/linear.py (TreeLinear 595-1018, TreeSlice 1021-1036, TreeEmbedding 1039-1067,
+torch.compile custom ops 1070-1095).
 
-Dispatch is one kernel per regime (no tuner, no multi-kernel ladder): batch <= GEMV_MAX rows run the memory-order
-fused decode GEMV, larger batches the fused decode + tcgen05 GEMM.  Workspaces (fp32 split partials and zeroed
+Dispatch is one kernel per regime (no tuner, no multi-kernel ladder): up to GEMV_MAX activation rows run the
+memory-order fused decode GEMV, more rows the fused decode + tcgen05 GEMM.  Workspaces (exchange slots and zeroed
 semaphores) are kept per (device, stream) because callers may run layers on side streams concurrently (the reason
 given at statetree/linear.py:457-466); they are sized once per shape, so steady-state calls allocate only the output.
 """
 import os
+import weakref
 
 import torch
 import torch.nn as nn
@@ -14,10 +16,9 @@ import torch.nn as nn
 from . import format as F
 from .ops import ext
 
-GEMV_MAX = int(os.environ.get("STATETREE_GEMV_MAX", "10"))     # rows up to which the GEMV kernel runs (<= 32);
-# measured on B200 (Qwen3-8B shapes, ms per step of 252 linears): GEMV 3.39 at 8 rows, 4.22 at 9, 4.54 at 12, 4.95 at
-# 16; tcgen05 GEMM 4.41-4.44 at 9-16 and 4.32 at 32
+GEMV_MAX = int(os.environ.get("STATETREE_GEMV_MAX", "10"))     # activation rows up to which the GEMV kernel runs (<= 32)
 _STATES = {}
+_BUFFERS = ("tree", "esc_rows", "esc_cols", "esc_bits")
 
 
 class EscapeHeavy(RuntimeError):
@@ -63,6 +64,25 @@ def _state(device):
     return st
 
 
+def _rows_2d(x, width):
+    """x [..., width] of any float dtype / layout -> BF16 [rows, width], contiguous and 16-byte aligned"""
+    flat = x.reshape(-1, width)
+    if flat.dtype != torch.bfloat16:
+        flat = flat.to(torch.bfloat16)
+    if flat.data_ptr() % 16 or not flat.is_contiguous():
+        flat = flat.clone(memory_format=torch.contiguous_format)
+    return flat
+
+
+# layers reachable from the custom ops by a string handle (torch.compile passes plain strings, not modules)
+_BY_HANDLE = weakref.WeakValueDictionary()
+
+
+def _tracing():
+    comp = getattr(torch, "compiler", None)
+    return comp is not None and hasattr(comp, "is_compiling") and comp.is_compiling()
+
+
 class TreeLinear(nn.Module):
     """y = x W^T (+ b) with W [out, in] BF16 stored as a lossless state tree (~12.1 bits/weight).
 
@@ -83,6 +103,8 @@ class TreeLinear(nn.Module):
             self.register_buffer("bias", torch.empty(out_features, dtype=torch.bfloat16, device=dev))
         else:
             self.bias = None
+        self._handle = f"tl{id(self):x}"
+        _BY_HANDLE[self._handle] = self
         self._reset_runtime()
 
     # ---------------------------------------------------------------- construction / state dict
@@ -95,31 +117,33 @@ class TreeLinear(nn.Module):
     def from_weight(cls, W, bias=None, verify=True, max_escape_fraction=None):
         """W [out, in] bf16.  max_escape_fraction: raise EscapeHeavy when more weights escape."""
         W = W.detach()
-        assert W.dtype == torch.bfloat16, f"TreeLinear: weight dtype {W.dtype}, expected bfloat16"
+        if W.dtype != torch.bfloat16:
+            raise TypeError(f"TreeLinear.from_weight: expected a bfloat16 weight, got {W.dtype}")
         if max_escape_fraction is not None:
-            k = F.escape_count(W)
-            if k > max_escape_fraction * W.numel():
-                raise EscapeHeavy(f"{k / W.numel():.2%} of the weights escape")
+            escapes = F.escape_count(W)
+            if escapes > max_escape_fraction * W.numel():
+                raise EscapeHeavy(f"{escapes / W.numel():.2%} of the weights escape")
         enc = F.encode(W)
-        self = cls(W.shape[1], W.shape[0], bias=bias is not None, device="meta", n_esc=int(enc["esc_rows"].numel()))
-        for name in ("tree", "esc_rows", "esc_cols", "esc_bits"):
-            self._buffers[name] = enc[name]
+        out_features, in_features = W.shape
+        layer = cls(in_features, out_features, bias=bias is not None, device="meta", n_esc=int(enc["esc_rows"].numel()))
+        layer._buffers.update({name: enc[name] for name in _BUFFERS})
         if bias is not None:
-            self._buffers["bias"] = bias.detach().to(device=W.device, dtype=torch.bfloat16).clone()
-        self._reset_runtime()
+            layer._buffers["bias"] = bias.detach().to(device=W.device, dtype=torch.bfloat16).clone()
+        layer._reset_runtime()
         if verify:
-            got = self.dequantize() if self.tree.is_cuda else F.decode_reference(self.tree, self.esc_rows,
-                                                                                  self.esc_cols, self.esc_bits)
-            if not torch.equal(got.view(torch.int16), W.view(torch.int16)):
-                raise RuntimeError("TreeLinear: decoded weights differ from the original (format bug)")
-        return self
+            back = layer.dequantize() if layer.tree.is_cuda else F.decode_reference(*(layer._buffers[n] for n in _BUFFERS))
+            if not torch.equal(back.view(torch.int16), W.view(torch.int16)):
+                raise RuntimeError("TreeLinear: the tree does not decode to the weights it was built from")
+        return layer
 
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
                               error_msgs):
-        for name in ("esc_rows", "esc_cols", "esc_bits"):        # data-dependent sizes: adopt the stored size
-            v = state_dict.get(prefix + name)
-            if v is not None and v.shape != self._buffers[name].shape:
-                self._buffers[name] = torch.empty(v.shape, dtype=v.dtype, device=self._buffers[name].device)
+        # how many weights escape depends on the data: make room for whatever the checkpoint holds
+        for name in _BUFFERS[1:]:
+            stored = state_dict.get(prefix + name)
+            mine = self._buffers[name]
+            if stored is not None and stored.shape != mine.shape:
+                self._buffers[name] = torch.empty(stored.shape, dtype=stored.dtype, device=mine.device)
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
                                       error_msgs)
         self._reset_runtime()
@@ -131,6 +155,7 @@ class TreeLinear(nn.Module):
 
     def _reset_runtime(self):
         self._tables = None                             # (eo, el, eb) on the tree's device
+        self.__dict__["_shared"] = None                 # product shared by the TreeSlice views of this layer
 
     def extra_repr(self):
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
@@ -141,16 +166,20 @@ class TreeLinear(nn.Module):
         return F.bits_per_weight(self.out_features, self.in_features, self.esc_rows.numel())
 
     def storage_bytes(self):
-        return sum(b.numel() * b.element_size() for b in (self.tree, self.esc_rows, self.esc_cols, self.esc_bits))
+        return sum(self._buffers[n].numel() * self._buffers[n].element_size() for n in _BUFFERS)
 
     def record_bytes(self):
         return self.tree.numel()
 
     def tables(self):
-        """(eo, el, eb) escape side tables, built on first use (outside any graph capture)"""
+        """(eo, el, eb) escape side tables, built on first use (outside any graph capture).  The kernels read them
+        before they wait for the preceding kernel of the stream (programmatic dependent launch), so the tables must be
+        complete before that kernel starts: the stream is synchronised once after building them."""
         if self._tables is None or self._tables[0].device != self.tree.device:
             self._tables = F.escape_tables(self.out_features, self.in_features, self.esc_rows, self.esc_cols,
                                            self.esc_bits)
+            if self.tree.is_cuda and not torch.cuda.is_current_stream_capturing():
+                torch.cuda.current_stream(self.tree.device).synchronize()
         return self._tables
 
     def dequantize(self):
@@ -163,14 +192,12 @@ class TreeLinear(nn.Module):
     @torch.no_grad()
     def rows(self, ids):
         """W[ids] (exact BF16 rows), decoded on the fly: the embedding lookup of a tree-stored table."""
-        dev = self.tree.device
-        flat = ids.reshape(-1)
-        if flat.dtype != torch.int64 or not flat.is_contiguous() or flat.device != dev:
-            flat = flat.to(device=dev, dtype=torch.int64).contiguous()
-        out = torch.empty(flat.numel(), self.in_features, dtype=torch.bfloat16, device=dev)
+        where = self.tree.device
+        index = ids.reshape(-1).to(device=where, dtype=torch.int64).contiguous()
+        gathered = torch.empty(index.numel(), self.in_features, dtype=torch.bfloat16, device=where)
         eo, el, _ = self.tables()
-        ext().rows(self.tree, eo, el, flat, out)
-        return out.view(*ids.shape, self.in_features)
+        ext().rows(self.tree, eo, el, index, gathered)
+        return gathered.view(*ids.shape, self.in_features)
 
     # ---------------------------------------------------------------- forward
     def _run(self, x, y, yf32=None):
@@ -194,27 +221,39 @@ class TreeLinear(nn.Module):
                        None if yf32 is None else yf32[b0:b0 + step])
 
     def forward(self, x):
+        if _tracing() and _OPS_READY:
+            return torch.ops.statetree.linear(x, self.tree, self._handle)
         return self._forward(x)
 
     def _forward(self, x, yf32=None):
-        dev, src = self.tree.device, x.device
-        if src != dev:
-            x = x.to(dev)
-        shp = x.shape
-        x2 = x.reshape(-1, self.in_features)
-        if x2.dtype != torch.bfloat16:
-            x2 = x2.to(torch.bfloat16)
-        if not x2.is_contiguous() or x2.data_ptr() % 16:
-            x2 = x2.clone(memory_format=torch.contiguous_format)
-        B = x2.shape[0]
-        y = torch.empty(B, self.out_features, dtype=torch.bfloat16, device=x2.device)
-        if B:
-            self._run(x2, y, yf32)
+        """any leading shape, any float dtype, any device: the product runs where the tree lives, in BF16, and comes
+        back in the caller's dtype on the caller's device"""
+        home, asked_dtype, asked_device = self.tree.device, x.dtype, x.device
+        if home.type != "cuda":
+            raise RuntimeError("statetree_b200: the kernels take CUDA tensors only (no CPU path); move the layer to a GPU")
+        lead = x.shape[:-1]
+        acts = _rows_2d(x if asked_device == home else x.to(home), self.in_features)
+        result = torch.empty(acts.shape[0], self.out_features, dtype=torch.bfloat16, device=home)
+        if acts.shape[0] > 0:
+            with torch.cuda.device(home):
+                self._run(acts, result, yf32)
         if self.bias is not None:
-            y += self.bias
-        y = y.view(*shp[:-1], self.out_features)
-        y = y if x.dtype == torch.bfloat16 else y.to(x.dtype)
-        return y if src == dev else y.to(src)
+            result += self.bias
+        result = result.view(*lead, self.out_features)
+        if asked_dtype != torch.bfloat16:
+            result = result.to(asked_dtype)
+        return result if asked_device == home else result.to(asked_device)
+
+    def _fused_part(self, x, start, size, nparts):
+        """rows [start, start + size) of the product for a TreeSlice: the first part called with an input computes the
+        whole fused output, the others reuse it; after the last part the shared result is dropped"""
+        shared = self.__dict__.get("_shared")
+        if shared is None or shared[0] is not x:
+            shared = self.__dict__["_shared"] = [x, self(x), 0]
+        shared[2] += 1
+        if shared[2] >= nparts:
+            self.__dict__["_shared"] = None
+        return shared[1].narrow(-1, start, size)
 
 
 def interleave_gate_up(gate, up):
@@ -237,42 +276,87 @@ def swiglu(self, x):
     return act
 
 
-class TreeSlice(nn.Module):
-    """Rows [start, start + size) of a fused TreeLinear (q / k / v of a fused qkv, gate / up of a fused gate_up):
-    parts called with the same input object share one product (reference: statetree/linear.py TreeSlice)."""
+TreeLinear.swiglu = swiglu
 
-    def __init__(self, parent, start, size, nparts):
+
+class TreeSlice(nn.Module):
+    """One of several linear layers that read the same input (q / k / v, gate / up), stored together as one TreeLinear
+    on the parent module: rows [start, start + size) of that layer's output.  `fused` is the shared layer; it is not
+    registered as a submodule here, its buffers belong to the parent (reference: statetree/linear.py:1021-1036)."""
+
+    def __init__(self, fused, start, size, nparts):
         super().__init__()
-        self.__dict__["_parent"] = parent               # not a submodule: the parent is registered once elsewhere
-        self.start, self.size, self.nparts = start, size, nparts
-        self.in_features, self.out_features = parent.in_features, size
+        object.__setattr__(self, "fused", fused)
+        self.in_features, self.out_features = fused.in_features, size
+        self.start, self.nparts = start, nparts
 
     def forward(self, x):
-        p = self._parent
-        c = getattr(p, "_fcache", None)
-        if c is None or c[0] is not x:
-            c = p._fcache = [x, p(x), 0]
-        out = c[1].narrow(-1, self.start, self.size)
-        c[2] += 1
-        if c[2] >= self.nparts:
-            p._fcache = None
-        return out
+        return self.fused._fused_part(x, self.start, self.out_features, self.nparts)
+
+    def extra_repr(self):
+        return f"in_features={self.in_features}, out_features={self.out_features}, rows from {self.start} of the fused layer"
 
 
 class TreeEmbedding(nn.Module):
-    """Embedding lookup from a tree-stored table (optionally shared with a tied lm_head TreeLinear)."""
+    """Embedding lookup from a tree-stored table: rows are decoded exactly on lookup.  The table is either owned
+    (`table`, a registered TreeLinear) or, for tied input / output embeddings, the output layer's TreeLinear
+    (`source`, not registered here) (reference: statetree/linear.py:1039-1067)."""
 
-    def __init__(self, table):
+    def __init__(self, num_embeddings, embedding_dim, table=None, source=None):
         super().__init__()
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
         self.table = table
-        self.num_embeddings, self.embedding_dim = table.out_features, table.in_features
+        object.__setattr__(self, "source", source)
 
     @classmethod
     def from_embedding(cls, emb, verify=True):
-        return cls(TreeLinear.from_weight(emb.weight, verify=verify))
+        return cls(emb.num_embeddings, emb.embedding_dim, table=TreeLinear.from_weight(emb.weight, verify=verify))
+
+    def _rows_from(self):
+        return self.table if self.table is not None else self.source
 
     def forward(self, ids):
-        return self.table.rows(ids)
+        src = self._rows_from()
+        if _tracing() and _OPS_READY:
+            return torch.ops.statetree.rows(ids, src.tree, src._handle)
+        return src.rows(ids)
+
+    def extra_repr(self):
+        return f"{self.num_embeddings}, {self.embedding_dim}, " + ("own table" if self.table is not None else "tied to the output layer")
 
 
-TreeLinear.swiglu = swiglu
+# ---------------------------------------------------------------------------------------------- torch.compile
+# Under torch.compile the layers appear in the traced graph as two opaque custom ops with shape-only fake kernels, so
+# Dynamo neither traces into the ctypes shim nor specialises on it (reference: statetree/linear.py:1070-1095).
+_OPS_READY = False
+
+
+def _register_ops():
+    global _OPS_READY
+    library = getattr(torch, "library", None)
+    if library is None or not hasattr(library, "custom_op"):
+        return
+
+    @library.custom_op("statetree::linear", mutates_args=())
+    def linear_op(x: torch.Tensor, tree: torch.Tensor, handle: str) -> torch.Tensor:
+        return _BY_HANDLE[handle]._forward(x)
+
+    @linear_op.register_fake
+    def _(x, tree, handle):
+        return x.new_empty(*x.shape[:-1], tree.shape[0] * 16)
+
+    @library.custom_op("statetree::rows", mutates_args=())
+    def rows_op(ids: torch.Tensor, tree: torch.Tensor, handle: str) -> torch.Tensor:
+        return _BY_HANDLE[handle].rows(ids)
+
+    @rows_op.register_fake
+    def _(ids, tree, handle):
+        return tree.new_empty(*ids.shape, tree.shape[1] * 64, dtype=torch.bfloat16)
+
+    _OPS_READY = True
+
+
+try:
+    _register_ops()
+except Exception:                                       # noqa: BLE001  (a torch without torch.library.custom_op,
+    _OPS_READY = False                                  # or the ops already registered by another copy of the package)

@@ -55,10 +55,17 @@ def main(ref_root):
                                (1024, 512, 6, "each"), (1024, 1024, 0, "llm"), (512, 768, 7, "llm")):
         bits = G.weights(M, N, seed, regime)
         enc = ref_encode(F, bits)
+        esc = (enc_t(enc, "esc_rows"), enc_t(enc, "esc_cols"), enc_t(enc, "esc_bits"))
+        side = {}                                        # the reference's side tables (format.py:141-216)
+        for tag, out in (("lists", F.escape_lists(M, N, *esc)), ("chunks", F.escape_chunks(M, N, *esc)),
+                         ("blocks1", F.escape_blocks(M, N, 1, *esc)), ("blocks2", F.escape_blocks(M, N, 2, *esc))):
+            side[tag] = [sha(t.numpy()) for t in out]
+        leaves_v1 = F._v1(enc_t(enc, "tree")[..., :1024].to(torch.int32)).to(torch.uint8).numpy()
         digests[f"{M}x{N}_s{seed}_{regime}"] = dict(
             M=M, N=N, seed=seed, regime=regime, n_esc=int(enc["esc_rows"].size), W=sha(bits), tree=sha(enc["tree"]),
             esc_rows=sha(enc["esc_rows"]), esc_cols=sha(enc["esc_cols"]), esc_bits=sha(enc["esc_bits"]),
-            bits_per_weight=F.bits_per_weight(M, N, int(enc["esc_rows"].size)))
+            bits_per_weight=F.bits_per_weight(M, N, int(enc["esc_rows"].size)), side_tables=side,
+            leaves_v1=sha(leaves_v1), PERM=list(F.PERM))
     with open(os.path.join(HERE, "weights_digests.json"), "w") as f:
         json.dump(digests, f, indent=1, sort_keys=True)
 

@@ -1,0 +1,56 @@
+"""Generates tests/golden/model_checkpoint.json by running the REFERENCE's convert + save_pretrained on tiny seeded
+Hugging Face models (CPU): the safetensors key names, the statetree.json structure and a SHA-256 of every stored tensor.
+The test (tests/test_model_io.py) rebuilds the same models, converts and saves them with this package and compares.
+
+    python tests/golden/make_model_golden.py          (needs the reference checkout at /root/reference)
+"""
+import hashlib
+import json
+import os
+import sys
+import tempfile
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def tiny_model(tied):
+    """a two-layer Qwen3-architecture model with BF16 weights from a fixed seed (shapes fit the format: out % 16, in % 64)"""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    cfg = Qwen3Config(vocab_size=256, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=32, max_position_embeddings=64, tie_word_embeddings=tied)
+    torch.manual_seed(1234 + int(tied))
+    model = Qwen3ForCausalLM(cfg).to(torch.bfloat16)
+    with torch.no_grad():
+        model.model.layers[0].mlp.down_proj.weight[3, 5] = 0.0          # a value the tree cannot hold: an escape
+        model.model.layers[1].self_attn.o_proj.weight[7, 70:80] = 1e-12
+    return model.eval()
+
+
+def digest(path):
+    from safetensors.torch import load_file
+    sd = load_file(os.path.join(path, "model.safetensors"))
+    tensors = {k: [str(v.dtype), list(v.shape), hashlib.sha256(v.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()]
+               for k, v in sorted(sd.items())}
+    with open(os.path.join(path, "statetree.json")) as fh:
+        info = json.load(fh)
+    return {"tensors": tensors, "info": info}
+
+
+def main():
+    sys.path.insert(0, "/root/reference")
+    import statetree.model as R
+    out = {}
+    for tied in (False, True):
+        model = R.convert(tiny_model(tied), verify=True, verbose=False)
+        with tempfile.TemporaryDirectory() as d:
+            R.save_pretrained(model, d)
+            out["tied" if tied else "untied"] = digest(d)
+    with open(os.path.join(HERE, "model_checkpoint.json"), "w") as fh:
+        json.dump(out, fh, indent=1, sort_keys=True)
+    print("wrote", os.path.join(HERE, "model_checkpoint.json"))
+
+
+if __name__ == "__main__":
+    main()

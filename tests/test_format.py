@@ -42,6 +42,25 @@ def test_digests_of_larger_cases():
         assert abs(F.bits_per_weight(d["M"], d["N"], d["n_esc"]) - d["bits_per_weight"]) < 1e-12
 
 
+def test_reference_side_tables_and_leaf_migration():
+    """escape_lists / escape_chunks / escape_blocks, PERM and the leaf-format migration give the reference's bits
+    (digests of statetree/format.py:141-216, 16-40 run on the same seeded matrices)"""
+    with open(os.path.join(GOLD, "weights_digests.json")) as f:
+        dig = json.load(f)
+    for key, d in dig.items():
+        M, N = d["M"], d["N"]
+        enc = F.encode(bits_to_torch(G.weights(M, N, d["seed"], d["regime"])))
+        esc = (enc["esc_rows"], enc["esc_cols"], enc["esc_bits"])
+        got = {"lists": F.escape_lists(M, N, *esc), "chunks": F.escape_chunks(M, N, *esc),
+               "blocks1": F.escape_blocks(M, N, 1, *esc), "blocks2": F.escape_blocks(M, N, 2, *esc)}
+        for tag, tensors in got.items():
+            assert [sha(t.numpy()) for t in tensors] == d["side_tables"][tag], (key, tag)
+        v1 = F.leaves_v2_to_v1(enc["tree"])
+        assert sha(v1[..., :1024].numpy()) == d["leaves_v1"], key
+        assert torch.equal(F.leaves_v1_to_v2(v1), enc["tree"]), key
+        assert F.PERM == d["PERM"]
+
+
 def test_side_tables_are_consistent():
     g = np.load(os.path.join(GOLD, "weights_small.npz"))
     for name in ("mixed", "heavy", "each"):
