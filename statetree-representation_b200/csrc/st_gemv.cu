@@ -567,22 +567,26 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act
   long long want = p.U / (min_units < 1 ? 1 : min_units);     // small matrices: no CTA with less than min_units units
   if (want < 1) want = 1;
   p.C = (int)(want < slots ? want : slots);
-  // Cutting tiles at arbitrary unit boundaries fills every slot with the same amount of work, but the CTA that meets
-  // its neighbour last on a cut tile pays a round trip at its tail.  That pays off when a CTA has many units (measured
-  // from about 12: 12288 x 4096 takes 15.6 us cut against 16.5 us on 256 whole-tile CTAs, 4096 x 4096 8.9 against
-  // 7.6).  Shorter CTAs prefer a grid whose boundaries fall on tile boundaries (or that cuts every tile into equal
-  // parts) when one exists within 20% of the slot count.
-  static const int cut_from = tune("STATETREE_GEMV_CUT_FROM", 12);
+  // Grid.  Cutting tiles at arbitrary unit boundaries fills every slot with the same amount of work, but the CTA that
+  // meets its neighbour last on a cut tile pays an exchange round trip at its tail: worth about three units of work.
+  // A grid whose boundaries fall on tile boundaries (or that cuts every tile into equal parts) pays nothing, but leaves
+  // slots empty and quantises the work.  Take the largest such grid with at least half the slots, and choose between
+  // the two by the units of the longest CTA (12288 x 4096: cut, 20.8 + 3 units against 24; 4096 x 4096: whole tiles,
+  // 8 against 6.9 + 3).
+  static const int cut_cost = tune("STATETREE_GEMV_CUT_COST", 3), align_pct = tune("STATETREE_GEMV_ALIGN_PCT", 50);
   if (act) {                                                   // SwiGLU epilogue: every CTA owns whole gate / up tile pairs
     const long long pairs = (long long)nprob * p.T / 2;
     for (long long c = p.C; c >= 1; --c)
       if (pairs % c == 0) { p.C = (int)c; break; }
-  } else if (align && p.U / p.C < cut_from) {
+  } else if (align) {
     const long long tiles = (long long)nprob * p.T;
-    for (long long c = p.C; c * 5 >= (long long)p.C * 4 && c >= 1; --c) {
+    for (long long c = p.C; c * 100 >= (long long)p.C * align_pct && c >= 1; --c) {
       const bool whole = tiles % c == 0;
       const bool even = c % tiles == 0 && p.CPT % (c / tiles) == 0;
-      if (whole || even) { p.C = (int)c; break; }
+      if (whole || even) {
+        if (p.U / c <= p.U / p.C + cut_cost) p.C = (int)c;
+        break;
+      }
     }
   }
   const long long per = p.U / p.C;
