@@ -159,7 +159,7 @@ def attention_workload(args):
     import torch
 
     from statetree_b200 import ops
-    from statetree_b200.kvcache import StateTreeKVLayer, decode_splits
+    from statetree_b200.kvcache import PageStore, decode_splits
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
@@ -193,7 +193,7 @@ def attention_workload(args):
     for ctx in ctxs:
         for B in batches:
             npg = ctx // 16
-            layer = StateTreeKVLayer(B * npg, Hkv, dev, pool_blocks=1 << 16)
+            layer = PageStore(B * npg, Hkv, dev, pool_blocks=1 << 16)
             bt = torch.randperm(B * npg, device=dev, generator=gen).view(B, npg).to(torch.int32)
             scale_k = torch.exp(torch.randn(Hkv, D, device=dev, generator=gen))
             Kd = torch.empty(B, ctx, Hkv, D, dtype=torch.bfloat16, device=dev)
@@ -393,7 +393,7 @@ def aux_workload(args):
 
     import statetree_b200 as S
     from statetree_b200 import ops
-    from statetree_b200.kvcache import StateTreeKVLayer
+    from statetree_b200.kvcache import PageStore
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
@@ -434,7 +434,7 @@ def aux_workload(args):
             row("rows: 64 rows of a 12288x4096 table", timed(lambda: tl.rows(ids)), 64 * (N // 64) * 1552 + 64 * N * 2)
     H = 8
     for n_tok, what in ((64, "decode step, batch 64 (one token per sequence)"), (8192, "prefill, 8192 tokens")):
-        layer = StateTreeKVLayer(max(64, n_tok // 16) * 2, H, dev, pool_blocks=1 << 14)
+        layer = PageStore(max(64, n_tok // 16) * 2, H, dev, pool_blocks=1 << 14)
         K = torch.randn(n_tok, H, 128, device=dev, generator=gen).to(torch.bfloat16)
         V = torch.randn(n_tok, H, 128, device=dev, generator=gen).to(torch.bfloat16)
         slots = (torch.arange(n_tok, device=dev) * 16) if n_tok == 64 else torch.arange(n_tok, device=dev)

@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as Fn
 
-from .kvcache import StateTreeKVCache
+from .kvcache import PagedKVCache
 from .linear import TreeLinear, interleave_gate_up
 from .ops import ext, kv_ext
 
@@ -115,7 +115,7 @@ class TreeDecoder:
         self.k_buf = torch.empty(batch, self.hkv, D, dtype=torch.bfloat16, device=self.dev)
         self.tokens = torch.zeros(batch, dtype=torch.long, device=self.dev)
         if compressed:
-            self.cache = StateTreeKVCache(c.layers, batch, max_len, self.hkv, self.dev, pool_blocks=1 << 14)
+            self.cache = PagedKVCache(c.layers, batch, max_len, self.hkv, self.dev, pool_blocks=1 << 14)
         else:
             self.kc = [torch.zeros(batch, max_len, self.hkv, D, dtype=torch.bfloat16, device=self.dev) for _ in range(c.layers)]
             self.vc = [torch.zeros_like(k) for k in self.kc]

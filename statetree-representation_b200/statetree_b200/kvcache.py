@@ -1,7 +1,9 @@
 """Paged state-tree KV cache: keys and values stored losslessly in 16-token pages of state-tree records (6400 B per
 page per KV head against 8192 B in BF16), appended on write and read by the decode attention kernel without ever
-being expanded.  Mirrors the page tensors, slot arithmetic and call order of the reference's statetree/kvcache.py
-(StateTreeKVLayer.update 61-89, statetree_attention 180-201, _splits 29-32) without the Hugging Face cache glue.
+being expanded.  PageStore holds one attention layer's pages (the tensors of the reference's statetree/kvcache.py
+StateTreeKVLayer 49-57, with its append / dense / attention calls); PagedKVCache is the static cache of the decode
+runner in this package.  The Hugging Face classes of the reference (StateTreeKVCache, StateTreeKVLayer,
+statetree_attention, enable) live in hf_cache.py and are re-exported here when transformers is importable.
 """
 import torch
 
@@ -23,7 +25,7 @@ def decode_splits(B, Hkv, max_pages, sms=148, min_pages=4):
     return min(most, max(2, min(by_length, by_fill, 64)))               # two splits at least: several waves of CTAs
 
 
-class StateTreeKVLayer:
+class PageStore:
     """pages of one attention layer: uint8 [blocks, H, 2, 2, 1600], escape pool int32 [P, 16], pool counter int32 [2]"""
 
     def __init__(self, num_blocks, num_kv_heads, device, pool_blocks=1 << 15):
@@ -70,13 +72,13 @@ class StateTreeKVLayer:
     def check(self):
         """raise if an escape could not be stored (extension pool exhausted): never silently lossy"""
         if int(self.pcnt[1].item()):
-            raise RuntimeError("StateTreeKVCache: escape pool exhausted (pool_blocks too small)")
+            raise RuntimeError("PagedKVCache: escape pool exhausted (pool_blocks too small)")
 
     def pool_usage(self):
         return int(self.pcnt[0].item()), self.pool.shape[0]
 
 
-class StateTreeKVCache:
+class PagedKVCache:
     """Static paged cache for a decoder: per-layer pages, one block table [B, max_pages] (sequence b owns pages
     b * max_pages ...), a GPU-side token count so decode steps are CUDA-graph safe."""
 
@@ -85,7 +87,7 @@ class StateTreeKVCache:
         self.max_pages = (max_cache_len + PAGE - 1) // PAGE
         self.max_len = self.max_pages * PAGE
         self.device = torch.device(device)
-        self.layers = [StateTreeKVLayer(batch_size * self.max_pages, num_kv_heads, device, pool_blocks)
+        self.layers = [PageStore(batch_size * self.max_pages, num_kv_heads, device, pool_blocks)
                        for _ in range(num_layers)]
         self.bt32 = torch.arange(batch_size * self.max_pages, dtype=torch.int32, device=device).view(batch_size, -1)
         self.bt64 = self.bt32.long()
@@ -98,7 +100,7 @@ class StateTreeKVCache:
         B, H, T, D = key_states.shape
         self._stored += T if layer_idx == len(self.layers) - 1 else 0
         if self._stored + (T if layer_idx != len(self.layers) - 1 else 0) > self.max_len:
-            raise ValueError(f"StateTreeKVCache.update: position {self._stored + T} exceeds the capacity of "
+            raise ValueError(f"PagedKVCache.update: position {self._stored + T} exceeds the capacity of "
                              f"{self.max_len} tokens")
         cp = torch.arange(T, device=self.device) + self.cum
         slots = (self.bt64[:B][:, cp // PAGE] * PAGE + (cp % PAGE)).reshape(-1)
@@ -141,3 +143,9 @@ class StateTreeKVCache:
         self.lens.zero_()
         for layer in self.layers:
             layer.pcnt.zero_()
+
+
+try:                                                   # the transformers glue, under the reference's names
+    from .hf_cache import StateTreeKVCache, StateTreeKVLayer, enable, statetree_attention  # noqa: E402,F401
+except ImportError:                                    # transformers absent or too old: the page store still works
+    pass

@@ -1,4 +1,4 @@
-"""GPU parity at the benchmark's own sizes, through the module API (TreeLinear, StateTreeKVLayer).
+"""GPU parity at the benchmark's own sizes, through the module API (TreeLinear, PageStore).
 
 Linears: the four Qwen3-8B shapes (4096x4096, 1024x4096, 12288x4096, 4096x12288), N(0, 0.02) weights with 1% of the
 columns scaled x8, seeds 0-4 at one activation row and one seed at 8 / 32 / 64 / 256 rows, so the GEMV (up to 10 rows)
@@ -82,11 +82,11 @@ def _merge64(wo, wml, B, Hq, S, D=128):
 @pytest.mark.parametrize("ctx,B", [(1024, 1), (1024, 8), (1024, 64), (4096, 1), (4096, 8), (4096, 64), (16384, 1),
                                    (16384, 8), (16384, 64)])
 def test_benchmark_attention_matches_fp64(ctx, B):
-    from statetree_b200.kvcache import StateTreeKVLayer, decode_splits
+    from statetree_b200.kvcache import PageStore, decode_splits
     Hq, Hkv, D = 32, 8, 128
     npg = ctx // 16
     gen = torch.Generator(device=DEV).manual_seed(ctx * 131 + B)
-    layer = StateTreeKVLayer(B * npg, Hkv, DEV, pool_blocks=1 << 14)
+    layer = PageStore(B * npg, Hkv, DEV, pool_blocks=1 << 14)
     bt = torch.randperm(B * npg, device=DEV, generator=gen).view(B, npg).to(torch.int32)
     chan = torch.exp(torch.randn(Hkv, D, device=DEV, generator=gen))
     pos = torch.arange(ctx, device=DEV)

@@ -247,11 +247,11 @@ def test_decode_attention_matches_fp64(tiny, left_pad):
 @pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 4), (16, 2), (6, 2)])
 def test_decode_attention_other_group_sizes(hq, hkv):
     """1, 2, 8 and 3 query heads per KV head (the kernel puts up to 8 heads on the N side of the tensor-core shape)"""
-    from statetree_b200.kvcache import StateTreeKVLayer
+    from statetree_b200.kvcache import PageStore
     B, ctx = 3, 333
     npg = (ctx + 15) // 16
     gen = torch.Generator(device=DEV).manual_seed(hq * 10 + hkv)
-    layer = StateTreeKVLayer(B * npg, hkv, DEV, pool_blocks=1 << 12)
+    layer = PageStore(B * npg, hkv, DEV, pool_blocks=1 << 12)
     bt = torch.randperm(B * npg, device=DEV, generator=gen).view(B, npg).to(torch.int32)
     pos = torch.arange(ctx, device=DEV)
     Ks, Vs = [], []
@@ -278,10 +278,10 @@ def test_decode_attention_other_group_sizes(hq, hkv):
 
 
 def test_cache_object_decode_steps():
-    """StateTreeKVCache: prefill + decode steps through update() / attention() against dense fp64 attention"""
-    from statetree_b200.kvcache import StateTreeKVCache
+    """PagedKVCache: prefill + decode steps through update() / attention() against dense fp64 attention"""
+    from statetree_b200.kvcache import PagedKVCache
     B, T0, steps = 3, 37, 5
-    cache = StateTreeKVCache(1, B, 64, H, DEV, pool_blocks=4096)
+    cache = PagedKVCache(1, B, 64, H, DEV, pool_blocks=4096)
     rs = np.random.RandomState(0)
     Kall = G.to_bf16_bits(rs.standard_normal((B, H, T0 + steps, D)))
     Vall = G.to_bf16_bits(rs.standard_normal((B, H, T0 + steps, D)))
@@ -304,7 +304,7 @@ def test_cache_object_decode_steps():
 def test_fused_rope_append_matches_rope_then_append():
     """q/k norm + rotary embedding + append in one launch leaves the same q and the same page bytes as the two kernels
     it replaces (several steps, so rows other than 0 and the page change at row 16 are covered)"""
-    from statetree_b200.kvcache import StateTreeKVLayer
+    from statetree_b200.kvcache import PageStore
     from statetree_b200.ops import ext, kv_ext
     dev = torch.device("cuda")
     B, hq, hkv, D, max_pos = 3, 8, 2, 128, 64
@@ -314,7 +314,7 @@ def test_fused_rope_append_matches_rope_then_append():
     inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))
     ang = torch.arange(max_pos, device=dev, dtype=torch.float32)[:, None] * inv[None]
     cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
-    la, lb = StateTreeKVLayer(8, hkv, dev, pool_blocks=256), StateTreeKVLayer(8, hkv, dev, pool_blocks=256)
+    la, lb = PageStore(8, hkv, dev, pool_blocks=256), PageStore(8, hkv, dev, pool_blocks=256)
     bt = torch.tensor([[0, 3], [1, 4], [2, 5]], device=dev)
     pos = torch.zeros(1, dtype=torch.long, device=dev)
     for step in range(20):
