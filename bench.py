@@ -476,11 +476,16 @@ def decode_workload(args):
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    cfg = DecoderConfig(layers=args.layers)
+    moe = args.model == "qwen3-30b-a3b"
+    if moe:                                                   # config 5: 48 layers, hidden 2048, 32 q / 4 kv heads, 128 experts top-8
+        cfg = DecoderConfig(layers=48 if args.layers == LAYERS else args.layers, hidden=2048, heads=32, kv_heads=4,
+                            inter=768, experts=128, top_k=8, moe_inter=768)
+    else:
+        cfg = DecoderConfig(layers=args.layers)
     B, P, Gn = args.batch, args.prompt, args.gen
     prompt = torch.randint(0, cfg.vocab, (B, P), generator=torch.Generator().manual_seed(1)).to(dev)
     res = {}
-    for name, compressed in (("statetree", True), ("bf16", False)):
+    for name, compressed in ((("statetree", True),) if moe else (("statetree", True), ("bf16", False))):
         m = TreeDecoder(cfg, dev, B, P + Gn + 16, compressed=compressed, seed=0, rank=rank, world=world)
         wbytes = m.weight_bytes()
         m.capture()
@@ -488,7 +493,8 @@ def decode_workload(args):
         if world > 1:
             dist.barrier()
         preds = []
-        toks = m.run(prompt, Gn, collect=preds)                   # warm pass (also the token streams that are compared)
+        margins = []
+        toks = m.run(prompt, Gn, collect=preds, margins=margins)  # warm pass (also the token streams that are compared)
         m.reset()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -508,14 +514,44 @@ def decode_workload(args):
             dist.all_reduce(t_, op=dist.ReduceOp.MAX)
             ms = float(t_.item())
         res[name] = {"ms_per_step": ms, "tok_s": B / (ms * 1e-3), "tokens": toks.cpu(), "weight_bytes_per_rank": wbytes,
-                     "teacher_forced": torch.stack(preds, 1).cpu()}
+                     "teacher_forced": torch.stack(preds, 1).cpu(),
+                     "margins": torch.stack(margins).cpu() if margins else None}
         if compressed:
             m.cache.check()
         del m
         torch.cuda.empty_cache()
-    st, bf = res["statetree"], res["bf16"]
+    st = res["statetree"]
+    if moe:
+        status = ops.device_status()
+        if rank == 0:
+            hbm, _, which = peaks()
+            eff = st["weight_bytes_per_rank"] / (st["ms_per_step"] * 1e-3) / 1e9
+            print(json.dumps({"metric": "greedy decode tokens/s, random-init Qwen3-30B-A3B architecture, compressed weights + KV",
+                              "value": st["tok_s"], "unit": "tokens/s", "n_gpus": world, "steps": Gn, "warmup": P,
+                              "ms_per_step": st["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                              "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                              "config": {"workload": f"Qwen3-30B-A3B-shape decode ({cfg.layers} layers, hidden 2048, 32 q / 4 kv "
+                                                     f"heads, 128 experts top-8, expert intermediate 768), batch {B}, {P} random "
+                                                     f"prompt tokens + {Gn} greedy tokens",
+                                         "parallelism": "single GPU" if world == 1 else
+                                         f"ep{world}: experts split over ranks, tokens replicated, partial outputs all-reduced; "
+                                         f"attention tensor-parallel"},
+                              "bf16_control": None,
+                              "roofline": {"bound": "hbm", "achieved": eff, "peak": hbm, "unit": "GB/s", "frac": eff / hbm,
+                                           "traffic": None, "peak_source": f"of {which}",
+                                           "note": "record bytes a step reads per rank (upper bound for the experts) / step time"},
+                              "device_status": status}))
+        if world > 1:
+            sys.stdout.flush()
+            os._exit(0)
+        return
+    bf = res["bf16"]
     same = (st["tokens"] == bf["tokens"])
     first_div = [int((~same[b]).nonzero()[0]) if (~same[b]).any() else Gn for b in range(B)]
+    # top-2 logit margin of the compressed model at the step where sequence 0's stream leaves the control's
+    margin = None
+    if first_div[0] < Gn and st["margins"] is not None:
+        margin = float(st["margins"][first_div[0]])
     tf_same = float((st["teacher_forced"] == bf["teacher_forced"]).float().mean())
     status = ops.device_status()
     if rank == 0:
@@ -533,6 +569,7 @@ def decode_workload(args):
                           "agreement_with_bf16": {"teacher_forced_top1": tf_same,
                                                   "greedy_fraction_equal": float(same.float().mean()),
                                                   "greedy_first_divergence_step_per_sequence": first_div,
+                                                  "top2_logit_margin_at_first_divergence": margin,
                                                   "note": "random-init weights give nearly flat logits: a different fp32 "
                                                           "summation order flips near-ties, after which greedy streams differ"},
                           "roofline": {"bound": "hbm", "achieved": eff, "peak": hbm, "unit": "GB/s", "frac": eff / hbm,
@@ -557,6 +594,8 @@ def main():
     ap.add_argument("--no-fused", action="store_true", help="skip the extra pass with fused q/k/v and gate/up trees")
     ap.add_argument("--moe-batch", default="1,8,32,64,512,2048")
     ap.add_argument("--moe-no-gemm", action="store_true", help="moe workload: grouped GEMV at every size (for comparison)")
+    ap.add_argument("--model", default="qwen3-8b", choices=["qwen3-8b", "qwen3-30b-a3b"],
+                    help="decode workload: the dense Qwen3-8B shape (config 4) or the Qwen3-30B-A3B mixture of experts (config 5)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=512)
     ap.add_argument("--workload", default="linear", choices=["linear", "attn", "moe", "decode", "aux"],

@@ -6,7 +6,10 @@ builds the BF16 control from the same seeds: dense weights, a dense BF16 KV cach
 
 Tensor parallelism (one process per GPU): q/k/v and gate/up are split by rows (heads / intermediate columns), o and
 down by input columns with an all-reduce of their outputs, the lm_head by vocabulary rows with an all-gather of the
-logits; embeddings and norms are replicated.  Every rank draws the full tensors from the same seeds and keeps its slice,
+logits; embeddings and norms are replicated.  With `experts > 0` the MLP is a routed expert block (softmax router,
+top-k, renormalised weights, TreeExperts): under several ranks the attention stays tensor-parallel and the experts are
+split over the ranks (expert parallelism: every rank routes all tokens, computes its own experts' weighted partial
+output, and the partial outputs are all-reduced).  Every rank draws the full tensors from the same seeds and keeps its slice,
 so a tensor-parallel run computes the same function as the single-GPU one.
 """
 import math
@@ -38,6 +41,10 @@ class DecoderConfig:
     vocab: int = 151936
     rope_theta: float = 1e6
     eps: float = 1e-6
+    experts: int = 0                 # > 0: the MLP of every layer is a routed mixture of experts (Qwen3-MoE shape)
+    top_k: int = 8
+    moe_inter: int = 768             # intermediate size of one expert
+    distinct_experts: int = 4        # random expert matrices drawn per layer; the others are copies in their own buffers
 
 
 class _Dense:
@@ -62,7 +69,12 @@ class TreeDecoder:
         assert c.heads % world == 0 and c.kv_heads % world == 0 and c.inter % (64 * world) == 0 and c.vocab % (16 * world) == 0
         self.hq, self.hkv = c.heads // world, c.kv_heads // world
         self.fused_act = False
-        if compressed and batch <= 8 and os.environ.get("STATETREE_FUSED_ACT", "1") != "0":
+        if c.experts:
+            assert compressed, "the mixture-of-experts decoder has no BF16 control"
+            assert c.experts % world == 0
+            from .parallel import expert_partition
+            self.e_lo, self.e_hi, self.emap = expert_partition(c.experts, rank, world, self.dev)
+        if compressed and not c.experts and batch <= 8 and os.environ.get("STATETREE_FUSED_ACT", "1") != "0":
             from .ops import lib
             with torch.cuda.device(self.dev):
                 self.fused_act = bool(lib().st_gemv_swiglu_supported(2 * c.inter // world, c.hidden, batch))
@@ -91,15 +103,18 @@ class TreeDecoder:
             o = draw(c.hidden, c.heads * D)
             per = o.shape[1] // world
             o = make(o[:, rank * per:(rank + 1) * per])
-            g, u = draw(c.inter, c.hidden), draw(c.inter, c.hidden)
-            if self.fused_act:                              # gate / up tiles in turn: SwiGLU in the GEMV's epilogue
-                gu = make(interleave_gate_up(rows(g).contiguous(), rows(u).contiguous()))
+            if c.experts:
+                gu, d = self._make_experts(draw), None
             else:
-                gu = make(torch.cat([rows(g), rows(u)]))
-            del g, u
-            d = draw(c.hidden, c.inter)
-            per = d.shape[1] // world
-            d = make(d[:, rank * per:(rank + 1) * per])
+                g, u = draw(c.inter, c.hidden), draw(c.inter, c.hidden)
+                if self.fused_act:                          # gate / up tiles in turn: SwiGLU in the GEMV's epilogue
+                    gu = make(interleave_gate_up(rows(g).contiguous(), rows(u).contiguous()))
+                else:
+                    gu = make(torch.cat([rows(g), rows(u)]))
+                del g, u
+                d = draw(c.hidden, c.inter)
+                per = d.shape[1] // world
+                d = make(d[:, rank * per:(rank + 1) * per])
             self.blocks.append((qkv, o, gu, d))
         self.lm_head = make(rows(draw(c.vocab, c.hidden)))
         ones = torch.ones(c.hidden, dtype=torch.bfloat16, device=self.dev)
@@ -126,10 +141,42 @@ class TreeDecoder:
             self.comm = peer_comm(group)
         self.graph = None
 
+    def _make_experts(self, draw):
+        """(router weight [E, hidden] BF16, TreeExperts over this rank's experts): `distinct_experts` random matrices per
+        projection, every expert a copy of one of them in a buffer of its own (so the records of every expert a step
+        touches stream from HBM), which keeps building a 128-expert x 48-layer model within minutes"""
+        from .experts import TreeExperts
+        c = self.cfg
+        router = draw(c.experts, c.hidden)
+        base13 = [TreeLinear.from_weight(draw(2 * c.moe_inter, c.hidden), verify=False) for _ in range(c.distinct_experts)]
+        base2 = [TreeLinear.from_weight(draw(c.hidden, c.moe_inter), verify=False) for _ in range(c.distinct_experts)]
+
+        def copy_of(tl):
+            m = TreeLinear(tl.in_features, tl.out_features, device="meta", n_esc=tl.esc_rows.numel())
+            m._buffers["tree"] = tl.tree.clone()
+            for k in ("esc_rows", "esc_cols", "esc_bits"):
+                m._buffers[k] = tl._buffers[k]
+            m._tables = tl.tables()
+            return m
+
+        mine = range(self.e_lo, self.e_hi)
+        te = TreeExperts([copy_of(base13[e % c.distinct_experts]) for e in mine],
+                         [copy_of(base2[e % c.distinct_experts]) for e in mine])
+        te.tables()
+        return (router, te)
+
     def weight_bytes(self):
-        n = self.lm_head.record_bytes()                          # (the embedding table is read B rows at a time)
-        for blk in self.blocks:
-            n += sum(m.record_bytes() for m in blk)
+        """record bytes a decode step reads on this rank (the embedding table is read B rows at a time; of the experts,
+        an upper bound: min(experts on the rank, batch x top_k) of them)"""
+        n = self.lm_head.record_bytes()
+        for qkv, o, gu, d in self.blocks:
+            n += qkv.record_bytes() + o.record_bytes()
+            if self.cfg.experts:
+                te = gu[1]
+                per = te.record_bytes() // te.num_experts
+                n += per * min(te.num_experts, self.B * self.cfg.top_k)
+            else:
+                n += gu.record_bytes() + d.record_bytes()
         return n
 
     def _add_norm(self, x, delta, h):
@@ -167,6 +214,13 @@ class TreeDecoder:
                                v=v.unsqueeze(1), cache_seqlens=self.lens, softmax_scale=scale)
             delta = o(att.reshape(B, self.hq * D))
             self._add_norm(x, delta, h)
+            if c.experts:
+                router, te = gu
+                probs = torch.softmax(Fn.linear(h, router).float(), -1)
+                w, ids = probs.topk(c.top_k, -1)
+                w = (w / w.sum(-1, keepdim=True)).contiguous()
+                delta = te(h, ids.to(torch.int32).contiguous(), w, self.emap if self.world > 1 else None)
+                continue                                     # (the all-reduce over ranks happens in the next _add_norm)
             if self.fused_act:
                 act = gu.swiglu(h)
             else:
@@ -224,9 +278,10 @@ class TreeDecoder:
         else:
             self.lens.zero_()
 
-    def run(self, prompt, n_new, collect=None):
+    def run(self, prompt, n_new, collect=None, margins=None):
         """prompt [B, P] token ids (teacher-forced one step at a time), then n_new greedy tokens -> [B, n_new].
-        collect (optional list): receives the model's prediction after every prompt step (teacher-forced top-1)."""
+        collect (optional list): receives the model's prediction after every prompt step (teacher-forced top-1).
+        margins (optional list): receives, per generated token, the top-2 logit margin of sequence 0 that chose it."""
         start = int(self.pos_buf.item())
         if start + prompt.shape[1] + n_new > self.max_len:       # beyond it the page lookup would leave the block table
             raise ValueError(f"TreeDecoder.run: {prompt.shape[1]} prompt + {n_new} new tokens from position {start} "
@@ -238,6 +293,9 @@ class TreeDecoder:
             if collect is not None:
                 collect.append(self.next_tok.clone())
         for _ in range(n_new):
+            if margins is not None:
+                top2 = self.logits[0].float().topk(2).values
+                margins.append(top2[0] - top2[1])
             self.tokens.copy_(self.next_tok)
             out.append(self.next_tok.clone())
             self.graph.replay()

@@ -351,7 +351,7 @@ def test_vllm_page_backend_data_path():
     rs = np.random.RandomState(4)
     used = []
     for rnd in range(3):                                                       # three rounds of requests over the same blocks
-        bt = torch.from_numpy(rs.permutation(nb)[:B * 10].reshape(B, 10).astype(np.int32)).to(DEV)
+        bt = torch.from_numpy(rs.permutation(B * 10).reshape(B, 10).astype(np.int32)).to(DEV)   # the same 30 blocks, reshuffled
         Ks, Vs = [], []
         for b in range(B):
             Kb, Vb = G.kv_tokens(ctx, H, seed=rnd * 10 + b, tiny=0.08)
