@@ -591,6 +591,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-bf16", action="store_true", help="skip the dense BF16 (cuBLAS) control pass")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the M = 8 / 32 / 64 / 256 points of the default run")
     ap.add_argument("--no-fused", action="store_true", help="skip the extra pass with fused q/k/v and gate/up trees")
     ap.add_argument("--moe-batch", default="1,8,32,64,512,2048")
     ap.add_argument("--moe-no-gemm", action="store_true", help="moe workload: grouped GEMV at every size (for comparison)")
@@ -887,7 +888,56 @@ def main():
         control = {"what": "same step, dense BF16 copies of the same weights, torch.matmul (cuBLAS) in one CUDA graph",
                    "ms_per_step": ms_d, "speedup_vs_bf16": ms_d / ms,
                    "speedup_vs_bf16_fused": (ms_d / fused["ms_per_step"]) if fused else None}
-        del dgraph, dense
+        del dgraph
+        # ---- the other activation-row counts of the benchmark configuration (M = 8, 32, 64, 256), each one graph over the
+        # same 36 x 7 record buffers and one over the dense copies: a few replays each
+        sweep = []
+        if B == 1 and not args.no_sweep:
+            for Bs in (8, 32, 64, 256):
+                gs = torch.Generator(device=dev).manual_seed(200 + Bs)
+                xs = {n: torch.randn(Bs, n, device=dev, generator=gs).to(torch.bfloat16) for n in (HIDDEN, INTER)}
+                ys = [torch.empty(Bs, tl.out_features, dtype=torch.bfloat16, device=dev) for tl in layers[0]]
+                gemv_path = Bs <= GEMV_MAX
+                ws_s = st.get_ws(max((E.gemv_workspace_bytes if gemv_path else E.gemm_workspace_bytes)(
+                    tl.out_features, tl.in_features, Bs) for tl in layers[0]))
+                cnt_s = st.get_cnt(4096)
+
+                def run_tree():
+                    for row in layers:
+                        for tl, y in zip(row, ys):
+                            eo, el, eb = tl._tables
+                            if gemv_path:
+                                E.gemv(tl.tree, eo, eb, el, xs[tl.in_features], y, ws_s, cnt_s)
+                            else:
+                                E.gemm(tl.tree, eo, el, xs[tl.in_features], y, ws_s, cnt_s)
+
+                def run_ctl():
+                    for row in dense:
+                        for W, y in zip(row, ys):
+                            torch.matmul(xs[W.shape[1]], W.t(), out=y)
+
+                point = {"batch": Bs, "kernel": "gemv_kernel" if gemv_path else "gemm_kernel (tcgen05)"}
+                for key, fn in (("ms_per_step", run_tree), ("bf16_control_ms", run_ctl)):
+                    torch.cuda.synchronize()
+                    with torch.cuda.stream(side):
+                        fn()
+                    side.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        fn()
+                    torch.cuda.synchronize()
+                    for _ in range(2):
+                        g.replay()
+                    point[key] = timed(g.replay, 5)
+                    del g
+                nb = sum(algorithmic_bytes(M, N, Bs) for _, M, N, _ in SHAPES) * args.layers
+                fl = sum(2 * Bs * M * N for _, M, N, _ in SHAPES) * args.layers
+                point.update(gbs=nb / (point["ms_per_step"] * 1e-3) / 1e9, tflops=fl / (point["ms_per_step"] * 1e-3) / 1e12,
+                             speedup_vs_bf16=point["bf16_control_ms"] / point["ms_per_step"])
+                sweep.append(point)
+                del xs, ys
+            control["sweep"] = sweep
+        del dense
     status = ops.device_status()
 
     def leave():
@@ -930,6 +980,8 @@ def main():
     if fused is not None:
         line["fused_qkv_gate_up"] = fused
     if control is not None:
+        if "sweep" in control:
+            line["sweep"] = control.pop("sweep")
         line["bf16_control"] = control
     if not args.no_cpu and world == 1:
         val, dt, cores = cpu_reference(2, 1, B)

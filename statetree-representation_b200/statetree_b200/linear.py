@@ -16,7 +16,7 @@ import torch.nn as nn
 from . import format as F
 from .ops import ext
 
-GEMV_MAX = int(os.environ.get("STATETREE_GEMV_MAX", "10"))     # activation rows up to which the GEMV kernel runs (<= 32)
+GEMV_MAX = int(os.environ.get("STATETREE_GEMV_MAX", "12"))     # activation rows up to which the GEMV kernel runs (<= 32)
 _STATES = {}
 _BUFFERS = ("tree", "esc_rows", "esc_cols", "esc_bits")
 
