@@ -41,128 +41,149 @@ struct AppendArgs {
   int gsz;                  // tokens of the call scanned per warp for segment starts (1: decode steps, 16: prefill)
 };
 
-// escape bookkeeping of one record while a warp appends rows to it (lane 0 owns the chain walk)
-struct EscCursor {
-  int cnt;   // in-record slots used
-  int head;  // first extension block, -1 = none
-  int tail;  // block currently appended to, -1 = not located yet
-  int fill;  // entries in tail
-};
+// ---- escapes of a record.  A value whose exponent lies more than 14 below its row's largest cannot be held by the
+// 4-bit state; its exact bits go to an entry (bits << 16 | row << 6 | col).  The first 11 entries of a record live in
+// the unit itself, the rest in a chain of 16-word pool blocks (word 0 = entries used | (next block + 1) << 8, then up to
+// 15 entries); the unit's header word is  entries in the unit | 16 if a chain exists | first block << 8.
 
-__device__ void chain_put(const AppendArgs& a, EscCursor& c, uint32_t* slots, uint32_t e) {
-  if (c.cnt < NSLOT) { slots[c.cnt++] = e; return; }
-  if (c.head >= 0 && c.tail < 0) {                 // first use of an existing chain: find its first non-full block
-    c.tail = c.head;
+// lane 0's view of a record's chain while it appends to it
+struct ChainTail {
+  uint32_t* pool;
+  int* pool_cnt;
+  int P;
+  int first;      // first block of the chain, -1 = the record has none
+  int blk;        // block being filled, -1 = not looked for yet
+  int used;       // entries in blk
+
+  __device__ uint32_t& word0(int b) const { return pool[(size_t)b * 16]; }
+  __device__ static int next_of(uint32_t w0) { return (int)(w0 >> 8) - 1; }
+
+  // an existing chain is entered at its first block that still has room (blocks before it are full)
+  __device__ void locate() {
+    blk = first;
     for (int hops = 0; hops < 4096; ++hops) {
-      const uint32_t w0 = a.pool[(size_t)c.tail * 16];
-      const int nx = (int)(w0 >> 8) - 1;
-      c.fill = (int)(w0 & 0xFFu);
-      if (c.fill < XSLOT || nx < 0 || nx >= a.P) break;
-      c.tail = nx;
+      const uint32_t w0 = word0(blk);
+      used = (int)(w0 & 0xFFu);
+      const int nx = next_of(w0);
+      if (used < XSLOT || nx < 0 || nx >= P) return;
+      blk = nx;
     }
   }
-  if (c.tail >= 0 && c.fill == XSLOT) {            // full: step to a recycled block that is already linked
-    const int nx = (int)(a.pool[(size_t)c.tail * 16] >> 8) - 1;
-    if (nx >= 0 && nx < a.P) { c.tail = nx; c.fill = (int)(a.pool[(size_t)nx * 16] & 0xFFu); }
+  // the block is full (or there is none): move to the next linked block (a recycled chain keeps its links) or take a
+  // fresh block from the pool and link it; false when the pool is exhausted (flagged for the host)
+  __device__ bool advance() {
+    if (blk >= 0) {
+      const int nx = next_of(word0(blk));
+      if (nx >= 0 && nx < P) {
+        blk = nx;
+        used = (int)(word0(nx) & 0xFFu);
+        if (used < XSLOT) return true;
+      }
+    }
+    const int fresh = atomicAdd(pool_cnt, 1);
+    if (fresh >= P) {
+      atomicExch(pool_cnt + 1, 1);
+      return false;
+    }
+    word0(fresh) = 0u;
+    if (blk < 0) first = fresh;
+    else word0(blk) = (word0(blk) & 0xFFu) | ((uint32_t)(fresh + 1) << 8);
+    blk = fresh;
+    used = 0;
+    return true;
   }
-  if (c.tail < 0 || c.fill == XSLOT) {             // take a new block from the pool
-    const int nb = atomicAdd(a.pool_cnt, 1);
-    if (nb >= a.P) { atomicExch(a.pool_cnt + 1, 1); return; }   // exhausted: flagged for the host, never silent
-    a.pool[(size_t)nb * 16] = 0u;
-    if (c.tail < 0) c.head = nb;
-    else a.pool[(size_t)c.tail * 16] = (a.pool[(size_t)c.tail * 16] & 0xFFu) | ((uint32_t)(nb + 1) << 8);
-    c.tail = nb;
-    c.fill = 0;
+  __device__ void push(uint32_t entry) {
+    if (first >= 0 && blk < 0) locate();
+    if ((blk < 0 || used >= XSLOT) && !advance()) return;
+    pool[(size_t)blk * 16 + 1 + used] = entry;
+    ++used;
+    word0(blk) = (word0(blk) & ~0xFFu) | (uint32_t)used;
   }
-  a.pool[(size_t)c.tail * 16 + 1 + c.fill] = e;
-  ++c.fill;
-  a.pool[(size_t)c.tail * 16] = (a.pool[(size_t)c.tail * 16] & ~0xFFu) | (uint32_t)c.fill;
-}
+};
 
 // Encodes nrow consecutive rows (r0 ..) of one record, whose values are pairs[i] (columns 2 lane, 2 lane + 1 of row i),
 // into the 1600-byte unit: staged in `rec` (shared memory, one per warp), written back to `grec` as 100 16-byte stores.
-__device__ __forceinline__ void append_rows(const AppendArgs& a, uint8_t* const grec, uint8_t* const rec, const int r0,
-                                            const int nrow, const uint32_t (&pairs)[PAGE], const int lane) {
-  uint32_t* const hdr = reinterpret_cast<uint32_t*>(rec + REC);
-  uint32_t* const slots = hdr + 1;
-  EscCursor c;
-  if (r0 == 0) {                                                  // row 0: the page starts over
-    int keep = -1;
+// Two phases: every row is encoded and its escape entries are queued in `queue` (shared memory, row-major, column
+// order, positions from warp ballots); then the queue is placed: into the unit's free slots by all lanes at once, and
+// whatever is left into the chain by lane 0.
+__device__ __forceinline__ void append_rows(const AppendArgs& a, uint8_t* const grec, uint8_t* const rec,
+                                            uint32_t* const queue, const int r0, const int nrow,
+                                            const uint32_t (&pairs)[PAGE], const int lane) {
+  uint32_t* const header = reinterpret_cast<uint32_t*>(rec + REC);
+  uint32_t* const slots = header + 1;
+  int in_unit, chain;                                             // entries already in the unit; first chain block or -1
+  if (r0 == 0) {
+    // the page starts over: an all-zero unit; with `reuse` the old chain is kept, emptied (its links stay)
+    chain = -1;
     if (a.reuse) {
-      const uint32_t old = *reinterpret_cast<const volatile uint32_t*>(grec + REC);
-      if ((old & 16u) && (int)(old >> 8) < a.P) keep = (int)(old >> 8);
+      const uint32_t was = *reinterpret_cast<const volatile uint32_t*>(grec + REC);
+      if ((was & 16u) && (int)(was >> 8) < a.P) chain = (int)(was >> 8);
     }
     for (int i = lane; i < RKV / 16; i += 32) reinterpret_cast<uint4*>(rec)[i] = make_uint4(0, 0, 0, 0);
-    if (keep >= 0 && lane == 0) {                                 // empty the kept chain, links stay
-      int b = keep;
+    if (chain >= 0 && lane == 0) {
+      int b = chain;
       for (int hops = 0; b >= 0 && b < a.P && hops < 4096; ++hops) {
         const uint32_t w0 = a.pool[(size_t)b * 16];
         a.pool[(size_t)b * 16] = w0 & ~0xFFu;
         b = (int)(w0 >> 8) - 1;
       }
     }
-    c.cnt = 0;
-    c.head = keep;
-  } else {                                                        // continue a page: bring the unit in
+    in_unit = 0;
+  } else {
     for (int i = lane; i < RKV / 16; i += 32) reinterpret_cast<uint4*>(rec)[i] = reinterpret_cast<const uint4*>(grec)[i];
     __syncwarp();
-    const uint32_t old = *hdr;
-    c.cnt = (int)(old & 15u);
-    c.head = (old & 16u) ? (int)(old >> 8) : -1;
+    const uint32_t was = *header;
+    in_unit = (int)(was & 15u);
+    chain = (was & 16u) ? (int)(was >> 8) : -1;
   }
   __syncwarp();
-  c.tail = -1;
-  c.fill = 0;
+  // ---- phase 1: rows
+  int queued = 0;
 #pragma unroll
   for (int i = 0; i < PAGE; ++i) {
     if (i >= nrow) break;
     const int r = r0 + i;
-    const uint32_t pr = pairs[i];
-    const uint32_t b0 = pr & 0xFFFFu, b1 = pr >> 16;
-    const int e0 = (int)((b0 >> 7) & 0xFFu), e1 = (int)((b1 >> 7) & 0xFFu);
-    int E = max(e0, e1);
+    const uint32_t v0 = pairs[i] & 0xFFFFu, v1 = pairs[i] >> 16;
+    const int e0 = (int)((v0 >> 7) & 0xFFu), e1 = (int)((v1 >> 7) & 0xFFu);
+    int top = max(e0, e1);                                        // the row's node: largest exponent of its 64 values
 #pragma unroll
-    for (int o = 16; o; o >>= 1) E = max(E, __shfl_xor_sync(FULL, E, o));
-    const int d0 = E - e0, d1 = E - e1;
-    const bool x0 = d0 > 14, x1 = d1 > 14;
-    const uint32_t leaf0 = ((x0 ? 0u : (b0 & 0x7Fu)) << 1) | (x1 ? 0u : (b1 >> 15));
-    const uint32_t leaf1 = ((x1 ? 0u : (b1 & 0x7Fu)) << 1) | (x0 ? 0u : (b0 >> 15));
-    *reinterpret_cast<uint16_t*>(rec + leaf_pair_off(r, lane)) = (uint16_t)(leaf0 | (leaf1 << 8));
+    for (int o = 16; o; o >>= 1) top = max(top, __shfl_xor_sync(FULL, top, o));
+    const bool out0 = top - e0 > 14, out1 = top - e1 > 14;
+    // leaf = mantissa << 1 | sign of the pair partner (zero for a value that escapes), state = exponent distance
+    const uint32_t leaf0 = (out0 ? 0u : (v0 & 0x7Fu) << 1) | (out1 ? 0u : v1 >> 15);
+    const uint32_t leaf1 = (out1 ? 0u : (v1 & 0x7Fu) << 1) | (out0 ? 0u : v0 >> 15);
+    *reinterpret_cast<uint16_t*>(rec + leaf_pair_off(r, lane)) = (uint16_t)(leaf0 | leaf1 << 8);
+    const uint32_t st0 = out0 ? 15u : (uint32_t)(top - e0), st1 = out1 ? 15u : (uint32_t)(top - e1);
     uint16_t* const sp = reinterpret_cast<uint16_t*>(rec + state_pair_off(r, lane));
-    const int sh = 4 * (r >> 3);
-    const uint32_t q0 = x0 ? 15u : (uint32_t)d0, q1 = x1 ? 15u : (uint32_t)d1;
-    const uint32_t keepmask = ~((0xFu << sh) | (0xFu << (8 + sh)));
-    *sp = (uint16_t)((*sp & keepmask) | (q0 << sh) | (q1 << (8 + sh)));
-    if (lane == 0) rec[1536 + 2 * (r & 7) + (r >> 3)] = (uint8_t)E;
-    const unsigned m0 = __ballot_sync(FULL, x0), m1 = __ballot_sync(FULL, x1);
-    const int tot = __popc(m0) + __popc(m1);
-    if (tot == 0) continue;
-    const uint32_t en0 = (b0 << 16) | ((uint32_t)r << 6) | (uint32_t)(2 * lane);
-    const uint32_t en1 = (b1 << 16) | ((uint32_t)r << 6) | (uint32_t)(2 * lane + 1);
-    if (c.cnt + tot <= NSLOT) {                                   // all fit in the record: column order
-      const unsigned below = (1u << lane) - 1u;
-      const int at = c.cnt + __popc(m0 & below) + __popc(m1 & below);
-      if (x0) slots[at] = en0;
-      if (x1) slots[at + (x0 ? 1 : 0)] = en1;
-      c.cnt += tot;
-    } else {                                                      // lane 0 places them one by one
-      for (int sl = 0; sl < 32; ++sl) {
-        const uint32_t f0 = __shfl_sync(FULL, en0, sl), f1 = __shfl_sync(FULL, en1, sl);
-        if (lane == 0) {
-          if ((m0 >> sl) & 1u) chain_put(a, c, slots, f0);
-          if ((m1 >> sl) & 1u) chain_put(a, c, slots, f1);
-        }
-      }
-      c.cnt = __shfl_sync(FULL, c.cnt, 0);
-      c.head = __shfl_sync(FULL, c.head, 0);
-      c.tail = __shfl_sync(FULL, c.tail, 0);
-      c.fill = __shfl_sync(FULL, c.fill, 0);
-    }
+    const int nib = 4 * (r >> 3);                                 // rows 0-7 low nibbles, rows 8-15 high nibbles
+    *sp = (uint16_t)((*sp & ~((0xFu << nib) | (0xF00u << nib))) | st0 << nib | st1 << (8 + nib));
+    if (lane == 0) rec[1536 + 2 * (r & 7) + (r >> 3)] = (uint8_t)top;
+    const unsigned m0 = __ballot_sync(FULL, out0), m1 = __ballot_sync(FULL, out1);
+    if ((m0 | m1) == 0u) continue;
+    const unsigned below = (1u << lane) - 1u;
+    const int at = queued + __popc(m0 & below) + __popc(m1 & below);
+    const uint32_t where = (uint32_t)r << 6 | (uint32_t)(2 * lane);
+    if (out0) queue[at] = v0 << 16 | where;
+    if (out1) queue[at + (out0 ? 1 : 0)] = v1 << 16 | (where + 1u);
+    queued += __popc(m0) + __popc(m1);
   }
-  if (lane == 0) *hdr = (uint32_t)c.cnt | (c.head >= 0 ? (16u | ((uint32_t)c.head << 8)) : 0u);
+  __syncwarp();
+  // ---- phase 2: place the queued entries
+  const int to_unit = min(queued, NSLOT - in_unit);
+  if (lane < to_unit) slots[in_unit + lane] = queue[lane];       // at most 11
+  in_unit += to_unit;
+  if (queued > to_unit) {
+    if (lane == 0) {
+      ChainTail tail{a.pool, a.pool_cnt, a.P, chain, -1, 0};
+      for (int i = to_unit; i < queued; ++i) tail.push(queue[i]);
+      chain = tail.first;
+    }
+    chain = __shfl_sync(FULL, chain, 0);
+  }
+  if (lane == 0) *header = (uint32_t)in_unit | (chain >= 0 ? 16u | (uint32_t)chain << 8 : 0u);
   __syncwarp();
   for (int i = lane; i < RKV / 16; i += 32) reinterpret_cast<uint4*>(grec)[i] = reinterpret_cast<const uint4*>(rec)[i];
-  __syncwarp();                                                   // the staging unit is reused by the next segment
+  __syncwarp();                                                   // the staging unit and the queue are reused
 }
 
 // One warp per (token, head, K/V, half); only the warp of a segment's first token works: a segment is a run of
@@ -172,6 +193,7 @@ __device__ __forceinline__ void append_rows(const AppendArgs& a, uint8_t* const 
 // encoded row by row with shared-memory byte stores, and the unit goes back to the page as 100 16-byte stores.
 __global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
   __shared__ __align__(16) uint8_t s_unit[8][RKV];
+  __shared__ uint32_t s_queue[8][PAGE * 64];                      // a segment's escape entries, worst case all of them
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -205,7 +227,7 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendArgs a) {
       pairs[i] = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
     }
   }
-  append_rows(a, grec, rec, r0, nrow, pairs, lane);
+  append_rows(a, grec, rec, s_queue[threadIdx.x >> 5], r0, nrow, pairs, lane);
   }
 }
 
@@ -232,6 +254,7 @@ __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(_
 
 __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs r, const AppendArgs a) {
   __shared__ __align__(16) uint8_t s_unit[8][RKV];
+  __shared__ uint32_t s_queue[8][64];                             // one row per launch: at most 64 escape entries
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -285,7 +308,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs r, cons
     const float c = r.cos_t[p * 64 + (d0 >> 1)], sn = r.sin_t[p * 64 + (d0 >> 1)];
     pairs[0] = rope_pair(n0, n1, c, sn);
   }
-  append_rows(a, a.kv + unit_off(blk, a.H, h, kvi, half), s_unit[threadIdx.x >> 5], (int)(s0 % PAGE), 1, pairs, lane);
+  append_rows(a, a.kv + unit_off(blk, a.H, h, kvi, half), s_unit[threadIdx.x >> 5], s_queue[threadIdx.x >> 5],
+              (int)(s0 % PAGE), 1, pairs, lane);
 }
 
 // ------------------------------------------------------------------------------------------------ record decode
