@@ -7,9 +7,10 @@
 // 512-column slice of every activation row.  Eight consumer warps each take one record of the unit: three 128-bit
 // shared loads per lane give the lane's fragment of the record, five integer ops per four weights decode it into the
 // mma.m16n8k16 A fragment, escapes are patched in registers, and the activations come in as B fragments by ldmatrix.
-// Accumulators stay in registers across the units of a tile; at the end of a tile the eight warps are summed in warp
-// order in shared memory.  A tile whose units span several CTAs is finished by the last CTA to arrive, which adds
-// the partial sums in CTA order, so results are bit-identical from run to run.
+// Accumulators stay in registers across the units of a tile; at the end of a tile a reducer warp sums the eight warps
+// in warp order in shared memory.  A tile whose units span several CTAs is finished through exchange slots in the
+// workspace (see the reducer warp): its parts are added in one fixed order, so results are bit-identical from run to
+// run, and the CTA that arrives second pays a single round trip.
 //
 // The same kernel serves the mixture-of-experts products: MODE 1 makes every (token, expert) slot its own problem
 // with one activation row; MODE 2 makes every block of 8 slots of one expert (moe_align_block_size layout) a problem.
@@ -547,8 +548,7 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act
   constexpr int EL = 16 * 8 * NT;
   const size_t fixed = XROW + p.xw_bytes + (size_t)(NT == 1 ? 4 : 2) * CW * EL * 4 + (2 * 16 + 9) * 8 + 16;
   // Two CTAs per SM, each with the deepest ring (at most 8 stages) that fits half of the SM's shared memory; one CTA
-  // when even two stages do not fit twice (32 activation rows).  Measured alternatives that lost: three CTAs of four
-  // stages at 64 registers per thread, and grids that cut tiles when a tile-aligned grid exists.
+  // when even two stages do not fit twice (32 activation rows).
   static const int want_per_sm = tune("STATETREE_GEMV_CTAS_PER_SM", 2), max_stages = tune("STATETREE_GEMV_STAGES", 8),
                    align = tune("STATETREE_GEMV_ALIGN", 1), min_units = tune("STATETREE_GEMV_MIN_UNITS", 2);
   int per_sm = want_per_sm < 1 ? 1 : (want_per_sm > 2 ? 2 : want_per_sm);
@@ -571,8 +571,8 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act
   // meets its neighbour last on a cut tile pays an exchange round trip at its tail: worth about three units of work.
   // A grid whose boundaries fall on tile boundaries (or that cuts every tile into equal parts) pays nothing, but leaves
   // slots empty and quantises the work.  Take the largest such grid with at least half the slots, and choose between
-  // the two by the units of the longest CTA (12288 x 4096: cut, 20.8 + 3 units against 24; 4096 x 4096: whole tiles,
-  // 8 against 6.9 + 3).
+  // the two by the units of the longest CTA (12288 x 4096 on 296 slots: cut, 20.8 + 3 units against 24 on 256 whole-
+  // tile CTAs; 4096 x 4096: whole tiles, 8 against 6.9 + 3).
   static const int cut_cost = tune("STATETREE_GEMV_CUT_COST", 3), align_pct = tune("STATETREE_GEMV_ALIGN_PCT", 50);
   if (act) {                                                   // SwiGLU epilogue: every CTA owns whole gate / up tile pairs
     const long long pairs = (long long)nprob * p.T / 2;
