@@ -593,6 +593,9 @@ def main():
     ap.add_argument("--no-bf16", action="store_true", help="skip the dense BF16 (cuBLAS) control pass")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M = 8 / 32 / 64 / 256 points of the default run")
     ap.add_argument("--no-fused", action="store_true", help="skip the extra pass with fused q/k/v and gate/up trees")
+    ap.add_argument("--per-linear", action="store_true",
+                    help="one GPU, GEMV batches: one launch per linear (7 per layer) as the main step instead of the list "
+                         "launches for q/k/v and gate/up (4 per layer)")
     ap.add_argument("--moe-batch", default="1,8,32,64,512,2048")
     ap.add_argument("--moe-no-gemm", action="store_true", help="moe workload: grouped GEMV at every size (for comparison)")
     ap.add_argument("--model", default="qwen3-8b", choices=["qwen3-8b", "qwen3-30b-a3b"],
@@ -625,7 +628,9 @@ def main():
                           f" x {args.layers} layers, batch M={args.batch}, seeds per shape, N(0,0.02) + 1% columns x8",
               "batch": args.batch, "layers": args.layers,
               "l2": "inputs larger than L2: 10.5 GB of distinct record buffers per step",
-              "parallelism": "single GPU, one launch per linear" if world == 1 else
+              "parallelism": ("single GPU, one launch per linear" if args.per_linear or args.batch > 12 else
+                              "single GPU; the seven trees of a layer in four launches: q/k/v and gate/up (separate trees, "
+                              "shared input) as one list launch each, o and down one launch each") if world == 1 else
               f"tp{world} (q/k/v and gate/up of a rank as fused trees, o/down column shards + all-reduce of their outputs "
               "over NVLink peer memory, one kernel per rank)"}
 
@@ -717,8 +722,21 @@ def main():
     st = _state(dev)
     ws_need = max((E.gemv_workspace_bytes if use_gemv else E.gemm_workspace_bytes)(tl.out_features, tl.in_features, B)
                   for tl in layers[0])
+    use_lists = world == 1 and use_gemv and not args.per_linear
+    if use_lists:
+        ws_need = max(ws_need, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, B),
+                      E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, B))
     ws = st.get_ws(ws_need)
     cnt = st.get_cnt(4096)
+
+    def list_args(row, lo, hi):
+        tabs = []
+        for tl in row[lo:hi]:
+            eo, el, eb = tl._tables
+            tabs.append((tl.tree, eo, eb, el))
+        return E.gemv_list_args(tabs, outs[lo:hi])
+
+    lists = [(list_args(row, 0, 3), list_args(row, 4, 6)) for row in layers] if use_lists else None
 
     def one(tl, xin, y):
         eo, el, eb = tl._tables
@@ -752,7 +770,16 @@ def main():
                             "unsharded weights; bit-identical on every rank"}
     del shard
 
-    def run_layers():
+    def run_lists():
+        # q / k / v and gate / up read the same activations: each group is one launch over the members' trees
+        for row, (qkv, gate_up) in zip(layers, lists):
+            E.gemv_list(qkv, x, ws)
+            one(row[3], ins[3], outs[3])
+            E.gemv_list(gate_up, x, ws)
+            one(row[6], ins[6], outs[6])
+        return 4 * len(layers)
+
+    def run_per_linear():
         n = 0
         for row in layers:
             for tl, xin, y, kind in zip(row, ins, outs, kinds):
@@ -762,6 +789,8 @@ def main():
                     reduce_partials(y)
                     n += 1                                   # the peer-memory all-reduce is one kernel of this library
         return n
+
+    run_layers = run_lists if use_lists else run_per_linear
 
     side = torch.cuda.Stream(dev)
     with torch.cuda.stream(side):
@@ -817,6 +846,23 @@ def main():
     ms_e2e = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- the same step with one launch per linear (7 per layer)
+    per_linear = None
+    if use_lists:
+        with torch.cuda.stream(side):
+            run_per_linear()
+        side.synchronize()
+        pgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(pgraph, stream=side):
+            run_per_linear()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            pgraph.replay()
+        ms_p = timed(pgraph.replay, args.steps)
+        per_linear = {"what": "the same trees and bytes, one launch per linear (7 per layer)", "ms_per_step": ms_p,
+                      "value": step_bytes / (ms_p * 1e-3) / 1e9, "unit": "GB/s",
+                      "frac": step_bytes / (ms_p * 1e-3) / 1e9 / peaks()[0], "gpu_launches": 7 * args.layers * args.steps}
+        del pgraph
     # ---- the same step with q/k/v and gate/up stored as fused trees (how the reference's model conversion stores
     # them, statetree/model.py DEFAULT_FUSE, and how its per-layer-kind GEMV table is measured): 4 launches per layer
     fused = None
@@ -977,6 +1023,8 @@ def main():
             "bf16_equivalent_gbs": value * 16.0 / 12.125}
     if tp_check is not None:
         line["tp_check"] = tp_check
+    if per_linear is not None:
+        line["one_launch_per_linear"] = per_linear
     if fused is not None:
         line["fused_qkv_gate_up"] = fused
     if control is not None:

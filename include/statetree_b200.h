@@ -57,6 +57,18 @@ int64_t st_gemv_workspace_bytes(int64_t M, int64_t N, int64_t B);
 int st_gemv(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* X, void* Y,
             float* Yf32, int64_t B, int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);
 
+/* One activation batch X [B, N] times a LIST of 1 to 4 matrices that share N (the q / k / v or gate / up projections of
+ * a checkpoint that stores them as separate trees), in one launch: Y[i] [B, M[i]] = X W[i]^T.  The members' tiles are
+ * concatenated into one virtual matrix, so the list pays one launch, one ring fill and one tail.  trees / eo / eb / el /
+ * Y / Yf32 / M are HOST arrays of n entries (Yf32 or any of its entries may be NULL); ws as for st_gemv, sized by
+ * st_gemv_list_workspace_bytes.  Results are bit-identical from run to run; they equal st_gemv on each member wherever
+ * both cut the member's tiles alike.  The reference reaches the same end by fusing the trees at conversion time
+ * (statetree/model.py:22-24 DEFAULT_FUSE); this entry gives unfused checkpoints the same launch count. */
+int64_t st_gemv_list_workspace_bytes(int64_t n, const int64_t* M, int64_t N, int64_t B);
+int st_gemv_list(int64_t n, const void* const* trees, const int32_t* const* eo, const uint32_t* const* eb,
+                 const uint32_t* const* el, const void* X, void* const* Y, float* const* Yf32, int64_t B,
+                 const int64_t* M, int64_t N, void* ws, int64_t ws_bytes, void* stream);
+
 /* st_gemv for callers that cannot allocate device memory and so have no workspace to pass: code running inside a
  * host framework that owns the whole device pool, or anywhere cudaMalloc is off limits.  The exchange slots of tiles
  * shared between CTAs live in a 4.06 MiB array built into the library (present on every GPU that loads it, until exit),

@@ -14,6 +14,9 @@
 //
 // The same kernel serves the mixture-of-experts products: MODE 1 makes every (token, expert) slot its own problem
 // with one activation row; MODE 2 makes every block of 8 slots of one expert (moe_align_block_size layout) a problem.
+// MODE 3 multiplies one activation batch by a short LIST of matrices with the same number of columns (q / k / v, or
+// gate / up, stored as separate trees) in one launch: their tiles are concatenated into one virtual matrix, so the list
+// pays the launch, ring fill and tail of a single kernel, and each member writes its own output.
 #include "../../include/statetree_b200.h"
 #include "st_common.cuh"
 #include <stdlib.h>
@@ -30,8 +33,17 @@ constexpr int CW = 8;                     // consumer warps = records per unit
 constexpr int UNIT_BYTES = CW * REC;      // 12416
 constexpr int SIDE_BYTES = 64;            // escape block of a unit
 constexpr int XROW = CW * 128 + 16;       // bytes per staged activation row (512 columns + pad: conflict-free ldmatrix)
-constexpr int MODE_DENSE = 0, MODE_SLOT = 1, MODE_GROUP = 2;
+constexpr int MODE_DENSE = 0, MODE_SLOT = 1, MODE_GROUP = 2, MODE_LIST = 3;
+constexpr int MAXL = 4;                   // matrices in one MODE_LIST launch
 constexpr uint32_t EMPTY_SLOT = 0xFFFFFFFFu;  // what every word of the workspace holds between launches
+
+struct ListTab {                          // MODE_LIST: the members of the list, by value in the kernel arguments
+  const uint8_t* tree[MAXL]; const int* eo[MAXL]; const uint32_t* eb[MAXL]; const uint32_t* el[MAXL];
+  uint16_t* Y[MAXL]; float* Yf[MAXL];
+  int M[MAXL];                            // rows of each member
+  int tend[MAXL];                         // first tile after each member in the concatenation
+  int n;
+};
 
 struct GemvArgs {
   // dense: one matrix; MoE: per-expert device address tables
@@ -46,8 +58,9 @@ struct GemvArgs {
   int E, xdiv;
   int NG, CPT, T;                         // column groups, units per tile, tiles per problem
   long long U;                            // units over all problems
-  int nprob, maxcover, stages, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
+  int nprob, maxcover, stages, fill, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
   int act;                                // dense mode: rows are gate / up tiles in turn, the reducer stores silu(gate) * up
+  ListTab lt;
 };
 
 struct Prob {                             // what a unit's problem resolves to
@@ -55,11 +68,28 @@ struct Prob {                             // what a unit's problem resolves to
   bool skip;
 };
 
+struct Member {                           // MODE_LIST: the list member a tile of the concatenation belongs to
+  const uint8_t* tree; const int* eo; const uint32_t* eb; const uint32_t* el;
+  uint16_t* Y; float* Yf; long long M;
+  int tile;                               // the tile's index inside the member
+  int end;                                // first tile (of the concatenation) after the member
+};
+__device__ __forceinline__ Member member_of(const GemvArgs& a, int tile) {
+  int m = 0;
+  while (m + 1 < a.lt.n && tile >= a.lt.tend[m]) ++m;
+  Member r;
+  r.tree = a.lt.tree[m]; r.eo = a.lt.eo[m]; r.eb = a.lt.eb[m]; r.el = a.lt.el[m];
+  r.Y = a.lt.Y[m]; r.Yf = a.lt.Yf[m]; r.M = a.lt.M[m];
+  r.tile = tile - (m ? a.lt.tend[m - 1] : 0);
+  r.end = a.lt.tend[m];
+  return r;
+}
+
 template <int MODE>
 __device__ __forceinline__ Prob resolve(const GemvArgs& a, int p) {
   Prob r;
   r.skip = false;
-  if (MODE == MODE_DENSE) {
+  if (MODE == MODE_DENSE || MODE == MODE_LIST) {               // (a list resolves per tile: UnitCursor::retile)
     r.tree = a.tree; r.eo = a.eo; r.eb = a.eb; r.el = a.el;
     return r;
   }
@@ -82,7 +112,7 @@ __device__ __forceinline__ Prob resolve(const GemvArgs& a, int p) {
 // activation row / output row of column n of problem p; -1 = unused column
 template <int MODE>
 __device__ __forceinline__ long long out_row(const GemvArgs& a, int p, int n) {
-  if (MODE == MODE_DENSE) return n < a.B ? n : -1;
+  if (MODE == MODE_DENSE || MODE == MODE_LIST) return n < a.B ? n : -1;
   if (MODE == MODE_SLOT) return n == 0 ? p : -1;
   const int s = a.sorted[p * 8 + n];
   return (n < 8 && s >= 0 && s < a.B) ? s : -1;
@@ -99,6 +129,18 @@ struct UnitCursor {
   int u, end, p, tile, c;
   int seg, b0, e0, b1, e1;
   Prob pr;
+  Member mb;                                                           // MODE_LIST only
+  __device__ __forceinline__ void retile(const GemvArgs& a) { if (MODE == MODE_LIST && u < end) mb = member_of(a, tile); }
+  __device__ __forceinline__ void next_tile(const GemvArgs& a) {     // tile was just incremented
+    if (MODE != MODE_LIST) return;
+    if (tile < mb.end) ++mb.tile;
+    else retile(a);
+  }
+  __device__ __forceinline__ int ltile() const { return MODE == MODE_LIST ? mb.tile : tile; }
+  __device__ __forceinline__ const uint8_t* tree() const { return MODE == MODE_LIST ? mb.tree : pr.tree; }
+  __device__ __forceinline__ const int* eo() const { return MODE == MODE_LIST ? mb.eo : pr.eo; }
+  __device__ __forceinline__ const uint32_t* eb() const { return MODE == MODE_LIST ? mb.eb : pr.eb; }
+  __device__ __forceinline__ const uint32_t* el() const { return MODE == MODE_LIST ? mb.el : pr.el; }
   __device__ __forceinline__ void seek(const GemvArgs& a, int ub, int ue) {
     u = ub; end = ue;
     if (u >= end) return;
@@ -107,6 +149,7 @@ struct UnitCursor {
     const int ul = u - p * upp;
     tile = ul / a.CPT; c = ul - tile * a.CPT;
     enter(a);
+    retile(a);
   }
   __device__ __forceinline__ void enter(const GemvArgs& a) {          // (p, tile, c) just changed problem
     while (u < end) {
@@ -134,6 +177,7 @@ struct UnitCursor {
     if (c == a.CPT) {
       c = 0;
       if (++tile == a.T) { tile = 0; ++p; enter(a); }
+      next_tile(a);
     }
     if (u >= end && seg == 0) { seg = 1; seek(a, b1, e1); }
   }
@@ -142,6 +186,7 @@ struct UnitCursor {
     if (++c == a.CPT) {
       c = 0;
       if (++tile == a.T) { tile = 0; ++p; enter(a); }
+      next_tile(a);
     }
     if (u >= end && seg == 0) { seg = 1; seek(a, b1, e1); }
   }
@@ -181,7 +226,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
   if (tid >= 64 && tid < 64 + XROW / 16) reinterpret_cast<uint4*>(zrow)[tid - 64] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   pdl_launch_dependents();                 // the next kernel in the stream may start its own weight prefetch
-  if (MODE != MODE_DENSE) pdl_wait();      // expert ids / slot tables come from earlier kernels: read nothing before
+  if (MODE == MODE_SLOT || MODE == MODE_GROUP) pdl_wait();   // expert ids / slot tables come from earlier kernels
   if (MODE == MODE_GROUP) {
     // The block table is sized for the worst case on the host; how many blocks the routing filled is known only here.
     // The CTAs share the tiles of the blocks in use, whole tiles each, so no CTA idles over the unused tail and no
@@ -207,7 +252,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       if (k.p != lastp) {
         lastp = k.p;
         const long long r = lane < NX ? out_row<MODE>(a, k.p, lane) : -1;
-        xrow = r < 0 ? nullptr : a.X + (MODE == MODE_DENSE ? r : r / a.xdiv) * a.N;
+        xrow = r < 0 ? nullptr : a.X + ((MODE == MODE_DENSE || MODE == MODE_LIST) ? r : r / a.xdiv) * a.N;
         nx = a.xwhole ? 0u : __popc(__ballot_sync(FULL, xrow != nullptr));
       }
     };
@@ -216,11 +261,11 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       uint8_t* st = ring + (size_t)s * STAGE;
       if (lane == 0) {
         mbar_expect_tx(full + s, (uint32_t)(nrec * REC + SIDE_BYTES) + nx * (uint32_t)(nrec * 128));
-        bulk_g2s(st, k.pr.tree + ((size_t)k.tile * a.NG + (size_t)k.c * CW) * REC, (uint32_t)(nrec * REC), full + s, pol_w);
+        bulk_g2s(st, k.tree() + ((size_t)k.ltile() * a.NG + (size_t)k.c * CW) * REC, (uint32_t)(nrec * REC), full + s, pol_w);
       }
       __syncwarp();
       if (lane == 1)
-        bulk_g2s(st + UNIT_BYTES, k.pr.eb + ((size_t)k.tile * a.CPT + k.c) * 16, SIDE_BYTES, full + s, pol_w);
+        bulk_g2s(st + UNIT_BYTES, k.eb() + ((size_t)k.ltile() * a.CPT + k.c) * 16, SIDE_BYTES, full + s, pol_w);
     };
     auto acts = [&](const UnitCursor<MODE>& k, int s) {
       if (!a.xwhole && xrow != nullptr)
@@ -232,19 +277,19 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     // first ring fill: weights, then wait for the previous kernel, then the activations
     UnitCursor<MODE> pre = cur;
     int filled = 0;
-    if (MODE == MODE_DENSE) {                                  // lane i fills stage i
-      const bool on = lane < S && mine.valid();
+    if (MODE == MODE_DENSE || MODE == MODE_LIST) {             // lane i fills stage i
+      const bool on = lane < a.fill && mine.valid();
       if (on) {
         const int nrec = mine.nrec(a);
         uint8_t* st = ring + (size_t)lane * STAGE;
         mbar_expect_tx(full + lane, (uint32_t)(nrec * REC + SIDE_BYTES) + (a.xwhole ? 0u : (uint32_t)(NX * nrec * 128)));
-        bulk_g2s(st, mine.pr.tree + ((size_t)mine.tile * a.NG + (size_t)mine.c * CW) * REC, (uint32_t)(nrec * REC),
+        bulk_g2s(st, mine.tree() + ((size_t)mine.ltile() * a.NG + (size_t)mine.c * CW) * REC, (uint32_t)(nrec * REC),
                  full + lane, pol_w);
-        bulk_g2s(st + UNIT_BYTES, mine.pr.eb + ((size_t)mine.tile * a.CPT + mine.c) * 16, SIDE_BYTES, full + lane, pol_w);
+        bulk_g2s(st + UNIT_BYTES, mine.eb() + ((size_t)mine.ltile() * a.CPT + mine.c) * 16, SIDE_BYTES, full + lane, pol_w);
       }
       filled = __popc(__ballot_sync(FULL, on));
     } else {
-      for (; pre.valid() && filled < S; pre.next(a), ++filled) { row_of(pre); weights(pre, filled); }
+      for (; pre.valid() && filled < a.fill; pre.next(a), ++filled) { row_of(pre); weights(pre, filled); }
     }
     pdl_wait();
     if (a.xwhole) {                                            // every activation row once, whole
@@ -259,11 +304,15 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       acts(cur, s);
       ++s;
     }
-    s = 0;                                                     // filled == S whenever units remain
-    uint32_t ph = 0;
+    // the stages beyond the first fill are taken without a wait on their first use
+    int fresh = S - filled;
+    s = fresh > 0 ? filled : 0;
+    uint32_t ph = fresh > 0 ? 1u : 0u;                         // flips to 0 at the first wrap
     for (; cur.valid(); cur.next(a)) {
       row_of(cur);
-      if (!mbar_wait(empty + s, ph)) {
+      if (fresh > 0) {
+        --fresh;
+      } else if (!mbar_wait(empty + s, ph)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
         break;
       }
@@ -311,6 +360,10 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       if (lane == 0) mbar_arrive(freeb + buf);
       const int tbase = cur.u - cur.c;                          // first unit of the tile
       const bool owned = tbase >= u0 && tbase + a.CPT <= u1;
+      uint16_t* const Yp = MODE == MODE_LIST ? cur.mb.Y : a.Y;  // where this tile's results go
+      float* const Yfp = MODE == MODE_LIST ? cur.mb.Yf : a.Yf;
+      const long long Mp = MODE == MODE_LIST ? cur.mb.M : a.M;
+      const size_t row0 = (size_t)cur.ltile() * 16;
       long long orow[EL / 32];                                  // output row of each of this lane's values, -1 = none
 #pragma unroll
       for (int k = 0; k < EL / 32; ++k) orow[k] = out_row<MODE>(a, cur.p, (lane + 32 * k) >> 4);
@@ -337,8 +390,8 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
             if (level == last_level) {
               const int r = (lane + 32 * k) & 15;
               const __nv_bfloat16 hv = __float2bfloat16_rn(v);
-              a.Y[orow[k] * a.M + (size_t)cur.tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-              if (a.Yf) a.Yf[orow[k] * a.M + (size_t)cur.tile * 16 + r] = v;
+              Yp[orow[k] * Mp + row0 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+              if (Yfp) Yfp[orow[k] * Mp + row0 + r] = v;
               break;
             }
             ++level;
@@ -369,8 +422,8 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
           const int r = (lane + 32 * k) & 15;
           if (orow[k] >= 0) {
             const __nv_bfloat16 hv = __float2bfloat16_rn(sum[k]);
-            a.Y[orow[k] * a.M + (size_t)cur.tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-            if (a.Yf) a.Yf[orow[k] * a.M + (size_t)cur.tile * 16 + r] = sum[k];
+            Yp[orow[k] * Mp + row0 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+            if (Yfp) Yfp[orow[k] * Mp + row0 + r] = sum[k];
           }
         }
       }
@@ -378,13 +431,12 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     return;
   }
 
-  // -------------------------------------------------------------------- consumers
+  // -------------------------------------------------------------------- consumers.  To them a list is one dense
+  // matrix (the concatenation): they walk it with the dense cursor and look a member up only for a crowded record.
+  UnitCursor<MODE == MODE_LIST ? MODE_DENSE : MODE> cc;
+  cc.init(a, u0, u1);
   const int g = lane >> 2, rec = warp;
-#ifdef ST_V3
-  constexpr int NCH = NT == 1 ? 4 : 2;                       // independent accumulator chains per column tile
-#else
-  constexpr int NCH = 2;
-#endif
+  constexpr int NCH = 2;                                     // independent accumulator chains per column tile
   float acc[NT][NCH][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -419,18 +471,26 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
           patch_entry(A, __shfl_sync(FULL, sw, src), lane);
         }
       } else {                                               // crowded unit: this record's own list
-        const size_t r = (size_t)cur.tile * a.NG + (size_t)c * CW + rec;
-        const int lo = __ldg(cur.pr.eo + r), hi = __ldg(cur.pr.eo + r + 1);
+        // (a list looks its member up here, on the rare path, so the consumers carry no member state in their loop)
+        const int* eo_ = cc.pr.eo;
+        const uint32_t* el_ = cc.pr.el;
+        int lt = cc.tile;
+        if (MODE == MODE_LIST) {
+            const Member mm = member_of(a, cc.tile);
+            eo_ = mm.eo; el_ = mm.el; lt = mm.tile;
+        }
+        const size_t r = (size_t)lt * a.NG + (size_t)c * CW + rec;
+        const int lo = __ldg(eo_ + r), hi = __ldg(eo_ + r + 1);
         for (int base = lo; base < hi; base += 32) {
           const int n = min(32, hi - base);
-          const uint32_t ent = (lane < n) ? __ldg(cur.pr.el + base + lane) : 0u;
+          const uint32_t ent = (lane < n) ? __ldg(el_ + base + lane) : 0u;
           for (int i = 0; i < n; ++i) patch_entry(A, __shfl_sync(FULL, ent, i), lane);
         }
       }
     }
   };
-  while (cur.valid()) {
-    const int len = cur.run_len(a), cbeg = cur.c;
+  while (cc.valid()) {
+    const int len = cc.run_len(a), cbeg = cc.c;
     for (int j = 0; j < len; ++j) {
       const int c = cbeg + j;
       if (!xready) {                                          // whole activation rows: waited for once
@@ -457,12 +517,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
           ldmatrix_x4(xa + 64, b[nt][4], b[nt][5], b[nt][6], b[nt][7]);
         }
         const uint32_t sw0 = *reinterpret_cast<const uint32_t*>(st + UNIT_BYTES);            // escape block, word 0
-#ifdef ST_V5
-        uint32_t sw = 0u;                                     // inline entries: read only when this record has escapes
-        if ((sw0 >> (16 + rec)) & 1u) sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];
-#else
         const uint32_t sw = reinterpret_cast<const uint32_t*>(st + UNIT_BYTES)[lane & 15];   // inline entries
-#endif
         const RecRegs raw = load_rec_shared(st + rec * REC, lane);
         // everything this warp needs from the stage is in registers: hand the slot back before the arithmetic
         __syncwarp();
@@ -495,7 +550,6 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         t4[q] = acc[nt][0][q] + acc[nt][1][q];
-        if (NCH == 4) t4[q] += acc[nt][2][q] + acc[nt][3][q];
       }
       mine[n0 * 16 + g] = t4[0];
       mine[(n0 + 1) * 16 + g] = t4[1];
@@ -506,12 +560,12 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(done + buf);
-    cur.advance(a, len);
+    cc.advance(a, len);
   }
 }
 
 struct Plan {
-  int C, stages, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
+  int C, stages, fill, maxcover, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
   size_t smem;
   long long U;
   int CPT, T, NG, nprob;
@@ -590,6 +644,12 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act
     }
   }
   const long long per = p.U / p.C;
+  // First ring fill.  A CTA with a short range starts sooner when it asks for three stages at first and for the others
+  // as it goes (the copies of a fill share the SM's load path, so the first one lands later the more there are); a CTA
+  // with a long range gains more from the deeper start.
+  static const int fill = tune("STATETREE_GEMV_FILL", 0), fill_units = tune("STATETREE_GEMV_FILL_UNITS", 16);
+  p.fill = fill > 0 ? fill : (per <= fill_units ? 3 : p.stages);
+  if (p.fill > p.stages) p.fill = p.stages;
   long long mc = (p.CPT + per - 1) / per + 1;
   if (mc > p.CPT) mc = p.CPT;
   p.maxcover = (int)(mc < 1 ? 1 : mc);
@@ -598,8 +658,8 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act
 
 template <int NT, int MODE>
 int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
-  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE, a.act != 0);
-  a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages;
+  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE || MODE == MODE_LIST, a.act != 0);
+  a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages; a.fill = p.fill;
   a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows; a.xwhole = p.xwhole; a.xw_stride = p.xw_stride;
   a.xw_bytes = p.xw_bytes;
   const long long need = (long long)nprob * p.T * p.maxcover * 16 * 8 * NT * 4;
@@ -679,14 +739,54 @@ extern "C" int st_gemv_swiglu(const void* tree, const int32_t* eo, const uint32_
                     (cudaStream_t)stream);
 }
 
+extern "C" int64_t st_gemv_list_workspace_bytes(int64_t n, const int64_t* M, int64_t N, int64_t B) {
+  if (n < 1 || n > MAXL || !M || N <= 0 || N % 64 || B < 1 || B > 32) return -1;
+  int64_t total = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    if (M[i] <= 0 || M[i] % 16) return -1;
+    total += M[i];
+  }
+  return B <= 8 ? ws_need<1>(total, N, 1, (int)B) : (B <= 16 ? ws_need<2>(total, N, 1, (int)B) : ws_need<4>(total, N, 1, (int)B));
+}
+
+extern "C" int st_gemv_list(int64_t n, const void* const* trees, const int32_t* const* eo, const uint32_t* const* eb,
+                            const uint32_t* const* el, const void* X, void* const* Y, float* const* Yf32, int64_t B,
+                            const int64_t* M, int64_t N, void* ws, int64_t ws_bytes, void* stream) {
+  const char* who = "st_gemv_list";
+  ST_REQUIRE(n >= 1 && n <= MAXL, "%s: 1 to %d matrices per call (got %lld)", who, MAXL, (long long)n);
+  ST_REQUIRE(trees && eo && eb && el && X && Y && M, "%s: null pointer", who);
+  ST_REQUIRE(st::aligned16(X), "%s: X must be 16-byte aligned", who);
+  GemvArgs a = {};
+  long long total = 0;
+  for (int i = 0; i < (int)n; ++i) {
+    ST_REQUIRE(trees[i] && eo[i] && eb[i] && el[i] && Y[i], "%s: null pointer in member %d", who, i);
+    ST_REQUIRE(st::aligned16(trees[i]) && st::aligned16(eb[i]), "%s: tree and eb of member %d must be 16-byte aligned", who, i);
+    ST_REQUIRE(M[i] > 0 && M[i] % 16 == 0 && M[i] < (1ll << 31), "%s: rows of member %d must be a positive multiple of 16", who, i);
+    a.lt.tree[i] = (const uint8_t*)trees[i]; a.lt.eo[i] = eo[i]; a.lt.eb[i] = eb[i]; a.lt.el[i] = el[i];
+    a.lt.Y[i] = (uint16_t*)Y[i]; a.lt.Yf[i] = Yf32 ? Yf32[i] : nullptr;
+    a.lt.M[i] = (int)M[i];
+    total += M[i];
+    a.lt.tend[i] = (int)(total / 16);
+  }
+  a.lt.n = (int)n;
+  if (int e = shape_checks(who, total, N, B)) return e;
+  a.tree = a.lt.tree[0]; a.eo = a.lt.eo[0]; a.eb = a.lt.eb[0]; a.el = a.lt.el[0];
+  a.X = (const uint16_t*)X; a.Y = a.lt.Y[0]; a.ws = (float*)ws;
+  a.M = total; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (B <= 8) return launch<1, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
+  if (B <= 16) return launch<2, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
+  return launch<4, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
+}
+
 // ---------------------------------------------------------------------------------------------- st_gemv_static
 // The same GEMV for callers that cannot hand over a workspace because they cannot allocate device memory at all: a
 // plugin running inside a serving process whose memory pool is owned (and fully reserved) by the host framework, or
-// code that runs where cudaMalloc is forbidden.  Its split partial sums and tile semaphores live in the file-scope
-// array below instead of caller buffers.  Every GPU that loads the library carries the array (4.06 MiB) until exit.
+// code that runs where cudaMalloc is forbidden.  The exchange slots of its cut tiles live in the file-scope array
+// below instead of a caller buffer.  Every GPU that loads the library carries the array (4.06 MiB) until exit.
 namespace {
-constexpr long long STATIC_WS_BYTES = 4ll << 20;        // fp32 partial sums of tiles shared between CTAs
-constexpr long long STATIC_TILES = 16384;               // one int32 semaphore per 16-row tile: M <= 262144
+constexpr long long STATIC_WS_BYTES = 4ll << 20;        // fp32 exchange slots of tiles cut between CTAs
+constexpr long long STATIC_TILES = 16384;               // tiles a shape may have (M <= 262144); the tail of the array is spare
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_WS_BYTES + STATIC_TILES * 4];
 unsigned char* g_static_addr[64];                       // device address of the array, per device
 std::mutex g_static_mu;
@@ -704,8 +804,8 @@ extern "C" int st_gemv_static(const void* tree, const int32_t* eo, const uint32_
   const long long need = B <= 8 ? ws_need<1>(M, N, 1, (int)B) : (B <= 16 ? ws_need<2>(M, N, 1, (int)B)
                                                                          : ws_need<4>(M, N, 1, (int)B));
   ST_REQUIRE(need <= STATIC_WS_BYTES && M / 16 <= STATIC_TILES,
-             "st_gemv_static: this shape needs %lld bytes of partial sums and %lld semaphores; the built-in scratch "
-             "holds %lld bytes and %lld semaphores (use st_gemv with a caller workspace)",
+             "st_gemv_static: this shape needs %lld bytes of exchange slots and has %lld tiles; the built-in scratch "
+             "holds %lld bytes and allows %lld tiles (use st_gemv with a caller workspace)",
              need, (long long)(M / 16), STATIC_WS_BYTES, STATIC_TILES);
   int dev = 0;
   if (int e = st::cuda_fail(cudaGetDevice(&dev), "st_gemv_static: cudaGetDevice")) return e;

@@ -279,6 +279,43 @@ def swiglu(self, x):
 TreeLinear.swiglu = swiglu
 
 
+@torch.no_grad()
+def forward_list(layers, x):
+    """[layer(x) for layer in layers] for TreeLinear layers that read the same input (q / k / v or gate / up of a
+    checkpoint that keeps them as separate trees): up to GEMV_MAX rows and four layers run as ONE launch over the
+    concatenation of their tiles; anything else falls back to one call per layer."""
+    first = layers[0]
+    home = first.tree.device
+    same = all(l.in_features == first.in_features and l.tree.device == home for l in layers)
+    lead = x.shape[:-1]
+    acts = _rows_2d(x if x.device == home else x.to(home), first.in_features) if same and home.type == "cuda" else None
+    if acts is None or not 1 <= acts.shape[0] <= min(GEMV_MAX, 32) or not 2 <= len(layers) <= 4:
+        return [l(x) for l in layers]
+    E, B = ext(), acts.shape[0]
+    widths = [l.out_features for l in layers]
+    flat = torch.empty(B * sum(widths), dtype=torch.bfloat16, device=home)
+    outs, at = [], 0
+    for w in widths:
+        outs.append(flat[at:at + B * w].view(B, w))
+        at += B * w
+    tabs = []
+    for l in layers:
+        eo, el, eb = l.tables()
+        tabs.append((l.tree, eo, eb, el))
+    with torch.cuda.device(home):
+        ws = _state(home).get_ws(E.gemv_list_workspace_bytes(widths, first.in_features, B))
+        E.gemv_list(E.gemv_list_args(tabs, outs), acts, ws)
+    res = []
+    for l, y in zip(layers, outs):
+        if l.bias is not None:
+            y += l.bias
+        y = y.view(*lead, l.out_features)
+        if x.dtype != torch.bfloat16:
+            y = y.to(x.dtype)
+        res.append(y if x.device == home else y.to(x.device))
+    return res
+
+
 class TreeSlice(nn.Module):
     """One of several linear layers that read the same input (q / k / v, gate / up), stored together as one TreeLinear
     on the parent module: rows [start, start + size) of that layer's output.  `fused` is the shared layer; it is not

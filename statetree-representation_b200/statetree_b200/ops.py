@@ -26,6 +26,8 @@ _SIGNATURES = {
     "st_gemv_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "st_gemv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_static": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "st_gemv_list_workspace_bytes": (_i64, [_i64, _vp, _i64, _i64]),
+    "st_gemv_list": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "st_gemm_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "st_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_moe_gemv_workspace_bytes": (_i64, [_i64, _i64, _i64]),
@@ -150,6 +152,34 @@ class _Weights:
         M = Y.shape[1]
         with _ctx(T):
             _check(lib().st_gemv_static(_ptr(T), _ptr(EO), _ptr(EB), _ptr(EL), _ptr(X), _ptr(Y), B, M, N, _stream(T)))
+
+    @staticmethod
+    def gemv_list_workspace_bytes(Ms, N, B):
+        arr = (ctypes.c_int64 * len(Ms))(*Ms)
+        return int(lib().st_gemv_list_workspace_bytes(len(Ms), arr, N, B))
+
+    @staticmethod
+    def gemv_list_args(tabs, Ys, Yf32s=None):
+        """host pointer arrays of a list call: tabs = [(T, EO, EB, EL), ...] (1 to 4 matrices that share their column
+        count), Ys = their outputs [B, M_i].  Build once for fixed buffers, pass to gemv_list on every call."""
+        n = len(tabs)
+        VP = ctypes.c_void_p * n
+        cols = [VP(*[_ptr(t[k]) for t in tabs]) for k in range(4)]
+        ys = VP(*[_ptr(y) for y in Ys])
+        yf = VP(*[_ptr(y) for y in Yf32s]) if Yf32s is not None else None
+        Ms = (ctypes.c_int64 * n)(*[t[0].shape[0] * 16 for t in tabs])
+        return (n, cols[0], cols[1], cols[2], cols[3], ys, yf, Ms, tabs[0][0].shape[1] * 64, tabs[0][0].device)
+
+    @staticmethod
+    def gemv_list(args, X, WS):
+        """Y_i = X W_i^T for every member of the list, in one launch"""
+        n, t, eo, eb, el, ys, yf, Ms, N, dev = args
+        B = X.shape[0]
+        if X.shape[1] != N or not X.is_contiguous():
+            raise RuntimeError(f"gemv_list: X must be contiguous [B, {N}]")
+        with torch.cuda.device(dev):
+            _check(lib().st_gemv_list(n, t, eo, eb, el, _ptr(X), ys, yf, B, Ms, N, _ptr(WS),
+                                      WS.numel() * WS.element_size(), torch.cuda.current_stream(dev).cuda_stream))
 
     @staticmethod
     def gemm_workspace_bytes(M, N, B):

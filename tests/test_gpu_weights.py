@@ -99,6 +99,58 @@ def test_gemm_matches_fp64(M, N, regime):
     _status_ok()
 
 
+@pytest.mark.parametrize("Ms,N,regime", [((256, 64, 64), 1024, "mixed"), ((512, 128), 512, "heavy"),
+                                         ((16, 16, 16, 16), 64, "mixed"), ((1024, 256, 256), 4096, "llm"),
+                                         ((768, 768), 2048, "each")])
+def test_gemv_list_matches_fp64(Ms, N, regime):
+    """one launch over a list of matrices that share the activations (q / k / v, gate / up as separate trees): every
+    member's fp32 accumulators against the oracle's fp64 product, BF16 == rounded accumulator, one-hot read-back of
+    escape columns, reruns identical, exchange slots left as they were found"""
+    from statetree_b200 import ops
+    from statetree_b200.linear import forward_list
+    E = ops.ext()
+    Ws = [G.weights(M, N, 11 * i + M + N, regime) for i, M in enumerate(Ms)]
+    made = [layer_from_oracle(W) for W in Ws]
+    tls, encs = [m[0] for m in made], [m[1] for m in made]
+    tabs = []
+    for tl in tls:
+        eo, el, eb = tl.tables()
+        tabs.append((tl.tree, eo, eb, el))
+    torch.cuda.synchronize()
+    for B in (1, 3, 8, 12, 16, 27, 32):
+        rs = np.random.RandomState(B)
+        X = G.to_bf16_bits(rs.standard_normal((B, N)))
+        x = bits_to_torch(X, DEV)
+        ys = [torch.empty(B, M, dtype=torch.bfloat16, device=DEV) for M in Ms]
+        yfs = [torch.empty(B, M, dtype=torch.float32, device=DEV) for M in Ms]
+        nbytes = E.gemv_list_workspace_bytes(list(Ms), N, B)
+        ws = torch.full((max(nbytes // 4, 1),), -1, dtype=torch.int32, device=DEV)
+        args = E.gemv_list_args(tabs, ys, yfs)
+        E.gemv_list(args, x, ws.view(torch.float32))
+        torch.cuda.synchronize()
+        assert bool((ws == -1).all()), (Ms, B, "exchange slots not restored")
+        for W, y, yf in zip(Ws, ys, yfs):
+            ref = oracle.linear_f64(W, X)
+            assert rel_fro(yf.cpu().numpy(), ref) < TOL, (Ms, N, B)
+            assert torch.equal(y, yf.to(torch.bfloat16))
+        again = [torch.empty_like(y) for y in ys]
+        E.gemv_list(E.gemv_list_args(tabs, again), x, ws.view(torch.float32))
+        for y, z in zip(ys, again):
+            assert torch.equal(y, z), (Ms, B, "nondeterministic")
+    # module-level helper (up to GEMV_MAX rows in one launch, more through one call per layer) and exact read-back
+    for B in (1, 8, 40):
+        cols = sorted(set(np.concatenate([e["esc_cols"] for e in encs]).tolist()))[:24] + [0, N - 1]
+        x = torch.zeros(B, N, dtype=torch.bfloat16, device=DEV)
+        for b in range(B):
+            x[b, cols[b % len(cols)]] = 1.0
+        for W, y in zip(Ws, forward_list(tls, x)):
+            want = bits_to_torch(np.stack([W[:, cols[b % len(cols)]] for b in range(B)]), DEV)
+            assert torch.equal(y, want), (Ms, B)
+    with pytest.raises(RuntimeError, match="1 to 4"):
+        E.gemv_list(E.gemv_list_args(tabs * 5, [ys[0]] * (5 * len(tabs))), x[:1].contiguous(), ws.view(torch.float32))
+    _status_ok()
+
+
 def _one_hot_check(tl, W, cols, B):
     N = W.shape[1]
     x = torch.zeros(B, N, dtype=torch.bfloat16, device=DEV)
