@@ -593,6 +593,9 @@ def main():
     ap.add_argument("--no-bf16", action="store_true", help="skip the dense BF16 (cuBLAS) control pass")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M = 8 / 32 / 64 / 256 points of the default run")
     ap.add_argument("--no-fused", action="store_true", help="skip the extra pass with fused q/k/v and gate/up trees")
+    ap.add_argument("--separate-allreduce", action="store_true",
+                    help="tensor parallel: o / down as a GEMV followed by the all-reduce kernel (two launches) instead of the "
+                         "GEMV that sums over the ranks itself")
     ap.add_argument("--per-linear", action="store_true",
                     help="one GPU, GEMV batches: one launch per linear (7 per layer) as the main step instead of the list "
                          "launches for q/k/v and gate/up (4 per layer)")
@@ -631,8 +634,8 @@ def main():
               "parallelism": ("single GPU, one launch per linear" if args.per_linear or args.batch > 12 else
                               "single GPU; the seven trees of a layer in four launches: q/k/v and gate/up (separate trees, "
                               "shared input) as one list launch each, o and down one launch each") if world == 1 else
-              f"tp{world} (q/k/v and gate/up of a rank as fused trees, o/down column shards + all-reduce of their outputs "
-              "over NVLink peer memory, one kernel per rank)"}
+              f"tp{world} (q/k/v and gate/up of a rank as fused trees; o/down column shards whose GEMV adds the ranks' "
+              "fp32 tile sums over NVLink peer memory itself: four launches per layer and rank)"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -658,9 +661,10 @@ def main():
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    comm = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        peer_comm()                                    # IPC set-up of the peer-memory all-reduce, outside any capture
+        comm = peer_comm()                             # IPC set-up of the peer-memory exchange, outside any capture
     E = ops.ext()
     B = args.batch
     assert 1 <= B <= 4096
@@ -745,6 +749,19 @@ def main():
         else:
             E.gemm(tl.tree, eo, el, xin, y, ws, cnt)
 
+    fused_ar = (world > 1 and use_gemv and comm is not None and not args.separate_allreduce
+                and comm.gemv_allreduce_fits(HIDDEN, B))
+
+    def row_parallel(tl, xin, y):
+        """o / down on this rank's column shard, summed over the ranks: returns the launches it took"""
+        if fused_ar:
+            eo, el, eb = tl._tables
+            comm.gemv_allreduce(tl.tree, eo, eb, el, xin, y, ws)
+            return 1
+        one(tl, xin, y)
+        reduce_partials(y)
+        return 2                                             # the peer-memory all-reduce is one kernel of this library
+
     # ---- tensor-parallel check (before any timing): the all-reduced outputs of the row-parallel projections of one
     # layer against the fp64 product over the unsharded weights, and the same bits on every rank
     tp_check = None
@@ -753,8 +770,7 @@ def main():
         for (name, _, xin, kind), tl, y in zip(plan, shard, outs):
             if kind != "row":
                 continue
-            one(tl, xin, y)
-            reduce_partials(y)
+            row_parallel(tl, xin, y)
             xf = (x_h if name == "o" else x2_h).to(dev).double()
             ref = xf @ full[name].double().t()
             err = float((y.double() - ref).norm() / ref.norm())
@@ -767,7 +783,8 @@ def main():
                                    f"all ranks: {same}")
         tp_check = {"result": "ok", "max_rel_err_vs_fp64": worst, "bar": 5e-3,
                     "what": "all-reduced o and down outputs of one layer (BF16) against the fp64 product over the "
-                            "unsharded weights; bit-identical on every rank"}
+                            "unsharded weights; bit-identical on every rank",
+                    "kernel": "gemv_kernel that adds the ranks' sums itself" if fused_ar else "gemv_kernel + allreduce_kernel"}
     del shard
 
     def run_lists():
@@ -783,11 +800,11 @@ def main():
         n = 0
         for row in layers:
             for tl, xin, y, kind in zip(row, ins, outs, kinds):
-                one(tl, xin, y)
-                n += 1
                 if world > 1 and kind == "row":
-                    reduce_partials(y)
-                    n += 1                                   # the peer-memory all-reduce is one kernel of this library
+                    n += row_parallel(tl, xin, y)
+                else:
+                    one(tl, xin, y)
+                    n += 1
         return n
 
     run_layers = run_lists if use_lists else run_per_linear

@@ -217,6 +217,21 @@ int st_allreduce(void* const* bufs, int rank, int world, const void* in, void* o
 int st_allreduce_add_rmsnorm(void* const* bufs, int rank, int world, void* x, const void* delta, const void* w,
                              void* out, int64_t rows, int64_t cols, double eps, void* stream);
 
+/* The row-parallel product of a tensor-parallel group in ONE launch per rank: Y [B, M] (BF16, the same bits on every
+ * rank) = sum over ranks of X_r [B, N_r] W_r [M, N_r]^T, where this rank passes its column shard (tree, eo, eb, el of
+ * W_r) and its slice X_r of the activations.  The GEMV's reducer warp writes every finished fp32 tile sum into the
+ * receive area of every rank's communication buffer (plain stores over NVLink, one self-validating word per value)
+ * and then adds the ranks' words from its own buffer in rank order, so no second kernel and no flag round trip follow
+ * the product, and the partial sums are added in fp32 (st_gemv + st_allreduce rounds them to BF16 first).
+ * bufs / rank / world as for st_allreduce; ws as for st_gemv (st_gemv_workspace_bytes(M, N, B)); 1 <= B <= 32 and
+ * (M / 16) * 128 * ceil(B / 8 rounded up to 1, 2 or 4) <= 131072 (M = 4096 at any B, M = 16384 at B <= 8).  Every rank
+ * makes the same calls in the same order; the wait for the peers' sums is bounded (st_comm_set_timeout_ms), a rank
+ * that never delivers leaves ERR_WAIT_PEER (5) in the status word and the affected outputs unwritten.  No counterpart
+ * in the reference (vLLM all-reduces the outputs of its RowParallelLinear with NCCL). */
+int st_gemv_allreduce(void* const* bufs, int rank, int world, const void* tree, const int32_t* eo, const uint32_t* eb,
+                      const uint32_t* el, const void* X, void* Y, float* Yf32, int64_t B, int64_t M, int64_t N, void* ws,
+                      int64_t ws_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,11 +2,8 @@
 // row-parallel linears (o and down projections: batch x hidden values per call), optionally fused with the residual
 // add and RMSNorm that consume it in a decode step.
 //
-// Every rank owns one communication buffer (plain device memory, exported to its peers as a CUDA IPC handle):
-//     flags  uint32 [MAX_RANKS][MAX_CTAS]   flags[p][c] = last epoch in which rank p's CTA c delivered its slice here
-//     epoch  uint32 [MAX_CTAS]              calls made so far, per CTA slot (all ranks make the same calls)
-//     data   2 x MAX_RANKS x MAX_CTAS x SLOT_BYTES   the partial sums of every rank: one region per (source rank, CTA
-//                                           slot), double-buffered by the parity of that slot's epoch
+// Every rank owns one communication buffer (layout in st_comm.cuh): per (source rank, CTA slot) a flag word and a data
+// region, double-buffered by the parity of that slot's epoch (all ranks make the same calls).
 // One call, CTA c of rank r: PUSH slice c of the local partials into region (r, c) of every rank's buffer (remote
 // stores; the own copy is a local store), system-scope fence, store the epoch into flags[r][c] of every peer; wait until
 // flags[p][c] of the own buffer reach the epoch for every p (local loads; bounded); add the world copies of slice c in
@@ -22,43 +19,14 @@
 #include <string.h>
 
 #include "../../include/statetree_b200.h"
+#include "st_comm.cuh"
 #include "st_common.cuh"
 #include "st_host.h"
 
 namespace {
 using namespace st;
 
-constexpr int MAX_RANKS = 8;
-constexpr int MAX_CTAS = 64;
-constexpr long long SLOT_BYTES = 16 << 10;                            // per CTA and call
-constexpr long long MAX_BYTES = MAX_CTAS * SLOT_BYTES;                // per call (1 MiB)
-constexpr size_t OFF_EPOCH = (size_t)MAX_RANKS * MAX_CTAS * 4;
-constexpr size_t OFF_DATA = OFF_EPOCH + MAX_CTAS * 4;                 // 2304: 256-byte aligned
-constexpr size_t COMM_BYTES = OFF_DATA + 2 * (size_t)MAX_RANKS * (size_t)MAX_BYTES;
 long long g_wait_ns = 20000000000ll;                                  // st_comm_set_timeout_ms
-
-struct Peers {
-  uint8_t* buf[MAX_RANKS];                                            // buf[rank] is the local buffer
-};
-
-__device__ __forceinline__ long long now_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_peer16(const void* p) {           // never served from a stale local cache line
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
 
 __device__ __forceinline__ uint8_t* slot_data(uint8_t* buf, int half, int src_rank, int cta) {
   return buf + OFF_DATA + ((size_t)half * MAX_RANKS + src_rank) * MAX_BYTES + (size_t)cta * SLOT_BYTES;
@@ -222,6 +190,8 @@ int fill_peers(Peers& P, void* const* bufs, int rank, int world, const char* who
 }
 }  // namespace
 
+long long st::comm_wait_ns() { return g_wait_ns; }
+
 extern "C" int64_t st_comm_bytes(void) { return (int64_t)COMM_BYTES; }
 
 extern "C" int st_comm_set_timeout_ms(int64_t ms) {
@@ -233,7 +203,8 @@ extern "C" int st_comm_set_timeout_ms(int64_t ms) {
 extern "C" int st_comm_alloc(void** buf) {
   ST_REQUIRE(buf != nullptr, "st_comm_alloc: null pointer");
   if (int e = st::cuda_fail(cudaMalloc(buf, COMM_BYTES), "st_comm_alloc")) return e;
-  return st::cuda_fail(cudaMemset(*buf, 0, COMM_BYTES), "st_comm_alloc: clear");
+  if (int e = st::cuda_fail(cudaMemset(*buf, 0, OFF_RECV), "st_comm_alloc: clear")) return e;
+  return st::cuda_fail(cudaMemset((uint8_t*)*buf + OFF_RECV, 0xFF, RECV_BYTES), "st_comm_alloc: clear");
 }
 
 extern "C" int st_comm_free(void* buf) { return st::cuda_fail(cudaFree(buf), "st_comm_free"); }

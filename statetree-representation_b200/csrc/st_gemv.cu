@@ -17,7 +17,12 @@
 // MODE 3 multiplies one activation batch by a short LIST of matrices with the same number of columns (q / k / v, or
 // gate / up, stored as separate trees) in one launch: their tiles are concatenated into one virtual matrix, so the list
 // pays the launch, ring fill and tail of a single kernel, and each member writes its own output.
+// MODE 4 is the row-parallel product of a tensor-parallel group: every rank multiplies its column shard, and the
+// reducer warp, instead of storing a finished tile, writes its fp32 sums into the receive area of every rank's
+// communication buffer over NVLink (plain peer stores, one self-validating word per value) and later adds the ranks'
+// words from its OWN buffer in rank order: the all-reduce costs no second launch and no flag round trip.
 #include "../../include/statetree_b200.h"
+#include "st_comm.cuh"
 #include "st_common.cuh"
 #include <stdlib.h>
 
@@ -33,7 +38,9 @@ constexpr int CW = 8;                     // consumer warps = records per unit
 constexpr int UNIT_BYTES = CW * REC;      // 12416
 constexpr int SIDE_BYTES = 64;            // escape block of a unit
 constexpr int XROW = CW * 128 + 16;       // bytes per staged activation row (512 columns + pad: conflict-free ldmatrix)
-constexpr int MODE_DENSE = 0, MODE_SLOT = 1, MODE_GROUP = 2, MODE_LIST = 3;
+constexpr int MODE_DENSE = 0, MODE_SLOT = 1, MODE_GROUP = 2, MODE_LIST = 3, MODE_AR = 4;
+constexpr int FIN_CAP = 32;               // MODE_AR: tiles a CTA may have delivered and not yet summed over the ranks
+__host__ __device__ constexpr bool one_matrix(int mode) { return mode == MODE_DENSE || mode == MODE_LIST || mode == MODE_AR; }
 constexpr int MAXL = 4;                   // matrices in one MODE_LIST launch
 constexpr uint32_t EMPTY_SLOT = 0xFFFFFFFFu;  // what every word of the workspace holds between launches
 
@@ -61,6 +68,9 @@ struct GemvArgs {
   int nprob, maxcover, stages, fill, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
   int act;                                // dense mode: rows are gate / up tiles in turn, the reducer stores silu(gate) * up
   ListTab lt;
+  uint8_t* peer[MAX_RANKS];               // MODE_AR: communication buffer of every rank (peer[rank] is the own one)
+  int rank, world;
+  long long wait_ns;                      // bound of the wait for the other ranks' sums
 };
 
 struct Prob {                             // what a unit's problem resolves to
@@ -89,7 +99,7 @@ template <int MODE>
 __device__ __forceinline__ Prob resolve(const GemvArgs& a, int p) {
   Prob r;
   r.skip = false;
-  if (MODE == MODE_DENSE || MODE == MODE_LIST) {               // (a list resolves per tile: UnitCursor::retile)
+  if (one_matrix(MODE)) {                                      // (a list resolves per tile: UnitCursor::retile)
     r.tree = a.tree; r.eo = a.eo; r.eb = a.eb; r.el = a.el;
     return r;
   }
@@ -112,7 +122,7 @@ __device__ __forceinline__ Prob resolve(const GemvArgs& a, int p) {
 // activation row / output row of column n of problem p; -1 = unused column
 template <int MODE>
 __device__ __forceinline__ long long out_row(const GemvArgs& a, int p, int n) {
-  if (MODE == MODE_DENSE || MODE == MODE_LIST) return n < a.B ? n : -1;
+  if (one_matrix(MODE)) return n < a.B ? n : -1;
   if (MODE == MODE_SLOT) return n == 0 ? p : -1;
   const int s = a.sorted[p * 8 + n];
   return (n < 8 && s >= 0 && s < a.B) ? s : -1;
@@ -209,6 +219,8 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
   uint64_t* done = empty + S;                                               // [NRED] partials of a tile are in red[buf]
   uint64_t* freeb = done + NRED;                                            // [NRED] red[buf] may be overwritten
   uint64_t* xbar = freeb + NRED;                                            // whole activation rows have landed
+  int* fin_tile = reinterpret_cast<int*>(xbar + 1);                         // MODE_AR: [FIN_CAP] delivered tiles
+  uint16_t* fin_mask = reinterpret_cast<uint16_t*>(fin_tile + FIN_CAP);     // MODE_AR: [FIN_CAP][32] values per lane
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = gridDim.x;
@@ -252,7 +264,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       if (k.p != lastp) {
         lastp = k.p;
         const long long r = lane < NX ? out_row<MODE>(a, k.p, lane) : -1;
-        xrow = r < 0 ? nullptr : a.X + ((MODE == MODE_DENSE || MODE == MODE_LIST) ? r : r / a.xdiv) * a.N;
+        xrow = r < 0 ? nullptr : a.X + (one_matrix(MODE) ? r : r / a.xdiv) * a.N;
         nx = a.xwhole ? 0u : __popc(__ballot_sync(FULL, xrow != nullptr));
       }
     };
@@ -277,7 +289,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     // first ring fill: weights, then wait for the previous kernel, then the activations
     UnitCursor<MODE> pre = cur;
     int filled = 0;
-    if (MODE == MODE_DENSE || MODE == MODE_LIST) {             // lane i fills stage i
+    if (one_matrix(MODE)) {                                    // lane i fills stage i
       const bool on = lane < a.fill && mine.valid();
       if (on) {
         const int nrec = mine.nrec(a);
@@ -340,10 +352,69 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     float gate[EL / 32];                                       // act mode: the gate tile, until its up tile is done
 #pragma unroll
     for (int k = 0; k < EL / 32; ++k) gate[k] = 0.f;
+    // MODE_AR.  A value this warp finishes (its tile, or its word of a cut tile) goes to every rank's receive area,
+    // word idx of (call parity, this rank); `mask` collects the lane's finished values of the current tile.  The sum
+    // over the ranks is taken later (settle), when the peers' words have had time to arrive.
+    uint8_t* const own = MODE == MODE_AR ? a.peer[a.rank] : nullptr;
+    uint32_t calls = 0;
+    if (MODE == MODE_AR) calls = ld_relaxed_sys(reinterpret_cast<const uint32_t*>(own + OFF_GEMV));
+    const int half = (int)(calls & 1u);
+    int nfin = 0;
+    unsigned mask = 0;
+    long long deadline = 0;                                    // set at the first word that is not here yet
+    auto deliver = [&](int tile, int k, float v) {
+      uint32_t bits = __float_as_uint(v);
+      if (bits == RECV_EMPTY) bits = 0x7FFFFFFFu;              // never the "not here yet" pattern
+      const long long idx = (long long)tile * EL + lane + 32 * k;
+      for (int p = 0; p < a.world; ++p) st_relaxed_sys(recv_word(a.peer[p], half, a.rank, idx), bits);
+      mask |= 1u << k;
+    };
+    // adds the ranks' words of this lane's values of `tile` in rank order, stores the result, empties the words
+    auto settle = [&](int tile, unsigned m) {
+#pragma unroll
+      for (int k = 0; k < EL / 32; ++k) {
+        if (!((m >> k) & 1u)) continue;
+        const long long idx = (long long)tile * EL + lane + 32 * k;
+        float v = 0.f;
+        bool ok = true;
+        for (int p = 0; p < a.world && ok; ++p) {
+          uint32_t* w = recv_word(own, half, p, idx);
+          uint32_t bits = ld_relaxed_sys(w);
+          while (bits == RECV_EMPTY) {                          // bounded by wall time, once for the whole CTA
+            const long long now = now_ns();
+            if (deadline == 0) deadline = now + a.wait_ns;
+            if (now > deadline) { ok = false; break; }
+            bits = ld_relaxed_sys(w);
+          }
+          v += __uint_as_float(bits);
+        }
+        if (!ok) {                                              // a rank never delivered: leave the output unwritten
+          atomicExch(a.status, ERR_WAIT_PEER);
+          continue;
+        }
+        for (int p = 0; p < a.world; ++p) *recv_word(own, half, p, idx) = RECV_EMPTY;
+        const int n = (lane + 32 * k) >> 4, r = (lane + 32 * k) & 15;
+        const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+        a.Y[(size_t)n * a.M + (size_t)tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+        if (a.Yf) a.Yf[(size_t)n * a.M + (size_t)tile * 16 + r] = v;
+      }
+    };
+    // every CTA counts itself out; the last one advances the call counter that the next call's parity comes from
+    auto leave_call = [&]() {
+      if (MODE == MODE_AR && lane == 0) {
+        uint32_t* g = reinterpret_cast<uint32_t*>(own + OFF_GEMV);
+        __threadfence();
+        if (atomicAdd(g + 1, 1u) == gridDim.x - 1) {
+          g[1] = 0u;
+          g[0] = calls + 1u;
+        }
+      }
+    };
     for (; cur.valid(); cur.advance(a, cur.run_len(a))) {      // one hand-over per run of units of a tile
       const int buf = nf % NRED;
       if (!mbar_wait(done + buf, (uint32_t)(nf / NRED) & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
+        leave_call();
         return;
       }
       ++nf;
@@ -367,6 +438,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       long long orow[EL / 32];                                  // output row of each of this lane's values, -1 = none
 #pragma unroll
       for (int k = 0; k < EL / 32; ++k) orow[k] = out_row<MODE>(a, cur.p, (lane + 32 * k) >> 4);
+      mask = 0;
       if (!owned) {
         const long long tg = (long long)cur.p * a.T + cur.tile;
         const int cfirst = cta_of_unit(tbase, a.U, C), clast = cta_of_unit(tbase + a.CPT - 1, a.U, C);
@@ -388,16 +460,24 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
             slots[(size_t)(level - 1) * EL + lane + 32 * k] = EMPTY_SLOT;
             v += __uint_as_float(o);
             if (level == last_level) {
-              const int r = (lane + 32 * k) & 15;
-              const __nv_bfloat16 hv = __float2bfloat16_rn(v);
-              Yp[orow[k] * Mp + row0 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-              if (Yfp) Yfp[orow[k] * Mp + row0 + r] = v;
+              if (MODE == MODE_AR) {
+                deliver(cur.tile, k, v);
+              } else {
+                const int r = (lane + 32 * k) & 15;
+                const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+                Yp[orow[k] * Mp + row0 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+                if (Yfp) Yfp[orow[k] * Mp + row0 + r] = v;
+              }
               break;
             }
             ++level;
             o = atomicExch(slots + (size_t)(level - 1) * EL + lane + 32 * k, __float_as_uint(v));
           }
         }
+      } else if (MODE == MODE_AR) {
+#pragma unroll
+        for (int k = 0; k < EL / 32; ++k)
+          if (orow[k] >= 0) deliver(cur.tile, k, sum[k]);
       } else if (MODE == MODE_DENSE && a.act) {
         // SwiGLU epilogue: tiles 2j and 2j + 1 hold rows 16j .. 16j + 15 of the gate and of the up projection; the host
         // only allows this when every CTA owns whole tiles in pairs, so the gate tile is always the one just before.
@@ -427,13 +507,27 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
           }
         }
       }
+      if (MODE == MODE_AR && __any_sync(FULL, mask != 0u)) {
+        if (nfin < FIN_CAP) {                                   // the peers' words need a while: sum them later
+          if (lane == 0) fin_tile[nfin] = cur.tile;
+          fin_mask[nfin * 32 + lane] = (uint16_t)mask;
+          ++nfin;
+        } else {
+          settle(cur.tile, mask);
+        }
+      }
+    }
+    if (MODE == MODE_AR) {
+      __syncwarp();
+      for (int e = 0; e < nfin; ++e) settle(fin_tile[e], fin_mask[e * 32 + lane]);
+      leave_call();
     }
     return;
   }
 
   // -------------------------------------------------------------------- consumers.  To them a list is one dense
   // matrix (the concatenation): they walk it with the dense cursor and look a member up only for a crowded record.
-  UnitCursor<MODE == MODE_LIST ? MODE_DENSE : MODE> cc;
+  UnitCursor<one_matrix(MODE) ? MODE_DENSE : MODE> cc;
   cc.init(a, u0, u1);
   const int g = lane >> 2, rec = warp;
   constexpr int NCH = 2;                                     // independent accumulator chains per column tile
@@ -584,7 +678,7 @@ static int tune(const char* name, int dflt) {
 
 // nx = activation rows staged per unit (the batch for a dense matrix, 1 per slot, 8 per block of slots).
 template <int NT>
-Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act = false) {
+Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act = false, bool ar = false) {
   Plan p;
   p.NG = (int)(N / 64);
   p.CPT = (p.NG + CW - 1) / CW;
@@ -600,7 +694,8 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act
   p.xw_bytes = p.xwhole ? nx * p.xw_stride : 0;
   p.stage_bytes = UNIT_BYTES + SIDE_BYTES + (p.xwhole ? 0 : nx * XROW);
   constexpr int EL = 16 * 8 * NT;
-  const size_t fixed = XROW + p.xw_bytes + (size_t)(NT == 1 ? 4 : 2) * CW * EL * 4 + (2 * 16 + 9) * 8 + 16;
+  const size_t fixed = XROW + p.xw_bytes + (size_t)(NT == 1 ? 4 : 2) * CW * EL * 4 + (2 * 16 + 9) * 8 + 16 +
+                       (ar ? (size_t)FIN_CAP * (4 + 32 * 2) : 0);
   // Two CTAs per SM, each with the deepest ring (at most 8 stages) that fits half of the SM's shared memory; one CTA
   // when even two stages do not fit twice (32 activation rows).
   static const int want_per_sm = tune("STATETREE_GEMV_CTAS_PER_SM", 2), max_stages = tune("STATETREE_GEMV_STAGES", 8),
@@ -658,7 +753,7 @@ Plan make_plan(long long M, long long N, int nprob, int nx, bool dense, bool act
 
 template <int NT, int MODE>
 int launch(GemvArgs& a, int nprob, int nx, long long ws_bytes, cudaStream_t stream, const char* who) {
-  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, MODE == MODE_DENSE || MODE == MODE_LIST, a.act != 0);
+  const Plan p = make_plan<NT>(a.M, a.N, nprob, nx, one_matrix(MODE), a.act != 0, MODE == MODE_AR);
   a.NG = p.NG; a.CPT = p.CPT; a.T = p.T; a.U = p.U; a.nprob = nprob; a.maxcover = p.maxcover; a.stages = p.stages; a.fill = p.fill;
   a.stage_bytes = p.stage_bytes; a.nxrows = p.nxrows; a.xwhole = p.xwhole; a.xw_stride = p.xw_stride;
   a.xw_bytes = p.xw_bytes;
@@ -777,6 +872,36 @@ extern "C" int st_gemv_list(int64_t n, const void* const* trees, const int32_t* 
   if (B <= 8) return launch<1, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
   if (B <= 16) return launch<2, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
   return launch<4, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
+}
+
+// ---------------------------------------------------------------------------------------------- st_gemv_allreduce
+extern "C" int st_gemv_allreduce(void* const* bufs, int rank, int world, const void* tree, const int32_t* eo,
+                                 const uint32_t* eb, const uint32_t* el, const void* X, void* Y, float* Yf32, int64_t B,
+                                 int64_t M, int64_t N, void* ws, int64_t ws_bytes, void* stream) {
+  const char* who = "st_gemv_allreduce";
+  ST_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "%s: rank %d of %d (2..%d ranks)", who, rank,
+             world, MAX_RANKS);
+  ST_REQUIRE(bufs != nullptr, "%s: null buffer table", who);
+  if (int e = shape_checks(who, M, N, B)) return e;
+  ST_REQUIRE(tree && eo && eb && el && X && Y, "%s: null pointer", who);
+  ST_REQUIRE(st::aligned16(tree) && st::aligned16(eb) && st::aligned16(X), "%s: tree, eb and X must be 16-byte aligned", who);
+  const int nt = B <= 8 ? 1 : (B <= 16 ? 2 : 4);
+  ST_REQUIRE((M / 16) * (long long)(128 * nt) <= RECV_VALUES,
+             "%s: %lld rows at batch %lld exceed the receive area (%lld padded values per call)", who, (long long)M,
+             (long long)B, (long long)RECV_VALUES);
+  GemvArgs a = {};
+  for (int p = 0; p < world; ++p) {
+    ST_REQUIRE(bufs[p] != nullptr, "%s: buffer of rank %d missing", who, p);
+    a.peer[p] = (uint8_t*)bufs[p];
+  }
+  a.rank = rank; a.world = world; a.wait_ns = st::comm_wait_ns();
+  a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
+  a.X = (const uint16_t*)X; a.Y = (uint16_t*)Y; a.Yf = Yf32; a.ws = (float*)ws;
+  a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (nt == 1) return launch<1, MODE_AR>(a, 1, (int)B, ws_bytes, s, who);
+  if (nt == 2) return launch<2, MODE_AR>(a, 1, (int)B, ws_bytes, s, who);
+  return launch<4, MODE_AR>(a, 1, (int)B, ws_bytes, s, who);
 }
 
 // ---------------------------------------------------------------------------------------------- st_gemv_static

@@ -26,6 +26,7 @@ _SIGNATURES = {
     "st_gemv_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "st_gemv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_static": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "st_gemv_allreduce": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "st_gemv_list_workspace_bytes": (_i64, [_i64, _vp, _i64, _i64]),
     "st_gemv_list": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "st_gemm_workspace_bytes": (_i64, [_i64, _i64, _i64]),

@@ -90,6 +90,23 @@ class PeerComm:
                                               ops._stream(y)))
         return y
 
+    GEMV_AR_VALUES = 128 << 10                                     # padded output values one fused call may deliver
+
+    def gemv_allreduce_fits(self, M, B):
+        nt = 1 if B <= 8 else (2 if B <= 16 else 4)
+        return 1 <= B <= 32 and (M // 16) * 128 * nt <= self.GEMV_AR_VALUES
+
+    def gemv_allreduce(self, tree, eo, eb, el, x, y, ws, yf32=None):
+        """y [B, M] <- sum over ranks of x_r [B, N_r] W_r^T: the row-parallel product and its all-reduce as one launch"""
+        from . import ops
+        B, N = x.shape
+        M = y.shape[1]
+        with torch.cuda.device(y.device):
+            ops._check(self._lib.st_gemv_allreduce(self._bufs, self.rank, self.world, ops._ptr(tree), ops._ptr(eo),
+                                                   ops._ptr(eb), ops._ptr(el), ops._ptr(x), ops._ptr(y), ops._ptr(yf32),
+                                                   B, M, N, ops._ptr(ws), ws.numel() * ws.element_size(), ops._stream(y)))
+        return y
+
     def all_reduce_add_rmsnorm(self, x, delta, w, out, eps):
         """x += sum over ranks of delta; out = RMSNorm(x) * w  (x, delta, out BF16 [rows, cols])"""
         from . import ops
@@ -153,7 +170,21 @@ class RowParallelTreeLinear(nn.Module):
         self.group = group
 
     def forward(self, x_local):
-        return reduce_partials(self.inner(x_local), self.group)
+        from .linear import GEMV_MAX, _rows_2d, _state
+        tl = self.inner
+        comm = peer_comm(self.group) if tl.tree.is_cuda else None
+        rows = x_local.numel() // tl.in_features
+        if comm is None or tl.bias is not None or not (1 <= rows <= min(GEMV_MAX, 32)) \
+                or not comm.gemv_allreduce_fits(tl.out_features, rows):
+            return reduce_partials(tl(x_local), self.group)
+        from . import ops
+        acts = _rows_2d(x_local, tl.in_features)
+        y = torch.empty(rows, tl.out_features, dtype=torch.bfloat16, device=tl.tree.device)
+        eo, el, eb = tl.tables()
+        ws = _state(tl.tree.device).get_ws(ops.ext().gemv_workspace_bytes(tl.out_features, tl.in_features, rows))
+        comm.gemv_allreduce(tl.tree, eo, eb, el, acts, y, ws)
+        y = y.view(*x_local.shape[:-1], tl.out_features)
+        return y if x_local.dtype == torch.bfloat16 else y.to(x_local.dtype)
 
 
 def expert_partition(num_experts, rank, world, device=None):

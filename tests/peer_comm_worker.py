@@ -68,6 +68,50 @@ def main():
         comm.all_reduce_add_rmsnorm(xb, delta, w, hb, 1e-6)
         assert torch.equal(xa, xb), (rows, cols)
         assert (ha.float() - hb.float()).abs().max().item() <= 2e-2 * ha.float().abs().max().item(), (rows, cols)
+    # the row-parallel GEMV that adds the ranks' sums itself: against the plain GEMV's fp32 accumulators gathered and
+    # added in rank order; eagerly (both call parities) and in a replayed graph; the same bits on every rank
+    from statetree_b200 import TreeLinear
+    from statetree_b200.linear import _state
+    for (M, N, B) in ((4096, 4096, 1), (4096, 12288, 1), (4096, 4096, 8), (1024, 2048, 12), (2048, 4096, 20)):
+        Nr = N // world // 64 * 64
+        if Nr == 0:
+            continue
+        Wr = (torch.randn(M, Nr, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+        tl = TreeLinear.from_weight(Wr, verify=False)
+        eo, el, eb = tl.tables()
+        torch.cuda.synchronize()
+        ws = _state(dev).get_ws(E.gemv_workspace_bytes(M, Nr, B))
+        for it in range(5):
+            x = torch.randn(B, Nr, device=dev, generator=gen).to(torch.bfloat16)
+            yf = torch.empty(B, M, dtype=torch.float32, device=dev)
+            E.gemv(tl.tree, eo, eb, el, x, torch.empty(B, M, dtype=torch.bfloat16, device=dev), ws,
+                   _state(dev).get_cnt(M // 16), yf)              # the plain GEMV's fp32 accumulators of this shard
+            parts = [torch.empty_like(yf) for _ in range(world)]
+            dist.all_gather(parts, yf)
+            acc = torch.zeros_like(yf)
+            for p_ in parts:
+                acc += p_
+            y = torch.empty(B, M, dtype=torch.bfloat16, device=dev)
+            got32 = torch.empty(B, M, dtype=torch.float32, device=dev)
+            comm.gemv_allreduce(tl.tree, eo, eb, el, x, y, ws, got32)
+            torch.cuda.synchronize()
+            assert torch.equal(got32, acc), (M, N, B, it, (got32 - acc).abs().max().item())
+            assert torch.equal(y, acc.to(torch.bfloat16)), (M, N, B, it)
+        if B == 1:
+            x = torch.randn(B, Nr, device=dev, generator=gen).to(torch.bfloat16)
+            y = torch.empty(B, M, dtype=torch.bfloat16, device=dev)
+            comm.gemv_allreduce(tl.tree, eo, eb, el, x, y, ws)
+            want = y.clone()
+            side.wait_stream(torch.cuda.current_stream(dev))
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=side):
+                for _ in range(7):                              # an odd count: replays start on alternating parities
+                    comm.gemv_allreduce(tl.tree, eo, eb, el, x, y, ws)
+            for _ in range(10):
+                y.zero_()
+                g2.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(y, want), (M, N)
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     dist.barrier()

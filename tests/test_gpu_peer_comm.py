@@ -51,3 +51,73 @@ def test_wait_on_absent_peer_runs_out_and_reports():
         ops._check(L.st_comm_set_timeout_ms(20000))
         ops._check(L.st_comm_free(own))
         ops._check(L.st_comm_free(absent))
+
+
+@pytest.mark.gpu
+def test_gemv_that_sums_over_ranks_on_one_gpu():
+    """The row-parallel GEMV that adds the ranks' sums itself (st_gemv_allreduce), two "ranks" on ONE GPU with a buffer
+    each.  Kernels that wait on one another cannot run together on one GPU, so the ranks run in turn: rank 1 first,
+    with a 300 ms limit; it delivers its sums to both buffers, finds rank 0's missing, gives up (status 5, its output
+    unwritten).  Rank 0 then finds rank 1's words waiting and completes: its output must equal the fp32 sum of both
+    shards' accumulators rounded to BF16, and the fp64 product over the whole matrix within the usual bars; its
+    receive words and exchange slots are left empty."""
+    import ctypes
+    import numpy as np
+    sys.path.insert(0, os.path.join(os.path.dirname(HERE), "statetree-representation_b200"))
+    sys.path.insert(0, HERE)
+    import gen_inputs as G
+    import oracle
+    from statetree_b200 import ops
+    from util import bits_to_torch, layer_from_oracle, rel_fro
+    L, E = ops.lib(), ops.ext()
+    torch.cuda.set_device(0)
+    assert ops.device_status() == 0
+    ops._check(L.st_comm_set_timeout_ms(300))
+    try:
+        for (M, N, B) in ((256, 1024, 1), (512, 2048, 5), (4096, 1024, 1), (1024, 512, 12), (192, 256, 20)):
+            b0, b1 = ctypes.c_void_p(), ctypes.c_void_p()
+            ops._check(L.st_comm_alloc(ctypes.byref(b0)))
+            ops._check(L.st_comm_alloc(ctypes.byref(b1)))
+            bufs = (ctypes.c_void_p * 2)(b0.value, b1.value)
+            W = G.weights(M, N, M + N + B, "mixed")
+            X = G.to_bf16_bits(np.random.RandomState(B).standard_normal((B, N)))
+            half = N // 2
+            parts, accs = [], []
+            for r in range(2):
+                tl, _ = layer_from_oracle(np.ascontiguousarray(W[:, r * half:(r + 1) * half]))
+                eo, el, eb = tl.tables()
+                xr = bits_to_torch(np.ascontiguousarray(X[:, r * half:(r + 1) * half]), "cuda")
+                yf = torch.empty(B, M, dtype=torch.float32, device="cuda")
+                E.gemv(tl.tree, eo, eb, el, xr, torch.empty(B, M, dtype=torch.bfloat16, device="cuda"),
+                       torch.full((max(E.gemv_workspace_bytes(M, half, B) // 4, 1),), -1, dtype=torch.int32,
+                                  device="cuda").view(torch.float32),
+                       torch.zeros(M // 16, dtype=torch.int32, device="cuda"), yf)   # the plain GEMV's fp32 accumulators
+                parts.append((tl, eo, el, eb, xr))
+                accs.append(yf)
+            nbytes = E.gemv_workspace_bytes(M, half, B)
+            ws = torch.full((max(nbytes // 4, 1),), -1, dtype=torch.int32, device="cuda")
+            ys = [torch.full((B, M), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+            yf0 = torch.empty(B, M, dtype=torch.float32, device="cuda")
+            torch.cuda.synchronize()
+            for r in (1, 0):
+                tl, eo, el, eb, xr = parts[r]
+                ops._check(L.st_gemv_allreduce(bufs, r, 2, tl.tree.data_ptr(), eo.data_ptr(), eb.data_ptr(), el.data_ptr(),
+                                               xr.data_ptr(), ys[r].data_ptr(), yf0.data_ptr() if r == 0 else None, B, M,
+                                               half, ws.data_ptr(), ws.numel() * 4,
+                                               torch.cuda.current_stream().cuda_stream))
+                torch.cuda.synchronize()
+                if r == 1:
+                    assert ops.device_status() == 5                      # rank 0 never delivered: the wait ran out
+                    assert bool((ys[1] == 7.0).all())
+                else:
+                    assert ops.device_status() == 0
+            want32 = accs[0] + accs[1]                                    # rank order, fp32
+            assert torch.equal(yf0, want32), (M, N, B)
+            assert torch.equal(ys[0], want32.to(torch.bfloat16)), (M, N, B)
+            ref = oracle.linear_f64(W, X)
+            assert rel_fro(yf0.cpu().numpy(), ref) < 1e-3
+            assert bool((ws == -1).all())
+            ops._check(L.st_comm_free(b0))
+            ops._check(L.st_comm_free(b1))
+    finally:
+        ops._check(L.st_comm_set_timeout_ms(20000))
