@@ -369,34 +369,51 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       for (int p = 0; p < a.world; ++p) st_relaxed_sys(recv_word(a.peer[p], half, a.rank, idx), bits);
       mask |= 1u << k;
     };
-    // adds the ranks' words of this lane's values of `tile` in rank order, stores the result, empties the words
+    // adds the ranks' words of this lane's values of `tile` in rank order, stores the result, empties the words.
+    // The words of up to four values are requested together (a local load at system scope costs a trip to L2), then
+    // whatever has not arrived yet is polled.
     auto settle = [&](int tile, unsigned m) {
+      constexpr int KC = EL / 32 < 4 ? EL / 32 : 4;
 #pragma unroll
-      for (int k = 0; k < EL / 32; ++k) {
-        if (!((m >> k) & 1u)) continue;
-        const long long idx = (long long)tile * EL + lane + 32 * k;
-        float v = 0.f;
-        bool ok = true;
-        for (int p = 0; p < a.world && ok; ++p) {
-          uint32_t* w = recv_word(own, half, p, idx);
-          uint32_t bits = ld_relaxed_sys(w);
-          while (bits == RECV_EMPTY) {                          // bounded by wall time, once for the whole CTA
-            const long long now = now_ns();
-            if (deadline == 0) deadline = now + a.wait_ns;
-            if (now > deadline) { ok = false; break; }
-            bits = ld_relaxed_sys(w);
+      for (int k0 = 0; k0 < EL / 32; k0 += KC) {
+        if (!((m >> k0) & ((1u << KC) - 1u))) continue;
+        uint32_t bits[KC][MAX_RANKS];
+#pragma unroll
+        for (int kk = 0; kk < KC; ++kk)
+#pragma unroll
+          for (int p = 0; p < MAX_RANKS; ++p)
+            bits[kk][p] = (p < a.world && ((m >> (k0 + kk)) & 1u))
+                              ? ld_relaxed_sys(recv_word(own, half, p, (long long)tile * EL + lane + 32 * (k0 + kk)))
+                              : 0u;
+#pragma unroll
+        for (int kk = 0; kk < KC; ++kk) {
+          const int k = k0 + kk;
+          if (!((m >> k) & 1u)) continue;
+          const long long idx = (long long)tile * EL + lane + 32 * k;
+          float v = 0.f;
+          bool ok = true;
+#pragma unroll
+          for (int p = 0; p < MAX_RANKS; ++p) {
+            if (p >= a.world || !ok) continue;
+            uint32_t b = bits[kk][p];
+            while (b == RECV_EMPTY) {                           // bounded by wall time, once for the whole CTA
+              const long long now = now_ns();
+              if (deadline == 0) deadline = now + a.wait_ns;
+              if (now > deadline) { ok = false; break; }
+              b = ld_relaxed_sys(recv_word(own, half, p, idx));
+            }
+            v += __uint_as_float(b);
           }
-          v += __uint_as_float(bits);
+          if (!ok) {                                            // a rank never delivered: leave the output unwritten
+            atomicExch(a.status, ERR_WAIT_PEER);
+            continue;
+          }
+          for (int p = 0; p < a.world; ++p) *recv_word(own, half, p, idx) = RECV_EMPTY;
+          const int n = (lane + 32 * k) >> 4, r = (lane + 32 * k) & 15;
+          const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+          a.Y[(size_t)n * a.M + (size_t)tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
+          if (a.Yf) a.Yf[(size_t)n * a.M + (size_t)tile * 16 + r] = v;
         }
-        if (!ok) {                                              // a rank never delivered: leave the output unwritten
-          atomicExch(a.status, ERR_WAIT_PEER);
-          continue;
-        }
-        for (int p = 0; p < a.world; ++p) *recv_word(own, half, p, idx) = RECV_EMPTY;
-        const int n = (lane + 32 * k) >> 4, r = (lane + 32 * k) & 15;
-        const __nv_bfloat16 hv = __float2bfloat16_rn(v);
-        a.Y[(size_t)n * a.M + (size_t)tile * 16 + r] = *reinterpret_cast<const uint16_t*>(&hv);
-        if (a.Yf) a.Yf[(size_t)n * a.M + (size_t)tile * 16 + r] = v;
       }
     };
     // every CTA counts itself out; the last one advances the call counter that the next call's parity comes from

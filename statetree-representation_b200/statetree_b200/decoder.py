@@ -179,11 +179,27 @@ class TreeDecoder:
                 n += gu.record_bytes() + d.record_bytes()
         return n
 
-    def _add_norm(self, x, delta, h):
+    def _row_parallel(self, layer, xin):
+        """(delta, summed): the output of a row-parallel projection (o, down) on this rank's activation slice.  A tree
+        layer at GEMV batch sizes sums over the ranks inside its own kernel (summed = True); otherwise the partial
+        output comes back and _add_norm adds the ranks."""
+        from .linear import GEMV_MAX, _state
+        B = xin.shape[0]
+        if (self.world > 1 and self.comm is not None and self.compressed and B <= min(GEMV_MAX, 32)
+                and layer.bias is None and self.comm.gemv_allreduce_fits(layer.out_features, B)):
+            eo, el, eb = layer.tables()
+            y = torch.empty(B, layer.out_features, dtype=torch.bfloat16, device=self.dev)
+            ws = _state(self.dev).get_ws(ext().gemv_workspace_bytes(layer.out_features, layer.in_features, B))
+            self.comm.gemv_allreduce(layer.tree, eo, eb, el, xin, y, ws)
+            return y, True
+        return layer(xin), False
+
+    def _add_norm(self, x, delta, h, summed=False):
         """x += (all-reduced) delta; h = RMSNorm(x) * w.  Under tensor parallelism delta is this rank's partial output of
-        a row-parallel projection: one kernel sums it over the ranks through peer memory and applies add + norm."""
+        a row-parallel projection unless `summed`: one kernel sums it over the ranks through peer memory and applies
+        add + norm."""
         c = self.cfg
-        if delta is not None and self.world > 1:
+        if delta is not None and self.world > 1 and not summed:
             if self.comm is not None:
                 self.comm.all_reduce_add_rmsnorm(x, delta, self.norm_w, h, c.eps)
                 return
@@ -198,9 +214,9 @@ class TreeDecoder:
         scale = 1.0 / math.sqrt(D)
         h, qb, kb = self.h_buf, self.q_buf, self.k_buf
         slots = self.cache.begin_step(B) if self.compressed else None
-        delta = None
+        delta, summed = None, False
         for li, (qkv, o, gu, d) in enumerate(self.blocks):
-            self._add_norm(x, delta, h)
+            self._add_norm(x, delta, h, summed)
             y = qkv(h)
             if self.compressed:
                 layer = self.cache.layers[li]               # norm + rope of q and k and the append of k, v: one launch
@@ -212,14 +228,14 @@ class TreeDecoder:
                 v = y[:, (self.hq + self.hkv) * D:].view(B, self.hkv, D)
                 att = _flash()(qb.view(B, 1, self.hq, D), self.kc[li], self.vc[li], k=kb.view(B, 1, self.hkv, D),
                                v=v.unsqueeze(1), cache_seqlens=self.lens, softmax_scale=scale)
-            delta = o(att.reshape(B, self.hq * D))
-            self._add_norm(x, delta, h)
+            delta, summed = self._row_parallel(o, att.reshape(B, self.hq * D))
+            self._add_norm(x, delta, h, summed)
             if c.experts:
                 router, te = gu
                 probs = torch.softmax(Fn.linear(h, router).float(), -1)
                 w, ids = probs.topk(c.top_k, -1)
                 w = (w / w.sum(-1, keepdim=True)).contiguous()
-                delta = te(h, ids.to(torch.int32).contiguous(), w, self.emap if self.world > 1 else None)
+                delta, summed = te(h, ids.to(torch.int32).contiguous(), w, self.emap if self.world > 1 else None), False
                 continue                                     # (the all-reduce over ranks happens in the next _add_norm)
             if self.fused_act:
                 act = gu.swiglu(h)
@@ -227,8 +243,8 @@ class TreeDecoder:
                 y = gu(h)
                 act = torch.empty(B, y.shape[1] // 2, dtype=torch.bfloat16, device=self.dev)
                 E.silu_mul(y, act)
-            delta = d(act)
-        self._add_norm(x, delta, h)
+            delta, summed = self._row_parallel(d, act)
+        self._add_norm(x, delta, h, summed)
         logits = self.lm_head(h)
         if self.world > 1:
             parts = [torch.empty_like(logits) for _ in range(self.world)]
