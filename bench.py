@@ -730,7 +730,7 @@ def main():
     if use_lists:
         ws_need = max(ws_need, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, B),
                       E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, B))
-    ws = st.get_ws(ws_need)
+    ws = st.get_ws(ws_need) if use_gemv else st.get_scratch(ws_need)   # (the GEMM's workspace is plain scratch)
     cnt = st.get_cnt(4096)
 
     def list_args(row, lo, hi):
@@ -961,11 +961,36 @@ def main():
                 xs = {n: torch.randn(Bs, n, device=dev, generator=gs).to(torch.bfloat16) for n in (HIDDEN, INTER)}
                 ys = [torch.empty(Bs, tl.out_features, dtype=torch.bfloat16, device=dev) for tl in layers[0]]
                 gemv_path = Bs <= GEMV_MAX
-                ws_s = st.get_ws(max((E.gemv_workspace_bytes if gemv_path else E.gemm_workspace_bytes)(
-                    tl.out_features, tl.in_features, Bs) for tl in layers[0]))
+                need_s = max((E.gemv_workspace_bytes if gemv_path else E.gemm_workspace_bytes)(
+                    tl.out_features, tl.in_features, Bs) for tl in layers[0])
+                ws_s = st.get_ws(need_s) if gemv_path else st.get_scratch(need_s)
                 cnt_s = st.get_cnt(4096)
 
+                lists_s = None
+                if gemv_path and use_lists:                  # q / k / v and gate / up as one list launch each, as above
+                    need_s = max(need_s, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, Bs),
+                                 E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, Bs))
+                    ws_s = st.get_ws(need_s)
+
+                    def largs(row, lo, hi):
+                        tabs = []
+                        for tl in row[lo:hi]:
+                            eo, el, eb = tl._tables
+                            tabs.append((tl.tree, eo, eb, el))
+                        return E.gemv_list_args(tabs, ys[lo:hi])
+
+                    lists_s = [(largs(row, 0, 3), largs(row, 4, 6)) for row in layers]
+
                 def run_tree():
+                    if lists_s is not None:
+                        for row, (qkv, gate_up) in zip(layers, lists_s):
+                            E.gemv_list(qkv, xs[HIDDEN], ws_s)
+                            eo, el, eb = row[3]._tables
+                            E.gemv(row[3].tree, eo, eb, el, xs[HIDDEN], ys[3], ws_s, cnt_s)
+                            E.gemv_list(gate_up, xs[HIDDEN], ws_s)
+                            eo, el, eb = row[6]._tables
+                            E.gemv(row[6].tree, eo, eb, el, xs[INTER], ys[6], ws_s, cnt_s)
+                        return
                     for row in layers:
                         for tl, y in zip(row, ys):
                             eo, el, eb = tl._tables
@@ -979,7 +1004,8 @@ def main():
                         for W, y in zip(row, ys):
                             torch.matmul(xs[W.shape[1]], W.t(), out=y)
 
-                point = {"batch": Bs, "kernel": "gemv_kernel" if gemv_path else "gemm_kernel (tcgen05)"}
+                point = {"batch": Bs, "kernel": ("gemv_kernel, list launches" if lists_s is not None else "gemv_kernel")
+                         if gemv_path else "gemm_kernel (tcgen05)"}
                 for key, fn in (("ms_per_step", run_tree), ("bf16_control_ms", run_ctl)):
                     torch.cuda.synchronize()
                     with torch.cuda.stream(side):

@@ -82,7 +82,10 @@ int st_gemv_static(const void* tree, const int32_t* eo, const uint32_t* eb, cons
 
 /* Large-batch fused decode + tcgen05 GEMM, B >= 1 (meant for B > 32), M % 128 == 0.  Replaces `_C.tm`, `_C.th`,
  * `_C.tt` (statetree/csrc/kernels.cu:1892-1924, statetree/csrc/hop.cu:864-925, statetree/csrc/tt.cu:508-556).
- * ws / cnt as for st_gemv (cnt: int32 [M/128 * ceil(B/256)]). */
+ * ws: scratch of st_gemm_workspace_bytes() bytes (possibly 0) for the partial tiles of k ranges split between CTAs;
+ * its contents do not matter on entry and are undefined on exit, so it must not be the buffer the GEMV entry points
+ * use for their exchange slots (or must be refilled with 0xFF before they see it again).  cnt: int32
+ * [M/128 * ceil(B/256)], zero on entry and on exit. */
 int64_t st_gemm_workspace_bytes(int64_t M, int64_t N, int64_t B);
 int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, const void* X, void* Y, float* Yf32, int64_t B,
             int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);

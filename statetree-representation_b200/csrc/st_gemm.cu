@@ -45,7 +45,7 @@ struct GemmArgs {
   const CUtensorMap* maps; const long long* eop; const long long* elp;
   const int* sorted; const int* bexp; const int* npost; int E;
   long long M, N;
-  int B, NG, NT, KS, RB, TT, stages, xstages, rstages, nmma, bar_off;
+  int B, NG, NT, KS, RB, TT, stages, rstages, nmma, bar_off;
   uint32_t idesc;
 };
 
@@ -88,66 +88,37 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-// Sixteen decode warps (one record each per k-step), a record producer, an activation producer and two MMA issuer
-// warps (one per 128-row half): one CTA per SM.
-constexpr int HALVES = 2;                                                   // 128-row halves of a CTA's row block
-constexpr int NISS = HALVES;                                                // MMA issuer warps
-constexpr int NDW = HALVES * NDEC;                                          // decode warps
-constexpr int A_STAGE = HALVES * A_TILE;                                    // decoded weights of one k-step (32 KB)
-constexpr int CH = 64;                                                      // token columns per epilogue pass
+// Two decode groups of eight warps (group g takes the k-tiles g, g + 2, ...), a record producer, an activation
+// producer and two MMA issuer warps: one CTA per SM.
+constexpr int DG = 2;
+constexpr int NDW = DG * NDEC;                                              // decode warps
 constexpr int W_RAW = NDW, W_X = NDW + 1, W_MMA = NDW + 2;                  // role warps
-constexpr int THREADS = (NDW + 2 + NISS) * 32;
-#ifdef ST_X_SPIN_ROLES
-#define GW mbar_wait_spin
-#else
+constexpr int THREADS = (NDW + 2 + DG) * 32;
 #define GW mbar_wait_look
-#endif
-__device__ __forceinline__ bool wait_decode(uint64_t* bar, uint32_t parity) {
-#ifdef ST_X_SPIN_ALL
-  return mbar_wait_spin(bar, parity);
-#else
-  return mbar_wait_look(bar, parity);
-#endif
-}
-constexpr int RAW_SLOT = HALVES * NDEC * REC;    // 24 832 B: the sixteen records of one k-step
+__device__ __forceinline__ bool wait_decode(uint64_t* bar, uint32_t parity) { return GW(bar, parity); }
+constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of one k-tile
 
-// A CTA computes 256 rows of W (two 128-row halves, one accumulator each) against one tile of NT tokens over a
-// contiguous range of k-steps (64 columns).  What bounds this kernel is the bytes an SM can take in from L2 per clock
-// (about 31 B): per k-step the sixteen records (24.8 KB) and the activation tile (NT x 128 B), which every CTA of
-// the grid reads again.  Two halves per activation tile halve that second term against a 128-row CTA.
-// Three rings share the shared memory: S weight stages (2 x 16 KB, decode group -> its MMA issuer), SX activation
-// tiles (a slot is free again when the MMAs that read it have completed), R record slots (cover the HBM latency).
+// Two rings.  The RAW ring (R slots of eight records) faces HBM: its depth sets the bytes in flight.  The TILE ring
+// (S stages of decoded weight tile + activation tile) covers the decode -> MMA hand-over and the L2 latency of the
+// activation loads; one mbarrier per stage counts both operands so the MMA thread waits once and commits once.
 // The KS CTAs that split the k range of one (row block, token tile) form a thread-block cluster (blockIdx.x % KS is
-// the rank).  After the main loop the fp32 accumulators are parked in shared memory 64 token columns at a time; after
-// a cluster barrier CTA j adds the KS partial tiles of its share of those columns through distributed shared memory in
-// rank order (bit-identical from run to run) and stores BF16.  No partial sums travel through global memory.
-#ifdef ST_X_PROF
-__device__ unsigned long long g_prof[16];
-#define PROF_V(v) long long v = 0
-#define PROF_T(v) const long long v = clock64()
-#define PROF_ACC(acc, since) acc += clock64() - since
-#define PROF_OUT(slot, v) do { if (blockIdx.x == 0) atomicAdd(&g_prof[slot], (unsigned long long)(v)); } while (0)
-#else
-#define PROF_V(v)
-#define PROF_T(v)
-#define PROF_ACC(acc, since)
-#define PROF_OUT(slot, v)
-#endif
-
+// the rank).  After its main loop every CTA parks its fp32 accumulator tile in its own shared memory; after a cluster
+// barrier CTA j adds the KS tiles for its share of the token columns through distributed shared memory, in rank
+// order (bit-identical from run to run), and stores BF16.  No partial sums travel through global memory.
 template <bool GROUPED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
+  constexpr int NMMA = DG;                                     // issuer warps; a.nmma of them work
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const int NT = a.NT, S = a.stages, SX = a.xstages, R = a.rstages;
+  const int NT = a.NT, S = a.stages, R = a.rstages;
   const int XT = NT * 128;                       // bytes of an activation tile
-  uint8_t* xring = smem + (size_t)S * A_STAGE;                       // [SX] activation tiles
-  uint8_t* rawring = xring + (size_t)SX * XT;                        // [R] record slots
-  uint64_t* ready = reinterpret_cast<uint64_t*>(smem + a.bar_off);   // [S] the decoded weights of the step are in place
+  const int STAGE = A_TILE + XT;                 // tile stage: decoded weight tile + activation tile
+  uint8_t* rawring = smem + (size_t)S * STAGE;                       // [R] record slots (deep: covers HBM latency)
+  // one barrier per tile stage collects both operands: 8 decode-warp arrivals + the activation tile's TMA bytes
+  uint64_t* ready = reinterpret_cast<uint64_t*>(smem + a.bar_off);   // [S] both operands of the stage are in place
   uint64_t* empty = ready + S;                                       // [S] MMAs that read the stage have completed
-  uint64_t* xfull = empty + S;                                       // [SX] activation tile landed
-  uint64_t* xempty = xfull + SX;                                     // [SX] MMAs that read the slot have completed
-  uint64_t* rfull = xempty + SX;                                     // [R] records landed
+  uint64_t* rfull = empty + S;                                       // [R] records landed
   uint64_t* rempty = rfull + R;                                      // [R] records copied to registers
   uint64_t* accbar = rempty + R;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accbar + 1);
@@ -159,7 +130,6 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
   const int k0 = (int)((long long)a.NG * ks / a.KS), k1 = (int)((long long)a.NG * (ks + 1) / a.KS);
   const int nk = k1 - k0;
   const int tok0 = tt * NT;
-  const int tiles_m = (int)(a.M / 16);                               // 16-row tiles of the matrix
   // the matrix this CTA multiplies by: the one of the call, or (grouped) the expert of pair block tt
   const int* eo = a.eo;
   const uint32_t* el = a.el;
@@ -175,14 +145,13 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
   }
 
   if (tid == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(ready + s, NDW); mbar_init(empty + s, NISS); }
-    for (int s = 0; s < SX; ++s) { mbar_init(xfull + s, 1); mbar_init(xempty + s, NISS); }
-    for (int r = 0; r < R; ++r) { mbar_init(rfull + r, 1); mbar_init(rempty + r, NDW); }
-    mbar_init(accbar, NISS);
+    for (int s = 0; s < S; ++s) { mbar_init(ready + s, NDEC + 1); mbar_init(empty + s, 1); }
+    for (int r = 0; r < R; ++r) { mbar_init(rfull + r, 1); mbar_init(rempty + r, NDEC); }
+    mbar_init(accbar, NMMA);                                       // every issuer warp arrives, working or not
     fence_barrier_init();
   }
   if (warp == W_MMA) {
-    tmem_alloc(tmem_slot, (uint32_t)(HALVES * NT));              // 128 .. 512 columns: one accumulator per half
+    tmem_alloc(tmem_slot, (uint32_t)(a.nmma * NT));              // 64 .. 256 columns: one accumulator per working issuer
     tmem_relinquish();
   }
   tc_fence_before();
@@ -192,23 +161,15 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
   pdl_launch_dependents();
 
   if (warp == W_RAW) {
-    // ---------------------------------------------------------------- record producer: one tiled TMA load per k-step
-    // fetches the sixteen records (row tiles rb * 16 .. + 15 of column group k0 + i) through a 3-D view of the tree
-    // [row tile][column group][194 x u64]; row tiles beyond the matrix come back as zeros
+    // ---------------------------------------------------------------- record producer: one tiled TMA load per k-tile
+    // fetches the eight records (row tiles rb * 8 .. + 7 of column group k0 + i) through a 3-D view of the tree
+    // [row tile][column group][194 x u64]; eight separate 1552-byte bulk copies per k-tile cost ~1 us of issue time
     if (lane == 0) {
-      PROF_V(rw);
       for (int i = 0, r = 0, k = 0; i < nk; ++i, r = (r + 1 == R ? 0 : r + 1), k += (r == 0)) {
-        PROF_T(r0);
         if (k > 0 && !GW(rempty + r, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
-        PROF_ACC(rw, r0);
-#ifdef ST_X_NOLOAD
-        mbar_arrive(rfull + r);
-#else
         mbar_expect_tx(rfull + r, (uint32_t)RAW_SLOT);
-        tma_load_3d(rawring + (size_t)r * RAW_SLOT, wm, 0, k0 + i, rb * (HALVES * NDEC), rfull + r);
-#endif
+        tma_load_3d(rawring + (size_t)r * RAW_SLOT, wm, 0, k0 + i, rb * 8, rfull + r);
       }
-      PROF_OUT(13, rw);
     }
   } else if (warp == W_X) {
     // ---------------------------------------------------------------- activation producer.  The activations are the
@@ -217,107 +178,87 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
     // waits for it.  Everything that touches the output is downstream of the first activation tile.
     if (lane == 0) {
       pdl_wait();
-      PROF_V(xw); PROF_V(xi); PROF_V(xl);
-      for (int i = 0, s = 0, k = 0; i < nk; ++i, s = (s + 1 == SX ? 0 : s + 1), k += (s == 0)) {
-        PROF_T(x0);
-        if (k > 0 && !GW(xempty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
-        PROF_ACC(xw, x0);
-        PROF_T(x1);
-        mbar_expect_tx(xfull + s, (uint32_t)XT);
-        tma_load_2d(xring + (size_t)s * XT, &xmap, (k0 + i) * 64, tok0, xfull + s);
-        PROF_ACC(xi, x1);
+      for (int i = 0, s = 0, k = 0; i < nk; ++i, s = (s + 1 == S ? 0 : s + 1), k += (s == 0)) {
+        if (k > 0 && !GW(empty + s, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
+        mbar_expect_tx(ready + s, (uint32_t)XT);
+        tma_load_2d(smem + (size_t)s * STAGE + A_TILE, &xmap, (k0 + i) * 64, tok0, ready + s);
       }
-      PROF_OUT(11, xi);
-      PROF_OUT(12, xl);
-      PROF_OUT(9, xw);
-      PROF_OUT(10, nk);
     }
   } else if (warp >= W_MMA) {
-    // ---------------------------------------------------------------- MMA issuers, one per 128-row half.  A thread
-    // pays several hundred cycles per k-step for its waits, four tcgen05.mma and two commits, so each half has its own.
-    // Both wait for the same stage and activation slot and both commit to them (the barriers count two arrivals); every
-    // ring has one producer and consumers that move through it in step order, so no waiter is ever more than one phase
-    // ahead of its barrier, whatever the slot counts.
+    // ---------------------------------------------------------------- MMA issuers.  One thread pays ~80 cycles per
+    // tcgen05.mma it issues plus the barrier wait and the commit, about 700 cycles per k-tile: more than the tile's
+    // share of HBM time.  Two issuers alternate k-tiles, each into its own accumulator (the epilogue adds the two in a
+    // fixed order), so the serial cost per k-tile halves and the result does not depend on which issuer ran first.
+    // This needs an even number of tile stages and record slots: then every stage and slot belongs to one decode group
+    // and one issuer, which use it in their own program order.  (A waiter may be at most one phase ahead of an mbarrier:
+    // with shared stages an issuer could ask for use k of a stage whose use k - 1, the other issuer's, has not
+    // completed, and the parity test would pass on use k - 2.)  With three stages (256-token tiles) one issuer works.
     const int m = warp - W_MMA;
-    if (lane == 0) {
+    if (lane == 0 && m >= a.nmma) mbar_arrive(accbar);
+    if (lane == 0 && m < a.nmma) {
       const uint32_t acc = tmem + (uint32_t)(m * NT);
-      PROF_V(iwx); PROF_V(iwa); PROF_V(iis);
-      for (int i = 0, s = 0, k = 0, xs = 0, xk = 0; i < nk; ++i) {
-        PROF_T(t0);
-        const bool okx = GW(xfull + xs, (uint32_t)xk & 1u);
-        PROF_ACC(iwx, t0);
-        PROF_T(t1);
-        if (!okx || !GW(ready + s, (uint32_t)k & 1u)) {
+      int s = m % S, k = m / S;
+      for (int i = m; i < nk; i += a.nmma) {
+        if (!GW(ready + s, (uint32_t)k & 1u)) {
           atomicExch(a.status, ERR_WAIT_MMA);
           break;
         }
-        PROF_ACC(iwa, t1);
-        PROF_T(t2);
         tc_fence_after();
-        const uint64_t da = smem_desc_sw128(smem_addr(smem + (size_t)s * A_STAGE + (size_t)m * A_TILE));
-        const uint64_t db = smem_desc_sw128(smem_addr(xring + (size_t)xs * XT));
+        const uint32_t sa = smem_addr(smem + (size_t)s * STAGE);
+        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TILE);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tc_mma(acc, da + 2 * j, db + 2 * j, a.idesc, (i || j) ? 1u : 0u);
+        for (int j = 0; j < 4; ++j) tc_mma(acc, da + 2 * j, db + 2 * j, a.idesc, (i >= a.nmma || j) ? 1u : 0u);
         tc_commit(empty + s);
-        tc_commit(xempty + xs);
-        if (++s == S) { s = 0; ++k; }
-        if (++xs == SX) { xs = 0; ++xk; }
-        PROF_ACC(iis, t2);
+        s += a.nmma; while (s >= S) { s -= S; ++k; }
       }
-      if (m == 0) { PROF_OUT(0, iwx); PROF_OUT(1, iwa); PROF_OUT(2, iis); PROF_OUT(3, nk); }
       tc_commit(accbar);                                          // arrives when every MMA of this issuer has completed
     }
   } else {
-    // ---------------------------------------------------------------- decode warps: warp w decodes record w of every
-    // k-step (rows 16 w .. 16 w + 15 of the row block: half w / 8, rows 16 (w % 8) .. of that half)
-    const int rowtile = rb * NDW + warp;
-    const bool live = rowtile < tiles_m;                           // M may end inside the row block
-    const size_t rbase = (size_t)rowtile * a.NG + k0;
-    // Escape entries are fetched one k-step ahead: the list offsets of this warp's records come 32 k-steps at a time
-    // (lane l holds the offsets of step eo_base + l) and the first 32 entries of the next record are requested before
+    // ---------------------------------------------------------------- decode warps: group g = warp / 8 takes the
+    // k-tiles i = g, g + DG, ...; warp r of a group decodes record r (rows 16 r .. 16 r + 15 of the block)
+    const int grp = warp / NDEC, rec = warp % NDEC;
+    const size_t rbase = (size_t)(rb * 8 + rec) * a.NG + k0;
+    // Escape entries are fetched one k-tile ahead: the list offsets of this warp's records come 32 k-tiles at a time
+    // (lane l holds the offsets of k-tile eo_base + l) and the first 32 entries of the next record are requested before
     // this record is decoded, so no global-load latency sits between the records landing and the tile being handed
-    // to the tensor core (one record in six has an escape; all warps must arrive before the MMAs can start)
+    // to the tensor core (one record in six has an escape; eight warps must all arrive before the MMA can start)
     int eo_base = 0, eo_lo = 0, eo_hi = 0;
-    unsigned emask = 0u;                                           // bit l: step eo_base + l of this warp has escapes
+    unsigned emask = 0u;                                           // bit l: k-tile eo_base + l of this warp has escapes
     auto load_offsets = [&](int first) {
       eo_base = first;
       const int j = first + lane;
-      eo_lo = (live && j < nk) ? __ldg(eo + rbase + j) : 0;
-      eo_hi = (live && j < nk) ? __ldg(eo + rbase + j + 1) : 0;
+      eo_lo = j < nk ? __ldg(eo + rbase + j) : 0;
+      eo_hi = j < nk ? __ldg(eo + rbase + j + 1) : 0;
       emask = __ballot_sync(FULL, eo_hi > eo_lo);
     };
     int lo = 0, hi = 0;
     uint32_t ent = 0u;
-    if (nk > 0) {
-      load_offsets(0);
+    if (grp < nk) {
+      load_offsets(grp);
       if (emask & 1u) {
         lo = __shfl_sync(FULL, eo_lo, 0);
         hi = __shfl_sync(FULL, eo_hi, 0);
         if (lane < hi - lo) ent = __ldg(el + lo + lane);
       }
     }
-    const int half = warp / NDEC, rec = warp % NDEC;
-    PROF_V(dwr); PROF_V(dwe); PROF_V(dall);
-    PROF_T(dstart);
-    for (int i = 0, s = 0, k = 0, r = 0, rk = 0; i < nk; ++i) {
+    int s = grp % S, k = grp / S, r = grp % R, rk = grp / R;          // tile stage / use count, record slot / use count
+    for (int i = grp; i < nk; i += DG) {
       int nlo = 0, nhi = 0;
       uint32_t nent = 0u;
-      if (i + 1 < nk) {
-        if (i + 1 - eo_base >= 32) load_offsets(i + 1);
-        const int off = i + 1 - eo_base;
+      if (i + DG < nk) {
+        if (i + DG - eo_base >= 32) load_offsets(i + DG);
+        const int off = i + DG - eo_base;
         if ((emask >> off) & 1u) {                                // five records in six have none: one bit test
           nlo = __shfl_sync(FULL, eo_lo, off);
           nhi = __shfl_sync(FULL, eo_hi, off);
           if (lane < nhi - nlo) nent = __ldg(el + nlo + lane);
         }
       }
-      PROF_T(d1);
       if (!wait_decode(rfull + r, (uint32_t)rk & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
         break;
       }
-      PROF_ACC(dwr, d1);
-      const RecRegs rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + warp * REC, lane);
+      const RecRegs rr = load_rec_shared(rawring + (size_t)r * RAW_SLOT + rec * REC, lane);
       __syncwarp();
       if (lane == 0) mbar_arrive(rempty + r);                     // the slot can be refilled while we decode
       uint32_t A[4][4];
@@ -332,13 +273,11 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
         for (int e = 0; e < n; ++e) patch_entry(A, __shfl_sync(FULL, mine, e), lane);
       }
       lo = nlo; hi = nhi; ent = nent;
-      PROF_T(d3);
       if (k > 0 && !wait_decode(empty + s, (uint32_t)(k - 1) & 1u)) {   // the MMAs of the stage's last use are done
         if (lane == 0) atomicExch(a.status, ERR_WAIT_EMPTY);
         break;
       }
-      PROF_ACC(dwe, d3);
-      uint8_t* st = smem + (size_t)s * A_STAGE + (size_t)half * A_TILE;
+      uint8_t* st = smem + (size_t)s * STAGE;
       // lane l addresses row (l & 7) of matrix (l >> 3): matrices = (rows 0-7 | 8-15) x (16-byte chunk 2q | 2q+1)
       const int mrow = rec * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
       const uint32_t rowaddr = smem_addr(st) + mrow * 128;
@@ -349,74 +288,82 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(ready + s);
-      if (++s == S) { s = 0; ++k; }
-      if (++r == R) { r = 0; ++rk; }
+      s += DG; while (s >= S) { s -= S; ++k; }
+      r += DG; while (r >= R) { r -= R; ++rk; }
     }
-    PROF_ACC(dall, dstart);
-    if (warp == 0 && lane == 0) { PROF_OUT(4, dwr); PROF_OUT(5, dwe); PROF_OUT(6, dall); PROF_OUT(8, nk); }
-    const bool acc_ok = GW(accbar, 0u);                          // every MMA of both issuers has completed
+    // ---------------------------------------------------------------- epilogue 1: accumulator -> own shared memory
+    const bool acc_ok = GW(accbar, 0u);
     if (!acc_ok && lane == 0) atomicExch(a.status, ERR_WAIT_ACC);
     tc_fence_after();
-  }
-  // -------------------------------------------------------------------- epilogue, CH token columns per pass
-  float* stg = reinterpret_cast<float*>(smem);                   // [CH][256] fp32, over the (now idle) rings
-  const int ncol = GROUPED ? NT : min(NT, a.B - tok0);          // grouped: padding pairs are filtered per column
-  for (int c0 = 0; c0 < NT; c0 += CH) {
-    if (warp < NDW) {
-      // pass 1: accumulators -> own shared memory.  A warp reads the TMEM lanes of its quadrant (warp % 4): it takes
-      // rows 32 q .. 32 q + 31 of half (warp / 4) % 2 and 32 of the pass's 64 columns
-      const int q4 = warp & 3, hf = (warp >> 2) & 1, cs = (warp >> 3) * 32;
+    float* stg = reinterpret_cast<float*>(smem);                 // [NT][128] fp32, over the (now idle) ring
+    const int q4 = warp & 3, cg = warp >> 2;                     // TMEM lane quadrant, column share of the warp
+    const int cper = NT / (NDW / 4);
+    const bool two = a.nmma > 1 && nk > 1;                       // the second issuer had a k-tile
+    for (int c0 = cg * cper; c0 < (cg + 1) * cper; c0 += 16) {
+      uint32_t v[32], w[32];                                     // (the x16 load fills the first sixteen)
+      const uint32_t t0 = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;
+      tmem_ld16(t0, v);
+      if (two) {
+        tmem_ld16(t0 + (uint32_t)NT, w);
 #pragma unroll
-      for (int cc = 0; cc < 32; cc += 16) {
-        uint32_t v[32];                                          // (the x16 load fills the first sixteen)
-        tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(hf * NT + c0 + cs + cc), v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) stg[(size_t)(cs + cc + j) * 256 + hf * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
+        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
       }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) stg[(size_t)(c0 + j) * 128 + q4 * 32 + lane] = __uint_as_float(v[j]);
     }
-    tc_fence_before();
-    __syncwarp();
-    cluster_sync_all();                                          // every CTA of the cluster has parked its columns
-    if (warp < NDW) {
-      // pass 2: CTA ks adds the KS partial tiles of its share of the pass's columns, in rank order
-      const int c_lo = (int)((long long)CH * ks / a.KS), c_hi = (int)((long long)CH * (ks + 1) / a.KS);
-      const int c_end = min(c_hi, ncol - c0);
-      const uint32_t mine = smem_addr(smem);
-      for (int c = c_lo + warp; c < c_end; c += NDW) {
-        long long row = tok0 + c0 + c;
+  }
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();                                            // every CTA of the cluster has parked its tile
+  if (warp < NDW) {
+    // ---------------------------------------------------------------- epilogue 2: add the KS tiles, rank order
+    const int ncol = GROUPED ? NT : min(NT, a.B - tok0);        // grouped: padding pairs are filtered per column
+    const int c_lo = (int)((long long)NT * ks / a.KS), c_hi = (int)((long long)NT * (ks + 1) / a.KS);
+    const uint32_t mine = smem_addr(smem);
+    const int c_end = min(c_hi, ncol);
+    // two columns per pass, every partial tile's float4 requested before the first add: distributed-shared-memory
+    // reads have a long latency, so the loads of a pass must all be in flight together
+    for (int c = c_lo + warp; c < c_end; c += 2 * NDW) {
+      const int c2 = c + NDW;
+      float4 v0[8], v1[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        if (p < a.KS) {
+          v0[p] = ld_cluster_f4(map_to_cta(mine + (uint32_t)((c * 128 + 4 * lane) * 4), (uint32_t)p));
+          if (c2 < c_end) v1[p] = ld_cluster_f4(map_to_cta(mine + (uint32_t)((c2 * 128 + 4 * lane) * 4), (uint32_t)p));
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int cc = h ? c2 : c;
+        if (cc >= c_end) break;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          if (p < a.KS) {
+            const float4 v = h ? v1[p] : v0[p];
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+          }
+        }
+        long long row = tok0 + cc;
         if (GROUPED) {                                            // result rows go back to their pair index
-          row = a.sorted[tok0 + c0 + c];
+          row = a.sorted[tok0 + cc];
           if (row < 0 || row >= a.B) continue;
         }
-#pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-          const long long m0 = (long long)rb * 256 + h * 128;
-          if (m0 >= a.M) continue;                                // the matrix ends inside this row block
-          // every partial tile's values requested before the first add: distributed-shared-memory reads have a long
-          // latency, so the loads of a column must all be in flight together
-          float4 v[8];
-#pragma unroll
-          for (int p = 0; p < 8; ++p)
-            if (p < a.KS) v[p] = ld_cluster_f4(map_to_cta(mine + (uint32_t)((c * 256 + h * 128 + 4 * lane) * 4), (uint32_t)p));
-          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int p = 0; p < 8; ++p)
-            if (p < a.KS) { sum.x += v[p].x; sum.y += v[p].y; sum.z += v[p].z; sum.w += v[p].w; }
-          const size_t o = (size_t)row * a.M + m0 + 4 * lane;
-          uint2 packed;
-          packed.x = pack_bf16(sum.x, sum.y);
-          packed.y = pack_bf16(sum.z, sum.w);
-          *reinterpret_cast<uint2*>(a.Y + o) = packed;
-          if (a.Yf) *reinterpret_cast<float4*>(a.Yf + o) = sum;
-        }
+        const size_t o = (size_t)row * a.M + rb * 128 + 4 * lane;
+        uint2 packed;
+        packed.x = pack_bf16(sum.x, sum.y);
+        packed.y = pack_bf16(sum.z, sum.w);
+        *reinterpret_cast<uint2*>(a.Y + o) = packed;
+        if (a.Yf) *reinterpret_cast<float4*>(a.Yf + o) = sum;
       }
     }
-    __syncwarp();
-    cluster_sync_all();                                          // nobody overwrites (or leaves) while a peer still reads
   }
+  __syncwarp();
+  cluster_sync_all();                                            // nobody leaves while a peer still reads its tile
   if (warp == W_MMA) {
     __syncwarp();
-    tmem_dealloc(tmem, (uint32_t)(HALVES * NT));
+    tmem_dealloc(tmem, (uint32_t)(a.nmma * NT));
   }
 }
 
@@ -438,7 +385,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-struct GemmPlan { int NT, TT, RB, KS, stages, xstages, rstages, nmma, bar_off; size_t smem; };
+struct GemmPlan { int NT, TT, RB, KS, stages, rstages, nmma, bar_off; size_t smem; };
 
 template <bool GROUPED>
 int gemm_attr() {                                                // once per device: opt in to the large dynamic shared memory
@@ -485,32 +432,26 @@ long long resident_ctas(int ks, int NT, size_t smem, int sms) {
   return (long long)cache[dev][ks][ti] * ks;
 }
 
-// development builds (-DST_TUNE) read ring depths from the environment; the shipped library does not
-static int gemm_tune(const char* name, int dflt) {
-#ifdef ST_TUNE
-  const char* v = getenv(name);
-  return v ? atoi(v) : dflt;
-#else
-  (void)name;
-  return dflt;
-#endif
-}
-
-// rings for a token tile of NT.  Three rings share the CTA's shared memory:
-//   weight stages (32 KB each): the hand-over between the decode warps and the MMA issuers;
-//   activation tiles (NT x 128 B each): loaded from L2 for every k-step; a slot is free again only when the MMAs that
-//     read it have completed;
-//   record slots (24 832 B each): cover the HBM latency of the weight stream.
+// rings and issuers for a token tile of NT
 void gemm_rings(GemmPlan& p) {
-  const size_t xt = (size_t)p.NT * 128;
-  const size_t stg = (size_t)CH * 256 * 4;                        // the parked accumulator columns reuse the rings
-  p.stages = gemm_tune("STATETREE_GEMM_S", p.NT >= 256 ? 2 : 3);
-  p.xstages = gemm_tune("STATETREE_GEMM_SX", p.NT >= 256 ? 2 : (p.NT >= 128 ? 2 : 4));
-  p.rstages = gemm_tune("STATETREE_GEMM_R", 3);
-  const size_t budget = 212 * 1024;
-  while (p.rstages > 2 && p.stages * (size_t)A_STAGE + p.xstages * xt + p.rstages * (size_t)RAW_SLOT > budget) --p.rstages;
-  p.nmma = NISS;
-  size_t ring = (size_t)p.stages * A_STAGE + (size_t)p.xstages * xt + (size_t)p.rstages * RAW_SLOT;
+  const size_t stage = A_TILE + (size_t)p.NT * 128;
+  const size_t stg = (size_t)p.NT * 128 * 4;                      // the parked accumulator tile reuses the rings
+  // tile stages (decoded weight tile + activation tile): enough to cover the L2 latency of the activation loads; the
+  // rest of the shared memory goes to the record ring, which covers the HBM latency
+  p.stages = p.NT >= 256 ? 3 : 4;
+  p.rstages = (int)((212 * 1024 - p.stages * stage) / RAW_SLOT);
+  if (p.rstages > 12) p.rstages = 12;
+  // The two decode groups alternate k-tiles.  A decode warp waits for the fill of a record slot by the parity of that
+  // slot's use count, and an mbarrier tells only the current phase from the previous one, so a waiter must never be
+  // two fills ahead.  With an even slot count every slot belongs to one group, whose own program order guarantees
+  // that; with an odd count the groups share slots, and a group that runs ahead while a bulk copy of the other
+  // group's k-tile is still in flight passes its wait on the stale phase, reads old records and releases the slot a
+  // second time.  So: always an even number of record slots.  (Tile stages may be odd: their waits are on the
+  // previous use of a stage.)
+  p.rstages &= ~1;
+  // two MMA issuers need every tile stage owned by one decode group as well: an even count of stages
+  p.nmma = (p.stages % 2 == 0 && p.rstages >= 4) ? 2 : 1;
+  size_t ring = (size_t)p.stages * stage + (size_t)p.rstages * RAW_SLOT;
   ring = (ring + 15) & ~(size_t)15;
   if (ring < stg) ring = stg;
   p.bar_off = (int)ring;
@@ -521,7 +462,7 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   GemmPlan p;
   p.NT = B <= 64 ? 64 : (B <= 128 ? 128 : 256);
   p.TT = (int)((B + p.NT - 1) / p.NT);
-  p.RB = (int)((M + 255) / 256);
+  p.RB = (int)(M / 128);
   const int NG = (int)(N / 64), sms = st::sm_count();
   const long long units = (long long)p.RB * p.TT;
   gemm_rings(p);
@@ -584,7 +525,7 @@ int make_wmap(CUtensorMap* map, const void* tree, long long M, long long N, cons
   ST_REQUIRE(enc != nullptr, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
   const cuuint64_t wd[3] = {194u, (cuuint64_t)(N / 64), (cuuint64_t)(M / 16)};
   const cuuint64_t wst[2] = {(cuuint64_t)REC, (cuuint64_t)(N / 64) * REC};
-  const cuuint32_t wbox[3] = {194u, 1u, 16u};
+  const cuuint32_t wbox[3] = {194u, 1u, 8u};
   const cuuint32_t we[3] = {1u, 1u, 1u};
   const CUresult wr = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(tree), wd, wst, wbox, we,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -596,16 +537,6 @@ int make_wmap(CUtensorMap* map, const void* tree, long long M, long long N, cons
 // instruction descriptor: D fp32, A and B bf16, both K-major, N = NT, M = 128
 uint32_t mma_idesc(int NT) { return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24); }
 }  // namespace
-
-
-#ifdef ST_X_PROF
-extern "C" int st_x_prof_read(unsigned long long* out16, int clear) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, g_prof, sizeof(unsigned long long) * 16);
-  if (clear) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
-  return 0;
-}
-#endif
 
 extern "C" int64_t st_gemm_workspace_bytes(int64_t M, int64_t N, int64_t B) {
   if (M <= 0 || N <= 0 || M % 128 || N % 64 || B < 1) return -1;
@@ -630,7 +561,7 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "st_gemm: no device status word");
   a.M = M; a.N = N; a.B = (int)B; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = p.KS; a.RB = p.RB; a.TT = p.TT;
-  a.stages = p.stages; a.xstages = p.xstages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
+  a.stages = p.stages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
   a.idesc = mma_idesc(p.NT);
   return gemm_launch<false>(p, a, xmap, wmap, (cudaStream_t)stream);
 }
@@ -666,7 +597,7 @@ extern "C" int st_moe_group_gemm(const void* maps, const int64_t* eop, const int
   GemmPlan p;
   p.NT = (int)bs;
   p.TT = (int)nblk;
-  p.RB = (int)((M + 255) / 256);
+  p.RB = (int)(M / 128);
   p.KS = 1;
   gemm_rings(p);
   ST_REQUIRE((long long)p.RB * p.TT < (1ll << 31), "st_moe_group_gemm: grid too large");
@@ -680,7 +611,7 @@ extern "C" int st_moe_group_gemm(const void* maps, const int64_t* eop, const int
   a.status = st::status_ptr();
   ST_REQUIRE(a.status != nullptr, "st_moe_group_gemm: no device status word");
   a.M = M; a.N = N; a.B = (int)S; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = 1; a.RB = p.RB; a.TT = p.TT;
-  a.stages = p.stages; a.xstages = p.xstages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
+  a.stages = p.stages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
   a.idesc = mma_idesc(p.NT);
   return gemm_launch<true>(p, a, xmap, unused, (cudaStream_t)stream);
 }

@@ -35,6 +35,7 @@ class _DevState:
         self.device = device
         self._retired = []
         self.ws = self._new_ws(1 << 20)
+        self.scratch = torch.empty(1 << 20, dtype=torch.float32, device=device)   # the GEMM's partial tiles (no contract)
         self.cnt = torch.zeros(1 << 16, dtype=torch.int32, device=device)
 
     def _new_ws(self, words):
@@ -45,6 +46,12 @@ class _DevState:
             self._retired.append(self.ws)
             self.ws = self._new_ws((nbytes + 3) // 4)
         return self.ws
+
+    def get_scratch(self, nbytes):
+        if self.scratch.numel() * 4 < nbytes:
+            self._retired.append(self.scratch)
+            self.scratch = torch.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.device)
+        return self.scratch
 
     def get_cnt(self, n):
         if self.cnt.numel() < n:
@@ -211,7 +218,7 @@ class TreeLinear(nn.Module):
             ws = st.get_ws(E.gemv_workspace_bytes(M, N, B))
             E.gemv(self.tree, eo, eb, el, x, y, ws, st.get_cnt(M // 16), yf32)
         elif M % 128 == 0:
-            ws = st.get_ws(E.gemm_workspace_bytes(M, N, B))
+            ws = st.get_scratch(E.gemm_workspace_bytes(M, N, B))
             E.gemm(self.tree, eo, el, x, y, ws, st.get_cnt((M // 128) * ((B + 255) // 256)), yf32)
         else:                                           # rows not a multiple of 128: GEMV kernel in row chunks
             step = min(32, max(GEMV_MAX, 16))
