@@ -53,7 +53,7 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def measured_traffic(batch, world, layers):
+def measured_traffic(batch, world, layers, launches_per_layer):
     """DRAM bytes per launch of the dominant kernel from the tracked ncu summary (a JSON next to the text summary that
     also names the kernel source it was captured from); (None, reason) when there is none for this workload or the
     kernel source has changed since the capture"""
@@ -68,6 +68,8 @@ def measured_traffic(batch, world, layers):
         sha = hashlib.sha256(f.read()).hexdigest()[:16]
     if rec.get("kernel_source_sha256_16") != sha:
         return None, "kernel source changed since the capture"
+    if rec.get("launches_per_layer") != launches_per_layer:
+        return None, "no capture for this launch layout"
     return rec["dram_bytes_per_launch"], f"ncu capture of {rec.get('captured', '?')}"
 
 
@@ -1047,7 +1049,7 @@ def main():
     hbm, tf, which = peaks()
     value = step_bytes / (ms * 1e-3) / 1e9
     per_gpu = value / world
-    traffic, traffic_source = measured_traffic(B, world, args.layers)
+    traffic, traffic_source = measured_traffic(B, world, args.layers, launches // max(args.layers, 1))
     roof = {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s", "frac": per_gpu / hbm,
             "traffic": traffic, "traffic_source": traffic_source, "peak_source": f"of {which}",
             "frac_of_nominal_8TBs": per_gpu / 8000.0,
