@@ -150,8 +150,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try(bar, parity)) return true;
   return false;
 }
-// the same with a non-blocking look first, for waiters whose barrier has usually flipped already (measured: 2 % on the
-// tcgen05 GEMM, whose warps wait twice per k-tile; nothing on the GEMV)
+// the same with a non-blocking look first, for waiters whose barrier has usually flipped already (the tcgen05 GEMM's
+// warps, which wait twice per k-tile)
 __device__ __forceinline__ bool mbar_wait_look(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"

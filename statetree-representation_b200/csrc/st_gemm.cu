@@ -163,7 +163,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
   if (warp == W_RAW) {
     // ---------------------------------------------------------------- record producer: one tiled TMA load per k-tile
     // fetches the eight records (row tiles rb * 8 .. + 7 of column group k0 + i) through a 3-D view of the tree
-    // [row tile][column group][194 x u64]; eight separate 1552-byte bulk copies per k-tile cost ~1 us of issue time
+    // [row tile][column group][194 x u64]; eight separate 1552-byte bulk copies per k-tile would cost far more issue time
     if (lane == 0) {
       for (int i = 0, r = 0, k = 0; i < nk; ++i, r = (r + 1 == R ? 0 : r + 1), k += (r == 0)) {
         if (k > 0 && !GW(rempty + r, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
@@ -185,9 +185,9 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
       }
     }
   } else if (warp >= W_MMA) {
-    // ---------------------------------------------------------------- MMA issuers.  One thread pays ~80 cycles per
-    // tcgen05.mma it issues plus the barrier wait and the commit, about 700 cycles per k-tile: more than the tile's
-    // share of HBM time.  Two issuers alternate k-tiles, each into its own accumulator (the epilogue adds the two in a
+    // ---------------------------------------------------------------- MMA issuers.  The serial cost of one thread
+    // per k-tile (its barrier wait, four tcgen05.mma and the commit) is of the order of a k-tile's share of the decode
+    // time, so one issuer would hold the pipeline back.  Two issuers alternate k-tiles, each into its own accumulator (the epilogue adds the two in a
     // fixed order), so the serial cost per k-tile halves and the result does not depend on which issuer ran first.
     // This needs an even number of tile stages and record slots: then every stage and slot belongs to one decode group
     // and one issuer, which use it in their own program order.  (A waiter may be at most one phase ahead of an mbarrier:

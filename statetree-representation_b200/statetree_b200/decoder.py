@@ -13,7 +13,6 @@ output, and the partial outputs are all-reduced).  Every rank draws the full ten
 so a tensor-parallel run computes the same function as the single-GPU one.
 """
 import math
-import os
 from dataclasses import dataclass
 
 import torch
@@ -74,7 +73,7 @@ class TreeDecoder:
             assert c.experts % world == 0
             from .parallel import expert_partition
             self.e_lo, self.e_hi, self.emap = expert_partition(c.experts, rank, world, self.dev)
-        if compressed and not c.experts and batch <= 8 and os.environ.get("STATETREE_FUSED_ACT", "1") != "0":
+        if compressed and not c.experts and batch <= 8:
             from .ops import lib
             with torch.cuda.device(self.dev):
                 self.fused_act = bool(lib().st_gemv_swiglu_supported(2 * c.inter // world, c.hidden, batch))

@@ -4,7 +4,6 @@ block (reference 337-519) over the sm_100a kernels.  One kernel serves both slot
 beyond "few pairs: one problem per (token, expert) slot; many pairs: slots grouped by expert, each expert's records
 read once per block of 8 slots".
 """
-import os
 
 import torch
 import torch.nn as nn
@@ -62,9 +61,6 @@ def moe_gemv(tables, x, ids, M, xdiv):
     return y
 
 
-ALIGN_KERNEL = os.environ.get("STATETREE_MOE_ALIGN_KERNEL", "1") != "0"   # 0: the torch formulation
-
-
 def moe_align(ids, E, bs=8, used_bins=None):
     """Pairs grouped by expert in blocks of bs (the moe_align_block_size layout), with torch ops and no host sync:
     (sorted_ids int32 [nblk * bs], padded with S; bexp int32 [nblk]; npost int32 [1] = entries of the first used_bins
@@ -72,7 +68,7 @@ def moe_align(ids, E, bs=8, used_bins=None):
     ids = ids.reshape(-1)
     S, dev = ids.numel(), ids.device
     nblk = S // bs + min(S, E) + 1
-    if (ALIGN_KERNEL and ids.is_cuda and 1 <= S <= (1 << 20) and E <= 1024
+    if (ids.is_cuda and 1 <= S <= (1 << 20) and E <= 1024
             and ids.dtype in (torch.int64, torch.int32)):
         # one CTA of the kernel library does the whole grouping (the torch formulation below is ~20 small launches)
         sorted_ids = torch.empty(nblk * bs, dtype=torch.int32, device=dev)

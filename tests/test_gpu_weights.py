@@ -242,3 +242,39 @@ def test_gemv_swiglu_matches_gemv_then_silu_mul():
     assert lib().st_gemv_swiglu_supported(2 * 48, 64, 1) in (0, 1)      # small shapes: answered, never a crash
     from statetree_b200 import ops
     assert ops.device_status() == 0
+
+
+def test_workspace_growth_keeps_captured_graphs_valid():
+    """a CUDA graph captured at one shape keeps replaying correctly after a much larger shape has made the shared
+    workspace grow: buffers that were handed out are retired, never freed"""
+    from statetree_b200.linear import _state
+    W = G.weights(512, 1024, 21, "mixed")
+    tl, _ = layer_from_oracle(W)
+    x = bits_to_torch(G.to_bf16_bits(np.random.RandomState(1).standard_normal((3, 1024))), DEV)
+    want = tl(x).clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        st = _state(torch.device(DEV))
+        y = tl(x)
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        y = tl(x)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        before = st.ws.data_ptr()
+        big, _ = layer_from_oracle(G.weights(4096, 8192, 22, "llm"))
+        xb = bits_to_torch(G.to_bf16_bits(np.random.RandomState(2).standard_normal((12, 8192))), DEV)
+        st.get_ws(st.ws.numel() * 4 + (64 << 20))             # force the workspace of this stream to grow
+        assert st.ws.data_ptr() != before and len(st._retired) >= 1
+        big(xb)
+        filler = [torch.full((1 << 20,), 0.5, device=DEV) for _ in range(8)]   # whatever the allocator hands out next
+    side.synchronize()
+    for _ in range(3):
+        y.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, want)
+    del filler
+    _status_ok()
