@@ -969,10 +969,11 @@ def main():
                 cnt_s = st.get_cnt(4096)
 
                 lists_s = None
-                if gemv_path and use_lists:                  # q / k / v and gate / up as one list launch each, as above
-                    need_s = max(need_s, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, Bs),
-                                 E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, Bs))
-                    ws_s = st.get_ws(need_s)
+                if use_lists:                                # q / k / v and gate / up as one list launch each, as above
+                    if gemv_path:
+                        need_s = max(need_s, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, Bs),
+                                     E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, Bs))
+                        ws_s = st.get_ws(need_s)
 
                     def largs(row, lo, hi):
                         tabs = []
@@ -984,7 +985,7 @@ def main():
                     lists_s = [(largs(row, 0, 3), largs(row, 4, 6)) for row in layers]
 
                 def run_tree():
-                    if lists_s is not None:
+                    if lists_s is not None and gemv_path:
                         for row, (qkv, gate_up) in zip(layers, lists_s):
                             E.gemv_list(qkv, xs[HIDDEN], ws_s)
                             eo, el, eb = row[3]._tables
@@ -992,6 +993,15 @@ def main():
                             E.gemv_list(gate_up, xs[HIDDEN], ws_s)
                             eo, el, eb = row[6]._tables
                             E.gemv(row[6].tree, eo, eb, el, xs[INTER], ys[6], ws_s, cnt_s)
+                        return
+                    if lists_s is not None:
+                        for row, (qkv, gate_up) in zip(layers, lists_s):
+                            E.gemm_list(qkv, xs[HIDDEN], cnt_s)
+                            eo, el, eb = row[3]._tables
+                            E.gemm(row[3].tree, eo, el, xs[HIDDEN], ys[3], ws_s, cnt_s)
+                            E.gemm_list(gate_up, xs[HIDDEN], cnt_s)
+                            eo, el, eb = row[6]._tables
+                            E.gemm(row[6].tree, eo, el, xs[INTER], ys[6], ws_s, cnt_s)
                         return
                     for row in layers:
                         for tl, y in zip(row, ys):
@@ -1007,7 +1017,8 @@ def main():
                             torch.matmul(xs[W.shape[1]], W.t(), out=y)
 
                 point = {"batch": Bs, "kernel": ("gemv_kernel, list launches" if lists_s is not None else "gemv_kernel")
-                         if gemv_path else "gemm_kernel (tcgen05)"}
+                         if gemv_path else ("gemm_kernel (tcgen05), list launches" if lists_s is not None
+                                            else "gemm_kernel (tcgen05)")}
                 for key, fn in (("ms_per_step", run_tree), ("bf16_control_ms", run_ctl)):
                     torch.cuda.synchronize()
                     with torch.cuda.stream(side):

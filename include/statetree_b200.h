@@ -90,6 +90,14 @@ int64_t st_gemm_workspace_bytes(int64_t M, int64_t N, int64_t B);
 int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, const void* X, void* Y, float* Yf32, int64_t B,
             int64_t M, int64_t N, void* ws, int64_t ws_bytes, int32_t* cnt, void* stream);
 
+/* st_gemm for a LIST of 1 to 4 matrices that share N and the activations (q / k / v, gate / up kept as separate
+ * trees), in one launch: Y[i] [B, M[i]] = X W[i]^T, M[i] % 128 == 0.  The members' 128-row blocks form one grid, so
+ * the list pays one launch, one pipeline fill and one epilogue.  trees / eo / el / Y / Yf32 / M are HOST arrays of n
+ * entries (Yf32 or any of its entries may be NULL).  Same results as st_gemm on each member wherever both split the k
+ * range alike.  The reference reaches the same end by fusing the trees at conversion time (statetree/model.py:22-24). */
+int st_gemm_list(int64_t n, const void* const* trees, const int32_t* const* eo, const uint32_t* const* el, const void* X,
+                 void* const* Y, float* const* Yf32, int64_t B, const int64_t* M, int64_t N, int32_t* cnt, void* stream);
+
 /* ---- mixture of experts ----------------------------------------------------------------------------------------- */
 /* y[s] = W[ids[s]] x[s / xdiv] for S (token, expert) slots; tp / eop / ebp / elp: int64 [E] device addresses of each
  * expert's tree, eo, eb and el tables (all experts M x N); ids int32 (ids64 = 0) or int64 (ids64 = 1), clamped to [0, E).

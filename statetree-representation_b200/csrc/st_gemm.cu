@@ -38,6 +38,8 @@ using namespace st;
 constexpr int A_TILE = 128 * 128;            // 128 rows x 64 bf16, one swizzle atom wide
 constexpr int NDEC = 8;                      // decode warps = records per k-tile
 
+constexpr int MAXL = 4;                       // matrices in one list launch
+
 struct GemmArgs {
   const uint8_t* tree; const int* eo; const uint32_t* el;
   uint16_t* Y; float* Yf; int* status;
@@ -47,7 +49,11 @@ struct GemmArgs {
   long long M, N;
   int B, NG, NT, KS, RB, TT, stages, rstages, nmma, bar_off;
   uint32_t idesc;
+  // list of matrices that share the activations (q / k / v, gate / up as separate trees): member of each row block
+  int nlist; int rbend[MAXL];                 // first row block after each member in the concatenation
+  const int* leo[MAXL]; const uint32_t* lel[MAXL]; uint16_t* lY[MAXL]; float* lYf[MAXL]; long long lM[MAXL];
 };
+struct WMaps { CUtensorMap m[MAXL]; };        // weight tensor maps: one, or one per member of a list
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -107,7 +113,7 @@ constexpr int RAW_SLOT = NDEC * REC;         // 12416 B: the eight records of on
 // order (bit-identical from run to run), and stores BF16.  No partial sums travel through global memory.
 template <bool GROUPED>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
+gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ WMaps wmaps) {
   constexpr int NMMA = DG;                                     // issuer warps; a.nmma of them work
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -133,7 +139,18 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
   // the matrix this CTA multiplies by: the one of the call, or (grouped) the expert of pair block tt
   const int* eo = a.eo;
   const uint32_t* el = a.el;
-  const CUtensorMap* wm = &wmap;
+  const CUtensorMap* wm = &wmaps.m[0];
+  int lrb = rb;                                                  // row block inside its matrix
+  uint16_t* Yp = a.Y;
+  float* Yfp = a.Yf;
+  long long Mp = a.M;
+  if (!GROUPED && a.nlist > 0) {                                 // a list: the member this row block belongs to
+    int m = 0;
+    while (m + 1 < a.nlist && rb >= a.rbend[m]) ++m;
+    lrb = rb - (m ? a.rbend[m - 1] : 0);
+    eo = a.leo[m]; el = a.lel[m]; wm = &wmaps.m[m];
+    Yp = a.lY[m]; Yfp = a.lYf[m]; Mp = a.lM[m];
+  }
   if (GROUPED) {
     pdl_wait();                                                  // the block table comes from an earlier kernel
     if (tok0 >= a.npost[0]) return;                              // beyond the blocks the routing filled
@@ -168,7 +185,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
       for (int i = 0, r = 0, k = 0; i < nk; ++i, r = (r + 1 == R ? 0 : r + 1), k += (r == 0)) {
         if (k > 0 && !GW(rempty + r, (uint32_t)(k - 1) & 1u)) { atomicExch(a.status, ERR_WAIT_EMPTY); break; }
         mbar_expect_tx(rfull + r, (uint32_t)RAW_SLOT);
-        tma_load_3d(rawring + (size_t)r * RAW_SLOT, wm, 0, k0 + i, rb * 8, rfull + r);
+        tma_load_3d(rawring + (size_t)r * RAW_SLOT, wm, 0, k0 + i, lrb * 8, rfull + r);
       }
     }
   } else if (warp == W_X) {
@@ -217,7 +234,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
     // ---------------------------------------------------------------- decode warps: group g = warp / 8 takes the
     // k-tiles i = g, g + DG, ...; warp r of a group decodes record r (rows 16 r .. 16 r + 15 of the block)
     const int grp = warp / NDEC, rec = warp % NDEC;
-    const size_t rbase = (size_t)(rb * 8 + rec) * a.NG + k0;
+    const size_t rbase = (size_t)(lrb * 8 + rec) * a.NG + k0;
     // Escape entries are fetched one k-tile ahead: the list offsets of this warp's records come 32 k-tiles at a time
     // (lane l holds the offsets of k-tile eo_base + l) and the first 32 entries of the next record are requested before
     // this record is decoded, so no global-load latency sits between the records landing and the tile being handed
@@ -350,12 +367,12 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap, const __
           row = a.sorted[tok0 + cc];
           if (row < 0 || row >= a.B) continue;
         }
-        const size_t o = (size_t)row * a.M + rb * 128 + 4 * lane;
+        const size_t o = (size_t)row * Mp + lrb * 128 + 4 * lane;
         uint2 packed;
         packed.x = pack_bf16(sum.x, sum.y);
         packed.y = pack_bf16(sum.z, sum.w);
-        *reinterpret_cast<uint2*>(a.Y + o) = packed;
-        if (a.Yf) *reinterpret_cast<float4*>(a.Yf + o) = sum;
+        *reinterpret_cast<uint2*>(Yp + o) = packed;
+        if (Yfp) *reinterpret_cast<float4*>(Yfp + o) = sum;
       }
     }
   }
@@ -485,7 +502,7 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
 }
 
 template <bool GROUPED>
-int gemm_launch(const GemmPlan& p, const GemmArgs& a, const CUtensorMap& xmap, const CUtensorMap& wmap, cudaStream_t stream) {
+int gemm_launch(const GemmPlan& p, const GemmArgs& a, const CUtensorMap& xmap, const WMaps& wmaps, cudaStream_t stream) {
   if (int e = gemm_attr<GROUPED>()) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(p.RB * p.TT * p.KS));
@@ -501,7 +518,7 @@ int gemm_launch(const GemmPlan& p, const GemmArgs& a, const CUtensorMap& xmap, c
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = st::pdl_enabled() ? 2 : 1;
-  return st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel<GROUPED>, a, xmap, wmap), GROUPED ? "st_moe_group_gemm launch" : "st_gemm launch");
+  return st::cuda_fail(cudaLaunchKernelEx(&cfg, gemm_kernel<GROUPED>, a, xmap, wmaps), GROUPED ? "st_moe_group_gemm launch" : "st_gemm launch");
 }
 
 // activations [rows, N] BF16 as 64-column x NT-row boxes with the 128-byte swizzle
@@ -553,9 +570,11 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   const GemmPlan p = gemm_plan(M, N, B);
   (void)ws; (void)ws_bytes;
   ST_REQUIRE((long long)p.RB * p.TT * p.KS < (1ll << 31), "st_gemm: grid too large");
-  CUtensorMap xmap, wmap;
+  CUtensorMap xmap;
+  WMaps wmaps;
+  memset(&wmaps, 0, sizeof(wmaps));
   if (int e = make_xmap(&xmap, X, B, N, p.NT, "st_gemm")) return e;
-  if (int e = make_wmap(&wmap, tree, M, N, "st_gemm")) return e;
+  if (int e = make_wmap(&wmaps.m[0], tree, M, N, "st_gemm")) return e;
   GemmArgs a = {};
   a.tree = (const uint8_t*)tree; a.eo = eo; a.el = el; a.Y = (uint16_t*)Y; a.Yf = Yf32;
   a.status = st::status_ptr();
@@ -563,7 +582,44 @@ extern "C" int st_gemm(const void* tree, const int32_t* eo, const uint32_t* el, 
   a.M = M; a.N = N; a.B = (int)B; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = p.KS; a.RB = p.RB; a.TT = p.TT;
   a.stages = p.stages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
   a.idesc = mma_idesc(p.NT);
-  return gemm_launch<false>(p, a, xmap, wmap, (cudaStream_t)stream);
+  return gemm_launch<false>(p, a, xmap, wmaps, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------- list of matrices
+extern "C" int st_gemm_list(int64_t n, const void* const* trees, const int32_t* const* eo, const uint32_t* const* el,
+                            const void* X, void* const* Y, float* const* Yf32, int64_t B, const int64_t* M, int64_t N,
+                            int32_t* cnt, void* stream) {
+  const char* who = "st_gemm_list";
+  ST_REQUIRE(n >= 1 && n <= MAXL, "%s: 1 to %d matrices per call (got %lld)", who, MAXL, (long long)n);
+  ST_REQUIRE(trees && eo && el && X && Y && M && cnt, "%s: null pointer", who);
+  ST_REQUIRE(N > 0 && N % 64 == 0, "%s: N %% 64 must be 0", who);
+  ST_REQUIRE(B >= 1 && B < (1ll << 24), "%s: batch out of range", who);
+  ST_REQUIRE(st::aligned16(X), "%s: X must be 16-byte aligned", who);
+  GemmArgs a = {};
+  WMaps wmaps;
+  memset(&wmaps, 0, sizeof(wmaps));
+  long long total = 0;
+  for (int i = 0; i < (int)n; ++i) {
+    ST_REQUIRE(trees[i] && eo[i] && el[i] && Y[i], "%s: null pointer in member %d", who, i);
+    ST_REQUIRE(st::aligned16(trees[i]), "%s: tree of member %d must be 16-byte aligned", who, i);
+    ST_REQUIRE(M[i] > 0 && M[i] % 128 == 0, "%s: rows of member %d must be a positive multiple of 128", who, i);
+    if (int e = make_wmap(&wmaps.m[i], trees[i], M[i], N, who)) return e;
+    a.leo[i] = eo[i]; a.lel[i] = el[i]; a.lY[i] = (uint16_t*)Y[i]; a.lYf[i] = Yf32 ? Yf32[i] : nullptr; a.lM[i] = M[i];
+    total += M[i];
+    a.rbend[i] = (int)(total / 128);
+  }
+  a.nlist = (int)n;
+  const GemmPlan p = gemm_plan(total, N, B);
+  ST_REQUIRE((long long)p.RB * p.TT * p.KS < (1ll << 31), "%s: grid too large", who);
+  CUtensorMap xmap;
+  if (int e = make_xmap(&xmap, X, B, N, p.NT, who)) return e;
+  a.eo = eo[0]; a.el = el[0]; a.Y = (uint16_t*)Y[0];
+  a.status = st::status_ptr();
+  ST_REQUIRE(a.status != nullptr, "%s: no device status word", who);
+  a.M = total; a.N = N; a.B = (int)B; a.NG = (int)(N / 64); a.NT = p.NT; a.KS = p.KS; a.RB = p.RB; a.TT = p.TT;
+  a.stages = p.stages; a.rstages = p.rstages; a.nmma = p.nmma; a.bar_off = p.bar_off;
+  a.idesc = mma_idesc(p.NT);
+  return gemm_launch<false>(p, a, xmap, wmaps, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------- grouped (MoE)
@@ -601,7 +657,8 @@ extern "C" int st_moe_group_gemm(const void* maps, const int64_t* eop, const int
   p.KS = 1;
   gemm_rings(p);
   ST_REQUIRE((long long)p.RB * p.TT < (1ll << 31), "st_moe_group_gemm: grid too large");
-  CUtensorMap xmap, unused;
+  CUtensorMap xmap;
+  WMaps unused;
   if (int e = make_xmap(&xmap, Xg, nblk * bs, N, p.NT, "st_moe_group_gemm")) return e;
   memset(&unused, 0, sizeof(unused));
   GemmArgs a = {};

@@ -289,14 +289,18 @@ TreeLinear.swiglu = swiglu
 @torch.no_grad()
 def forward_list(layers, x):
     """[layer(x) for layer in layers] for TreeLinear layers that read the same input (q / k / v or gate / up of a
-    checkpoint that keeps them as separate trees): up to GEMV_MAX rows and four layers run as ONE launch over the
-    concatenation of their tiles; anything else falls back to one call per layer."""
+    checkpoint that keeps them as separate trees): up to four layers run as ONE launch over the concatenation of their
+    tiles (the GEMV up to GEMV_MAX rows, the tcgen05 GEMM beyond, if every layer has a multiple of 128 rows); anything
+    else falls back to one call per layer."""
     first = layers[0]
     home = first.tree.device
     same = all(l.in_features == first.in_features and l.tree.device == home for l in layers)
     lead = x.shape[:-1]
     acts = _rows_2d(x if x.device == home else x.to(home), first.in_features) if same and home.type == "cuda" else None
-    if acts is None or not 1 <= acts.shape[0] <= min(GEMV_MAX, 32) or not 2 <= len(layers) <= 4:
+    if acts is None or acts.shape[0] < 1 or not 2 <= len(layers) <= 4:
+        return [l(x) for l in layers]
+    use_gemm = acts.shape[0] > min(GEMV_MAX, 32)
+    if use_gemm and any(l.out_features % 128 for l in layers):
         return [l(x) for l in layers]
     E, B = ext(), acts.shape[0]
     widths = [l.out_features for l in layers]
@@ -310,8 +314,11 @@ def forward_list(layers, x):
         eo, el, eb = l.tables()
         tabs.append((l.tree, eo, eb, el))
     with torch.cuda.device(home):
-        ws = _state(home).get_ws(E.gemv_list_workspace_bytes(widths, first.in_features, B))
-        E.gemv_list(E.gemv_list_args(tabs, outs), acts, ws)
+        if use_gemm:
+            E.gemm_list(E.gemv_list_args(tabs, outs), acts, _state(home).get_cnt((sum(widths) // 128) * ((B + 255) // 256)))
+        else:
+            ws = _state(home).get_ws(E.gemv_list_workspace_bytes(widths, first.in_features, B))
+            E.gemv_list(E.gemv_list_args(tabs, outs), acts, ws)
     res = []
     for l, y in zip(layers, outs):
         if l.bias is not None:

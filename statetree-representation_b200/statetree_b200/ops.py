@@ -27,6 +27,7 @@ _SIGNATURES = {
     "st_gemv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_static": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "st_gemv_allreduce": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "st_gemm_list": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_list_workspace_bytes": (_i64, [_i64, _vp, _i64, _i64]),
     "st_gemv_list": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "st_gemm_workspace_bytes": (_i64, [_i64, _i64, _i64]),
@@ -181,6 +182,17 @@ class _Weights:
         with torch.cuda.device(dev):
             _check(lib().st_gemv_list(n, t, eo, eb, el, _ptr(X), ys, yf, B, Ms, N, _ptr(WS),
                                       WS.numel() * WS.element_size(), torch.cuda.current_stream(dev).cuda_stream))
+
+    @staticmethod
+    def gemm_list(args, X, CNT):
+        """the same list (gemv_list_args; the eb column is not used) through the tcgen05 GEMM: any batch, rows % 128 == 0"""
+        n, t, eo, eb, el, ys, yf, Ms, N, dev = args
+        B = X.shape[0]
+        if X.shape[1] != N or not X.is_contiguous():
+            raise RuntimeError(f"gemm_list: X must be contiguous [B, {N}]")
+        with torch.cuda.device(dev):
+            _check(lib().st_gemm_list(n, t, eo, el, _ptr(X), ys, yf, B, Ms, N, _ptr(CNT),
+                                      torch.cuda.current_stream(dev).cuda_stream))
 
     @staticmethod
     def gemm_workspace_bytes(M, N, B):

@@ -43,6 +43,7 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert L.st_comm_bytes() == 8 * 64 * 4 + 64 * 4 + 256 + 2 * 8 * 64 * 16384 + 2 * 8 * (128 << 10) * 4
     assert L.st_gemv_allreduce(None, 0, 9, None, None, None, None, None, None, None, 1, 64, 64, None, 0, None) != 0
     assert b"ranks" in L.st_last_error()
+    assert L.st_gemm_list(0, None, None, None, None, None, None, 1, None, 64, None, None) != 0
     assert L.st_gemv_list(5, None, None, None, None, None, None, None, 1, None, 64, None, 0, None) != 0
     assert b"1 to 4" in L.st_last_error()
     assert L.st_comm_set_timeout_ms(0) != 0

@@ -137,7 +137,21 @@ def test_gemv_list_matches_fp64(Ms, N, regime):
         E.gemv_list(E.gemv_list_args(tabs, again), x, ws.view(torch.float32))
         for y, z in zip(ys, again):
             assert torch.equal(y, z), (Ms, B, "nondeterministic")
-    # module-level helper (up to GEMV_MAX rows in one launch, more through one call per layer) and exact read-back
+    if all(M % 128 == 0 for M in Ms):                      # the same list through the tcgen05 GEMM
+        from statetree_b200.linear import _state
+        for B in (13, 64, 100, 256, 300):
+            X = G.to_bf16_bits(np.random.RandomState(B).standard_normal((B, N)))
+            x = bits_to_torch(X, DEV)
+            ys = [torch.empty(B, M, dtype=torch.bfloat16, device=DEV) for M in Ms]
+            yfs = [torch.empty(B, M, dtype=torch.float32, device=DEV) for M in Ms]
+            cnt = _state(torch.device(DEV)).get_cnt((sum(Ms) // 128) * ((B + 255) // 256))
+            E.gemm_list(E.gemv_list_args(tabs, ys, yfs), x, cnt)
+            torch.cuda.synchronize()
+            for W, y, yf in zip(Ws, ys, yfs):
+                assert rel_fro(yf.cpu().numpy(), oracle.linear_f64(W, X)) < TOL, (Ms, N, B)
+                assert torch.equal(y, yf.to(torch.bfloat16))
+            assert int(cnt.abs().sum()) == 0
+    # module-level helper (one launch for the list at any batch where the shapes allow) and exact read-back
     for B in (1, 8, 40):
         cols = sorted(set(np.concatenate([e["esc_cols"] for e in encs]).tolist()))[:24] + [0, N - 1]
         x = torch.zeros(B, N, dtype=torch.bfloat16, device=DEV)
