@@ -483,19 +483,21 @@ GemmPlan gemm_plan(long long M, long long N, long long B) {
   const int NG = (int)(N / 64), sms = st::sm_count();
   const long long units = (long long)p.RB * p.TT;
   gemm_rings(p);
-  // split of the k range = cluster size (<= 8): fill the CTA slots, but every extra split costs an accumulator tile
-  // of distributed-shared-memory traffic in the epilogue, and a second wave pays the start-up and the epilogue again:
-  // among the splits whose clusters are all resident at once take the one that fills the SMs best
+  // Split of the k range = cluster size (<= 8).  A CTA's time is its k-tiles plus a fixed part (start-up, pipeline fill,
+  // epilogue; the epilogue grows with the tiles to add through distributed shared memory); a grid larger than the
+  // CTAs that are resident at once runs in waves, each paying all of it again.  Take the split with the least
+  // estimated time (the constants are in units of one k-tile of a 64-token tile).
   int best = 1;
-  double best_score = -1.0;
+  double best_t = 1e30;
   const int ksmax = NG / 4 < 1 ? 1 : (NG / 4 > 8 ? 8 : NG / 4);
+  const double tile = p.NT >= 256 ? 1.4 : (p.NT >= 128 ? 1.08 : 1.0);
   for (int ks = 1; ks <= ksmax; ++ks) {
     const long long ctas = units * ks;
     const long long slots = resident_ctas(ks, p.NT, p.smem, sms);
-    if (ctas > slots && ks > 1) continue;
+    if (slots <= 0) continue;
     const long long waves = (ctas + slots - 1) / slots;
-    const double score = (double)ctas / (double)(waves * sms) - 0.01 * ks * p.NT / 256.0;
-    if (score > best_score + 1e-9) { best_score = score; best = ks; }
+    const double t = (double)waves * ((double)((NG + ks - 1) / ks) * tile + 14.0 + 0.8 * ks * p.NT / 64.0);
+    if (t < best_t - 1e-9) { best_t = t; best = ks; }
   }
   p.KS = best;
   return p;
