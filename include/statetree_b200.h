@@ -140,6 +140,13 @@ int st_moe_gather(const void* X, const int32_t* sorted, const int32_t* npost, in
 int st_moe_group_gemm(const void* maps, const int64_t* eop, const int64_t* elp, int64_t E, const void* Xg,
                       const int32_t* sorted, const int32_t* bexp, const int32_t* npost, int64_t nblk, int64_t bs,
                       void* Y, float* Yf32, int64_t S, int64_t M, int64_t N, void* stream);
+/* Router of a mixture-of-experts layer in one launch: softmax over the E <= 1024 expert logits of each of T tokens
+ * (BF16, or float32 with logits_f32 = 1), the K <= 32 largest probabilities in descending order (ties: the lower
+ * expert first) -> ids int32 [T, K], w float32 [T, K]; renorm != 0 divides the K weights by their sum.  expert_map
+ * (optional, int32 [E]: global id -> local id or -1) returns local ids; pairs of other ranks' experts get id 0 and
+ * weight 0.  No counterpart in the reference (the model's own PyTorch code routes). */
+int st_moe_route(const void* logits, int logits_f32, int64_t T, int64_t E, int64_t K, int renorm,
+                 const int32_t* expert_map, int32_t* ids, float* w, void* stream);
 /* out[t] = sum_j w[t, j] * Y[t * K + j] in fp32, expert order, BF16 out; w float32 (w_bf16 = 0) or BF16 (1).
  * Replaces `_C.wsum` (statetree/csrc/kernels.cu:1489-1535). */
 int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H, void* stream);

@@ -179,6 +179,87 @@ extern "C" int st_moe_gather(const void* X, const int32_t* sorted, const int32_t
                     (uint4*)Xg);
 }
 
+// Router of a mixture-of-experts layer for a decode step: softmax over the E expert logits of a token, the K largest
+// probabilities (ties: the lower expert first) and, optionally, their renormalisation to sum 1, in one launch of one
+// warp per token (PyTorch takes five).  expert_map (optional, int32 [E]) turns the ids into this rank's local ids;
+// a pair routed to another rank's expert gets id 0 and weight 0 (it then contributes nothing).
+__global__ void __launch_bounds__(128) moe_route_kernel(const void* logits, int f32, int T, int E, int K, int renorm,
+                                                        const int* expert_map, int* ids, float* w) {
+  st::pdl_wait();
+  st::pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  constexpr int PER = 32;                                            // E <= 1024
+  float v[PER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    float x = -INFINITY;
+    if (e < E)
+      x = f32 ? reinterpret_cast<const float*>(logits)[(size_t)t * E + e]
+              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[(size_t)t * E + e]);
+    v[i] = x;
+    mx = fmaxf(mx, x);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(st::FULL, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    v[i] = (i * 32 + lane < E) ? __expf(v[i] - mx) : -1.f;          // (-1 marks "no expert" and "already taken")
+    sum += fmaxf(v[i], 0.f);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(st::FULL, sum, o);
+  const float inv = 1.f / sum;
+  float mine_w = 0.f;                                                // lane k keeps the k-th pick
+  int mine_e = 0;
+  float tot = 0.f;
+  for (int k = 0; k < K; ++k) {
+    float best = -1.f;
+    int be = 0x7FFFFFFF;
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (v[i] > best) { best = v[i]; be = i * 32 + lane; }         // ascending e per lane: ties keep the lower expert
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ob = __shfl_xor_sync(st::FULL, best, o);
+      const int oe = __shfl_xor_sync(st::FULL, be, o);
+      if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+    }
+    if ((be & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i)
+        if (i == (be >> 5)) v[i] = -1.f;
+    }
+    const float p = best * inv;
+    tot += p;
+    if (lane == k) { mine_w = p; mine_e = be; }
+  }
+  if (lane < K) {
+    float p = renorm ? mine_w / tot : mine_w;
+    int e = mine_e;
+    if (expert_map != nullptr) {
+      const int local = expert_map[e];
+      if (local < 0) { e = 0; p = 0.f; } else { e = local; }
+    }
+    ids[(size_t)t * K + lane] = e;
+    w[(size_t)t * K + lane] = p;
+  }
+}
+
+extern "C" int st_moe_route(const void* logits, int logits_f32, int64_t T, int64_t E, int64_t K, int renorm,
+                            const int32_t* expert_map, int32_t* ids, float* w, void* stream) {
+  ST_REQUIRE(T >= 0 && E >= 1 && E <= 1024 && K >= 1 && K <= 32 && K <= E,
+             "st_moe_route: 1..1024 experts, 1..32 picks per token (got E = %lld, K = %lld)", (long long)E, (long long)K);
+  if (T == 0) return 0;
+  ST_REQUIRE(logits && ids && w, "st_moe_route: null pointer");
+  return st::launch("st_moe_route launch", moe_route_kernel, dim3((unsigned)((T + 3) / 4)), dim3(128), 0,
+                    (cudaStream_t)stream, logits, logits_f32, (int)T, (int)E, (int)K, renorm, (const int*)expert_map,
+                    (int*)ids, w);
+}
+
 extern "C" int st_wsum(const void* Y, const void* w, int w_bf16, void* out, int64_t T, int64_t K, int64_t H,
                        void* stream) {
   ST_REQUIRE(T >= 0 && K >= 1 && H > 0 && H % 8 == 0, "st_wsum: H must be a multiple of 8, K >= 1");

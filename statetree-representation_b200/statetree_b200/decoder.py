@@ -231,10 +231,16 @@ class TreeDecoder:
             self._add_norm(x, delta, h, summed)
             if c.experts:
                 router, te = gu
-                probs = torch.softmax(Fn.linear(h, router).float(), -1)
-                w, ids = probs.topk(c.top_k, -1)
-                w = (w / w.sum(-1, keepdim=True)).contiguous()
-                delta, summed = te(h, ids.to(torch.int32).contiguous(), w, self.emap if self.world > 1 else None), False
+                # softmax, top-k and renormalisation in one launch; with few pairs under expert parallelism the router
+                # also maps the ids to this rank's experts (foreign pairs: weight 0), which the experts then run as is
+                from .experts import SLOT_MAX
+                logits = Fn.linear(h, router)
+                if self.world > 1 and B * c.top_k <= SLOT_MAX:
+                    ids, w = E.moe_route(logits, c.top_k, True, self.emap)
+                    delta, summed = te(h, ids, w, None), False
+                else:
+                    ids, w = E.moe_route(logits, c.top_k, True, None)
+                    delta, summed = te(h, ids, w, self.emap if self.world > 1 else None), False
                 continue                                     # (the all-reduce over ranks happens in the next _add_norm)
             if self.fused_act:
                 act = gu.swiglu(h)

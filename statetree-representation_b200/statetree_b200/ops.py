@@ -27,6 +27,7 @@ _SIGNATURES = {
     "st_gemv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_static": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "st_gemv_allreduce": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "st_moe_route": (_int, [_vp, _int, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "st_gemm_list": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_list_workspace_bytes": (_i64, [_i64, _vp, _i64, _i64]),
     "st_gemv_list": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
@@ -193,6 +194,19 @@ class _Weights:
         with torch.cuda.device(dev):
             _check(lib().st_gemm_list(n, t, eo, el, _ptr(X), ys, yf, B, Ms, N, _ptr(CNT),
                                       torch.cuda.current_stream(dev).cuda_stream))
+
+    @staticmethod
+    def moe_route(logits, K, renorm=True, expert_map=None):
+        """(ids int32 [T, K], w float32 [T, K]): softmax + top-K (+ renormalisation) of router logits [T, E] in one launch"""
+        T, E = logits.shape
+        if logits.dtype not in (torch.bfloat16, torch.float32) or not logits.is_contiguous():
+            raise RuntimeError("moe_route: contiguous BF16 or float32 logits")
+        ids = torch.empty(T, K, dtype=torch.int32, device=logits.device)
+        w = torch.empty(T, K, dtype=torch.float32, device=logits.device)
+        with _ctx(logits):
+            _check(lib().st_moe_route(_ptr(logits), 1 if logits.dtype == torch.float32 else 0, T, E, K, 1 if renorm else 0,
+                                      _ptr(expert_map), _ptr(ids), _ptr(w), _stream(logits)))
+        return ids, w
 
     @staticmethod
     def gemm_workspace_bytes(M, N, B):

@@ -198,3 +198,41 @@ def test_tree_experts_prefill_sized_call_uses_the_grouped_gemm():
     act = torch.nn.functional.silu(gu[..., :I]) * gu[..., I:]
     ref = (torch.einsum("tkhi,tki->tkh", down[ids].double(), act) * w.double().unsqueeze(-1)).sum(1)
     assert float((got - ref).norm() / ref.norm()) < 2e-2
+
+
+def test_moe_route_matches_torch():
+    """softmax + top-k + renormalisation in one launch against the PyTorch formulation it replaces; the expert-map form
+    returns local ids and zero weights for other ranks' experts"""
+    from statetree_b200 import ops
+    E_ = ops.ext()
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    for (T, E, K, dt) in ((1, 128, 8, torch.bfloat16), (7, 128, 8, torch.float32), (64, 60, 4, torch.bfloat16),
+                          (3, 1024, 32, torch.float32), (5, 8, 2, torch.bfloat16), (2, 1, 1, torch.float32)):
+        logits = (torch.randn(T, E, device=DEV, generator=gen) * 3).to(dt)
+        probs = torch.softmax(logits.float(), -1)
+        w_ref, i_ref = probs.topk(K, -1)
+        w_ref = w_ref / w_ref.sum(-1, keepdim=True)
+        ids, w = E_.moe_route(logits, K, True)
+        torch.cuda.synchronize()
+        # ties in BF16 logits may be ordered differently by topk: compare the picked probabilities, and the ids where
+        # the picked values are distinct
+        assert torch.allclose(w, w_ref, rtol=2e-5, atol=1e-7), (T, E, K)
+        picked = torch.gather(probs, 1, ids.long())
+        assert torch.allclose(picked / picked.sum(-1, keepdim=True), w_ref, rtol=2e-5, atol=1e-7)
+        distinct = torch.ones_like(ids, dtype=torch.bool)
+        srt = torch.sort(logits.float(), -1, descending=True).values[:, :K + 1] if E > K else None
+        if srt is not None:
+            distinct = (srt[:, :-1] != srt[:, 1:]) & torch.cat([torch.ones(T, 1, dtype=torch.bool, device=DEV),
+                                                                 srt[:, :-2] != srt[:, 1:-1]], 1)
+        assert torch.equal(ids[distinct], i_ref.to(torch.int32)[distinct]), (T, E, K)
+        ids2, w2 = E_.moe_route(logits, K, False)
+        assert torch.allclose(w2, probs.topk(K, -1).values, rtol=2e-5, atol=1e-7)
+        if E >= 4:
+            emap = torch.where(torch.arange(E, device=DEV) % 2 == 0, torch.arange(E, device=DEV) // 2,
+                               torch.full((E,), -1, device=DEV)).to(torch.int32)
+            ids3, w3 = E_.moe_route(logits, K, True, emap)
+            local = emap[ids.long()]
+            assert torch.equal(ids3, local.clamp(min=0))
+            assert torch.equal(w3, torch.where(local >= 0, w, torch.zeros_like(w)))
+    _ = ops.device_status()
+    assert _ == 0
