@@ -6,6 +6,11 @@ N(0, 0.02) with 1% of the columns scaled x8.
 
 One step = every linear of all 36 layers once at batch M (default 1), captured in one CUDA graph.  All 36 layers own
 distinct record buffers (10.5 GB in total, far beyond the 126 MB L2), so every step streams the records from HBM.
+Launch layout of the step on one GPU: q / k / v and gate / up as fused trees, four launches per layer (the layout the
+reference's conversion writes by default and its per-layer-kind GEMV table measures: qkv, o, gate_up, down); the
+records of a layer's q, k, v (and gate, up) lie back to back, so the same buffers also serve as separate trees, and
+the line reports the two other layouts beside it: one list launch per group over the separate trees
+(`separate_trees_list_launches`, also `--lists`) and one launch per linear (`one_launch_per_linear`, `--per-linear`).
 value    = algorithmic bytes (records + activations in + out) / device time, inputs resident in HBM
 e2e      = the same through the C-ABI shim (statetree_b200.ops.ext().gemv / .gemm, the call TreeLinear.forward makes) with
            pinned host activations copied in and results copied out every step
@@ -13,8 +18,8 @@ roofline = the GEMV (or GEMM) kernel's achieved algorithmic GB/s against the mea
 cpu_baseline / --impl reference = the reference's CPU path (decode + BF16 matmul) restated in C, on the host cores,
 on a bounded sample (the linears of one layer).
 With N > 1 ranks (torchrun) the linears are tensor-parallel: q/k/v and gate/up split by rows and stored per rank as
-fused trees (four launches per layer), o/down split by columns and followed by an all-reduce of their [M, 4096] outputs
-over NVLink peer memory; total work is fixed (strong scaling).  Before timing, the all-reduced outputs of one layer
+fused trees (four launches per layer), o/down split by columns, their GEMV adding the ranks' partial sums over NVLink
+peer memory itself; total work is fixed (strong scaling).  Before timing, the all-reduced outputs of one layer
 are checked against the fp64 product over the unsharded weights (`tp_check`).
 """
 import argparse
@@ -53,7 +58,7 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def measured_traffic(batch, world, layers, launches_per_layer):
+def measured_traffic(batch, world, layers, layout):
     """DRAM bytes per launch of the dominant kernel from the tracked ncu summary (a JSON next to the text summary that
     also names the kernel source it was captured from); (None, reason) when there is none for this workload or the
     kernel source has changed since the capture"""
@@ -68,7 +73,7 @@ def measured_traffic(batch, world, layers, launches_per_layer):
         sha = hashlib.sha256(f.read()).hexdigest()[:16]
     if rec.get("kernel_source_sha256_16") != sha:
         return None, "kernel source changed since the capture"
-    if rec.get("launches_per_layer") != launches_per_layer:
+    if rec.get("layout") != layout:
         return None, "no capture for this launch layout"
     return rec["dram_bytes_per_launch"], f"ncu capture of {rec.get('captured', '?')}"
 
@@ -594,13 +599,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-bf16", action="store_true", help="skip the dense BF16 (cuBLAS) control pass")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M = 8 / 32 / 64 / 256 points of the default run")
-    ap.add_argument("--no-fused", action="store_true", help="skip the extra pass with fused q/k/v and gate/up trees")
+    ap.add_argument("--no-fused", action="store_true", help="skip the extra passes over the other launch layouts")
     ap.add_argument("--separate-allreduce", action="store_true",
                     help="tensor parallel: o / down as a GEMV followed by the all-reduce kernel (two launches) instead of the "
                          "GEMV that sums over the ranks itself")
     ap.add_argument("--per-linear", action="store_true",
-                    help="one GPU, GEMV batches: one launch per linear (7 per layer) as the main step instead of the list "
-                         "launches for q/k/v and gate/up (4 per layer)")
+                    help="one GPU: one launch per linear (7 per layer) as the main step instead of q/k/v and gate/up as "
+                         "fused trees (4 per layer)")
+    ap.add_argument("--lists", action="store_true",
+                    help="one GPU: q/k/v and gate/up as separate trees, one list launch per group, as the main step")
     ap.add_argument("--moe-batch", default="1,8,32,64,512,2048")
     ap.add_argument("--moe-no-gemm", action="store_true", help="moe workload: grouped GEMV at every size (for comparison)")
     ap.add_argument("--model", default="qwen3-8b", choices=["qwen3-8b", "qwen3-30b-a3b"],
@@ -633,9 +640,12 @@ def main():
                           f" x {args.layers} layers, batch M={args.batch}, seeds per shape, N(0,0.02) + 1% columns x8",
               "batch": args.batch, "layers": args.layers,
               "l2": "inputs larger than L2: 10.5 GB of distinct record buffers per step",
-              "parallelism": ("single GPU, one launch per linear" if args.per_linear or args.batch > 12 else
+              "parallelism": ("single GPU, one launch per linear (7 per layer)" if args.per_linear else
                               "single GPU; the seven trees of a layer in four launches: q/k/v and gate/up (separate trees, "
-                              "shared input) as one list launch each, o and down one launch each") if world == 1 else
+                              "shared input) as one list launch each, o and down one launch each" if args.lists else
+                              "single GPU; q/k/v and gate/up stored as fused trees, the layout the reference's conversion "
+                              "writes (DEFAULT_FUSE) and its per-layer-kind GEMV table measures: 4 launches per layer "
+                              "(qkv 6144x4096, o, gate_up 24576x4096, down)") if world == 1 else
               f"tp{world} (q/k/v and gate/up of a rank as fused trees; o/down column shards whose GEMV adds the ranks' "
               "fp32 tile sums over NVLink peer memory itself: four launches per layer and rank)"}
 
@@ -708,17 +718,29 @@ def main():
     shard = [S.TreeLinear.from_weight(W.contiguous(), verify=(i == 0)) for i, (_, W, _, _) in enumerate(plan)]
     ins = [xin for _, _, xin, _ in plan]
     kinds = [k for _, _, _, k in plan]
-    layers = []
+    layers, fbufs = [], []
+    groups = [(0, 3), (4, 6)] if world == 1 else []          # q / k / v and gate / up: stored back to back per layer
     for _ in range(args.layers):
+        trees = [None] * len(shard)
+        bufs = []
+        for lo, hi in groups:                                # one buffer per group; the members' trees are views into it
+            buf = torch.cat([shard[i].tree for i in range(lo, hi)])
+            at = 0
+            for i in range(lo, hi):
+                n = shard[i].tree.shape[0]
+                trees[i] = buf[at:at + n]
+                at += n
+            bufs.append(buf)
         row = []
-        for tl in shard:
+        for i, tl in enumerate(shard):
             c = S.TreeLinear(tl.in_features, tl.out_features, device="meta", n_esc=tl.esc_rows.numel())
-            c._buffers["tree"] = tl.tree.clone()
+            c._buffers["tree"] = trees[i] if trees[i] is not None else tl.tree.clone()
             for k in ("esc_rows", "esc_cols", "esc_bits"):
                 c._buffers[k] = tl._buffers[k]
             c._tables = tl.tables()
             row.append(c)
         layers.append(row)
+        fbufs.append(bufs)
     torch.cuda.synchronize()
 
     outs = [torch.empty(B, tl.out_features, dtype=torch.bfloat16, device=dev) for tl in layers[0]]
@@ -728,12 +750,34 @@ def main():
     st = _state(dev)
     ws_need = max((E.gemv_workspace_bytes if use_gemv else E.gemm_workspace_bytes)(tl.out_features, tl.in_features, B)
                   for tl in layers[0])
-    use_lists = world == 1 and use_gemv and not args.per_linear
-    if use_lists:
-        ws_need = max(ws_need, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, B),
-                      E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, B))
+    use_lists = world == 1                                   # (the list and fused variants exist on one GPU)
+    main_mode = "per_linear" if (world > 1 or args.per_linear) else ("lists" if args.lists else "fused")
+    Mq, Mg = (sum(tl.out_features for tl in layers[0][0:3]), sum(tl.out_features for tl in layers[0][4:6])) if world == 1 else (0, 0)
+    if world == 1:
+        wsb = E.gemv_workspace_bytes if use_gemv else E.gemm_workspace_bytes
+        ws_need = max(ws_need, wsb(Mq, HIDDEN, B), wsb(Mg, HIDDEN, B))
+        if use_gemv:
+            ws_need = max(ws_need, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, B),
+                          E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, B))
     ws = st.get_ws(ws_need) if use_gemv else st.get_scratch(ws_need)   # (the GEMM's workspace is plain scratch)
     cnt = st.get_cnt(4096)
+    # escape tables of the fused trees (the members' lists with their rows shifted)
+    ftabs, fouts, fouts_h = None, None, None
+    if world == 1:
+        from statetree_b200 import format as F
+
+        def fuse(tls):
+            rows, off = [], 0
+            for t in tls:
+                rows.append(t.esc_rows + off)
+                off += t.out_features
+            return F.escape_tables(off, tls[0].in_features, torch.cat(rows), torch.cat([t.esc_cols for t in tls]),
+                                   torch.cat([t.esc_bits for t in tls]))
+
+        ftabs = (fuse(layers[0][0:3]), fuse(layers[0][4:6]))
+        fouts = [torch.empty(B, Mq, dtype=torch.bfloat16, device=dev), torch.empty(B, Mg, dtype=torch.bfloat16, device=dev)]
+        fouts_h = [torch.empty(o.shape, dtype=torch.bfloat16).pin_memory() for o in fouts]
+        torch.cuda.synchronize()
 
     def list_args(row, lo, hi):
         tabs = []
@@ -792,9 +836,31 @@ def main():
     def run_lists():
         # q / k / v and gate / up read the same activations: each group is one launch over the members' trees
         for row, (qkv, gate_up) in zip(layers, lists):
-            E.gemv_list(qkv, x, ws)
+            if use_gemv:
+                E.gemv_list(qkv, x, ws)
+            else:
+                E.gemm_list(qkv, x, cnt)
             one(row[3], ins[3], outs[3])
-            E.gemv_list(gate_up, x, ws)
+            if use_gemv:
+                E.gemv_list(gate_up, x, ws)
+            else:
+                E.gemm_list(gate_up, x, cnt)
+            one(row[6], ins[6], outs[6])
+        return 4 * len(layers)
+
+    def fused_one(tree, tabs, y):
+        eo, el, eb = tabs
+        if use_gemv:
+            E.gemv(tree, eo, eb, el, x, y, ws, cnt)
+        else:
+            E.gemm(tree, eo, el, x, y, ws, cnt)
+
+    def run_fused():
+        # q / k / v and gate / up of a layer are one tree each (their records lie back to back): four launches per layer
+        for row, (qkv_buf, gu_buf) in zip(layers, fbufs):
+            fused_one(qkv_buf, ftabs[0], fouts[0])
+            one(row[3], ins[3], outs[3])
+            fused_one(gu_buf, ftabs[1], fouts[1])
             one(row[6], ins[6], outs[6])
         return 4 * len(layers)
 
@@ -809,7 +875,9 @@ def main():
                     n += 1
         return n
 
-    run_layers = run_lists if use_lists else run_per_linear
+    variants = {"fused": run_fused, "lists": run_lists, "per_linear": run_per_linear}
+    run_layers = variants[main_mode]
+    main_outs = ([fouts[0], outs[3], fouts[1], outs[6]], [fouts_h[0], outs_h[3], fouts_h[1], outs_h[6]]) if main_mode == "fused" else (outs, outs_h)
 
     side = torch.cuda.Stream(dev)
     with torch.cuda.stream(side):
@@ -850,7 +918,7 @@ def main():
         x_o.copy_(x_h[:, rank * Hs:(rank + 1) * Hs], non_blocking=True)
         x_d.copy_(x2_h[:, rank * Is:(rank + 1) * Is], non_blocking=True)
         graph.replay()
-        for o, oh in zip(outs, outs_h):
+        for o, oh in zip(*main_outs):
             oh.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()            # the caller reads the result every step
 
@@ -865,181 +933,166 @@ def main():
     ms_e2e = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- the same step with one launch per linear (7 per layer)
-    per_linear = None
-    if use_lists:
-        with torch.cuda.stream(side):
-            run_per_linear()
-        side.synchronize()
-        pgraph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(pgraph, stream=side):
-            run_per_linear()
-        torch.cuda.synchronize()
-        for _ in range(3):
-            pgraph.replay()
-        ms_p = timed(pgraph.replay, args.steps)
-        per_linear = {"what": "the same trees and bytes, one launch per linear (7 per layer)", "ms_per_step": ms_p,
-                      "value": step_bytes / (ms_p * 1e-3) / 1e9, "unit": "GB/s",
-                      "frac": step_bytes / (ms_p * 1e-3) / 1e9 / peaks()[0], "gpu_launches": 7 * args.layers * args.steps}
-        del pgraph
-    # ---- the same step with q/k/v and gate/up stored as fused trees (how the reference's model conversion stores
-    # them, statetree/model.py DEFAULT_FUSE, and how its per-layer-kind GEMV table is measured): 4 launches per layer
-    fused = None
-    if world == 1 and use_gemv and not args.no_fused:
-        from statetree_b200 import format as F
-
-        def fuse(tls):
-            M = sum(t.out_features for t in tls)
-            rows, off = [], 0
-            for t in tls:
-                rows.append(t.esc_rows + off)
-                off += t.out_features
-            er, ec, eb_ = torch.cat(rows), torch.cat([t.esc_cols for t in tls]), torch.cat([t.esc_bits for t in tls])
-            return M, F.escape_tables(M, tls[0].in_features, er, ec, eb_)
-
-        Mq, tq = fuse(layers[0][0:3])
-        Mg, tg = fuse(layers[0][4:6])
-        flayers = []
-        for row in layers:
-            flayers.append([(torch.cat([t.tree for t in row[0:3]]), tq, Mq, x), (row[3].tree, row[3]._tables, HIDDEN, x_o),
-                            (torch.cat([t.tree for t in row[4:6]]), tg, Mg, x), (row[6].tree, row[6]._tables, HIDDEN, x_d)])
-        fouts = {m: torch.empty(B, m, dtype=torch.bfloat16, device=dev) for m in (Mq, Mg, HIDDEN)}
-        ws_f = st.get_ws(max(E.gemv_workspace_bytes(m, n, B) for m, n in ((Mq, HIDDEN), (HIDDEN, HIDDEN), (Mg, HIDDEN), (HIDDEN, INTER))))
-        cnt_f = st.get_cnt(Mg // 16)
-
-        def run_fused():
-            for row in flayers:
-                for tree, (eo, el, eb), m, xin in row:
-                    E.gemv(tree, eo, eb, el, xin, fouts[m], ws_f, cnt_f)
-
-        torch.cuda.synchronize()
-        with torch.cuda.stream(side):
-            run_fused()
-        side.synchronize()
-        fgraph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(fgraph, stream=side):
-            run_fused()
-        torch.cuda.synchronize()
-        for _ in range(3):
-            fgraph.replay()
-        ms_f = timed(fgraph.replay, args.steps)
-        fused = {"what": "q/k/v and gate/up as fused trees (6144x4096, 24576x4096): 4 launches per layer, same bytes",
-                 "ms_per_step": ms_f, "value": step_bytes / (ms_f * 1e-3) / 1e9, "unit": "GB/s",
-                 "frac": step_bytes / (ms_f * 1e-3) / 1e9 / peaks()[0], "gpu_launches": 4 * args.layers * args.steps}
-        del fgraph, flayers
+    # ---- the same bytes through the other launch layouts (one GPU): fused trees, list launches, one launch per linear
+    WHAT = {"fused": ("fused_qkv_gate_up", "q/k/v and gate/up as fused trees (6144x4096, 24576x4096), the layout the "
+                      "reference's conversion writes: 4 launches per layer", 4),
+            "lists": ("separate_trees_list_launches", "q/k/v and gate/up as separate trees, one list launch per group: "
+                      "4 launches per layer", 4),
+            "per_linear": ("one_launch_per_linear", "separate trees, one launch per linear: 7 per layer", 7)}
+    others = {}
+    if world == 1 and not args.no_fused:
+        for mode, fn in variants.items():
+            if mode == main_mode:
+                continue
+            with torch.cuda.stream(side):
+                fn()
+            side.synchronize()
+            vg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(vg, stream=side):
+                fn()
+            torch.cuda.synchronize()
+            for _ in range(3):
+                vg.replay()
+            ms_v = timed(vg.replay, args.steps)
+            key, what, per_layer = WHAT[mode]
+            others[key] = {"what": what, "ms_per_step": ms_v, "value": step_bytes / (ms_v * 1e-3) / 1e9, "unit": "GB/s",
+                           "frac": step_bytes / (ms_v * 1e-3) / 1e9 / peaks()[0],
+                           "gpu_launches": per_layer * args.layers * args.steps}
+            del vg
     # ---- BF16 control: the same step over dense BF16 copies of the same weights through torch.matmul (cuBLAS), the
     # comparison the reference's per-layer GEMV table makes (RESULTS.md:176-183); 36 distinct buffers per shape as above
     control = None
     if world == 1 and not args.no_bf16:
-        dense = [[tl.dequantize() for tl in row] for row in layers]
+        # dense copies in the fused layout; the separate q / k / v and gate / up weights are row slices of them
+        dense_f, dense = [], []
+        for row, (qkv_buf, gu_buf) in zip(layers, fbufs):
+            Wqkv = torch.empty(Mq, HIDDEN, dtype=torch.bfloat16, device=dev)
+            Wgu = torch.empty(Mg, HIDDEN, dtype=torch.bfloat16, device=dev)
+            E.dec(qkv_buf, ftabs[0][0], ftabs[0][1], Wqkv)
+            E.dec(gu_buf, ftabs[1][0], ftabs[1][1], Wgu)
+            Wo, Wd = row[3].dequantize(), row[6].dequantize()
+            dense_f.append([Wqkv, Wo, Wgu, Wd])
+            sep, at = [], 0
+            for tl in row[0:3]:
+                sep.append(Wqkv[at:at + tl.out_features])
+                at += tl.out_features
+            sep.append(Wo)
+            at = 0
+            for tl in row[4:6]:
+                sep.append(Wgu[at:at + tl.out_features])
+                at += tl.out_features
+            sep.append(Wd)
+            dense.append(sep)
+        fused_main = main_mode == "fused"
+
+        def control_fn(xs_, ys_, fys_):
+            """the control in the launch layout of the main step: 4 matmuls per layer over fused weights, or 7"""
+            if fused_main:
+                def run():
+                    for Wqkv, Wo, Wgu, Wd in dense_f:
+                        torch.matmul(xs_[0], Wqkv.t(), out=fys_[0])
+                        torch.matmul(xs_[1], Wo.t(), out=ys_[3])
+                        torch.matmul(xs_[0], Wgu.t(), out=fys_[1])
+                        torch.matmul(xs_[2], Wd.t(), out=ys_[6])
+                return run
+
+            def run():
+                for row_d in dense:
+                    for W, xin, y in zip(row_d, [xs_[0]] * 3 + [xs_[1]] + [xs_[0]] * 2 + [xs_[2]], ys_):
+                        torch.matmul(xin, W.t(), out=y)
+            return run
+
+        def graph_time(fn, steps):
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                fn()
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                fn()
+            torch.cuda.synchronize()
+            for _ in range(3):
+                g.replay()
+            t = timed(g.replay, steps)
+            del g
+            return t
+
         douts = [torch.empty_like(o) for o in outs]
-
-        def run_dense():
-            for row in dense:
-                for W, xin, y in zip(row, ins, douts):
-                    torch.matmul(xin, W.t(), out=y)
-
-        torch.cuda.synchronize()
-        with torch.cuda.stream(side):
-            run_dense()
-        side.synchronize()
-        dgraph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(dgraph, stream=side):
-            run_dense()
-        torch.cuda.synchronize()
-        for _ in range(3):
-            dgraph.replay()
-        ms_d = timed(dgraph.replay, args.steps)
-        control = {"what": "same step, dense BF16 copies of the same weights, torch.matmul (cuBLAS) in one CUDA graph",
-                   "ms_per_step": ms_d, "speedup_vs_bf16": ms_d / ms,
-                   "speedup_vs_bf16_fused": (ms_d / fused["ms_per_step"]) if fused else None}
-        del dgraph
+        dfouts = [torch.empty_like(o) for o in fouts]
+        ms_d = graph_time(control_fn([x, x_o, x_d], douts, dfouts), args.steps)
+        control = {"what": "same step in the same launch layout (" + ("4 matmuls per layer over fused weights"
+                                                                       if fused_main else "7 matmuls per layer")
+                           + "), dense BF16 copies of the same weights, torch.matmul (cuBLAS) in one CUDA graph",
+                   "ms_per_step": ms_d, "speedup_vs_bf16": ms_d / ms}
+        if fused_main:                                       # the control with one matmul per linear, for the other layouts
+            fused_main = False
+            ms_d7 = graph_time(control_fn([x, x_o, x_d], douts, dfouts), args.steps)
+            fused_main = True
+            control["ms_per_step_one_matmul_per_linear"] = ms_d7
         # ---- the other activation-row counts of the benchmark configuration (M = 8, 32, 64, 256), each one graph over the
-        # same 36 x 7 record buffers and one over the dense copies: a few replays each
+        # same record buffers in the launch layout of the main step and one over the dense copies: a few replays each
         sweep = []
         if B == 1 and not args.no_sweep:
             for Bs in (8, 32, 64, 256):
                 gs = torch.Generator(device=dev).manual_seed(200 + Bs)
-                xs = {n: torch.randn(Bs, n, device=dev, generator=gs).to(torch.bfloat16) for n in (HIDDEN, INTER)}
+                xs = [torch.randn(Bs, n, device=dev, generator=gs).to(torch.bfloat16) for n in (HIDDEN, HIDDEN, INTER)]
                 ys = [torch.empty(Bs, tl.out_features, dtype=torch.bfloat16, device=dev) for tl in layers[0]]
+                fys = [torch.empty(Bs, Mq, dtype=torch.bfloat16, device=dev), torch.empty(Bs, Mg, dtype=torch.bfloat16, device=dev)]
                 gemv_path = Bs <= GEMV_MAX
-                need_s = max((E.gemv_workspace_bytes if gemv_path else E.gemm_workspace_bytes)(
-                    tl.out_features, tl.in_features, Bs) for tl in layers[0])
+                wsb = E.gemv_workspace_bytes if gemv_path else E.gemm_workspace_bytes
+                need_s = max([wsb(tl.out_features, tl.in_features, Bs) for tl in layers[0]] + [wsb(Mq, HIDDEN, Bs), wsb(Mg, HIDDEN, Bs)])
+                if gemv_path:
+                    need_s = max(need_s, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, Bs),
+                                 E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, Bs))
                 ws_s = st.get_ws(need_s) if gemv_path else st.get_scratch(need_s)
                 cnt_s = st.get_cnt(4096)
 
-                lists_s = None
-                if use_lists:                                # q / k / v and gate / up as one list launch each, as above
+                def mm(tree, tabs, xin, y):
+                    eo, el, eb = tabs
                     if gemv_path:
-                        need_s = max(need_s, E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][0:3]], HIDDEN, Bs),
-                                     E.gemv_list_workspace_bytes([tl.out_features for tl in layers[0][4:6]], HIDDEN, Bs))
-                        ws_s = st.get_ws(need_s)
+                        E.gemv(tree, eo, eb, el, xin, y, ws_s, cnt_s)
+                    else:
+                        E.gemm(tree, eo, el, xin, y, ws_s, cnt_s)
 
-                    def largs(row, lo, hi):
-                        tabs = []
-                        for tl in row[lo:hi]:
-                            eo, el, eb = tl._tables
-                            tabs.append((tl.tree, eo, eb, el))
-                        return E.gemv_list_args(tabs, ys[lo:hi])
+                def largs(row, lo, hi):
+                    tabs = []
+                    for tl in row[lo:hi]:
+                        eo, el, eb = tl._tables
+                        tabs.append((tl.tree, eo, eb, el))
+                    return E.gemv_list_args(tabs, ys[lo:hi])
 
-                    lists_s = [(largs(row, 0, 3), largs(row, 4, 6)) for row in layers]
+                lists_s = [(largs(row, 0, 3), largs(row, 4, 6)) for row in layers] if main_mode == "lists" else None
 
                 def run_tree():
-                    if lists_s is not None and gemv_path:
-                        for row, (qkv, gate_up) in zip(layers, lists_s):
-                            E.gemv_list(qkv, xs[HIDDEN], ws_s)
-                            eo, el, eb = row[3]._tables
-                            E.gemv(row[3].tree, eo, eb, el, xs[HIDDEN], ys[3], ws_s, cnt_s)
-                            E.gemv_list(gate_up, xs[HIDDEN], ws_s)
-                            eo, el, eb = row[6]._tables
-                            E.gemv(row[6].tree, eo, eb, el, xs[INTER], ys[6], ws_s, cnt_s)
-                        return
-                    if lists_s is not None:
-                        for row, (qkv, gate_up) in zip(layers, lists_s):
-                            E.gemm_list(qkv, xs[HIDDEN], cnt_s)
-                            eo, el, eb = row[3]._tables
-                            E.gemm(row[3].tree, eo, el, xs[HIDDEN], ys[3], ws_s, cnt_s)
-                            E.gemm_list(gate_up, xs[HIDDEN], cnt_s)
-                            eo, el, eb = row[6]._tables
-                            E.gemm(row[6].tree, eo, el, xs[INTER], ys[6], ws_s, cnt_s)
-                        return
-                    for row in layers:
-                        for tl, y in zip(row, ys):
-                            eo, el, eb = tl._tables
-                            if gemv_path:
-                                E.gemv(tl.tree, eo, eb, el, xs[tl.in_features], y, ws_s, cnt_s)
-                            else:
-                                E.gemm(tl.tree, eo, el, xs[tl.in_features], y, ws_s, cnt_s)
+                    for li, row in enumerate(layers):
+                        if main_mode == "fused":
+                            mm(fbufs[li][0], ftabs[0], xs[0], fys[0])
+                            mm(row[3].tree, row[3]._tables, xs[1], ys[3])
+                            mm(fbufs[li][1], ftabs[1], xs[0], fys[1])
+                            mm(row[6].tree, row[6]._tables, xs[2], ys[6])
+                        elif main_mode == "lists":
+                            for k, grp in enumerate(lists_s[li]):
+                                if gemv_path:
+                                    E.gemv_list(grp, xs[0], ws_s)
+                                else:
+                                    E.gemm_list(grp, xs[0], cnt_s)
+                                mm(row[3 + 3 * k].tree, row[3 + 3 * k]._tables, xs[1 + k], ys[3 + 3 * k])
+                        else:
+                            for tl, xin, y in zip(row, [xs[0]] * 3 + [xs[1]] + [xs[0]] * 2 + [xs[2]], ys):
+                                mm(tl.tree, tl._tables, xin, y)
 
-                def run_ctl():
-                    for row in dense:
-                        for W, y in zip(row, ys):
-                            torch.matmul(xs[W.shape[1]], W.t(), out=y)
-
-                point = {"batch": Bs, "kernel": ("gemv_kernel, list launches" if lists_s is not None else "gemv_kernel")
-                         if gemv_path else ("gemm_kernel (tcgen05), list launches" if lists_s is not None
-                                            else "gemm_kernel (tcgen05)")}
-                for key, fn in (("ms_per_step", run_tree), ("bf16_control_ms", run_ctl)):
-                    torch.cuda.synchronize()
-                    with torch.cuda.stream(side):
-                        fn()
-                    side.synchronize()
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=side):
-                        fn()
-                    torch.cuda.synchronize()
-                    for _ in range(2):
-                        g.replay()
-                    point[key] = timed(g.replay, 5)
-                    del g
+                kern = "gemv_kernel" if gemv_path else "gemm_kernel (tcgen05)"
+                point = {"batch": Bs, "kernel": kern, "layout": main_mode}
+                point["ms_per_step"] = graph_time(run_tree, 5)
+                point["bf16_control_ms"] = graph_time(control_fn(xs, ys, fys), 5)
                 nb = sum(algorithmic_bytes(M, N, Bs) for _, M, N, _ in SHAPES) * args.layers
                 fl = sum(2 * Bs * M * N for _, M, N, _ in SHAPES) * args.layers
                 point.update(gbs=nb / (point["ms_per_step"] * 1e-3) / 1e9, tflops=fl / (point["ms_per_step"] * 1e-3) / 1e12,
                              speedup_vs_bf16=point["bf16_control_ms"] / point["ms_per_step"])
                 sweep.append(point)
-                del xs, ys
+                del xs, ys, fys
             control["sweep"] = sweep
-        del dense
+        del dense, dense_f
     status = ops.device_status()
 
     def leave():
@@ -1060,7 +1113,7 @@ def main():
     hbm, tf, which = peaks()
     value = step_bytes / (ms * 1e-3) / 1e9
     per_gpu = value / world
-    traffic, traffic_source = measured_traffic(B, world, args.layers, launches // max(args.layers, 1))
+    traffic, traffic_source = measured_traffic(B, world, args.layers, main_mode)
     roof = {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s", "frac": per_gpu / hbm,
             "traffic": traffic, "traffic_source": traffic_source, "peak_source": f"of {which}",
             "frac_of_nominal_8TBs": per_gpu / 8000.0,
@@ -1079,10 +1132,7 @@ def main():
             "bf16_equivalent_gbs": value * 16.0 / 12.125}
     if tp_check is not None:
         line["tp_check"] = tp_check
-    if per_linear is not None:
-        line["one_launch_per_linear"] = per_linear
-    if fused is not None:
-        line["fused_qkv_gate_up"] = fused
+    line.update(others)
     if control is not None:
         if "sweep" in control:
             line["sweep"] = control.pop("sweep")
