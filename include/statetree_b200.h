@@ -69,6 +69,17 @@ int st_gemv_list(int64_t n, const void* const* trees, const int32_t* const* eo, 
                  const uint32_t* const* el, const void* X, void* const* Y, float* const* Yf32, int64_t B,
                  const int64_t* M, int64_t N, void* ws, int64_t ws_bytes, void* stream);
 
+/* st_gemv (or, with act != 0, st_gemv_swiglu) whose activations are formed inside the kernel from what a decode step
+ * holds in front of a projection: X = RMSNorm(x + delta) * norm_w, the sum rounded to BF16 as the residual stream is
+ * (delta may be NULL: X = RMSNorm(x) * norm_w).  Every CTA computes its own copy in shared memory; CTA 0 also writes
+ * the new residual stream x + delta to x_out (may be NULL; must not alias x or delta).  It replaces the
+ * st_add_rmsnorm launch in front of the q / k / v and the gate / up projection.  1 <= B <= 8; ask
+ * st_gemv_prenorm_supported first.  ws as for st_gemv.  No counterpart in the reference. */
+int st_gemv_prenorm_supported(int64_t M, int64_t N, int64_t B, int act);
+int st_gemv_prenorm(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* x,
+                    const void* delta, const void* norm_w, double eps, void* x_out, void* Y, int64_t B, int64_t M,
+                    int64_t N, int act, void* ws, int64_t ws_bytes, void* stream);
+
 /* st_gemv for callers that cannot allocate device memory and so have no workspace to pass: code running inside a
  * host framework that owns the whole device pool, or anywhere cudaMalloc is off limits.  The exchange slots of tiles
  * shared between CTAs live in a 4.06 MiB array built into the library (present on every GPU that loads it, until exit),

@@ -21,6 +21,10 @@
 // reducer warp, instead of storing a finished tile, writes its fp32 sums into the receive area of every rank's
 // communication buffer over NVLink (plain peer stores, one self-validating word per value) and later adds the ranks'
 // words from its OWN buffer in rank order: the all-reduce costs no second launch and no flag round trip.
+// MODE 5 takes the activations as the decode step has them before a projection: the residual stream x, the previous
+// block's output delta and the RMSNorm weights.  Every CTA forms x + delta, normalises it and scales it into its own
+// shared-memory copy of the activations (a few KB per row, read from L2), so the add + norm launch in front of the
+// q / k / v and gate / up projections disappears; CTA 0 also writes the new residual stream.
 #include "../../include/statetree_b200.h"
 #include "st_comm.cuh"
 #include "st_common.cuh"
@@ -38,9 +42,11 @@ constexpr int CW = 8;                     // consumer warps = records per unit
 constexpr int UNIT_BYTES = CW * REC;      // 12416
 constexpr int SIDE_BYTES = 64;            // escape block of a unit
 constexpr int XROW = CW * 128 + 16;       // bytes per staged activation row (512 columns + pad: conflict-free ldmatrix)
-constexpr int MODE_DENSE = 0, MODE_SLOT = 1, MODE_GROUP = 2, MODE_LIST = 3, MODE_AR = 4;
+constexpr int MODE_DENSE = 0, MODE_SLOT = 1, MODE_GROUP = 2, MODE_LIST = 3, MODE_AR = 4, MODE_NORM = 5;
 constexpr int FIN_CAP = 32;               // MODE_AR: tiles a CTA may have delivered and not yet summed over the ranks
-__host__ __device__ constexpr bool one_matrix(int mode) { return mode == MODE_DENSE || mode == MODE_LIST || mode == MODE_AR; }
+__host__ __device__ constexpr bool one_matrix(int mode) {
+  return mode == MODE_DENSE || mode == MODE_LIST || mode == MODE_AR || mode == MODE_NORM;
+}
 constexpr int MAXL = 4;                   // matrices in one MODE_LIST launch
 constexpr uint32_t EMPTY_SLOT = 0xFFFFFFFFu;  // what every word of the workspace holds between launches
 
@@ -68,6 +74,7 @@ struct GemvArgs {
   int nprob, maxcover, stages, fill, stage_bytes, nxrows, xwhole, xw_stride, xw_bytes;
   int act;                                // dense mode: rows are gate / up tiles in turn, the reducer stores silu(gate) * up
   ListTab lt;
+  const uint16_t* delta; const uint16_t* nw; uint16_t* xout; float eps;   // MODE_NORM: X = RMSNorm(X + delta) * nw
   uint8_t* peer[MAX_RANKS];               // MODE_AR: communication buffer of every rank (peer[rank] is the own one)
   int rank, world;
   long long wait_ns;                      // bound of the wait for the other ranks' sums
@@ -304,7 +311,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
       for (; pre.valid() && filled < a.fill; pre.next(a), ++filled) { row_of(pre); weights(pre, filled); }
     }
     pdl_wait();
-    if (a.xwhole) {                                            // every activation row once, whole
+    if (a.xwhole && MODE != MODE_NORM) {                       // every activation row once, whole
       if (lane == 0) mbar_expect_tx(xbar, (uint32_t)(NX * a.N * 2));
       __syncwarp();
       if (lane < NX) bulk_g2s(xw + (size_t)lane * a.xw_stride, a.X + (size_t)lane * a.N, (uint32_t)(a.N * 2), xbar, pol_x);
@@ -495,7 +502,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
 #pragma unroll
         for (int k = 0; k < EL / 32; ++k)
           if (orow[k] >= 0) deliver(cur.tile, k, sum[k]);
-      } else if (MODE == MODE_DENSE && a.act) {
+      } else if ((MODE == MODE_DENSE || MODE == MODE_NORM) && a.act) {
         // SwiGLU epilogue: tiles 2j and 2j + 1 hold rows 16j .. 16j + 15 of the gate and of the up projection; the host
         // only allows this when every CTA owns whole tiles in pairs, so the gate tile is always the one just before.
         // Rounding as the separate kernels: both outputs to BF16, silu in fp32 to BF16, BF16 product.
@@ -567,6 +574,63 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     else xo[nt] = (uint32_t)(UNIT_BYTES + SIDE_BYTES + n * XROW) + colo;
   }
   bool xready = !a.xwhole;
+  if (MODE == MODE_NORM) {
+    // x + delta -> new residual stream (BF16), its RMSNorm times the norm weights -> this CTA's activation rows.  The
+    // eight consumer warps share the work: 16-byte vectors, thread t takes vectors t, t + 256, ...
+    pdl_wait();
+    const int ct = warp * 32 + lane, nvec = (int)(a.N / 8);
+    float* part = red;                                         // [rows][CW] partial sums of squares (red is still idle)
+    for (int b = 0; b < a.B; ++b) {
+      float ss = 0.f;
+      for (int v = ct; v < nvec; v += CW * 32) {
+        uint4 xv = *reinterpret_cast<const uint4*>(a.X + (size_t)b * a.N + (size_t)v * 8);
+        if (a.delta != nullptr) {
+          const uint4 dv = *reinterpret_cast<const uint4*>(a.delta + (size_t)b * a.N + (size_t)v * 8);
+          const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ds[4] = {dv.x, dv.y, dv.z, dv.w};
+          uint32_t so[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)                           // the residual stream stays BF16
+            so[q] = pack_bf16(__uint_as_float(xs[q] << 16) + __uint_as_float(ds[q] << 16),
+                              __uint_as_float(xs[q] & 0xFFFF0000u) + __uint_as_float(ds[q] & 0xFFFF0000u));
+          xv = make_uint4(so[0], so[1], so[2], so[3]);
+        }
+        if (blockIdx.x == 0 && a.xout != nullptr) *reinterpret_cast<uint4*>(a.xout + (size_t)b * a.N + (size_t)v * 8) = xv;
+        *reinterpret_cast<uint4*>(xw + (size_t)b * a.xw_stride + (size_t)v * 16) = xv;
+        const uint32_t ws_[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float lo = __uint_as_float(ws_[q] << 16), hi = __uint_as_float(ws_[q] & 0xFFFF0000u);
+          ss += lo * lo + hi * hi;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(FULL, ss, o);
+      if (lane == 0) part[b * CW + warp] = ss;
+    }
+    asm volatile("bar.sync 2, %0;" :: "n"(CW * 32) : "memory");
+    for (int b = 0; b < a.B; ++b) {
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < CW; ++i) tot += part[b * CW + i];
+      const float r = rsqrtf(tot / (float)a.N + a.eps);
+      for (int v = ct; v < nvec; v += CW * 32) {
+        uint4* slot = reinterpret_cast<uint4*>(xw + (size_t)b * a.xw_stride + (size_t)v * 16);
+        const uint4 xv = *slot;
+        const uint4 gv = *reinterpret_cast<const uint4*>(a.nw + (size_t)v * 8);
+        const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, gs[4] = {gv.x, gv.y, gv.z, gv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {                           // normalised value rounded, then scaled
+          const uint32_t n = pack_bf16(__uint_as_float(xs[q] << 16) * r, __uint_as_float(xs[q] & 0xFFFF0000u) * r);
+          o[q] = pack_bf16(__uint_as_float(n << 16) * __uint_as_float(gs[q] << 16),
+                           __uint_as_float(n & 0xFFFF0000u) * __uint_as_float(gs[q] & 0xFFFF0000u));
+        }
+        *slot = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    asm volatile("bar.sync 2, %0;" :: "n"(CW * 32) : "memory");
+    xready = true;
+  }
   const int last_nrec = a.NG - (a.CPT - 1) * CW;
   // escapes of this warp's record: word 0 of the unit's escape block = escapes in the unit | (mask of the unit's records
   // that have any) << 16, so seven warps in eight are done after one broadcast load
@@ -889,6 +953,34 @@ extern "C" int st_gemv_list(int64_t n, const void* const* trees, const int32_t* 
   if (B <= 8) return launch<1, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
   if (B <= 16) return launch<2, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
   return launch<4, MODE_LIST>(a, 1, (int)B, ws_bytes, s, who);
+}
+
+// ---------------------------------------------------------------------------------------------- st_gemv_prenorm
+extern "C" int st_gemv_prenorm_supported(int64_t M, int64_t N, int64_t B, int act) {
+  if (M <= 0 || N <= 0 || M % 16 || N % 64 || N % 8 || B < 1 || B > 8) return 0;
+  if (act && !st_gemv_swiglu_supported(M, N, B)) return 0;
+  const Plan p = make_plan<1>(M, N, 1, (int)B, true, act != 0);
+  return (p.xwhole && p.stages >= 2) ? 1 : 0;
+}
+
+extern "C" int st_gemv_prenorm(const void* tree, const int32_t* eo, const uint32_t* eb, const uint32_t* el, const void* x,
+                               const void* delta, const void* norm_w, double eps, void* x_out, void* Y, int64_t B,
+                               int64_t M, int64_t N, int act, void* ws, int64_t ws_bytes, void* stream) {
+  const char* who = "st_gemv_prenorm";
+  if (int e = shape_checks(who, M, N, B)) return e;
+  ST_REQUIRE(st_gemv_prenorm_supported(M, N, B, act), "%s: shape not supported (batch <= 8, the activation rows must fit in "
+             "shared memory%s)", who, act ? "; the SwiGLU epilogue needs whole gate / up tile pairs per CTA" : "");
+  ST_REQUIRE(tree && eo && eb && el && x && norm_w && Y, "%s: null pointer", who);
+  ST_REQUIRE(st::aligned16(tree) && st::aligned16(eb) && st::aligned16(x) && st::aligned16(norm_w) &&
+             (!delta || st::aligned16(delta)) && (!x_out || st::aligned16(x_out)), "%s: 16-byte alignment", who);
+  ST_REQUIRE(x_out == nullptr || (x_out != x && x_out != delta), "%s: x_out must not alias x or delta (every CTA reads them)", who);
+  GemvArgs a = {};
+  a.tree = (const uint8_t*)tree; a.eo = eo; a.eb = eb; a.el = el;
+  a.X = (const uint16_t*)x; a.delta = (const uint16_t*)delta; a.nw = (const uint16_t*)norm_w; a.xout = (uint16_t*)x_out;
+  a.eps = (float)eps;
+  a.Y = (uint16_t*)Y; a.ws = (float*)ws;
+  a.M = M; a.N = N; a.B = (int)B; a.E = 1; a.xdiv = 1; a.act = act ? 1 : 0;
+  return launch<1, MODE_NORM>(a, 1, (int)B, ws_bytes, (cudaStream_t)stream, who);
 }
 
 // ---------------------------------------------------------------------------------------------- st_gemv_allreduce

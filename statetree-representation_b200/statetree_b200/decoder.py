@@ -139,6 +139,31 @@ class TreeDecoder:
             from .parallel import peer_comm
             self.comm = peer_comm(group)
         self.graph = None
+        # RMSNorm(x + delta) formed inside the GEMV that consumes it (no add + norm launch in front of q/k/v, gate/up
+        # and the output head) where the kernel takes the shape
+        self.pre_qkv = self.pre_gu = self.pre_head = False
+        if compressed and batch <= 8:
+            E = ext()
+            qkv0, _, gu0, _ = self.blocks[0]
+            with torch.cuda.device(self.dev):
+                self.pre_qkv = E.gemv_prenorm_supported(qkv0.out_features, c.hidden, batch, False)
+                self.pre_gu = (not c.experts) and E.gemv_prenorm_supported(gu0.out_features, c.hidden, batch, self.fused_act)
+                self.pre_head = E.gemv_prenorm_supported(self.lm_head.out_features, c.hidden, batch, False)
+            self._xbuf = [torch.empty(batch, c.hidden, dtype=torch.bfloat16, device=self.dev) for _ in range(2)]
+
+    def _prenorm_linear(self, layer, x, delta, act=False):
+        """(layer(RMSNorm(x + delta) * w), x + delta) in one launch; the new residual stream goes to the buffer x is not in"""
+        from .linear import _state
+        E = ext()
+        B, M, N = x.shape[0], layer.out_features, layer.in_features
+        eo, el, eb = layer.tables()
+        y = torch.empty(B, M // 2 if act else M, dtype=torch.bfloat16, device=self.dev)
+        x_out = None
+        if delta is not None:
+            x_out = self._xbuf[1] if x is self._xbuf[0] else self._xbuf[0]
+        ws = _state(self.dev).get_ws(E.gemv_workspace_bytes(M, N, B))
+        E.gemv_prenorm(layer.tree, eo, eb, el, x, delta, self.norm_w, self.cfg.eps, x_out, y, ws, act)
+        return y, (x if x_out is None else x_out)
 
     def _make_experts(self, draw):
         """(router weight [E, hidden] BF16, TreeExperts over this rank's experts): `distinct_experts` random matrices per
@@ -215,8 +240,11 @@ class TreeDecoder:
         slots = self.cache.begin_step(B) if self.compressed else None
         delta, summed = None, False
         for li, (qkv, o, gu, d) in enumerate(self.blocks):
-            self._add_norm(x, delta, h, summed)
-            y = qkv(h)
+            if self.pre_qkv and (delta is None or summed or self.world == 1):
+                y, x = self._prenorm_linear(qkv, x, delta)
+            else:
+                self._add_norm(x, delta, h, summed)
+                y = qkv(h)
             if self.compressed:
                 layer = self.cache.layers[li]               # norm + rope of q and k and the append of k, v: one launch
                 kv_ext().rope_append(y, self.head_norm_w, self.head_norm_w, self.cos, self.sin, self.pos_buf, qb,
@@ -228,6 +256,14 @@ class TreeDecoder:
                 att = _flash()(qb.view(B, 1, self.hq, D), self.kc[li], self.vc[li], k=kb.view(B, 1, self.hkv, D),
                                v=v.unsqueeze(1), cache_seqlens=self.lens, softmax_scale=scale)
             delta, summed = self._row_parallel(o, att.reshape(B, self.hq * D))
+            if self.pre_gu and (summed or self.world == 1):
+                act, x = self._prenorm_linear(gu, x, delta, self.fused_act)
+                if not self.fused_act:
+                    y2 = act
+                    act = torch.empty(B, y2.shape[1] // 2, dtype=torch.bfloat16, device=self.dev)
+                    E.silu_mul(y2, act)
+                delta, summed = self._row_parallel(d, act)
+                continue
             self._add_norm(x, delta, h, summed)
             if c.experts:
                 router, te = gu
@@ -249,8 +285,11 @@ class TreeDecoder:
                 act = torch.empty(B, y.shape[1] // 2, dtype=torch.bfloat16, device=self.dev)
                 E.silu_mul(y, act)
             delta, summed = self._row_parallel(d, act)
-        self._add_norm(x, delta, h, summed)
-        logits = self.lm_head(h)
+        if self.pre_head and (summed or self.world == 1):
+            logits, x = self._prenorm_linear(self.lm_head, x, delta)
+        else:
+            self._add_norm(x, delta, h, summed)
+            logits = self.lm_head(h)
         if self.world > 1:
             parts = [torch.empty_like(logits) for _ in range(self.world)]
             dist.all_gather(parts, logits, group=self.group)

@@ -27,6 +27,9 @@ _SIGNATURES = {
     "st_gemv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_static": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "st_gemv_allreduce": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "st_gemv_prenorm_supported": (_int, [_i64, _i64, _i64, _int]),
+    "st_gemv_prenorm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_double, _vp, _vp, _i64, _i64, _i64, _int, _vp,
+                               _i64, _vp]),
     "st_moe_route": (_int, [_vp, _int, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "st_gemm_list": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp]),
     "st_gemv_list_workspace_bytes": (_i64, [_i64, _vp, _i64, _i64]),
@@ -194,6 +197,20 @@ class _Weights:
         with torch.cuda.device(dev):
             _check(lib().st_gemm_list(n, t, eo, el, _ptr(X), ys, yf, B, Ms, N, _ptr(CNT),
                                       torch.cuda.current_stream(dev).cuda_stream))
+
+    @staticmethod
+    def gemv_prenorm_supported(M, N, B, act=False):
+        return bool(lib().st_gemv_prenorm_supported(M, N, B, 1 if act else 0))
+
+    @staticmethod
+    def gemv_prenorm(T, EO, EB, EL, x, delta, norm_w, eps, x_out, Y, WS, act=False):
+        """Y = RMSNorm(x + delta) * norm_w times W^T (act: the SwiGLU of a gate / up tree), x_out = x + delta"""
+        B, N = x.shape
+        M = T.shape[0] * 16
+        with _ctx(T):
+            _check(lib().st_gemv_prenorm(_ptr(T), _ptr(EO), _ptr(EB), _ptr(EL), _ptr(x), _ptr(delta), _ptr(norm_w),
+                                         float(eps), _ptr(x_out), _ptr(Y), B, M, N, 1 if act else 0, _ptr(WS),
+                                         WS.numel() * WS.element_size(), _stream(T)))
 
     @staticmethod
     def moe_route(logits, K, renorm=True, expert_map=None):

@@ -292,3 +292,42 @@ def test_workspace_growth_keeps_captured_graphs_valid():
         assert torch.equal(y, want)
     del filler
     _status_ok()
+
+
+@pytest.mark.parametrize("M,N,B,act", [(512, 1024, 1, False), (1024, 4096, 3, False), (2048, 2048, 8, False),
+                                       (24576, 4096, 1, True), (12288, 2048, 4, True)])
+def test_gemv_prenorm_equals_add_rmsnorm_then_gemv(M, N, B, act):
+    """the GEMV that forms RMSNorm(x + delta) * w itself against the two-launch sequence it replaces: the new residual
+    stream bit for bit, the product within a BF16 step (the two sum the squares in different orders)"""
+    from statetree_b200 import ops, TreeLinear
+    from statetree_b200.linear import _state, interleave_gate_up
+    E = ops.ext()
+    gen = torch.Generator(device=DEV).manual_seed(M + N + B)
+    W = (torch.randn(M, N, device=DEV, generator=gen) * 0.05).to(torch.bfloat16)
+    if act:
+        W = interleave_gate_up(W[:M // 2].contiguous(), W[M // 2:].contiguous())
+    if not E.gemv_prenorm_supported(M, N, B, act):
+        pytest.skip("shape not taken by the fused epilogue on this GPU")
+    tl = TreeLinear.from_weight(W, verify=False)
+    eo, el, eb = tl.tables()
+    torch.cuda.synchronize()
+    x = torch.randn(B, N, device=DEV, generator=gen).to(torch.bfloat16)
+    d = torch.randn(B, N, device=DEV, generator=gen).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(N, device=DEV, generator=gen)).to(torch.bfloat16)
+    st = _state(torch.device(DEV))
+    ws = st.get_ws(E.gemv_workspace_bytes(M, N, B))
+    for delta in (d, None):
+        x_ref, h = x.clone(), torch.empty_like(x)
+        E.add_rmsnorm(x_ref, delta, nw, h, 1e-6)
+        want = tl.swiglu(h) if act else tl(h)
+        x_out = torch.zeros_like(x)
+        got = torch.empty(B, M // 2 if act else M, dtype=torch.bfloat16, device=DEV)
+        E.gemv_prenorm(tl.tree, eo, eb, el, x, delta, nw, 1e-6, x_out, got, ws, act)
+        torch.cuda.synchronize()
+        assert torch.equal(x_out, x_ref)
+        err = (got.float() - want.float()).abs().max().item()
+        assert err <= 2 ** -6 * want.float().abs().max().item() + 1e-6, (M, N, B, act, err)
+        again = torch.empty_like(got)
+        E.gemv_prenorm(tl.tree, eo, eb, el, x, delta, nw, 1e-6, x_out, again, ws, act)
+        assert torch.equal(got, again)
+    _status_ok()
