@@ -364,7 +364,19 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     // over the ranks is taken later (settle), when the peers' words have had time to arrive.
     uint8_t* const own = MODE == MODE_AR ? a.peer[a.rank] : nullptr;
     uint32_t calls = 0;
-    if (MODE == MODE_AR) calls = ld_relaxed_sys(reinterpret_cast<const uint32_t*>(own + OFF_GEMV));
+    if (MODE == MODE_AR) {
+      // Every CTA reads the call counter, then counts itself in; the last one to do so advances the counter for the next
+      // call (whose kernel reads it only after this grid has completed).  Done here, not at the end, so that it costs
+      // the tail of the launch nothing.
+      uint32_t* g = reinterpret_cast<uint32_t*>(own + OFF_GEMV);
+      calls = ld_relaxed_sys(g);
+      calls = __shfl_sync(FULL, calls, 0);
+      __threadfence();                                         // the read is ordered before the count
+      if (lane == 0 && atomicAdd(g + 1, 1u) == gridDim.x - 1) {
+        g[1] = 0u;
+        g[0] = calls + 1u;
+      }
+    }
     const int half = (int)(calls & 1u);
     int nfin = 0;
     unsigned mask = 0;
@@ -423,22 +435,10 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
         }
       }
     };
-    // every CTA counts itself out; the last one advances the call counter that the next call's parity comes from
-    auto leave_call = [&]() {
-      if (MODE == MODE_AR && lane == 0) {
-        uint32_t* g = reinterpret_cast<uint32_t*>(own + OFF_GEMV);
-        __threadfence();
-        if (atomicAdd(g + 1, 1u) == gridDim.x - 1) {
-          g[1] = 0u;
-          g[0] = calls + 1u;
-        }
-      }
-    };
     for (; cur.valid(); cur.advance(a, cur.run_len(a))) {      // one hand-over per run of units of a tile
       const int buf = nf % NRED;
       if (!mbar_wait(done + buf, (uint32_t)(nf / NRED) & 1u)) {
         if (lane == 0) atomicExch(a.status, ERR_WAIT_FULL);
-        leave_call();
         return;
       }
       ++nf;
@@ -544,7 +544,6 @@ __global__ void __launch_bounds__((CW + 2) * 32, NT <= 2 ? 2 : 1) gemv_kernel(co
     if (MODE == MODE_AR) {
       __syncwarp();
       for (int e = 0; e < nfin; ++e) settle(fin_tile[e], fin_mask[e * 32 + lane]);
-      leave_call();
     }
     return;
   }
