@@ -151,18 +151,101 @@ def silu_mul(gu):
     return act
 
 
+UP_NAMES = ("gate_up_proj", "up_proj")
+
+
+def expert_layout(mod):
+    """What a Transformers experts module (3-D `gate_up_proj` / `up_proj` and `down_proj` parameters, with the layout
+    flags its `use_experts_implementation` decorator sets) looks like: (name of the up projection, stored transposed,
+    has biases), or None for anything else.  A module without `is_transposed` is left alone, its layout cannot be known;
+    one without `has_gate` is accepted only when the up projection is called gate_up_proj
+    (reference: statetree/experts.py:301-320)."""
+    if isinstance(mod, TreeExperts) or not hasattr(mod, "is_transposed"):
+        return None
+    params = mod._parameters
+    up = None
+    for name in UP_NAMES:
+        t = params.get(name)
+        if isinstance(t, torch.Tensor) and t.dim() == 3:
+            up = name
+            break
+    down = params.get("down_proj")
+    if up is None or not isinstance(down, torch.Tensor) or down.dim() != 3 or down.shape[0] != params[up].shape[0]:
+        return None
+    if up != "gate_up_proj" and not hasattr(mod, "has_gate"):
+        return None
+    biased = bool(getattr(mod, "has_bias", False))
+    if biased and not all(isinstance(params.get(n + "_bias"), torch.Tensor) for n in (up, "down_proj")):
+        return None
+    return up, bool(mod.is_transposed), biased
+
+
+def _expert_shape(P, transposed):
+    """(out, in) of one expert's matrix inside the 3-D parameter P"""
+    return (int(P.shape[2]), int(P.shape[1])) if transposed else (int(P.shape[1]), int(P.shape[2]))
+
+
+def experts_eligible(mod, layout):
+    """BF16 tensors on a real device whose per-expert matrices fit the format (out % 16 == 0, in % 64 == 0)
+    (reference: statetree/experts.py:328-334)"""
+    up, transposed, _ = layout
+    U, D = mod._parameters[up], mod._parameters["down_proj"]
+    if any(t.dtype != torch.bfloat16 or t.device.type == "meta" for t in (U, D)):
+        return False
+    return all(o % 16 == 0 and i % 64 == 0 for o, i in (_expert_shape(U, transposed), _expert_shape(D, transposed)))
+
+
 class TreeExperts(nn.Module):
-    """Routed SwiGLU experts with tree-stored weights: w13[e] [2I, H] (gate rows first) and w2[e] [H, I].
+    """Routed experts with tree-stored weights; a drop-in for a Transformers 5 experts module.
 
-    forward(x [T, H], topk_ids [T, k], topk_w [T, k]) -> [T, H] = sum_j w[t, j] W2[e] (silu(Wg[e] x) * Wu[e] x)."""
+    forward(hidden_states [T, H], top_k_index [T, k], top_k_weights [T, k]) -> [T, H].  The experts' matrices are the
+    TreeLinear layers '<up name>.<e>' (gate_up_proj: [2I, H], gate rows first; or up_proj) and 'down_proj.<e>' ([H, I]),
+    so the state dict carries the reference's keys (reference: statetree/experts.py:337-372).  SwiGLU experts without
+    biases (the usual case) run on the fused kernels; other gatings, biases or a post-expert norm go expert by expert
+    through the source module's own activation."""
 
-    def __init__(self, w13, w2):
+    def __init__(self, w13, w2, up_name="gate_up_proj", source=None, has_bias=False):
         super().__init__()
-        self.w13, self.w2 = nn.ModuleList(w13), nn.ModuleList(w2)
-        self.num_experts = len(w13)
-        self.hidden, self.inter = w13[0].in_features, w13[0].out_features // 2
+        self.up_name, self.has_bias = up_name, bool(has_bias)
+        self.src_class, self._gate_fn, self.config = None, None, None
+        self.has_gate, self.has_post_expert_norm = up_name == "gate_up_proj", False
+        if source is not None:
+            # keep what the source module's forward needs: its flags and scalars, its activation / norm submodules, its
+            # class's gating function
+            for key, val in vars(source).items():
+                if not key.startswith("_") and key != "training" and isinstance(val, (bool, int, float, str)):
+                    setattr(self, key, val)
+            self.config = getattr(source, "config", None)
+            for key, sub in source._modules.items():
+                if sub is not None:
+                    self.add_module(key, sub)
+            self._gate_fn = getattr(type(source), "_apply_gate", None)
+            self.src_class = f"{type(source).__module__}.{type(source).__qualname__}"
+            self.has_gate = bool(getattr(source, "has_gate", up_name == "gate_up_proj"))
+            self.has_post_expert_norm = bool(getattr(source, "has_post_expert_norm", False))
+            self.up_name, self.has_bias = up_name, bool(has_bias)
+        self.add_module(up_name, nn.ModuleList(w13))
+        self.down_proj = nn.ModuleList(w2)
+        self.num_experts = len(self.down_proj)
+        up0 = self.w13[0]
+        self.hidden = up0.in_features
+        self.inter = up0.out_features // 2 if self.has_gate else up0.out_features
         self._tabs = None
         self._maps = None
+        self.sentinels = source is not None                 # callers of the Transformers interface may pass ids >= E
+
+    @property
+    def w13(self):
+        return getattr(self, self.up_name)
+
+    @property
+    def w2(self):
+        return self.down_proj
+
+    def _apply(self, fn, *args, **kwargs):
+        out = super()._apply(fn, *args, **kwargs)
+        self._tabs = self._maps = None                      # the trees may have moved
+        return out
 
     @classmethod
     @torch.no_grad()
@@ -170,6 +253,91 @@ class TreeExperts(nn.Module):
         """gate_up [E, 2I, H], down [E, H, I] bf16"""
         return cls([TreeLinear.from_weight(gate_up[e], verify=verify) for e in range(gate_up.shape[0])],
                    [TreeLinear.from_weight(down[e], verify=verify) for e in range(down.shape[0])])
+
+    @classmethod
+    @torch.no_grad()
+    def from_experts(cls, source, verify=True):
+        """Encode every expert of a Transformers experts module (see expert_layout).  Each 3-D BF16 tensor is dropped
+        from the source module as soon as its trees exist, so the peak is one tensor plus its trees."""
+        layout = expert_layout(source)
+        if layout is None or not experts_eligible(source, layout):
+            raise ValueError("TreeExperts.from_experts: not a BF16 experts module this format can hold")
+        up, transposed, biased = layout
+        params = source._parameters
+        lists = {}
+        for name in (up, "down_proj"):
+            P = params[name]
+            bias = params.get(name + "_bias") if biased else None
+            mods = []
+            for e in range(int(P.shape[0])):
+                W = P[e].t().contiguous() if transposed else P[e]
+                mods.append(TreeLinear.from_weight(W, None if bias is None else bias[e], verify=verify))
+            lists[name] = mods
+            del P, bias
+            params.pop(name)
+            params.pop(name + "_bias", None)
+            if torch.cuda.is_available():
+                torch.cuda.empty_cache()
+        return cls(lists[up], lists["down_proj"], up_name=up, source=source, has_bias=biased)
+
+    def spec(self):
+        """what load_pretrained needs, beside the model's config, to build this module empty"""
+        u, d = self.w13[0], self.w2[0]
+        return dict(up=self.up_name, num_experts=self.num_experts, up_shape=[u.out_features, u.in_features],
+                    down_shape=[d.out_features, d.in_features], bias=self.has_bias, source=self.src_class)
+
+    @classmethod
+    def skeleton(cls, source, spec):
+        """an empty (meta) TreeExperts in the place of `source`, to be filled by load_state_dict"""
+        (uo, ui), (do, di) = spec["up_shape"], spec["down_shape"]
+        n, biased = int(spec["num_experts"]), bool(spec["bias"])
+        return cls([TreeLinear(ui, uo, bias=biased, device="meta") for _ in range(n)],
+                   [TreeLinear(di, do, bias=biased, device="meta") for _ in range(n)],
+                   up_name=spec["up"], source=source, has_bias=biased)
+
+    def storage_bytes(self):
+        return sum(m.storage_bytes() for m in self.modules() if isinstance(m, TreeLinear))
+
+    def _fast_ok(self):
+        """the fused kernels compute silu(gate) * up of a [2I, H] gate_up_proj without biases: the default gating"""
+        act = getattr(self, "act_fn", None)
+        plain_gate = self._gate_fn is None or getattr(self._gate_fn, "__name__", "") == "_default_apply_gate"
+        silu = act is None or isinstance(act, nn.SiLU) or "SiLU" in type(act).__name__
+        u, d = self.w13[0], self.w2[0]
+        return (self.has_gate and not self.has_bias and not self.has_post_expert_norm and plain_gate and silu
+                and self.up_name == "gate_up_proj" and u.out_features == 2 * d.in_features
+                and u.in_features == d.out_features)
+
+    def _gated(self, h):
+        if self._gate_fn is not None:
+            return self._gate_fn(self, h)
+        gate, up = h.chunk(2, dim=-1)
+        act = getattr(self, "act_fn", None)
+        return (act(gate) if act is not None else torch.nn.functional.silu(gate)) * up
+
+    def _expert_by_expert(self, x, ids, w, T, K):
+        """every pair through its expert's TreeLinear layers, experts in turn (biases live in the layers); ids >= E
+        (another rank's experts) contribute nothing"""
+        E = self.num_experts
+        order = torch.sort(ids.long()).indices
+        sorted_ids = ids.long()[order]
+        rows = x[order // K]
+        counts = torch.bincount(sorted_ids.clamp(max=E), minlength=E + 1)[:E].tolist()
+        out = x.new_zeros(rows.shape[0], self.w2[0].out_features)
+        at = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            h = self.w13[e](rows[at:at + n])
+            h = self._gated(h) if self.has_gate else self.act_fn(h)
+            out[at:at + n] = self.w2[e](h)
+            at += n
+        if self.has_post_expert_norm:
+            out = self.post_expert_norm(out)
+        out = out * w.reshape(-1)[order].to(out.dtype).unsqueeze(-1)
+        back = torch.empty_like(order)
+        back[order] = torch.arange(order.numel(), device=order.device)
+        return out[back].view(T, K, -1).sum(1).to(x.dtype)
 
     def tables(self):
         if self._tabs is None:
@@ -195,6 +363,29 @@ class TreeExperts(nn.Module):
         other ranks' experts contribute zero."""
         T, K = topk_ids.shape
         S = T * K
+        if S == 0:
+            return x.new_zeros(T, self.w2[0].out_features)
+        if not (self._fast_ok() and x.is_cuda):
+            ids = topk_ids.reshape(-1)
+            if expert_map is not None:
+                local = expert_map[ids.long()]
+                ids = torch.where(local >= 0, local, torch.full_like(local, self.num_experts))
+            return self._expert_by_expert(x, ids, topk_w, T, K)
+        asked = x.dtype
+        if asked != torch.bfloat16:
+            x = x.to(torch.bfloat16)
+        x = _aligned(x)
+        if self.sentinels and expert_map is None:
+            # ids >= E mark pairs of another rank's experts (the convention of expert-parallel callers): weight 0
+            valid = topk_ids < self.num_experts
+            topk_w = torch.where(valid, topk_w, torch.zeros_like(topk_w))
+            topk_ids = topk_ids.clamp(max=self.num_experts - 1)
+        if topk_ids.dtype not in (torch.int32, torch.int64):
+            topk_ids = topk_ids.to(torch.int64)
+        out = self._fast(x, topk_ids.contiguous(), topk_w, expert_map, T, K, S)
+        return out if asked == torch.bfloat16 else out.to(asked)
+
+    def _fast(self, x, topk_ids, topk_w, expert_map, T, K, S):
         t13, t2 = self.tables()
         ids = topk_ids.reshape(-1)
         w = topk_w

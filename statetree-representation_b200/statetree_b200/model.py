@@ -19,6 +19,7 @@ import torch
 import torch.nn as nn
 
 from . import format as F
+from .experts import TreeExperts, expert_layout, experts_eligible
 from .linear import EscapeHeavy, TreeEmbedding, TreeLinear, TreeSlice
 
 FORMAT_NAME = "statetree"
@@ -66,8 +67,9 @@ def convert(model, include=None, exclude=(), fuse=DEFAULT_FUSE, embeddings=True,
     include / exclude   module-name patterns (fnmatch, a full name, or a bare attribute name such as "lm_head")
     verify      decode every tree and compare it bit for bit with the source weights
     max_escape_fraction matrices with more escapes stay BF16 (default 1%, STATETREE_MAX_ESCAPES)
-    experts     accepted for call compatibility; expert tensors held as 3-D parameters are left in BF16 by this
-                implementation (experts held as nn.Linear modules are ordinary linear layers and are converted)"""
+    experts     also store mixture-of-experts weights kept as 3-D parameters (Transformers 5 experts modules) as one tree
+                per expert matrix: the module becomes a TreeExperts (experts held as nn.Linear modules are ordinary
+                linear layers and are converted either way)"""
     t_start = time.perf_counter()
     limit = MAX_ESCAPE_FRACTION if max_escape_fraction is None else max_escape_fraction
     cfg = getattr(model, "config", None)
@@ -87,7 +89,31 @@ def convert(model, include=None, exclude=(), fuse=DEFAULT_FUSE, embeddings=True,
                 pending[name] = mod
             else:
                 left_out.append(name)
-    tally = dict(bf16=0, tree=0, linears=0, groups=0, tables=0, heavy=0)
+    tally = dict(bf16=0, tree=0, linears=0, groups=0, tables=0, heavy=0, moe=0, moe_mats=0)
+
+    # mixture-of-experts weights held as 3-D parameters: one tree per expert matrix, each BF16 tensor freed once encoded
+    if experts:
+        for name, mod in list(model.named_modules()):
+            layout = expert_layout(mod)
+            if layout is None or not chosen(name):
+                continue
+            if not experts_eligible(mod, layout):
+                left_out.append(name)
+                continue
+            worst = _expert_escape_fraction(mod, layout)
+            if worst > limit:
+                left_out.append(f"{name} (escape-heavy: {worst:.2%})")
+                tally["heavy"] += 1
+                continue
+            up = layout[0]
+            tally["bf16"] += sum(2 * t.numel() for k, t in mod._parameters.items()
+                                 if t is not None and k in (up, "down_proj", up + "_bias", "down_proj_bias"))
+            te = TreeExperts.from_experts(mod, verify=verify)
+            parent, attr = _owner(model, name)
+            setattr(parent, attr, te)
+            tally["tree"] += te.storage_bytes()
+            tally["moe"] += 1
+            tally["moe_mats"] += 2 * te.num_experts
 
     # siblings that share their input: one tree, the parts become views of its output
     for pname, parent in list(model.named_modules()):
@@ -216,12 +242,28 @@ def size_report(model):
                 other_bytes=total - tree_bytes, total_bytes=total)
 
 
+@torch.no_grad()
+def _expert_escape_fraction(mod, layout):
+    """the larger of the escape fractions of the up and the down projection tensor of an experts module"""
+    up, transposed, _ = layout
+    worst = 0.0
+    for name in (up, "down_proj"):
+        P = mod._parameters[name]
+        if transposed:                                     # [E, in, out]: the 64-column groups run along `in`
+            n = sum(F.escape_count(P[e].t().contiguous()) for e in range(P.shape[0]))
+        else:
+            n = F.escape_count(P.reshape(-1, P.shape[-1]))
+        worst = max(worst, n / P.numel())
+    return worst
+
+
 # ---------------------------------------------------------------------------------------------- checkpoints
 def _describe(model):
-    """the three tables of statetree.json that describe module structure"""
+    """the tables of statetree.json that describe module structure"""
     name_of = {id(m): n for n, m in tree_modules(model)}
+    expert_specs = {n: m.spec() for n, m in model.named_modules() if isinstance(m, TreeExperts)}
     modules = {n: dict(in_features=m.in_features, out_features=m.out_features, bias=m.bias is not None)
-               for n, m in tree_modules(model)}
+               for n, m in tree_modules(model) if n.rsplit(".", 2)[0] not in expert_specs}   # expert trees: under `experts`
     fused, tables = {}, {}
     for n, m in model.named_modules():
         if isinstance(m, TreeSlice):
@@ -229,7 +271,7 @@ def _describe(model):
         elif isinstance(m, TreeEmbedding):
             tables[n] = dict(num_embeddings=m.num_embeddings, embedding_dim=m.embedding_dim,
                              source=None if m.table is not None else name_of[id(m.source)])
-    return modules, fused, tables
+    return modules, fused, tables, expert_specs
 
 
 def save_pretrained(model, path, tokenizer=None):
@@ -247,9 +289,9 @@ def save_pretrained(model, path, tokenizer=None):
         if ident is not None:
             owner_of[ident] = key
         stored[key] = t.detach().contiguous()
-    modules, fused, tables = _describe(model)
+    modules, fused, tables, expert_specs = _describe(model)
     info = dict(format=FORMAT_NAME, version=FORMAT_VERSION, modules=modules, fused=fused, embeddings=tables,
-                experts={}, aliases=aliases, dtype="bfloat16", architecture=type(model).__name__)
+                experts=expert_specs, aliases=aliases, dtype="bfloat16", architecture=type(model).__name__)
     save_file(stored, os.path.join(path, WEIGHTS_NAME), metadata={"format": "pt", FORMAT_NAME: str(FORMAT_VERSION)})
     with open(os.path.join(path, INFO_NAME), "w") as fh:
         json.dump(info, fh, indent=1)
@@ -292,8 +334,6 @@ def load_pretrained(path, device=None, device_map=None, max_memory=None, model_c
         info = json.load(fh)
     if info.get("format") != FORMAT_NAME:
         raise ValueError(f"{path}: not a statetree checkpoint")
-    if info.get("experts"):
-        raise NotImplementedError("statetree_b200.load_pretrained: checkpoints with 3-D expert modules are not supported")
     if device_map not in (None, "auto") or max_memory is not None:
         raise NotImplementedError("statetree_b200.load_pretrained: one device only (pass device=...)")
     if device is None:
@@ -308,6 +348,9 @@ def load_pretrained(path, device=None, device_map=None, max_memory=None, model_c
             model = build(config, dtype=torch.bfloat16)
         except TypeError:
             model = build(config, torch_dtype=torch.bfloat16)
+    for name, spec in info.get("experts", {}).items():     # empty TreeExperts in place of the 3-D parameter modules
+        parent, attr = _owner(model, name)
+        setattr(parent, attr, TreeExperts.skeleton(getattr(parent, attr), spec))
     tables = info.get("embeddings", {})
     for name, e in tables.items():
         own = None if e["source"] else TreeLinear(e["embedding_dim"], e["num_embeddings"], device="meta")

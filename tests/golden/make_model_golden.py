@@ -28,6 +28,20 @@ def tiny_model(tied):
     return model.eval()
 
 
+def tiny_moe_model():
+    """a two-layer Qwen3-MoE-architecture model (4 experts held as 3-D parameters, top-2) with BF16 weights from a seed"""
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+    cfg = Qwen3MoeConfig(vocab_size=256, hidden_size=128, intermediate_size=256, moe_intermediate_size=64,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                         max_position_embeddings=64, num_experts=4, num_experts_per_tok=2, decoder_sparse_step=1,
+                         mlp_only_layers=[], tie_word_embeddings=False)
+    torch.manual_seed(4321)
+    model = Qwen3MoeForCausalLM(cfg).to(torch.bfloat16)
+    with torch.no_grad():
+        model.model.layers[0].mlp.experts.down_proj[2, 3, 5] = 0.0      # an escape inside an expert
+    return model.eval()
+
+
 def digest(path):
     from safetensors.torch import load_file
     sd = load_file(os.path.join(path, "model.safetensors"))
@@ -47,6 +61,10 @@ def main():
         with tempfile.TemporaryDirectory() as d:
             R.save_pretrained(model, d)
             out["tied" if tied else "untied"] = digest(d)
+    model = R.convert(tiny_moe_model(), verify=True, verbose=False)
+    with tempfile.TemporaryDirectory() as d:
+        R.save_pretrained(model, d)
+        out["moe"] = digest(d)
     with open(os.path.join(HERE, "model_checkpoint.json"), "w") as fh:
         json.dump(out, fh, indent=1, sort_keys=True)
     print("wrote", os.path.join(HERE, "model_checkpoint.json"))

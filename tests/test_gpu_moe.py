@@ -236,3 +236,65 @@ def test_moe_route_matches_torch():
             assert torch.equal(w3, torch.where(local >= 0, w, torch.zeros_like(w)))
     _ = ops.device_status()
     assert _ == 0
+
+
+def test_tree_experts_replaces_a_transformers_experts_module():
+    """TreeExperts.from_experts on a Transformers 5 experts module (3-D gate_up_proj / down_proj): same call, same
+    result as the BF16 module within BF16 rounding, for few pairs (slot kernel), many pairs (grouped kernels) and ids
+    beyond the experts (another rank's pairs contribute nothing); a module with biases takes the expert-by-expert path"""
+    transformers = pytest.importorskip("transformers")
+    from transformers import Qwen3MoeConfig
+    from transformers.models.qwen3_moe.modeling_qwen3_moe import Qwen3MoeExperts
+    from statetree_b200.experts import TreeExperts, expert_layout
+    cfg = Qwen3MoeConfig(hidden_size=128, moe_intermediate_size=64, num_experts=8, num_experts_per_tok=2)
+    torch.manual_seed(7)
+    src = Qwen3MoeExperts(cfg).to(torch.bfloat16).to(DEV)
+    with torch.no_grad():
+        for prm in src.parameters():
+            prm.copy_((torch.randn(prm.shape, device=DEV) * 0.05).to(torch.bfloat16))
+    import copy
+    ref = copy.deepcopy(src)
+    te = TreeExperts.from_experts(src, verify=True)
+    assert expert_layout(src) is None and te._fast_ok()          # the source's 3-D tensors are gone
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    for T in (1, 4, 64, 700):
+        x = torch.randn(T, 128, device=DEV, generator=gen).to(torch.bfloat16)
+        ids = torch.stack([torch.randperm(8, device=DEV, generator=gen)[:2] for _ in range(T)])
+        w = torch.rand(T, 2, device=DEV, generator=gen).to(torch.bfloat16)
+        want = ref(x, ids, w).float()
+        got = te(x, ids, w).float()
+        assert got.shape == want.shape
+        assert (got - want).abs().max().item() <= 0.02 * want.abs().max().item() + 1e-3, T
+        # pairs of another rank's experts (ids >= E) contribute nothing
+        ids2 = ids.clone()
+        ids2[:, 1] = 8
+        only_first = te(x, ids2, w).float()
+        w0 = w.clone()
+        w0[:, 1] = 0
+        assert torch.allclose(only_first, te(x, ids, w0).float(), atol=1e-6)
+    # biases: the generic path through the layers
+    class Biased(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.is_transposed, self.has_bias, self.has_gate, self.num_experts = True, True, True, 4
+            mk = lambda *sh: torch.nn.Parameter((torch.randn(*sh, device=DEV) * 0.05).to(torch.bfloat16))   # noqa: E731
+            self.gate_up_proj, self.gate_up_proj_bias = mk(4, 128, 128), mk(4, 128)
+            self.down_proj, self.down_proj_bias = mk(4, 64, 128), mk(4, 128)
+            self.act_fn = torch.nn.SiLU()
+    b = Biased()
+    Wu, bu, Wd, bd = (t.detach().clone() for t in (b.gate_up_proj, b.gate_up_proj_bias, b.down_proj, b.down_proj_bias))
+    tb = TreeExperts.from_experts(b, verify=True)
+    assert not tb._fast_ok() and tb.has_bias
+    x = torch.randn(6, 128, device=DEV, generator=gen).to(torch.bfloat16)
+    ids = torch.randint(0, 4, (6, 2), device=DEV, generator=gen)
+    w = torch.rand(6, 2, device=DEV, generator=gen)
+    got = tb(x, ids, w).float()
+    want = torch.zeros(6, 128, device=DEV)
+    for t in range(6):
+        for j in range(2):
+            e = int(ids[t, j])
+            h = (x[t].float() @ Wu[e].float() + bu[e].float()).to(torch.bfloat16)
+            g, u = h.chunk(2)
+            a = torch.nn.functional.silu(g) * u
+            want[t] += w[t, j] * (a.float() @ Wd[e].float() + bd[e].float()).to(torch.bfloat16).float()
+    assert (got - want).abs().max().item() <= 0.03 * want.abs().max().item() + 1e-3

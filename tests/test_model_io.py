@@ -62,6 +62,40 @@ def test_checkpoint_equals_the_reference_format(tied, tmp_path):
     assert loaded.model.layers[0].mlp.up_proj.fused is loaded.model.layers[0].mlp.gate_up_proj
 
 
+def test_moe_checkpoint_equals_the_reference_format(tmp_path):
+    """experts held as 3-D parameters become a TreeExperts whose state dict, statetree.json entry and tensor bytes are
+    the reference's; the checkpoint loads back into empty TreeExperts skeletons"""
+    from make_model_golden import digest, tiny_moe_model
+    from statetree_b200 import format as F
+    from statetree_b200 import model as M
+    from statetree_b200.experts import TreeExperts, expert_layout
+    src = tiny_moe_model()
+    experts0 = src.model.layers[0].mlp.experts
+    assert expert_layout(experts0) == ("gate_up_proj", False, False)
+    original = {k: v.clone() for k, v in src.state_dict().items()}
+    model = M.convert(src, verify=True, verbose=False)
+    te = model.model.layers[0].mlp.experts
+    assert isinstance(te, TreeExperts) and te.num_experts == 4 and te.up_name == "gate_up_proj"
+    assert expert_layout(te) is None
+    M.save_pretrained(model, str(tmp_path))
+    got, want = digest(str(tmp_path)), _golden()["moe"]
+    assert sorted(got["tensors"]) == sorted(want["tensors"])
+    assert got["info"] == want["info"]
+    for key in want["tensors"]:
+        assert got["tensors"][key] == want["tensors"][key], key
+    loaded = M.load_pretrained(str(tmp_path), device="cpu")
+    le = loaded.model.layers[1].mlp.experts
+    assert isinstance(le, TreeExperts)
+    for e in range(4):
+        up, down = le.gate_up_proj[e], le.down_proj[e]
+        Wu = F.decode_reference(up.tree, up.esc_rows, up.esc_cols, up.esc_bits)
+        Wd = F.decode_reference(down.tree, down.esc_rows, down.esc_cols, down.esc_bits)
+        assert torch.equal(Wu.view(torch.int16), original["model.layers.1.mlp.experts.gate_up_proj"][e].view(torch.int16))
+        assert torch.equal(Wd.view(torch.int16), original["model.layers.1.mlp.experts.down_proj"][e].view(torch.int16))
+    assert M.convert(tiny_moe_model(), experts=False, verify=False, verbose=False).model.layers[0].mlp.experts.__class__ \
+        is not TreeExperts
+
+
 def test_version_2_checkpoint_is_migrated(tmp_path):
     from safetensors.torch import load_file, save_file
     from make_model_golden import tiny_model
