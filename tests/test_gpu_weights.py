@@ -90,7 +90,8 @@ def test_gemv_matches_fp64(M, N, regime, monkeypatch):
 
 
 @pytest.mark.parametrize("M,N,regime", [(512, 1024, "mixed"), (1024, 512, "mixed"), (256, 2048, "heavy"),
-                                        (128, 768, "each"), (2048, 4096, "llm")])
+                                        (128, 768, "each"), (2048, 4096, "llm"), (1280, 64, "mixed"),
+                                        (1280, 192, "mixed"), (5120, 256, "mixed"), (128, 64, "mixed")])
 def test_gemm_matches_fp64(M, N, regime):
     W = G.weights(M, N, M + N + 1, regime)
     tl, _ = layer_from_oracle(W)
