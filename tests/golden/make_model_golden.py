@@ -2,7 +2,7 @@
 Hugging Face models (CPU): the safetensors key names, the statetree.json structure and a SHA-256 of every stored tensor.
 The test (tests/test_model_io.py) rebuilds the same models, converts and saves them with this package and compares.
 
-    python tests/golden/make_model_golden.py          (needs the reference checkout at /root/reference)
+    python tests/golden/make_model_golden.py /path/to/reference-checkout
 """
 import hashlib
 import json
@@ -53,7 +53,9 @@ def digest(path):
 
 
 def main():
-    sys.path.insert(0, "/root/reference")
+    if len(sys.argv) != 2 or not os.path.isdir(os.path.join(sys.argv[1], "statetree")):
+        sys.exit("usage: make_model_golden.py /path/to/reference-checkout")
+    sys.path.insert(0, sys.argv[1])
     import statetree.model as R
     out = {}
     for tied in (False, True):
