@@ -1092,6 +1092,62 @@ def main():
                 sweep.append(point)
                 del xs, ys, fys
             control["sweep"] = sweep
+        # ---- prefill-size batches (512 / 1024 / 2048 / 4096 rows): the two ways the tree-stored layers can run them, the
+        # tcgen05 kernel (every token tile decodes the records again) and decode once + cuBLAS with the next layer
+        # decoded on a side stream meanwhile (what TreeLinear does above PREFILL_MIN rows), against cuBLAS over the
+        # dense copies.  Eager launches: a launch takes tens of microseconds of device time here
+        prefill = []
+        if B == 1 and not args.no_sweep and main_mode == "fused":
+            import weakref
+
+            def shell(tree, tabs, M, N):
+                c = S.TreeLinear(N, M, device="meta")
+                c._buffers["tree"] = tree
+                c._tables = tabs
+                return c
+
+            chain = []
+            for row, (qkv_buf, gu_buf) in zip(layers, fbufs):
+                chain += [shell(qkv_buf, ftabs[0], Mq, HIDDEN), row[3], shell(gu_buf, ftabs[1], Mg, HIDDEN), row[6]]
+            for a_, b_ in zip(chain, chain[1:] + chain[:1]):
+                a_.__dict__["_next"] = weakref.ref(b_)
+            for Bs in (512, 1024, 2048, 4096):
+                gs = torch.Generator(device=dev).manual_seed(300 + Bs)
+                xs = [torch.randn(Bs, n, device=dev, generator=gs).to(torch.bfloat16) for n in (HIDDEN, HIDDEN, INTER)]
+                ys = [torch.empty(Bs, m, dtype=torch.bfloat16, device=dev) for m in (Mq, HIDDEN, Mg, HIDDEN)]
+                xin4 = [xs[0], xs[1], xs[0], xs[2]]
+                ws_p = st.get_scratch(max(E.gemm_workspace_bytes(m, n, Bs) for m, n in
+                                          ((Mq, HIDDEN), (HIDDEN, HIDDEN), (Mg, HIDDEN), (HIDDEN, INTER))))
+                cnt_p = st.get_cnt(4096)
+
+                def run_kernel():
+                    for i, tl in enumerate(chain):
+                        eo, el, eb = tl._tables
+                        E.gemm(tl.tree, eo, el, xin4[i % 4], ys[i % 4], ws_p, cnt_p)
+
+                def run_dense_stage():
+                    for i, tl in enumerate(chain):
+                        st.dense_stage().run(tl, xin4[i % 4], ys[i % 4])
+
+                def run_control():
+                    for Wqkv, Wo, Wgu, Wd in dense_f:
+                        torch.matmul(xs[0], Wqkv.t(), out=ys[0])
+                        torch.matmul(xs[1], Wo.t(), out=ys[1])
+                        torch.matmul(xs[0], Wgu.t(), out=ys[2])
+                        torch.matmul(xs[2], Wd.t(), out=ys[3])
+
+                def eager_time(fn):
+                    fn()
+                    torch.cuda.synchronize()
+                    return timed(fn, 3)
+
+                fl = sum(2 * Bs * M * N for _, M, N, _ in SHAPES) * args.layers
+                t_k, t_d, t_c = eager_time(run_kernel), eager_time(run_dense_stage), eager_time(run_control)
+                prefill.append({"batch": Bs, "tcgen05_kernel_ms": t_k, "decode_plus_cublas_ms": t_d, "bf16_control_ms": t_c,
+                                "tflops_decode_plus_cublas": fl / (t_d * 1e-3) / 1e12,
+                                "speedup_vs_bf16": t_c / min(t_k, t_d)})
+                del xs, ys
+            control["prefill"] = prefill
         del dense, dense_f
     status = ops.device_status()
 
@@ -1136,6 +1192,8 @@ def main():
     if control is not None:
         if "sweep" in control:
             line["sweep"] = control.pop("sweep")
+        if control.get("prefill"):
+            line["prefill"] = control.pop("prefill")
         line["bf16_control"] = control
     if not args.no_cpu and world == 1:
         val, dt, cores = cpu_reference(2, 1, B)

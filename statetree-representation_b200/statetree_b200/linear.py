@@ -3,7 +3,8 @@ surface of the reference's statetree/linear.py (TreeLinear 595-1018, TreeSlice 1
 torch.compile custom ops 1070-1095).
 
 Dispatch is one kernel per regime (no tuner, no multi-kernel ladder): up to GEMV_MAX activation rows run the
-memory-order fused decode GEMV, more rows the fused decode + tcgen05 GEMM.  Workspaces (exchange slots and zeroed
+memory-order fused decode GEMV, more rows the fused decode + tcgen05 GEMM, more than PREFILL_MIN rows the decode kernel
+into a BF16 scratch matrix + cuBLAS (the reference's prefill path).  Workspaces (exchange slots and zeroed
 semaphores) are kept per (device, stream) because callers may run layers on side streams concurrently (the reason
 given at statetree/linear.py:457-466); they are sized once per shape, so steady-state calls allocate only the output.
 """
@@ -17,6 +18,11 @@ from . import format as F
 from .ops import ext
 
 GEMV_MAX = int(os.environ.get("STATETREE_GEMV_MAX", "12"))     # activation rows up to which the GEMV kernel runs (<= 32)
+# more activation rows than this (prefill): the tree is decoded once into a BF16 scratch matrix and cuBLAS multiplies by
+# it, the reference's path above 1024 rows (statetree/linear.py:37, 879-886), here from the size at which it overtakes the
+# tcgen05 kernel; 0 turns it off
+PREFILL_MIN = int(os.environ.get("STATETREE_PREFILL_MIN", "512"))
+DENSE_MAX = 1 << 28                 # weights: larger matrices (vocabulary-sized tables) never get a dense scratch copy
 _STATES = {}
 _BUFFERS = ("tree", "esc_rows", "esc_cols", "esc_bits")
 
@@ -53,11 +59,84 @@ class _DevState:
             self.scratch = torch.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.device)
         return self.scratch
 
+    def dense_stage(self):
+        if self.__dict__.get("_dense") is None:
+            self._dense = _DenseStage(self.device)
+        return self._dense
+
     def get_cnt(self, n):
         if self.cnt.numel() < n:
             self._retired.append(self.cnt)
             self.cnt = torch.zeros(n, dtype=torch.int32, device=self.device)
         return self.cnt
+
+
+class _DenseStage:
+    """Prefill-size batches: decode once, multiply with cuBLAS (statetree/linear.py:286-368 is the reference's form).
+    Two BF16 scratch matrices per (device, stream).  While the GEMM reads one, a side stream decodes the layer linked
+    as `_next` (by model.prepare, in module order) into the other: the decode is HBM-bound, the GEMM tensor-bound, so
+    from the second layer of a pass on the decode hides under the GEMM.  A wrong guess of the next layer costs one
+    wasted decode, never a wrong result: a scratch matrix is used only if it holds exactly the asked tree."""
+
+    def __init__(self, device):
+        self.device = device
+        self.side = torch.cuda.Stream(device)                # (a high-priority stream measured slower: 17.2 against 14.8 ms at 1024 rows)
+        self.mat = [None, None]                              # flat BF16 scratch
+        self.holds = [None, None]                            # identity of the tree decoded into each
+        self.decoded = [None, None]                          # event: that decode has finished
+        self.read = [None, None]                             # event: the last GEMM that read it has finished
+        self.turn = 0
+
+    @staticmethod
+    def _ident(layer):
+        return (id(layer), layer.tree.data_ptr(), layer.tree._version)
+
+    def _matrix(self, slot, layer):
+        need = layer.out_features * layer.in_features
+        if self.mat[slot] is None or self.mat[slot].numel() < need:
+            if self.mat[slot] is not None:
+                self.mat[slot].record_stream(self.side)       # a decode on the side stream may still be writing it
+            self.mat[slot] = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+            self.mat[slot].record_stream(self.side)
+            self.holds[slot] = None
+        return self.mat[slot][:need].view(layer.out_features, layer.in_features)
+
+    def run(self, layer, x, y):
+        cur = torch.cuda.current_stream(self.device)
+        me = self._ident(layer)
+        if me in self.holds:
+            slot = self.holds.index(me)
+            cur.wait_event(self.decoded[slot])
+            W = self._matrix(slot, layer)
+        else:
+            slot = self.turn
+            if self.decoded[slot] is not None:
+                cur.wait_event(self.decoded[slot])           # a prefetch of some other layer into this slot
+            W = self._matrix(slot, layer)
+            eo, el, _ = layer.tables()
+            ext().dec(layer.tree, eo, el, W)
+            self.holds[slot] = me
+            self.decoded[slot] = cur.record_event()
+        other = 1 - slot
+        nxt = layer._next() if layer._next is not None else None
+        fork = None
+        if (nxt is not None and nxt.dense_ok() and nxt.tree.device == layer.tree.device
+                and self.holds[other] != self._ident(nxt)):
+            nxt.tables()                                     # built on the caller's stream, before the fork
+            Wn = self._matrix(other, nxt)
+            fork = cur.record_event()
+        torch.matmul(x, W.t(), out=y)
+        self.read[slot] = cur.record_event()
+        self.turn = other
+        if fork is not None:
+            self.side.wait_event(fork)
+            if self.read[other] is not None:
+                self.side.wait_event(self.read[other])       # the GEMM that last read the other matrix
+            with torch.cuda.stream(self.side):
+                eo, el, _ = nxt.tables()
+                ext().dec(nxt.tree, eo, el, Wn)
+                self.decoded[other] = self.side.record_event()
+            self.holds[other] = self._ident(nxt)
 
 
 def _state(device):
@@ -163,6 +242,16 @@ class TreeLinear(nn.Module):
     def _reset_runtime(self):
         self._tables = None                             # (eo, el, eb) on the tree's device
         self.__dict__["_shared"] = None                 # product shared by the TreeSlice views of this layer
+        self.__dict__.setdefault("_next", None)         # weak reference to the layer that runs after this one
+
+    def __getstate__(self):
+        state = self.__dict__.copy()
+        state["_next"] = None                           # (a weak reference cannot be pickled; prepare() links again)
+        return state
+
+    def dense_ok(self):
+        """may this layer be decoded into a BF16 scratch matrix for prefill-size batches"""
+        return self.tree.is_cuda and self.out_features * self.in_features <= DENSE_MAX
 
     def extra_repr(self):
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
@@ -217,6 +306,8 @@ class TreeLinear(nn.Module):
         if B <= min(GEMV_MAX, 32):
             ws = st.get_ws(E.gemv_workspace_bytes(M, N, B))
             E.gemv(self.tree, eo, eb, el, x, y, ws, st.get_cnt(M // 16), yf32)
+        elif 0 < PREFILL_MIN < B and yf32 is None and self.dense_ok() and not torch.cuda.is_current_stream_capturing():
+            st.dense_stage().run(self, x, y)                # decode once + cuBLAS, the next layer decoded meanwhile
         elif M % 128 == 0:
             ws = st.get_scratch(E.gemm_workspace_bytes(M, N, B))
             E.gemm(self.tree, eo, el, x, y, ws, st.get_cnt((M // 128) * ((B + 255) // 256)), yf32)

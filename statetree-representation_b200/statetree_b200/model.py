@@ -209,6 +209,9 @@ def prepare(model, batch_sizes=(1,), verbose=False):
     from .ops import ext
     mods = [m for _, m in tree_modules(model) if m.tree.device.type == "cuda"]
     E = ext() if mods else None
+    import weakref
+    for m, after in zip(mods, mods[1:] + mods[:1]):          # prefill: decode the next layer while this one multiplies
+        m.__dict__["_next"] = weakref.ref(after)
     for m in mods:
         m.tables()
         st = _state(m.tree.device)

@@ -92,7 +92,9 @@ def test_gemv_matches_fp64(M, N, regime, monkeypatch):
 @pytest.mark.parametrize("M,N,regime", [(512, 1024, "mixed"), (1024, 512, "mixed"), (256, 2048, "heavy"),
                                         (128, 768, "each"), (2048, 4096, "llm"), (1280, 64, "mixed"),
                                         (1280, 192, "mixed"), (5120, 256, "mixed"), (128, 64, "mixed")])
-def test_gemm_matches_fp64(M, N, regime):
+def test_gemm_matches_fp64(M, N, regime, monkeypatch):
+    import statetree_b200.linear as L
+    monkeypatch.setattr(L, "PREFILL_MIN", 0)                    # every batch here through the tcgen05 kernel
     W = G.weights(M, N, M + N + 1, regime)
     tl, _ = layer_from_oracle(W)
     for B in (17, 33, 48, 64, 100, 128, 200, 256, 300, 600):
@@ -331,4 +333,44 @@ def test_gemv_prenorm_equals_add_rmsnorm_then_gemv(M, N, B, act):
         again = torch.empty_like(got)
         E.gemv_prenorm(tl.tree, eo, eb, el, x, delta, nw, 1e-6, x_out, again, ws, act)
         assert torch.equal(got, again)
+    _status_ok()
+
+
+def test_prefill_batches_decode_once_and_use_the_dense_product():
+    """more than PREFILL_MIN activation rows: the layer is decoded into a BF16 scratch matrix and cuBLAS multiplies by
+    it (the reference's path above 1024 rows); the layer linked as next is decoded on a side stream meanwhile.  Same
+    bits as the product with the dequantized weight, within BF16 rounding of the fp64 product, whatever the order the
+    layers are called in."""
+    import pickle
+    import weakref
+    import statetree_b200.linear as L
+    shapes = [(512, 1024), (1024, 512), (256, 1024)]
+    Ws = [G.weights(M, N, 31 * i + M, "mixed") for i, (M, N) in enumerate(shapes)]
+    tls = [layer_from_oracle(W)[0] for W in Ws]
+    for a, b in zip(tls, tls[1:] + tls[:1]):
+        a.__dict__["_next"] = weakref.ref(b)
+    B = L.PREFILL_MIN + 300
+    stage = L._state(torch.device(DEV)).dense_stage()
+
+    def check(i, seed):
+        W, tl = Ws[i], tls[i]
+        X = G.to_bf16_bits(np.random.RandomState(seed).standard_normal((B, W.shape[1])))
+        x = bits_to_torch(X, DEV)
+        y = tl(x)
+        assert torch.equal(y, torch.matmul(x, tl.dequantize().t())), (i, "not the dense product")
+        assert rel_fro(y.float().cpu().numpy(), oracle.linear_f64(W, X)) < 5e-3, i
+
+    check(0, 1)
+    assert stage.holds[1 - stage.holds.index(stage._ident(tls[0]))] == stage._ident(tls[1])   # next layer prefetched
+    check(1, 2)                                             # served from the prefetched matrix
+    check(2, 3)
+    check(0, 4)                                             # wrapped around
+    check(2, 5)                                             # not the predicted layer: decoded on demand
+    check(2, 6)
+    check(1, 7)
+    torch.cuda.synchronize()
+    y_small = tls[0](bits_to_torch(G.to_bf16_bits(np.random.RandomState(9).standard_normal((64, 1024))), DEV))
+    assert y_small.shape == (64, 512)                       # smaller batches still take the tree kernels
+    clone = pickle.loads(pickle.dumps(tls[0].cpu()))        # the link to the next layer does not travel
+    assert clone.__dict__["_next"] is None
     _status_ok()
