@@ -62,3 +62,14 @@ def test_cpu_tensors_are_rejected():
     with pytest.raises(RuntimeError):
         ops.ext().dec(torch.zeros(1, 1, 1552, dtype=torch.uint8), torch.zeros(2, dtype=torch.int32),
                       torch.zeros(1, dtype=torch.int32), torch.zeros(16, 64, dtype=torch.bfloat16))
+
+
+def test_package_exports_the_reference_names():
+    """`import statetree_b200 as statetree` keeps a caller's lines: the names statetree/__init__.py:10-17 exports"""
+    import statetree_b200 as S
+    names = ["TreeLinear", "TreeSlice", "TreeEmbedding", "TreeExperts", "DEFAULT_FUSE", "convert", "prepare",
+             "save_pretrained", "load_pretrained", "size_report", "tree_modules", "encode", "decode_reference"]
+    assert sorted(S.__all__) == sorted(names)
+    for n in names:
+        assert hasattr(S, n), n
+    assert S.DEFAULT_FUSE["qkv_proj"] == ("q_proj", "k_proj", "v_proj")
