@@ -143,6 +143,31 @@ def moe_wsum(y, w):
     return out
 
 
+def moe_gemv_w(tables, x, ids, M, xdiv, nbps=None):
+    """moe_gemv under the name the reference gives its small-K kernel (statetree/experts.py:270-279): one GEMV kernel
+    serves every K here, so this is the same call; nbps (the reference's blocks per SM) has no meaning and is ignored"""
+    return moe_gemv(tables, x, ids, M, xdiv)
+
+
+def moe_group_gemv_w(tables, x, aligned, S, M, xdiv, nbps=None):
+    """moe_group_gemv under the reference's small-K name (statetree/experts.py:282-290); nbps is ignored"""
+    return moe_group_gemv(tables, x, aligned, S, M, xdiv)
+
+
+def moe_fused_decode(t13, t2, x, ids, w, I):
+    """out[t] = sum_j w[t, j] W2[e] (silu(W13gate[e] x[t]) * W13up[e] x[t]), e = ids[t k + j]: the routed-expert block
+    of a decode step (statetree/experts.py:231-249).  t13 / t2: pointer tables of the [2I, H] gate-up (gate rows first)
+    and [H, I] down trees, x [T, H] BF16, ids [T k] int32 / int64, w [T, k] routing weights.  The reference has one
+    launch for it (off by default there); here it is the four launches TreeExperts uses: slot GEMV, silu * up, slot
+    GEMV, weighted sum.  Deterministic."""
+    x = _aligned(x)
+    T, H = x.shape
+    K = w.shape[-1]
+    gu = moe_gemv(t13, x, ids, 2 * I, K)
+    y = moe_gemv(t2, silu_mul(gu), ids, H, 1)
+    return moe_wsum(y, w.reshape(T, K))
+
+
 def silu_mul(gu):
     """act = silu(gate) * up for gu [S, 2I] = [gate | up] (silu in fp32, rounded to BF16, then the product)"""
     gu = _aligned(gu)
@@ -297,6 +322,13 @@ class TreeExperts(nn.Module):
 
     def storage_bytes(self):
         return sum(m.storage_bytes() for m in self.modules() if isinstance(m, TreeLinear))
+
+    def extra_repr(self):
+        up, down = self.w13[0], self.down_proj[0]
+        weights = sum(m.in_features * m.out_features for m in self.modules() if isinstance(m, TreeLinear))
+        return (f"{self.num_experts} experts as state trees: {self.up_name} {up.out_features}x{up.in_features}, down_proj "
+                f"{down.out_features}x{down.in_features}, gate={self.has_gate}, bias={self.has_bias}, "
+                f"{8 * self.storage_bytes() / max(1, weights):.2f} bits per weight")
 
     def _fast_ok(self):
         """the fused kernels compute silu(gate) * up of a [2I, H] gate_up_proj without biases: the default gating"""

@@ -98,6 +98,8 @@ class StateTreeKVLayer(CacheLayerMixin):
     def get_max_cache_shape(self):
         return self.max_cache_len
 
+    get_max_length = get_max_cache_shape                   # the name older Transformers releases call
+
     get_max_length = get_max_cache_shape
 
     def reset(self):

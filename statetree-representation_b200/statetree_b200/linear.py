@@ -193,6 +193,29 @@ class TreeLinear(nn.Module):
         _BY_HANDLE[self._handle] = self
         self._reset_runtime()
 
+    def set_handle(self, name):
+        """The string under which the torch.compile custom ops find this layer; a stable name (the module path) keeps a
+        compiled graph valid in another process (statetree/linear.py:621-625)."""
+        self._handle = str(name)
+        _BY_HANDLE[self._handle] = self
+
+    def prepare(self, batch_sizes=(1,)):
+        """Side tables and workspaces for these batch sizes now, so that a later call (or a CUDA-graph capture)
+        allocates nothing (statetree/linear.py:1014-1018; there is no plan to pick here: one kernel per regime)."""
+        if not self.tree.is_cuda:
+            raise RuntimeError("TreeLinear.prepare: the layer must be on a GPU")
+        E, st = ext(), _state(self.tree.device)
+        self.tables()
+        M, N = self.out_features, self.in_features
+        for B in batch_sizes:
+            if B <= min(GEMV_MAX, 32) or M % 128:
+                st.get_ws(E.gemv_workspace_bytes(M, N, min(B, 32)))
+                st.get_cnt(M // 16)
+            else:
+                st.get_scratch(E.gemm_workspace_bytes(M, N, B))
+                st.get_cnt((M // 128) * ((B + 255) // 256))
+        return self
+
     # ---------------------------------------------------------------- construction / state dict
     @classmethod
     def from_linear(cls, lin, verify=True, max_escape_fraction=None):

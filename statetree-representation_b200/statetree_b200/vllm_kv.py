@@ -83,6 +83,28 @@ class SharedPool:
         return used, self.pool.shape[0], bool(exhausted)
 
 
+_POOLS = {}
+
+
+def shared_pool(device, num_q_heads, num_kv_heads):
+    """the process's SharedPool of a device, made on first use (one pool serves every layer of a model, so all layers
+    must have the same head counts; reference: statetree/vllm_kv.py:88-98)"""
+    device = torch.device(device)
+    key = (device.type, device.index)
+    pool = _POOLS.get(key)
+    if pool is None:
+        pool = _POOLS[key] = SharedPool(device, num_q_heads, num_kv_heads)
+    elif (pool.num_q_heads, pool.num_kv_heads) != (num_q_heads, num_kv_heads):
+        raise NotImplementedError("statetree KV: layers with different head counts in one model")
+    return pool
+
+
+def pool_usage():
+    """{(device type, index): (blocks used, blocks, exhausted)} of this process's pools; synchronises (for tests;
+    reference: statetree/vllm_kv.py:101-107)"""
+    return {key: pool.usage() for key, pool in _POOLS.items()}
+
+
 class PageBackend:
     """The data path of the vLLM backend for one attention layer configuration (reference: StateTreeKVImpl,
     statetree/vllm_kv.py:228-318): write, decode, and the exact decode of cached pages for prefill."""

@@ -109,6 +109,14 @@ def test_tree_experts_block_matches_dense():
                 act = torch.nn.functional.silu(gu[:I]) * gu[I:]
                 ref[t] += float(w[t, j]) * (down[e].double() @ act)
         assert float((got - ref).norm() / ref.norm()) < 2e-2, T
+        if T <= 8:
+            # the reference's functional names for the same block and its small-K products
+            from statetree_b200 import experts as X
+            t13, t2 = X.expert_tables(list(te.w13)), X.expert_tables(list(te.w2))
+            fused = X.moe_fused_decode(t13, t2, x, ids.reshape(-1), w, I)
+            assert float((fused.double() - ref).norm() / ref.norm()) < 2e-2, T
+            flat = ids.reshape(-1)
+            assert torch.equal(X.moe_gemv_w(t13, x, flat, 2 * I, K), X.moe_gemv(t13, x, flat, 2 * I, K))
         # expert parallelism: experts split over two ranks, partial outputs add up
         emap0 = torch.where(torch.arange(E, device=DEV) < E // 2, torch.arange(E, device=DEV), -1).int()
         emap1 = torch.where(torch.arange(E, device=DEV) >= E // 2, torch.arange(E, device=DEV) - E // 2, -1).int()

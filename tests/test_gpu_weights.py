@@ -374,3 +374,30 @@ def test_prefill_batches_decode_once_and_use_the_dense_product():
     clone = pickle.loads(pickle.dumps(tls[0].cpu()))        # the link to the next layer does not travel
     assert clone.__dict__["_next"] is None
     _status_ok()
+
+
+def test_layer_prepare_then_graph_capture():
+    """TreeLinear.prepare builds the side tables and sizes the workspaces, so the first call may be a captured one"""
+    W = G.weights(256, 512, 5, "mixed")
+    tl, _ = layer_from_oracle(W)
+    assert tl._tables is None
+    tl.prepare([1, 64]).set_handle("blk0.q_proj")
+    assert tl._tables is not None
+    import statetree_b200.linear as L
+    assert L._BY_HANDLE["blk0.q_proj"] is tl
+    for B in (1, 64):
+        x = bits_to_torch(G.to_bf16_bits(np.random.RandomState(B).standard_normal((B, 512))), DEV)
+        y = torch.empty(B, 256, dtype=torch.bfloat16, device=DEV)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            L._state(torch.device(DEV))                     # (workspaces are per stream: size this stream's too)
+            tl.prepare([B])
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                tl._run(x, y)
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, tl(x)), B
+    _status_ok()

@@ -34,6 +34,18 @@ def test_pool_watch_raises_one_step_late():
         sh.poll()
 
 
+def test_one_pool_per_process_and_device(monkeypatch):
+    import statetree_b200.vllm_kv as V
+    monkeypatch.setenv("STATETREE_KV_POOL_MB", "1")
+    monkeypatch.setattr(V, "_POOLS", {})
+    a = V.shared_pool("cpu", 32, 8)
+    assert V.shared_pool(torch.device("cpu"), 32, 8) is a                    # every layer of a model shares it
+    with pytest.raises(NotImplementedError, match="different head counts"):
+        V.shared_pool("cpu", 16, 8)
+    a.cnt[0] = 7
+    assert V.pool_usage() == {("cpu", None): (7, 16384, False)}
+
+
 def test_prefill_page_tables():
     from statetree_b200.vllm_kv import prefill_page_tables
     bt = torch.arange(40, dtype=torch.int32).view(4, 10) + 100               # 4 requests, the first is a decode
