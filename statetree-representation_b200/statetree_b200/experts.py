@@ -44,8 +44,10 @@ def expert_tables(mods):
     return t
 
 
-def moe_gemv(tables, x, ids, M, xdiv):
-    """y[s] = W[ids[s]] x[s // xdiv] for every slot s; ids int32 / int64, clamped to [0, E) in the kernel"""
+def moe_gemv(tables, x, ids, M, xdiv, cfg=None):
+    """y[s] = W[ids[s]] x[s // xdiv] for every slot s; ids int32 / int64, clamped to [0, E) in the kernel.  cfg (the
+    reference's kernel configuration, statetree/experts.py:52) is accepted and ignored: the grid is chosen in the
+    library."""
     x = _aligned(x)
     if ids.dtype not in (torch.int32, torch.int64):
         ids = ids.to(torch.int64)
@@ -99,10 +101,13 @@ def _moe_align_torch(ids, E, bs=8, used_bins=None):
     return sorted_ids, bexp, end[nb - 1:nb].to(torch.int32)
 
 
-def moe_group_gemv(tables, x, aligned, S, M, xdiv, zero=False):
+def moe_group_gemv(tables, x, aligned, S, M, xdiv, NT=1, E=None, cfg=None, zero=False):
     """y[s] = W[expert of s] x[s // xdiv], slots grouped by expert: aligned = moe_align(ids, E, 8).  Rows of blocks
     whose expert id is negative or >= the number of tables (another rank's expert) are left untouched (zero=True:
-    they read as zeros)."""
+    they read as zeros).  NT / E / cfg keep the reference's argument order (statetree/experts.py:152): blocks are
+    always 8 slots here (NT = 1; larger groups go to moe_group_gemm), E and cfg are not needed."""
+    if NT != 1:
+        raise ValueError("moe_group_gemv: blocks of 8 slots only (NT = 1); use moe_group_gemm for blocks of 64 / 128")
     sorted_ids, bexp, npost = (t.contiguous() for t in aligned)
     x = _aligned(x)
     N = x.shape[1]
@@ -390,9 +395,11 @@ class TreeExperts(nn.Module):
     def record_bytes(self):
         return sum(m.record_bytes() for m in self.w13) + sum(m.record_bytes() for m in self.w2)
 
-    def forward(self, x, topk_ids, topk_w, expert_map=None):
-        """expert_map (optional int32 [E_global]): global expert id -> local id or -1 (expert parallelism); pairs of
-        other ranks' experts contribute zero."""
+    def forward(self, hidden_states, top_k_index, top_k_weights, expert_map=None):
+        """The call of a Transformers experts module (statetree/experts.py: TreeExperts.forward).  expert_map (optional
+        int32 [E_global]): global expert id -> local id or -1 (expert parallelism); pairs of other ranks' experts
+        contribute zero."""
+        x, topk_ids, topk_w = hidden_states, top_k_index, top_k_weights
         T, K = topk_ids.shape
         S = T * K
         if S == 0:
