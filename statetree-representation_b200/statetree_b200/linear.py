@@ -266,6 +266,8 @@ class TreeLinear(nn.Module):
         self._tables = None                             # (eo, el, eb) on the tree's device
         self.__dict__["_shared"] = None                 # product shared by the TreeSlice views of this layer
         self.__dict__.setdefault("_next", None)         # weak reference to the layer that runs after this one
+        self.__dict__.setdefault("allow_dec", True)     # False: never a dense scratch copy (the reference's flag for
+                                                        # vocabulary-sized tables, statetree/linear.py:808-810)
 
     def __getstate__(self):
         state = self.__dict__.copy()
@@ -274,7 +276,7 @@ class TreeLinear(nn.Module):
 
     def dense_ok(self):
         """may this layer be decoded into a BF16 scratch matrix for prefill-size batches"""
-        return self.tree.is_cuda and self.out_features * self.in_features <= DENSE_MAX
+        return self.allow_dec and self.tree.is_cuda and self.out_features * self.in_features <= DENSE_MAX
 
     def extra_repr(self):
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "

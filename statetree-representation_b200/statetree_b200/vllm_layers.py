@@ -102,6 +102,7 @@ class StateTreeEmbeddingMethod(StateTreeLinearMethod):
         except EscapeHeavy:
             return
         layer.weight = _empty_like_param(layer.weight)
+        tl.allow_dec = False                                 # a vocabulary-sized table never gets a dense scratch copy
         _attach(layer, tl)
         tl.tables()
         if self.lm_head:

@@ -371,6 +371,11 @@ def test_prefill_batches_decode_once_and_use_the_dense_product():
     torch.cuda.synchronize()
     y_small = tls[0](bits_to_torch(G.to_bf16_bits(np.random.RandomState(9).standard_normal((64, 1024))), DEV))
     assert y_small.shape == (64, 512)                       # smaller batches still take the tree kernels
+    tls[1].allow_dec = False                                # as for a vocabulary-sized table: tree kernels at any batch
+    xb = bits_to_torch(G.to_bf16_bits(np.random.RandomState(11).standard_normal((B, 512))), DEV)
+    yk = tls[1](xb)
+    parts = torch.cat([tls[1](xb[i:i + 512]) for i in range(0, B, 512)])
+    assert rel_fro(yk.float().cpu().numpy(), parts.float().cpu().numpy()) < 5e-3
     clone = pickle.loads(pickle.dumps(tls[0].cpu()))        # the link to the next layer does not travel
     assert clone.__dict__["_next"] is None
     _status_ok()
