@@ -43,6 +43,24 @@ def test_converted_model_runs_saves_and_loads(kind, tmp_path):
     for g, w in zip(got, want):
         rel = float((g - w).norm() / w.norm())
         assert rel < 3e-2, (kind, rel)
+    if kind == "dense":
+        # a prefill-size batch (640 rows > PREFILL_MIN): decode once + cuBLAS, the next layer decoded meanwhile, against
+        # the same batch through the tcgen05 kernel
+        import statetree_b200.linear as L
+        layers = [m for _, m in M.tree_modules(model)]
+        assert all(m._next is not None and isinstance(m._next(), TreeLinear) for m in layers)
+        wide = torch.randint(0, 256, (16, 40), device="cuda", generator=gen)
+        dense_way = _logits(model, wide)
+        stage = L._state(torch.device("cuda", torch.cuda.current_device())).dense_stage()
+        assert any(h is not None for h in stage.holds)
+        keep, L.PREFILL_MIN = L.PREFILL_MIN, 0
+        try:
+            kernel_way = _logits(model, wide)
+        finally:
+            L.PREFILL_MIN = keep
+        rel = float((dense_way - kernel_way).norm() / kernel_way.norm())
+        assert rel < 1e-2, rel
+        assert float((dense_way - _logits(ref, wide)).norm() / kernel_way.norm()) < 3e-2
     rep = M.size_report(model)
     assert rep["bits_per_weight"] < 12.7 and rep["total_bytes"] < sum(t.numel() * 2 for t in ref.parameters())
     M.save_pretrained(model, str(tmp_path))
