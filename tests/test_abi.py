@@ -73,3 +73,22 @@ def test_package_exports_the_reference_names():
     for n in names:
         assert hasattr(S, n), n
     assert S.DEFAULT_FUSE["qkv_proj"] == ("q_proj", "k_proj", "v_proj")
+
+
+def test_install_as_makes_the_reference_imports_resolve_here():
+    import importlib
+    import sys
+    import statetree_b200 as S
+    try:
+        S.install_as("statetree_alias_for_test")
+        import statetree_alias_for_test as A                      # noqa: F401
+        from statetree_alias_for_test.linear import TreeLinear
+        assert A is S and TreeLinear is S.TreeLinear
+        assert importlib.import_module("statetree_alias_for_test.ops").ext is S.ops.ext
+        assert importlib.import_module("statetree_alias_for_test._vllm").StateTreeLinearMethod is not None
+        sys.modules["taken_name_for_test"] = sys
+        with pytest.raises(RuntimeError, match="already imported"):
+            S.install_as("taken_name_for_test")
+    finally:
+        for k in [k for k in sys.modules if k.startswith("statetree_alias_for_test") or k == "taken_name_for_test"]:
+            del sys.modules[k]
